@@ -1,0 +1,187 @@
+/*
+ * muser-cuda: C ABI of the B200 (sm_100a) backend for muser's quantized linear layers.
+ *
+ * Every entry point is what a Rust `muser-cuda` crate binds 1:1 so that the engine's
+ * forward-graph drivers can select this backend the way they select Metal
+ * (crates/muser-engine/src/api.rs:626-631).  Each declaration cites the reference
+ * interface it stands in for.  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Conventions (the reference's, crates/muser-engine/src/weights.rs:398-421 and
+ * src/metal/encode/qkv.rs:414-424):
+ *   - weights are row-major quantized rows, rows = n_out, contiguous dim = n_in;
+ *   - activations are token-major [tokens][n_in], outputs token-major [tokens][n_out];
+ *   - dtype ids are the GgmlType discriminants (src/gguf/types.rs:9-39).
+ *
+ * Unless a comment says "host", data pointers are device pointers on the context's device.
+ * Calls enqueue work on the caller's stream and never synchronize; errors detected on the
+ * host come back as a status, never as an abort.  `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef MUSER_CUDA_H
+#define MUSER_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MUSER_CUDA_ABI_VERSION 1u
+
+#if defined(__GNUC__)
+#define MUSER_CUDA_API __attribute__((visibility("default")))
+#else
+#define MUSER_CUDA_API
+#endif
+
+/* GgmlType discriminants, src/gguf/types.rs:9-39 */
+#define MUSER_DTYPE_F32 0u
+#define MUSER_DTYPE_F16 1u
+#define MUSER_DTYPE_Q4_K 12u
+#define MUSER_DTYPE_Q5_K 13u
+#define MUSER_DTYPE_Q6_K 14u
+#define MUSER_DTYPE_BF16 30u
+#define MUSER_DTYPE_NVFP4_E2M1 1000u
+#define MUSER_DTYPE_F8_E4M3FN 1001u
+
+/* The reference's encoders return () and debug_assert / panic on misuse
+ * (src/metal/encode/qkv.rs:141-145,459,627); device trouble surfaces later as
+ * MetalError::{Command,Deadline} (src/metal/context.rs:8-30).  Here every call validates
+ * on the host and reports one of these. */
+typedef enum muser_cuda_status {
+    MUSER_CUDA_OK = 0,
+    MUSER_CUDA_BAD_ARG = 1,           /* null pointer, zero size, bad enum */
+    MUSER_CUDA_BAD_SHAPE = 2,         /* n_in / n_out / tokens not supported by the dtype */
+    MUSER_CUDA_BAD_ALIGN = 3,         /* a device pointer is not 16-byte aligned */
+    MUSER_CUDA_UNSUPPORTED_DTYPE = 4, /* supports_projection() is false for it */
+    MUSER_CUDA_NAN_SCALE = 5,         /* an E4M3FN NaN code or non-finite tensor scale */
+    MUSER_CUDA_ERROR = 6,             /* a CUDA runtime call failed; see last_error */
+    MUSER_CUDA_NCCL_ERROR = 7,
+    MUSER_CUDA_TIMEOUT = 8,           /* a bounded device-side wait gave up */
+    MUSER_CUDA_WORKSPACE_TOO_SMALL = 9
+} muser_cuda_status;
+
+typedef struct muser_cuda_ctx muser_cuda_ctx;       /* one per device; thread-compatible */
+typedef struct muser_cuda_weight muser_cuda_weight; /* immutable repacked device image */
+
+/* How one projection is split across tensor-parallel ranks.  The reference has no tensor
+ * parallelism (scripts/gx10/vllm/muser_vllm/connector.py:119-120 refuses it), so this has no
+ * counterpart there. */
+#define MUSER_SHARD_NONE 0u
+#define MUSER_SHARD_ROWS 1u /* column-parallel: this rank keeps n_out/world output rows */
+#define MUSER_SHARD_K 2u    /* row-parallel: this rank keeps n_in/world inputs; outputs are partial sums */
+typedef struct muser_cuda_shard {
+    uint32_t rank, world, axis;
+} muser_cuda_shard;
+
+/* Work fused behind a projection, reproducing src/reference.rs:59-80 (RMSNorm scale of the
+ * input rows), :511-513 (silu(gate)*up) and :475-477,536-538 (residual add). */
+typedef struct muser_cuda_epilogue {
+    const float *row_scale; /* [tokens] multiplies every output row (the 1/rms of a fused input norm), or NULL */
+    const void *residual;   /* [tokens][n_out] in y's dtype, added after scaling, or NULL */
+    uint32_t swiglu;        /* 1: weight rows interleave gate/up pairs; y is [tokens][n_out/2] = silu(gate)*up */
+    uint32_t reserved;
+} muser_cuda_epilogue;
+
+typedef struct muser_cuda_weight_info {
+    uint32_t dtype;
+    uint32_t shard_axis, shard_rank, shard_world;
+    uint64_t n_in, n_out;             /* geometry this image multiplies: the local shard's */
+    uint64_t n_in_full, n_out_full;   /* geometry of the unsharded tensor */
+    uint64_t image_bytes;             /* device bytes of the repacked image */
+    uint64_t image_hash;              /* 64-bit digest of the image bytes: repacking is deterministic */
+    float scale2;
+    float input_scale_inv;
+    uint32_t has_input_scale_inv;
+    uint32_t reserved;
+} muser_cuda_weight_info;
+
+MUSER_CUDA_API uint32_t muser_cuda_abi_version(void);
+
+/* MetalKernels::supports_projection, src/metal/encode.rs:370-385 */
+MUSER_CUDA_API int muser_cuda_supports_projection(uint32_t ggml_type);
+
+/* MetalContext::new + MetalKernels::new (src/metal/context.rs, src/metal/encode.rs:278-280).
+ * workspace_bytes sizes the one scratch arena the context owns (quantized activations of
+ * the NVFP4 lane); no entry point below allocates per call. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muser_cuda_ctx **out);
+MUSER_CUDA_API void muser_cuda_ctx_destroy(muser_cuda_ctx *ctx);
+/* Text of the most recent failure on this context (or of the last create failure when ctx is NULL). */
+MUSER_CUDA_API const char *muser_cuda_last_error(const muser_cuda_ctx *ctx);
+/* The bounded wait of MetalContext::wait_for_completion (src/metal/context.rs:149-211):
+ * synchronizes `stream` and folds asynchronous faults and device-side give-ups into a status. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, void *stream);
+
+/* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file
+ * (src/weights.rs:171-373, src/decode.rs:148-161): takes the tensor exactly as stored
+ * (K-quant: rows of blocks; NVFP4: packed E2M1 [n_out][n_in/2] plus E4M3FN scales
+ * [n_out][n_in/16], scale2, optional input_scale_inv) from HOST memory and builds the
+ * tiled device image the kernels read.  `shard` may be NULL (unsharded).  NVFP4 NaN scale
+ * codes are rejected as the loader does (src/weights.rs:244-248). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_weight_repack(muser_cuda_ctx *ctx, uint32_t ggml_type, const uint8_t *host_blocks,
+                                           const uint8_t *host_block_scales, float scale2,
+                                           int has_input_scale_inv, float input_scale_inv, uint64_t n_in,
+                                           uint64_t n_out, const muser_cuda_shard *shard,
+                                           muser_cuda_weight **out);
+/* Same, with the stored tensor already resident on the device. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_weight_repack_device(muser_cuda_ctx *ctx, uint32_t ggml_type, const uint8_t *dev_blocks,
+                                                  const uint8_t *dev_block_scales, float scale2,
+                                                  int has_input_scale_inv, float input_scale_inv, uint64_t n_in,
+                                                  uint64_t n_out, const muser_cuda_shard *shard, void *stream,
+                                                  muser_cuda_weight **out);
+MUSER_CUDA_API void muser_cuda_weight_free(muser_cuda_weight *w);
+MUSER_CUDA_API muser_cuda_status muser_cuda_weight_info_get(const muser_cuda_weight *w, muser_cuda_weight_info *out);
+
+/* weights::dequant_row over every row (src/weights.rs:82-108; quant/k_block.rs:12-49,
+ * quant/k_block/q6.rs:283-325, quant/nvfp4.rs:240-255): decodes the repacked image back to
+ * f32 [n_out][n_in].  Results are bit-identical to the reference decoders. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_dequant(muser_cuda_ctx *ctx, const muser_cuda_weight *w, float *out, void *stream);
+
+/* MetalKernels::encode_quantized_matmul (src/metal/encode/qkv.rs:414-424) and its CPU twin
+ * weights::matmul (src/weights.rs:398-421) for K-quant weights: y[t][r] = dot(W_r, x_t).
+ * x_dtype is F32 or BF16, y_dtype F32 or BF16; 1 <= tokens <= 64 (decode, decode groups as in
+ * encode_quantized_decode_group qkv.rs:234-244, and speculative-verify batches). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
+                                              uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
+                                              const muser_cuda_epilogue *epilogue, void *stream);
+
+/* MetalKernels::encode_ffn_q4k_gate_up_silu_4r2s (src/metal/encode/ffn.rs:10-19):
+ * y[t][j] = silu(Wgate_j . x_t) * (Wup_j . x_t), x read once. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_ffn_gate_up_silu(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,
+                                              const muser_cuda_weight *w_up, const void *x, uint32_t x_dtype,
+                                              void *y, uint32_t y_dtype, uint32_t tokens, void *stream);
+
+/* quant::quantize_nvfp4_activation (src/quant/nvfp4.rs:221-238) with the scale layout of the
+ * GB10 producer's quantizer (scripts/gx10/vllm/muser_vllm/exact_fp4_quant.py:149-162):
+ * packed [tokens][n_in/2], scales swizzled [ceil(tokens/128)][ceil(n_in/64)][32][4][4].
+ * Codes and scale bytes are bit-identical to the reference. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_quantize_nvfp4_activation(muser_cuda_ctx *ctx, const void *x, uint32_t x_dtype,
+                                                       uint32_t tokens, uint64_t n_in, float input_scale_inv,
+                                                       uint8_t *packed, uint8_t *scales_swizzled, void *stream);
+MUSER_CUDA_API size_t muser_cuda_nvfp4_swizzled_scale_bytes(uint64_t rows, uint64_t n_in);
+
+/* MetalKernels::encode_nvfp4_matmul with input_scale_inv = Some(..) (src/metal/encode/qkv.rs:128-227),
+ * i.e. weights::matmul's W4A4 lane (src/weights.rs:111-121, quant/nvfp4.rs:304-338): quantizes x
+ * into the context workspace, then runs the block-scaled tensor-core GEMM.  y_dtype F32, F16 or BF16
+ * (F16 is the reference's output boundary, nvfp4.rs:337). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
+                                          uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
+                                          const muser_cuda_epilogue *epilogue, void *stream);
+
+/* MetalKernels::encode_nvfp4_w4a4_prequant_m16 (src/metal/encode/qkv.rs:13-26) generalized to any
+ * token count: the GEMM alone on activations quantized earlier by
+ * muser_cuda_quantize_nvfp4_activation. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx *ctx, const muser_cuda_weight *w,
+                                                   const uint8_t *x_packed, const uint8_t *x_scales_swizzled,
+                                                   void *y, uint32_t y_dtype, uint32_t tokens,
+                                                   const muser_cuda_epilogue *epilogue, void *stream);
+
+/* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
+ * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const float *x_host,
+                                         uint32_t tokens, float *y_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUSER_CUDA_H */

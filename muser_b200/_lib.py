@@ -1,0 +1,86 @@
+"""ctypes binding of libmuser_cuda.so (include/muser_cuda.h), one Python function per C entry point.
+
+The library is the product; there is no fallback.  Importing this module fails loudly when the
+shared object has not been built (run `python -m muser_b200.build` or `__graft_entry__.build()`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmuser_cuda.so"
+
+F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
+SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
+STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
+                "TIMEOUT", "WORKSPACE_TOO_SMALL"]
+
+# every symbol include/muser_cuda.h declares
+EXPORTS = [
+    "muser_cuda_abi_version", "muser_cuda_supports_projection", "muser_cuda_ctx_create", "muser_cuda_ctx_destroy",
+    "muser_cuda_last_error", "muser_cuda_sync_status", "muser_cuda_weight_repack", "muser_cuda_weight_repack_device",
+    "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
+    "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
+    "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
+]
+
+
+class Shard(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("axis", C.c_uint32)]
+
+
+class Epilogue(C.Structure):
+    _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class WeightInfo(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_uint32), ("shard_axis", C.c_uint32), ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32),
+        ("n_in", C.c_uint64), ("n_out", C.c_uint64), ("n_in_full", C.c_uint64), ("n_out_full", C.c_uint64),
+        ("image_bytes", C.c_uint64), ("image_hash", C.c_uint64), ("scale2", C.c_float), ("input_scale_inv", C.c_float),
+        ("has_input_scale_inv", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class MuserCudaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__(f"muser-cuda {name}: {message}")
+        self.status = status
+        self.status_name = name
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built and there is no CPU fallback. "
+            "Run `python -m muser_b200.build`.")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, u32, u64, f32, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_float, C.c_int
+    sig = {
+        "muser_cuda_abi_version": (u32, []),
+        "muser_cuda_supports_projection": (i32, [u32]),
+        "muser_cuda_ctx_create": (i32, [i32, C.c_size_t, C.POINTER(vp)]),
+        "muser_cuda_ctx_destroy": (None, [vp]),
+        "muser_cuda_last_error": (C.c_char_p, [vp]),
+        "muser_cuda_sync_status": (i32, [vp, vp]),
+        "muser_cuda_weight_repack": (i32, [vp, u32, vp, vp, f32, i32, f32, u64, u64, C.POINTER(Shard), C.POINTER(vp)]),
+        "muser_cuda_weight_repack_device": (i32, [vp, u32, vp, vp, f32, i32, f32, u64, u64, C.POINTER(Shard), vp, C.POINTER(vp)]),
+        "muser_cuda_weight_free": (None, [vp]),
+        "muser_cuda_weight_info_get": (i32, [vp, C.POINTER(WeightInfo)]),
+        "muser_cuda_dequant": (i32, [vp, vp, vp, vp]),
+        "muser_cuda_quantized_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
+        "muser_cuda_ffn_gate_up_silu": (i32, [vp, vp, vp, vp, u32, vp, u32, u32, vp]),
+        "muser_cuda_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, f32, vp, vp, vp]),
+        "muser_cuda_nvfp4_swizzled_scale_bytes": (C.c_size_t, [u64, u64]),
+        "muser_cuda_nvfp4_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
+        "muser_cuda_nvfp4_matmul_prequant": (i32, [vp, vp, vp, vp, vp, u32, u32, C.POINTER(Epilogue), vp]),
+        "muser_cuda_matmul_host": (i32, [vp, vp, vp, u32, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)  # AttributeError here means the library does not export what the header declares
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()

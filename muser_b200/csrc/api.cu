@@ -1,0 +1,432 @@
+// C ABI of the library: argument validation, handle lifetime, dispatch.  See include/muser_cuda.h.
+#include <cmath>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "kquant_layout.cuh"
+
+namespace muser {
+thread_local std::string g_create_error;
+
+static bool is_kquant(uint32_t t) { return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q6_K; }
+
+// 64-bit digest of a device buffer, independent of thread scheduling: sum over 8-byte words of a
+// position-keyed multiplicative mix.
+__global__ void image_hash_kernel(const uint64_t *__restrict__ p, uint64_t n, unsigned long long *out) {
+    uint64_t h = 0;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t v = (p[i] + 0x9E3779B97F4A7C15ull * (i + 1)) * 0xBF58476D1CE4E5B9ull;
+        v ^= v >> 29;
+        h += v * 0x94D049BB133111EBull;
+    }
+    for (int o = 16; o > 0; o >>= 1) h += __shfl_xor_sync(0xffffffffu, h, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(out, (unsigned long long)h);
+}
+
+static muser_cuda_status validate_shard(Ctx *ctx, uint32_t dtype, uint64_t n_in, uint64_t n_out,
+                                        const muser_cuda_shard *shard, Weight *w) {
+    w->n_in_full = n_in;
+    w->n_out_full = n_out;
+    w->n_in = n_in;
+    w->n_out = n_out;
+    w->shard = muser_cuda_shard{0, 1, MUSER_SHARD_NONE};
+    if (!shard || shard->axis == MUSER_SHARD_NONE || shard->world <= 1) return MUSER_CUDA_OK;
+    if (shard->rank >= shard->world || shard->axis > MUSER_SHARD_K) return fail(ctx, MUSER_CUDA_BAD_ARG, "bad shard descriptor");
+    w->shard = *shard;
+    if (shard->axis == MUSER_SHARD_ROWS) {
+        // whole 16-row groups per rank keep K-quant tiles unshared; NVFP4 needs nothing beyond divisibility
+        if (n_out % shard->world) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "n_out is not divisible by the shard count");
+        w->n_out = n_out / shard->world;
+    } else {
+        const uint64_t gran = dtype == MUSER_DTYPE_Q4_K ? 32 : dtype == MUSER_DTYPE_Q6_K ? 16 : 64;
+        if (n_in % shard->world || (n_in / shard->world) % gran)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the K shard is not a whole number of sub-blocks");
+        w->n_in = n_in / shard->world;
+    }
+    return MUSER_CUDA_OK;
+}
+
+static muser_cuda_status repack_common(Ctx *ctx, uint32_t dtype, const uint8_t *blocks, const uint8_t *scales,
+                                       bool on_host, float scale2, int has_isi, float isi, uint64_t n_in,
+                                       uint64_t n_out, const muser_cuda_shard *shard, cudaStream_t stream,
+                                       muser_cuda_weight **out) {
+    if (!ctx || !out) return MUSER_CUDA_BAD_ARG;
+    *out = nullptr;
+    if (!muser_cuda_supports_projection(dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "dtype has no CUDA projection kernel");
+    if (!blocks || n_in == 0 || n_out == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "null weight bytes or empty geometry");
+    if (n_in > (1ull << 30) || n_out > (1ull << 30)) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "dimension too large");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    Weight *w = new (std::nothrow) Weight();
+    if (!w) return fail(ctx, MUSER_CUDA_ERROR, "out of host memory");
+    w->dtype = dtype;
+    w->device = ctx->device;
+    muser_cuda_status st = validate_shard(ctx, dtype, n_in, n_out, shard, w);
+    auto bail = [&](muser_cuda_status s) {
+        muser_cuda_weight_free(reinterpret_cast<muser_cuda_weight *>(w));
+        return s;
+    };
+    if (st != MUSER_CUDA_OK) return bail(st);
+    size_t raw_bytes = 0, raw_scale_bytes = 0;
+    if (is_kquant(dtype)) {
+        if (n_in % 256) return bail(fail(ctx, MUSER_CUDA_BAD_SHAPE, "K-quant rows need n_in % 256 == 0"));
+        raw_bytes = n_out * (n_in / 256) * (dtype == MUSER_DTYPE_Q4_K ? 144 : 210);
+        const uint64_t k0 = w->shard.axis == MUSER_SHARD_K ? w->shard.rank * w->n_in : 0;
+        w->k_off = (uint32_t)(k0 % 256);
+        w->nsb = (uint32_t)((w->k_off + w->n_in + 255) / 256);
+        w->row_tiles = (uint32_t)((w->n_out + 15) / 16);
+        w->image_bytes = (uint64_t)w->row_tiles * w->nsb * (dtype == MUSER_DTYPE_Q4_K ? kQ4TileBytes : kQ6TileBytes);
+        cudaError_t e = cudaMalloc(&w->image, w->image_bytes);
+        if (e != cudaSuccess) return bail(fail(ctx, MUSER_CUDA_ERROR, std::string("cudaMalloc(image): ") + cudaGetErrorString(e)));
+    } else {
+        if (!scales) return bail(fail(ctx, MUSER_CUDA_BAD_ARG, "NVFP4 weights need their block scales"));
+        if (n_in % 64) return bail(fail(ctx, MUSER_CUDA_BAD_SHAPE, "NVFP4 rows need n_in % 64 == 0"));
+        if (!std::isfinite(scale2) || (has_isi && !(std::isfinite(isi) && isi > 0.0f)))
+            return bail(fail(ctx, MUSER_CUDA_NAN_SCALE, "non-finite NVFP4 tensor scale"));
+        raw_bytes = n_out * (n_in / 2);
+        raw_scale_bytes = n_out * (n_in / 16);
+        w->scale2 = scale2;
+        w->has_input_scale_inv = has_isi != 0;
+        w->input_scale_inv = has_isi ? isi : 0.0f;
+        w->n_out_pad = (w->n_out + 255) / 256 * 256; // whole 256-row GEMM tiles
+        const size_t packed_bytes = w->n_out_pad * (w->n_in / 2);
+        const size_t scale_bytes = (w->n_out_pad / 128) * ((w->n_in + 63) / 64) * 512;
+        w->image_bytes = packed_bytes + scale_bytes;
+        cudaError_t e = cudaMalloc(&w->packed, packed_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&w->scales, scale_bytes);
+        if (e != cudaSuccess) return bail(fail(ctx, MUSER_CUDA_ERROR, std::string("cudaMalloc(nvfp4): ") + cudaGetErrorString(e)));
+    }
+    const uint8_t *dev_blocks = blocks, *dev_scales = scales;
+    uint8_t *tmp = nullptr, *tmp_s = nullptr;
+    if (on_host) {
+        cudaError_t e = cudaMalloc(&tmp, raw_bytes);
+        if (e == cudaSuccess && raw_scale_bytes) e = cudaMalloc(&tmp_s, raw_scale_bytes);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(tmp, blocks, raw_bytes, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess && raw_scale_bytes) e = cudaMemcpyAsync(tmp_s, scales, raw_scale_bytes, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) {
+            cudaFree(tmp);
+            cudaFree(tmp_s);
+            return bail(fail(ctx, MUSER_CUDA_ERROR, std::string("staging the stored tensor: ") + cudaGetErrorString(e)));
+        }
+        dev_blocks = tmp;
+        dev_scales = tmp_s;
+    }
+    st = is_kquant(dtype) ? launch_repack_kquant(ctx, w, dev_blocks, stream)
+                          : launch_repack_nvfp4(ctx, w, dev_blocks, dev_scales, stream);
+    cudaError_t e = cudaStreamSynchronize(stream);
+    cudaFree(tmp);
+    cudaFree(tmp_s);
+    if (st != MUSER_CUDA_OK) return bail(st);
+    if (e != cudaSuccess) return bail(fail(ctx, MUSER_CUDA_ERROR, std::string("repack: ") + cudaGetErrorString(e)));
+    if (dtype == MUSER_DTYPE_NVFP4_E2M1) {
+        st = nvfp4_build_tensor_map(ctx, w);
+        if (st != MUSER_CUDA_OK) return bail(st);
+    }
+    *out = reinterpret_cast<muser_cuda_weight *>(w);
+    return MUSER_CUDA_OK;
+}
+
+static muser_cuda_status check_io(Ctx *ctx, const Weight *w, const void *x, uint32_t x_dtype, const void *y,
+                                  uint32_t y_dtype, uint32_t tokens, bool y_f16_ok) {
+    if (!ctx || !w || !x || !y) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (w->device != ctx->device) return fail(ctx, MUSER_CUDA_BAD_ARG, "weight lives on another device");
+    if (tokens == 0) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "tokens must be positive");
+    if (x_dtype != MUSER_DTYPE_F32 && x_dtype != MUSER_DTYPE_BF16) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "activations must be f32 or bf16");
+    if (y_dtype != MUSER_DTYPE_F32 && y_dtype != MUSER_DTYPE_BF16 && !(y_f16_ok && y_dtype == MUSER_DTYPE_F16))
+        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "unsupported output dtype");
+    if (!aligned16(x) || !aligned16(y)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "x and y must be 16-byte aligned");
+    return MUSER_CUDA_OK;
+}
+
+} // namespace muser
+
+using namespace muser;
+
+extern "C" {
+
+uint32_t muser_cuda_abi_version(void) { return MUSER_CUDA_ABI_VERSION; }
+
+int muser_cuda_supports_projection(uint32_t t) {
+    return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q6_K || t == MUSER_DTYPE_NVFP4_E2M1;
+}
+
+muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muser_cuda_ctx **out) {
+    if (!out) return MUSER_CUDA_BAD_ARG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device < 0 || device >= count) {
+        g_create_error = e != cudaSuccess ? std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e)
+                                          : "no such CUDA device";
+        return e != cudaSuccess ? MUSER_CUDA_ERROR : MUSER_CUDA_BAD_ARG;
+    }
+    cudaDeviceProp prop;
+    e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("cudaSetDevice: ") + cudaGetErrorString(e);
+        return MUSER_CUDA_ERROR;
+    }
+    if (prop.major != 10) {
+        g_create_error = "this library is built for sm_100a only (found sm_" + std::to_string(prop.major) + std::to_string(prop.minor) + ")";
+        return MUSER_CUDA_ERROR;
+    }
+    Ctx *ctx = new (std::nothrow) Ctx();
+    if (!ctx) return MUSER_CUDA_ERROR;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->workspace_bytes = workspace_bytes;
+    e = cudaMalloc(&ctx->dev_status, 4 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 4 * sizeof(int));
+    if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("context allocation: ") + cudaGetErrorString(e);
+        muser_cuda_ctx_destroy(reinterpret_cast<muser_cuda_ctx *>(ctx));
+        return MUSER_CUDA_ERROR;
+    }
+    *out = reinterpret_cast<muser_cuda_ctx *>(ctx);
+    return MUSER_CUDA_OK;
+}
+
+void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->workspace);
+    cudaFree(ctx->dev_status);
+    cudaFree(ctx->dev_stage);
+    if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    delete ctx;
+}
+
+const char *muser_cuda_last_error(const muser_cuda_ctx *c) {
+    const Ctx *ctx = reinterpret_cast<const Ctx *>(c);
+    return ctx ? ctx->last_error.c_str() : g_create_error.c_str();
+}
+
+muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *c, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx) return MUSER_CUDA_BAD_ARG;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int flags[4] = {0, 0, 0, 0};
+    MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(flags, ctx->dev_status, sizeof(flags), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MUSER_CUDA_TRY(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    if (flags[1]) {
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(flags), (cudaStream_t)stream);
+        return fail(ctx, MUSER_CUDA_TIMEOUT, "a device-side bounded wait gave up (code " + std::to_string(flags[1]) + ")");
+    }
+    return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_weight_repack(muser_cuda_ctx *c, uint32_t t, const uint8_t *blocks, const uint8_t *scales,
+                                           float scale2, int has_isi, float isi, uint64_t n_in, uint64_t n_out,
+                                           const muser_cuda_shard *shard, muser_cuda_weight **out) {
+    return repack_common(reinterpret_cast<Ctx *>(c), t, blocks, scales, true, scale2, has_isi, isi, n_in, n_out, shard, nullptr, out);
+}
+
+muser_cuda_status muser_cuda_weight_repack_device(muser_cuda_ctx *c, uint32_t t, const uint8_t *blocks,
+                                                  const uint8_t *scales, float scale2, int has_isi, float isi,
+                                                  uint64_t n_in, uint64_t n_out, const muser_cuda_shard *shard,
+                                                  void *stream, muser_cuda_weight **out) {
+    return repack_common(reinterpret_cast<Ctx *>(c), t, blocks, scales, false, scale2, has_isi, isi, n_in, n_out, shard,
+                         (cudaStream_t)stream, out);
+}
+
+void muser_cuda_weight_free(muser_cuda_weight *wp) {
+    Weight *w = reinterpret_cast<Weight *>(wp);
+    if (!w) return;
+    cudaSetDevice(w->device);
+    cudaFree(w->image);
+    cudaFree(w->packed);
+    cudaFree(w->scales);
+    nvfp4_free_tensor_map(w);
+    delete w;
+}
+
+muser_cuda_status muser_cuda_weight_info_get(const muser_cuda_weight *wp, muser_cuda_weight_info *out) {
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    if (!w || !out) return MUSER_CUDA_BAD_ARG;
+    std::memset(out, 0, sizeof(*out));
+    out->dtype = w->dtype;
+    out->shard_axis = w->shard.axis;
+    out->shard_rank = w->shard.rank;
+    out->shard_world = w->shard.world;
+    out->n_in = w->n_in;
+    out->n_out = w->n_out;
+    out->n_in_full = w->n_in_full;
+    out->n_out_full = w->n_out_full;
+    out->image_bytes = w->image_bytes;
+    out->scale2 = w->scale2;
+    out->input_scale_inv = w->input_scale_inv;
+    out->has_input_scale_inv = w->has_input_scale_inv;
+    // digest computed on request (load-time diagnostics, synchronizes the device)
+    if (cudaSetDevice(w->device) != cudaSuccess) return MUSER_CUDA_ERROR;
+    unsigned long long *acc = nullptr;
+    if (cudaMalloc(&acc, 8) != cudaSuccess) return MUSER_CUDA_ERROR;
+    cudaMemset(acc, 0, 8);
+    if (w->image) {
+        image_hash_kernel<<<592, 256>>>(reinterpret_cast<const uint64_t *>(w->image), w->image_bytes / 8, acc);
+    } else {
+        const uint64_t pb = w->n_out_pad * (w->n_in / 2);
+        image_hash_kernel<<<592, 256>>>(reinterpret_cast<const uint64_t *>(w->packed), pb / 8, acc);
+        image_hash_kernel<<<592, 256>>>(reinterpret_cast<const uint64_t *>(w->scales), (w->image_bytes - pb) / 8, acc);
+    }
+    unsigned long long h = 0;
+    cudaError_t e = cudaMemcpy(&h, acc, 8, cudaMemcpyDeviceToHost);
+    cudaFree(acc);
+    if (e != cudaSuccess) return MUSER_CUDA_ERROR;
+    out->image_hash = h;
+    return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_dequant(muser_cuda_ctx *c, const muser_cuda_weight *wp, float *out, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    if (!ctx || !w || !out) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_dequant(ctx, w, out, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *c, const muser_cuda_weight *wp, const void *x,
+                                              uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
+                                              const muser_cuda_epilogue *ep, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    muser_cuda_status st = check_io(ctx, w, x, x_dtype, y, y_dtype, tokens, false);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!is_kquant(w->dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "quantized_matmul takes K-quant weights; use nvfp4_matmul");
+    if (tokens > 64) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "quantized_matmul serves 1..64 tokens per call");
+    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "use muser_cuda_ffn_gate_up_silu for the fused K-quant gate/up");
+    Epilogue e;
+    if (ep) e.row_scale = ep->row_scale, e.residual = ep->residual;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_kquant_matmul(ctx, w, nullptr, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_ffn_gate_up_silu(muser_cuda_ctx *c, const muser_cuda_weight *gp, const muser_cuda_weight *up,
+                                              const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
+                                              uint32_t tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *g = reinterpret_cast<const Weight *>(gp), *u = reinterpret_cast<const Weight *>(up);
+    muser_cuda_status st = check_io(ctx, g, x, x_dtype, y, y_dtype, tokens, false);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!u) return fail(ctx, MUSER_CUDA_BAD_ARG, "null up weight");
+    if (!is_kquant(g->dtype) || g->dtype != u->dtype) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "gate and up must share one K-quant dtype");
+    if (g->n_in != u->n_in || g->n_out != u->n_out || g->k_off != u->k_off || g->nsb != u->nsb)
+        return fail(ctx, MUSER_CUDA_BAD_SHAPE, "gate and up geometry differ");
+    if (g->shard.axis == MUSER_SHARD_K) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "silu cannot be applied to K-sharded partial sums");
+    if (tokens > 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused gate/up call serves 1..16 tokens");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_kquant_matmul(ctx, g, u, x, x_dtype, y, y_dtype, tokens, Epilogue{}, (cudaStream_t)stream);
+}
+
+size_t muser_cuda_nvfp4_swizzled_scale_bytes(uint64_t rows, uint64_t n_in) {
+    return (size_t)((rows + 127) / 128 * ((n_in + 63) / 64) * 512);
+}
+
+muser_cuda_status muser_cuda_quantize_nvfp4_activation(muser_cuda_ctx *c, const void *x, uint32_t x_dtype,
+                                                       uint32_t tokens, uint64_t n_in, float isi, uint8_t *packed,
+                                                       uint8_t *scales, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !x || !packed || !scales) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (tokens == 0 || n_in == 0 || n_in % 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "NVFP4 rows are grouped by 16");
+    if (x_dtype != MUSER_DTYPE_F32 && x_dtype != MUSER_DTYPE_BF16) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "activations must be f32 or bf16");
+    if (!(std::isfinite(isi) && isi > 0.0f)) return fail(ctx, MUSER_CUDA_NAN_SCALE, "input_scale_inv must be finite and positive");
+    if (!aligned16(x) || !aligned16(packed) || !aligned16(scales)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "buffers must be 16-byte aligned");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_quantize(ctx, x, x_dtype, tokens, n_in, isi, packed, scales, (cudaStream_t)stream);
+}
+
+static muser_cuda_status nvfp4_checks(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e) {
+    if (w->dtype != MUSER_DTYPE_NVFP4_E2M1) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "nvfp4_matmul takes NVFP4 weights");
+    if (!w->has_input_scale_inv)
+        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "weight-only NVFP4 (no input_scale_inv) has no CUDA kernel yet");
+    if (ep && ep->swiglu && (w->n_out % 2)) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "swiglu needs an even n_out");
+    if (ep) e->row_scale = ep->row_scale, e->residual = ep->residual;
+    return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx *c, const muser_cuda_weight *wp, const uint8_t *xp,
+                                                   const uint8_t *xs, void *y, uint32_t y_dtype, uint32_t tokens,
+                                                   const muser_cuda_epilogue *ep, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    muser_cuda_status st = check_io(ctx, w, xp, MUSER_DTYPE_BF16, y, y_dtype, tokens, true);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!xs || !aligned16(xs)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "activation scales must be 16-byte aligned");
+    Epilogue e;
+    st = nvfp4_checks(ctx, w, ep, &e);
+    if (st != MUSER_CUDA_OK) return st;
+    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "swiglu epilogue is not available on this entry point yet");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_weight *wp, const void *x, uint32_t x_dtype,
+                                          void *y, uint32_t y_dtype, uint32_t tokens, const muser_cuda_epilogue *ep,
+                                          void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    muser_cuda_status st = check_io(ctx, w, x, x_dtype, y, y_dtype, tokens, true);
+    if (st != MUSER_CUDA_OK) return st;
+    Epilogue e;
+    st = nvfp4_checks(ctx, w, ep, &e);
+    if (st != MUSER_CUDA_OK) return st;
+    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "swiglu epilogue is not available on this entry point yet");
+    const size_t tok_pad = ((size_t)tokens + 127) / 128 * 128;
+    const size_t packed_bytes = tok_pad * (w->n_in / 2);
+    const size_t scale_bytes = muser_cuda_nvfp4_swizzled_scale_bytes(tokens, w->n_in);
+    if (packed_bytes + scale_bytes > ctx->workspace_bytes)
+        return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL,
+                    "context workspace holds " + std::to_string(ctx->workspace_bytes) + " bytes, this call needs " +
+                        std::to_string(packed_bytes + scale_bytes));
+    uint8_t *xp = reinterpret_cast<uint8_t *>(ctx->workspace), *xs = xp + packed_bytes;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    st = launch_nvfp4_quantize(ctx, x, x_dtype, tokens, w->n_in, w->input_scale_inv, xp, xs, (cudaStream_t)stream);
+    if (st != MUSER_CUDA_OK) return st;
+    return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *c, const muser_cuda_weight *wp, const float *x_host,
+                                         uint32_t tokens, float *y_host) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    if (!ctx || !w || !x_host || !y_host || tokens == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)tokens * w->n_in * 4, yb = (size_t)tokens * w->n_out * 4;
+    const size_t need = (xb + 255) / 256 * 256 + yb;
+    if (need > ctx->dev_stage_bytes) { // grows on first use / larger shapes only
+        cudaFree(ctx->dev_stage);
+        if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
+        ctx->dev_stage = ctx->host_stage = nullptr;
+        ctx->dev_stage_bytes = 0;
+        MUSER_CUDA_TRY(ctx, cudaMalloc(&ctx->dev_stage, need));
+        MUSER_CUDA_TRY(ctx, cudaMallocHost(&ctx->host_stage, need));
+        ctx->dev_stage_bytes = ctx->host_stage_bytes = need;
+    }
+    uint8_t *dx = reinterpret_cast<uint8_t *>(ctx->dev_stage), *dy = dx + (xb + 255) / 256 * 256;
+    uint8_t *hx = reinterpret_cast<uint8_t *>(ctx->host_stage), *hy = hx + (xb + 255) / 256 * 256;
+    std::memcpy(hx, x_host, xb);
+    cudaStream_t s = ctx->copy_stream;
+    MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(dx, hx, xb, cudaMemcpyHostToDevice, s));
+    muser_cuda_status st;
+    if (w->dtype == MUSER_DTYPE_NVFP4_E2M1) {
+        st = muser_cuda_nvfp4_matmul(c, wp, dx, MUSER_DTYPE_F32, dy, MUSER_DTYPE_F32, tokens, nullptr, s);
+    } else {
+        st = MUSER_CUDA_OK;
+        for (uint32_t t0 = 0; t0 < tokens && st == MUSER_CUDA_OK; t0 += 64) {
+            const uint32_t n = tokens - t0 < 64 ? tokens - t0 : 64;
+            st = muser_cuda_quantized_matmul(c, wp, dx + (size_t)t0 * w->n_in * 4, MUSER_DTYPE_F32,
+                                             dy + (size_t)t0 * w->n_out * 4, MUSER_DTYPE_F32, n, nullptr, s);
+        }
+    }
+    if (st != MUSER_CUDA_OK) return st;
+    MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(hy, dy, yb, cudaMemcpyDeviceToHost, s));
+    MUSER_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    std::memcpy(y_host, hy, yb);
+    return MUSER_CUDA_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,97 @@
+// Shared declarations of the muser-cuda library: handles, error plumbing, tile geometry.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/muser_cuda.h"
+
+namespace muser {
+
+// ---- tile geometry of the repacked K-quant images -------------------------------------------
+// A tile covers 16 weight rows x one 256-element super-block and is contiguous in memory; tiles
+// are ordered [row_tile][super_block].  Inside a tile the quants are laid out in the order the
+// 32 lanes of a warp consume them (one 16-byte load per lane), followed by the scale headers.
+constexpr int kTileRows = 16;
+constexpr int kQ4TileBytes = 2048 + 256;             // nibbles | 16 x (d, dmin, scales[12])
+constexpr int kQ6TileBytes = 2048 + 1024 + 256 + 32; // low nibbles | high 2-bit | 16 x sc[16] | 16 x d
+constexpr int kQ6OffHi = 2048, kQ6OffSc = 3072, kQ6OffD = 3328;
+
+struct Ctx {
+    int device = 0;
+    int sm_count = 0;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int *dev_status = nullptr; // device-side give-up flags (bounded waits), read by sync_status
+    cudaStream_t copy_stream = nullptr;
+    void *host_stage = nullptr; // pinned staging for matmul_host
+    size_t host_stage_bytes = 0;
+    void *dev_stage = nullptr;
+    size_t dev_stage_bytes = 0;
+    std::string last_error;
+};
+
+struct Weight {
+    uint32_t dtype = 0;
+    int device = 0;
+    uint64_t n_in = 0, n_out = 0;           // local (shard) geometry
+    uint64_t n_in_full = 0, n_out_full = 0; // unsharded geometry
+    muser_cuda_shard shard{0, 1, 0};
+    // K-quants
+    uint8_t *image = nullptr; // tiles
+    uint32_t row_tiles = 0;   // ceil(n_out / 16)
+    uint32_t nsb = 0;         // super-block tiles per row tile
+    uint32_t k_off = 0;       // elements of the first tile that precede this shard's first input
+    // NVFP4
+    uint8_t *packed = nullptr; // [n_out_pad][n_in/2]
+    uint8_t *scales = nullptr; // swizzled [n_out_pad/128][ceil(n_in/64)][32][4][4], unsigned magnitudes
+    uint64_t n_out_pad = 0;
+    float scale2 = 1.0f;
+    float input_scale_inv = 0.0f;
+    bool has_input_scale_inv = false;
+    uint64_t image_bytes = 0;
+    void *tmap_cache = nullptr; // CUtensorMap of `packed`, built at repack time
+};
+
+inline muser_cuda_status fail(Ctx *ctx, muser_cuda_status st, const std::string &msg) {
+    if (ctx) ctx->last_error = msg;
+    return st;
+}
+
+extern thread_local std::string g_create_error;
+
+#define MUSER_CUDA_TRY(ctx, expr)                                                                     \
+    do {                                                                                              \
+        cudaError_t e__ = (expr);                                                                     \
+        if (e__ != cudaSuccess)                                                                       \
+            return ::muser::fail((ctx), MUSER_CUDA_ERROR,                                             \
+                                 std::string(#expr) + ": " + cudaGetErrorString(e__));                \
+    } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- launchers implemented in the .cu files ---------------------------------------------------
+struct Epilogue {
+    const float *row_scale = nullptr;
+    const void *residual = nullptr;
+};
+
+muser_cuda_status launch_repack_kquant(Ctx *, Weight *, const uint8_t *dev_blocks, cudaStream_t);
+muser_cuda_status launch_repack_nvfp4(Ctx *, Weight *, const uint8_t *dev_packed, const uint8_t *dev_scales,
+                                      cudaStream_t);
+muser_cuda_status launch_dequant(Ctx *, const Weight *, float *out, cudaStream_t);
+muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
+                                       void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &,
+                                       cudaStream_t);
+muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
+                                        float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t);
+muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
+                                    void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t);
+muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);
+void nvfp4_free_tensor_map(Weight *);
+
+} // namespace muser

@@ -1,0 +1,366 @@
+// NVFP4 x NVFP4 block-scaled GEMM on the 5th-generation tensor cores: y[t][n] = sum_k x[t][k] * w[n][k].
+//
+// Stands in for MetalKernels::encode_nvfp4_matmul / encode_nvfp4_w4a4_prequant_m16
+// (crates/muser-engine/src/metal/encode/qkv.rs:13-65,128-227) and the W4A4 lane of weights::matmul
+// (src/weights.rs:111-121, quant/nvfp4.rs:304-338): E2M1 codes of activations and weights, one E4M3 scale per
+// 16 values on each side, then (acc * weight_scale2) * (1 / input_scale_inv) in that order.
+//
+// Shape of the kernel: one CTA computes a 128-token x 256-row output tile.  Warp 0 streams 128-byte-swizzled
+// K slabs (256 values) of both operands with TMA plus their scale factors with bulk copies through a
+// 4-stage shared-memory ring; warp 1 copies the scale factors into tensor memory (tcgen05.cp) and issues
+// tcgen05.mma kind::mxf4nvf4 (K = 64 per instruction) into a 128 x 256 f32 accumulator in tensor memory;
+// warps 2-5 read the accumulator back (tcgen05.ld), apply the two tensor scales and the fused epilogue, and
+// store.  Every mbarrier wait is bounded: on expiry the CTA records a code in the context's status word,
+// stops issuing work, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace muser {
+
+constexpr int BM = 128, BN = 256, BK = 256;      // tile: tokens x weight rows x values
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK / 2;             // 16 KiB
+constexpr int kBBytes = BN * BK / 2;             // 32 KiB
+constexpr int kSfaBytes = 4 * 512;               // 128 rows x 16 scales
+constexpr int kSfbBytes = 2 * 4 * 512;           // 256 rows x 16 scales
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;              // 256 accumulator + 16 SFA + 32 SFB, rounded to a power of two
+constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct GemmArgs {
+    const uint8_t *a_scales; // activations, swizzled
+    const uint8_t *b_scales; // weights, swizzled
+    void *y;
+    const float *row_scale;
+    const void *residual;
+    int *status;
+    uint32_t tokens, n_out, k_tiles, kt64; // kt64: 64-value blocks per row (one MMA and one scale chunk each)
+    uint32_t y_dtype;
+    float scale2, inv_input_scale;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// K-major operand tile, 128 bytes per row, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;            // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+    d |= (uint64_t)1 << 46;            // descriptor version
+    d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+    return d;
+}
+// Scale-factor chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(128 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+__device__ __forceinline__ void tmem_cp_scales(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStages * kStageBytes);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages), bar_acc = smem_u32(bars + 2 * kStages);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tile_m = blockIdx.y, tile_n = blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
+            const uint8_t *sfb0 = g.b_scales + (size_t)(2 * tile_n) * g.kt64 * 512;
+            const uint8_t *sfb1 = sfb0 + (size_t)g.kt64 * 512;
+            uint32_t issued = 0;
+            bool ok = true;
+            for (uint32_t kt = 0; kt < g.k_tiles && ok; ++kt) {
+                const uint32_t s = kt % kStages, round = kt / kStages;
+                if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
+                if (!ok) break;
+                const uint32_t st = base + s * kStageBytes;
+                const uint32_t full = bar_full + 8 * s;
+                // the last slab may hold fewer than four 64-value blocks: the operand boxes are zero-filled
+                // past the row end, and only the scale chunks that exist are fetched
+                const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
+                mbar_expect_tx(full, kABytes + kBBytes + 3 * sf_bytes);
+                tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
+                tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                bulk_load(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
+                bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
+                bulk_load(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
+                issued = kt + 1;
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(g.status + 1, 101);
+                // let the copies already in flight land before the CTA's shared memory goes away
+                const uint32_t first = issued > kStages ? issued - kStages : 0;
+                for (uint32_t kt = first; kt < issued; ++kt) {
+                    uint32_t done = 0;
+                    for (uint32_t i = 0; i < kSpinLimit && !done; ++i)
+                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(done) : "r"(bar_full + 8 * (kt % kStages)), "r"((kt / kStages) & 1) : "memory");
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            // kind::mxf4nvf4: A and B E2M1 (format 1), K-major, UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (uint32_t kt = 0; kt < g.k_tiles; ++kt) {
+                const uint32_t s = kt % kStages, round = kt / kStages;
+                ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = base + s * kStageBytes;
+                const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
+                const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
+                const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
+                for (uint32_t kb = 0; kb < nkb; ++kb) {
+                    tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(sfa + 512 * kb));
+                    tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(sfb + 512 * kb));
+                    tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                    // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
+                    mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb,
+                             (kt | kb) != 0);
+                }
+                mma_commit(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
+            }
+            if (ok) {
+                mma_commit(bar_acc);
+            } else {
+                *abort_flag = 1;
+                atomicExch(g.status + 1, 102);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc, 0, abort_flag));
+        if (!ok && lane == 0) {
+            *abort_flag = 1;
+            atomicCAS(g.status + 1, 0, 103);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t quad = warp & 3;                 // the 32 accumulator lanes this warp may read
+            const uint32_t tok = tile_m * BM + quad * 32 + lane;
+            const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
+            for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(tmem + ((quad * 32) << 16) + c0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const uint32_t n0 = tile_n * BN + c0;
+                if (tok < g.tokens && n0 < g.n_out) {
+                    const size_t o = (size_t)tok * g.n_out + n0;
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        // quant/nvfp4.rs:334-336: tensor scales applied one after the other
+                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), g.scale2), g.inv_input_scale) * rs;
+                    }
+                    const bool full = n0 + 32 <= g.n_out;
+                    if (g.y_dtype == MUSER_DTYPE_F32) {
+                        float *y = reinterpret_cast<float *>(g.y) + o;
+                        const float *res = g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr;
+                        if (full && ((g.n_out & 3) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 q = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                if (res) {
+                                    const float4 rr = *reinterpret_cast<const float4 *>(res + i);
+                                    q.x += rr.x, q.y += rr.y, q.z += rr.z, q.w += rr.w;
+                                }
+                                *reinterpret_cast<float4 *>(y + i) = q;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && n0 + i < g.n_out; ++i) y[i] = v[i] + (res ? res[i] : 0.0f);
+                        }
+                    } else if (g.y_dtype == MUSER_DTYPE_BF16) {
+                        __nv_bfloat16 *y = reinterpret_cast<__nv_bfloat16 *>(g.y) + o;
+                        const __nv_bfloat16 *res = g.residual ? reinterpret_cast<const __nv_bfloat16 *>(g.residual) + o : nullptr;
+                        for (int i = 0; i < 32 && n0 + i < g.n_out; ++i)
+                            y[i] = __float2bfloat16_rn(v[i] + (res ? __bfloat162float(res[i]) : 0.0f));
+                    } else {
+                        __half *y = reinterpret_cast<__half *>(g.y) + o;
+                        const __half *res = g.residual ? reinterpret_cast<const __half *>(g.residual) + o : nullptr;
+                        for (int i = 0; i < 32 && n0 + i < g.n_out; ++i)
+                            y[i] = __float2half_rn(v[i] + (res ? __half2float(res[i]) : 0.0f));
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// rows x (k/2 bytes), K contiguous; box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside.
+static bool make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {
+    CUtensorMap *m = new CUtensorMap;
+    if (!make_map(m, w->packed, w->n_out_pad, w->n_in / 2, BN)) {
+        delete m;
+        return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the weight image");
+    }
+    w->tmap_cache = m;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        attr_set = true;
+    }
+    return MUSER_CUDA_OK;
+}
+
+void nvfp4_free_tensor_map(Weight *w) {
+    delete reinterpret_cast<CUtensorMap *>(w->tmap_cache);
+    w->tmap_cache = nullptr;
+}
+
+muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales, void *y,
+                                    uint32_t y_dtype, uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
+    CUtensorMap map_a;
+    if (!make_map(&map_a, x_packed, tokens, w->n_in / 2, BM))
+        return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the activations");
+    GemmArgs g;
+    g.a_scales = x_scales;
+    g.b_scales = w->scales;
+    g.y = y;
+    g.row_scale = ep.row_scale;
+    g.residual = ep.residual;
+    g.status = ctx->dev_status;
+    g.tokens = tokens;
+    g.n_out = (uint32_t)w->n_out;
+    g.k_tiles = (uint32_t)((w->n_in + BK - 1) / BK);
+    g.kt64 = (uint32_t)(w->n_in / 64);
+    g.y_dtype = y_dtype;
+    g.scale2 = w->scale2;
+    g.inv_input_scale = 1.0f / w->input_scale_inv;
+    dim3 grid((unsigned)(w->n_out_pad / BN), (tokens + BM - 1) / BM);
+    nvfp4_gemm_kernel<<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
+}
+
+} // namespace muser

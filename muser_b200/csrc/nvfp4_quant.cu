@@ -1,0 +1,110 @@
+// NVFP4 activation quantizer: f32/bf16 rows -> packed E2M1 codes + one E4M3FN scale per 16 values.
+//
+// Reproduces quant::activation_group_codes / quantize_nvfp4_activation bit for bit
+// (crates/muser-engine/src/quant/nvfp4.rs:173-238): round to f16, amax/6 * input_scale_inv saturated at 448
+// and rounded to E4M3 (nearest, ties to even), then threshold compares of |x| * input_scale_inv against
+// scale * {0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5} with the reference's <= / < pattern.  Scales are written in
+// the 128-row x 4-group swizzle of scripts/gx10/vllm/muser_vllm/exact_fp4_quant.py:149-162, which is also
+// the order the block-scaled MMA wants them in tensor memory.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace muser {
+
+__device__ __forceinline__ float e4m3_to_f32(uint32_t code) { // finite, non-negative codes only
+    const uint32_t ex = (code >> 3) & 15u, man = code & 7u;
+    if (ex == 0) return (float)man * (1.0f / 512.0f);
+    return __fmul_rn(1.0f + (float)man * 0.125f, __uint_as_float((ex + 120u) << 23));
+}
+
+__device__ __forceinline__ uint32_t e2m1_code(float r, float isi, float scale) {
+    const uint32_t sign = (__float_as_uint(r) >> 31) << 3;
+    if (scale == 0.0f) return sign;
+    const float m = __fmul_rn(fabsf(r), isi);
+    uint32_t code = 0;
+    code += m > __fmul_rn(scale, 0.25f);
+    code += m >= __fmul_rn(scale, 0.75f);
+    code += m > __fmul_rn(scale, 1.25f);
+    code += m >= __fmul_rn(scale, 1.75f);
+    code += m > __fmul_rn(scale, 2.5f);
+    code += m >= __fmul_rn(scale, 3.5f);
+    code += m > __fmul_rn(scale, 5.0f);
+    return sign | code;
+}
+
+// One thread per 16-value group; the four threads of a 64-value span merge their scale bytes into one
+// aligned 32-bit store.  Rows tokens..tokens_pad-1 only clear their scale slots.
+template <bool XF32>
+__global__ void nvfp4_quantize_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t tokens_pad, uint32_t n_in,
+                                      uint32_t kt, float isi, uint8_t *__restrict__ packed,
+                                      uint8_t *__restrict__ scales) {
+    const uint32_t groups_pad = kt * 4; // group slots per row in the swizzled plane
+    const uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)tokens_pad * groups_pad) return; // groups_pad % 4 == 0: quads never straddle the edge
+    const uint32_t row = (uint32_t)(idx / groups_pad), grp = (uint32_t)(idx % groups_pad);
+    uint32_t scale_code = 0;
+    if (row < tokens && grp * 16 < n_in) {
+        float r[16];
+        if constexpr (XF32) {
+            const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + (size_t)row * n_in + grp * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = __ldg(p + i);
+                r[4 * i] = v.x, r[4 * i + 1] = v.y, r[4 * i + 2] = v.z, r[4 * i + 3] = v.w;
+            }
+        } else {
+            const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + (size_t)row * n_in + grp * 16);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint4 v = __ldg(p + i);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    r[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                    r[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                }
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            r[i] = __half2float(__float2half_rn(r[i]));
+            amax = fmaxf(amax, fabsf(r[i]));
+        }
+        const float target = fminf(__fmul_rn(__fmul_rn(amax, 1.0f / 6.0f), isi), 448.0f);
+        scale_code = __nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3) & 0x7Fu;
+        const float scale = e4m3_to_f32(scale_code);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo |= e2m1_code(r[i], isi, scale) << (4 * i);
+            hi |= e2m1_code(r[8 + i], isi, scale) << (4 * i);
+        }
+        *reinterpret_cast<uint2 *>(packed + (size_t)row * (n_in / 2) + grp * 8) = make_uint2(lo, hi);
+    }
+    uint32_t word = scale_code;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 1) << 8;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 2) << 16;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 3) << 24;
+    if ((grp & 3) == 0) {
+        const size_t off = (size_t)(row / 128) * ((size_t)kt * 512) + (size_t)(grp / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4;
+        *reinterpret_cast<uint32_t *>(scales + off) = word;
+    }
+}
+
+muser_cuda_status launch_nvfp4_quantize(Ctx *ctx, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
+                                        float isi, uint8_t *packed, uint8_t *scales, cudaStream_t stream) {
+    const uint32_t kt = (uint32_t)((n_in + 63) / 64);
+    const uint32_t tokens_pad = (tokens + 127) / 128 * 128;
+    const uint64_t total = (uint64_t)tokens_pad * kt * 4;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (x_dtype == MUSER_DTYPE_F32)
+        nvfp4_quantize_kernel<true><<<blocks, 256, 0, stream>>>(x, tokens, tokens_pad, (uint32_t)n_in, kt, isi, packed, scales);
+    else
+        nvfp4_quantize_kernel<false><<<blocks, 256, 0, stream>>>(x, tokens, tokens_pad, (uint32_t)n_in, kt, isi, packed, scales);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
+}
+
+} // namespace muser

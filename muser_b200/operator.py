@@ -1,0 +1,238 @@
+"""Host-side mirror of the reference's quantized-matmul operator interface, over the C ABI.
+
+Names, argument meaning and error behaviour follow the reference so that a test written against
+`MetalKernels` / `weights::matmul` reads the same here:
+
+    crates/muser-engine/src/weights.rs:29-48     TensorView / Nvfp4AuxView   -> TensorView
+    src/weights.rs:398-421                       matmul(w, x, n_tokens, out) -> matmul
+    src/metal/encode.rs:370-385                  supports_projection         -> CudaKernels.supports_projection
+    src/metal/encode/qkv.rs:414-424              encode_quantized_matmul     -> CudaKernels.encode_quantized_matmul
+    src/metal/encode/qkv.rs:128-140              encode_nvfp4_matmul         -> CudaKernels.encode_nvfp4_matmul
+    src/metal/encode/qkv.rs:13-26                encode_nvfp4_w4a4_prequant_m16 -> CudaKernels.encode_nvfp4_prequant
+    src/metal/encode/ffn.rs:10-19                encode_ffn_q4k_gate_up_silu_4r2s -> CudaKernels.encode_ffn_gate_up_silu
+
+torch supplies device memory and streams only; every computation goes through libmuser_cuda.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, MuserCudaError
+
+_L = _lib.lib
+_TORCH_DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+@dataclass
+class TensorView:
+    """The stored tensor, exactly as the reference's weight loader sees it (weights.rs:29-48).
+
+    raw: K-quant rows of blocks, or NVFP4 packed E2M1 bytes [n_out][n_in/2]; a host numpy array or a
+    torch uint8 tensor (host or device).  block_scales / scale2 / input_scale_inv are the NVFP4 companions.
+    """
+    raw: object
+    dtype: int
+    n_in: int
+    n_out: int
+    block_scales: object = None
+    scale2: float = 1.0
+    input_scale_inv: float | None = None
+
+
+class Context:
+    """One per device: owns the workspace that the NVFP4 lane quantizes activations into."""
+
+    def __init__(self, device: int = 0, workspace_bytes: int = 64 << 20):
+        self.device = device
+        h = C.c_void_p()
+        st = _L.muser_cuda_ctx_create(device, workspace_bytes, C.byref(h))
+        if st != 0:
+            raise MuserCudaError(st, (_L.muser_cuda_last_error(None) or b"").decode())
+        self._h = h
+
+    def check(self, st: int) -> None:
+        if st != 0:
+            raise MuserCudaError(st, (_L.muser_cuda_last_error(self._h) or b"").decode())
+
+    def sync_status(self) -> None:
+        self.check(_L.muser_cuda_sync_status(self._h, _stream_ptr(self.device)))
+
+    def close(self) -> None:
+        if self._h:
+            _L.muser_cuda_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Weight:
+    """A repacked device image of one projection (or of one tensor-parallel shard of it)."""
+
+    def __init__(self, ctx: Context, view: TensorView, shard: tuple[int, int, int] | None = None):
+        self.ctx = ctx
+        h = C.c_void_p()
+        sh = _lib.Shard(*shard) if shard else None
+        raw, scales = view.raw, view.block_scales
+        on_device = isinstance(raw, torch.Tensor) and raw.is_cuda
+        has_isi = 0 if view.input_scale_inv is None else 1
+        isi = 0.0 if view.input_scale_inv is None else float(view.input_scale_inv)
+        if on_device:
+            raw = raw.contiguous()
+            sp = None
+            if scales is not None:
+                scales = scales.contiguous()
+                sp = scales.data_ptr()
+            st = _L.muser_cuda_weight_repack_device(ctx._h, view.dtype, raw.data_ptr(), sp, view.scale2, has_isi, isi,
+                                                    view.n_in, view.n_out, C.byref(sh) if sh else None,
+                                                    _stream_ptr(ctx.device), C.byref(h))
+        else:
+            raw = np.ascontiguousarray(raw.numpy() if isinstance(raw, torch.Tensor) else raw, dtype=np.uint8)
+            sp = None
+            if scales is not None:
+                scales = np.ascontiguousarray(scales.numpy() if isinstance(scales, torch.Tensor) else scales, dtype=np.uint8)
+                sp = scales.ctypes.data
+            expect = view.n_out * _row_bytes(view.dtype, view.n_in)
+            if raw.size != expect:
+                raise MuserCudaError(2, f"weight bytes {raw.size} do not match the geometry ({expect})")
+            st = _L.muser_cuda_weight_repack(ctx._h, view.dtype, raw.ctypes.data, sp, view.scale2, has_isi, isi,
+                                             view.n_in, view.n_out, C.byref(sh) if sh else None, C.byref(h))
+        ctx.check(st)
+        self._h = h
+        info = _lib.WeightInfo()
+        self.dtype, self.view_dtype = view.dtype, view.dtype
+        self._info = None
+        self.n_in_full, self.n_out_full = view.n_in, view.n_out
+        world = shard[1] if shard else 1
+        axis = shard[2] if shard else SHARD_NONE
+        self.n_in = view.n_in // world if axis == SHARD_K else view.n_in
+        self.n_out = view.n_out // world if axis == SHARD_ROWS else view.n_out
+        self.scale2, self.input_scale_inv = view.scale2, view.input_scale_inv
+        del info
+
+    def info(self) -> _lib.WeightInfo:
+        out = _lib.WeightInfo()
+        st = _L.muser_cuda_weight_info_get(self._h, C.byref(out))
+        self.ctx.check(st)
+        return out
+
+    def free(self) -> None:
+        if self._h:
+            _L.muser_cuda_weight_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _row_bytes(dtype: int, n_in: int) -> int:
+    if dtype == Q4_K:
+        return n_in // 256 * 144
+    if dtype == Q6_K:
+        return n_in // 256 * 210
+    if dtype == NVFP4:
+        return n_in // 2
+    raise MuserCudaError(4, f"dtype {dtype} has no CUDA projection kernel")
+
+
+def _epilogue(row_scale, residual):
+    if row_scale is None and residual is None:
+        return None
+    return _lib.Epilogue(row_scale.data_ptr() if row_scale is not None else None,
+                         residual.data_ptr() if residual is not None else None, 0, 0)
+
+
+class CudaKernels:
+    """Counterpart of the reference's `MetalKernels` for the projections of one device."""
+
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        self.launches = 0  # kernels this object has enqueued
+
+    @staticmethod
+    def supports_projection(dtype: int) -> bool:
+        return bool(_L.muser_cuda_supports_projection(dtype))
+
+    def dequant(self, w: Weight) -> torch.Tensor:
+        out = torch.empty((w.n_out, w.n_in), dtype=torch.float32, device=f"cuda:{self.ctx.device}")
+        self.ctx.check(_L.muser_cuda_dequant(self.ctx._h, w._h, out.data_ptr(), _stream_ptr(self.ctx.device)))
+        self.launches += 1
+        return out
+
+    def encode_quantized_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, tokens: int,
+                                row_scale=None, residual=None) -> None:
+        """y[t][r] = dot(W_r, x_t) for K-quant weights; input [tokens][n_in] f32|bf16, output [tokens][n_out] f32|bf16."""
+        ep = _epilogue(row_scale, residual)
+        self.ctx.check(_L.muser_cuda_quantized_matmul(
+            self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
+            _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+    def encode_ffn_gate_up_silu(self, gate_w: Weight, up_w: Weight, input: torch.Tensor, output: torch.Tensor,
+                                tokens: int) -> None:
+        self.ctx.check(_L.muser_cuda_ffn_gate_up_silu(
+            self.ctx._h, gate_w._h, up_w._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
+            _TORCH_DTYPE[output.dtype], tokens, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+    def quantize_nvfp4_activation(self, input: torch.Tensor, input_scale_inv: float):
+        tokens, n_in = input.shape
+        dev = input.device
+        packed = torch.empty((tokens, n_in // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty((_L.muser_cuda_nvfp4_swizzled_scale_bytes(tokens, n_in),), dtype=torch.uint8, device=dev)
+        self.ctx.check(_L.muser_cuda_quantize_nvfp4_activation(
+            self.ctx._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, n_in, input_scale_inv, packed.data_ptr(),
+            scales.data_ptr(), _stream_ptr(self.ctx.device)))
+        self.launches += 1
+        return packed, scales
+
+    def encode_nvfp4_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int,
+                            row_scale=None, residual=None) -> None:
+        """W4A4 lane: quantizes `input` with the weight's input_scale_inv, then the block-scaled GEMM."""
+        ep = _epilogue(row_scale, residual)
+        self.ctx.check(_L.muser_cuda_nvfp4_matmul(
+            self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
+            _TORCH_DTYPE[output.dtype], columns, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
+        self.launches += 2
+
+    def encode_nvfp4_prequant(self, weights: Weight, packed: torch.Tensor, scales: torch.Tensor, output: torch.Tensor,
+                              columns: int, row_scale=None, residual=None) -> None:
+        ep = _epilogue(row_scale, residual)
+        self.ctx.check(_L.muser_cuda_nvfp4_matmul_prequant(
+            self.ctx._h, weights._h, packed.data_ptr(), scales.data_ptr(), output.data_ptr(),
+            _TORCH_DTYPE[output.dtype], columns, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+
+def matmul(ctx: Context, w: Weight, x: np.ndarray, n_tokens: int, out: np.ndarray | None = None) -> np.ndarray:
+    """weights::matmul (weights.rs:398): host f32 slices in and out, the device path in between."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(n_tokens, w.n_in)
+    if out is None:
+        out = np.empty((n_tokens, w.n_out), dtype=np.float32)
+    ctx.check(_L.muser_cuda_matmul_host(ctx._h, w._h, x.ctypes.data, n_tokens, out.ctypes.data))
+    return out
+
+
+def unswizzle_scales(swizzled: torch.Tensor, rows: int, n_in: int) -> torch.Tensor:
+    """Logical [rows][n_in/16] view of the [rows/128][n_in/64][32][4][4] scale plane (test helper)."""
+    groups = n_in // 16
+    kt = (n_in + 63) // 64
+    r = torch.arange(rows, device=swizzled.device)[:, None]
+    g = torch.arange(groups, device=swizzled.device)[None, :]
+    off = (r // 128) * (kt * 512) + (g // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + g % 4
+    return swizzled.reshape(-1)[off]

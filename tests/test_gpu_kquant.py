@@ -1,0 +1,183 @@
+"""GPU parity of the K-quant path (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-3          # the stated bound: relative L2 against the f32-accumulating CPU lane
+REF_REL, REF_ABS = 2e-4, 0.02  # the reference's own envelope for f32-order kernels (metal.rs:213)
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from muser_b200 import operator as op
+    ctx = op.Context(0)
+    yield op, ctx, op.CudaKernels(ctx)
+    ctx.close()
+
+
+def fixtures(dtype):
+    from muser_b200 import synth
+    bs = O.BLOCK_BYTES[dtype]
+    closed = H.quant_rows(144, 64) if dtype == O.Q4_K else H.q6_rows(64)
+    yield "closed-form", closed, 256, 64
+    yield "lcg-13x512", H.lcg_weights(dtype, 13, 2, seed=41 + dtype), 512, 13
+    yield "lcg-37x1024", H.lcg_weights(dtype, 37, 4, seed=97 + dtype), 1024, 37
+    w = synth.normal_weights(48, 2048, seed=0, stream=dtype)
+    yield "synthetic-48x2048", synth.quantize_kquant(w, dtype).numpy(), 2048, 48
+    assert closed.shape[1] == bs
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_dequantised_weights_are_bit_exact(gpu, dtype):
+    op, ctx, k = gpu
+    for name, raw, n_in, n_out in fixtures(dtype):
+        w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+        got = k.dequant(w).cpu().numpy()
+        want = O.dequant_blocks(dtype, raw).reshape(n_out, n_in)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+        w.free()
+
+
+def check_close(got, want, name):
+    assert H.rel_l2(got, want) <= REL_L2_TOL, (name, H.rel_l2(got, want))
+    assert np.all(np.abs(got - want) <= np.maximum(REF_ABS, REF_REL * np.abs(want))), name
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float32])
+def test_matmul_matches_cpu_lane(gpu, dtype, x_dtype):
+    op, ctx, k = gpu
+    for name, raw, n_in, n_out in fixtures(dtype):
+        w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+        ow = O.TensorView(raw, dtype, n_in, n_out)
+        for tokens in (1, 2, 3, 4, 8, 9, 16, 33, 64):
+            x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=5 + tokens).reshape(tokens, n_in)).to(x_dtype)
+            want = O.matmul(ow, x.float().numpy(), threads=4)
+            y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+            k.encode_quantized_matmul(w, x.cuda(), y, tokens)
+            check_close(y.cpu().numpy(), want, (name, tokens))
+        w.free()
+
+
+def test_epilogue_row_scale_residual_and_bf16_output(gpu):
+    op, ctx, k = gpu
+    raw = H.lcg_weights(O.Q4_K, 37, 2, seed=3)
+    w = op.Weight(ctx, op.TensorView(raw, O.Q4_K, 512, 37))
+    x = torch.from_numpy(H.lcg_activations(5 * 512, seed=8).reshape(5, 512)).to(torch.bfloat16)
+    base = O.matmul(O.TensorView(raw, O.Q4_K, 512, 37), x.float().numpy())
+    rs = torch.tensor([0.5, 2.0, 1.0, -1.5, 0.25], device="cuda")
+    res = torch.from_numpy(H.lcg_activations(5 * 37, seed=2).reshape(5, 37)).cuda()
+    y = torch.empty((5, 37), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(w, x.cuda(), y, 5, row_scale=rs, residual=res)
+    want = base * rs.cpu().numpy()[:, None] + res.cpu().numpy()
+    assert np.allclose(y.cpu().numpy(), want, rtol=1e-4, atol=1e-4)
+    yb = torch.empty((5, 37), dtype=torch.bfloat16, device="cuda")
+    k.encode_quantized_matmul(w, x.cuda(), yb, 5)
+    assert np.allclose(yb.float().cpu().numpy(), base, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_fused_gate_up_silu(gpu, dtype):
+    op, ctx, k = gpu
+    n_in, n_out = 1024, 37
+    rg, ru = H.lcg_weights(dtype, n_out, 4, seed=21), H.lcg_weights(dtype, n_out, 4, seed=22)
+    wg, wu = (op.Weight(ctx, op.TensorView(r, dtype, n_in, n_out)) for r in (rg, ru))
+    for tokens in (1, 4, 11):
+        x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=6).reshape(tokens, n_in) * 0.3).to(torch.bfloat16)
+        g = O.matmul(O.TensorView(rg, dtype, n_in, n_out), x.float().numpy())
+        u = O.matmul(O.TensorView(ru, dtype, n_in, n_out), x.float().numpy())
+        want = O.silu_mul(g, u)
+        y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        k.encode_ffn_gate_up_silu(wg, wu, x.cuda(), y, tokens)
+        assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_tensor_parallel_shards(gpu, dtype):
+    """Row shards concatenate to the unsharded result exactly; K shards sum to it within tolerance."""
+    op, ctx, k = gpu
+    n_in, n_out, tokens = 1280, 64, 3   # 1280 / 4 = 320 inputs per K shard = 1.25 super-blocks
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=77)
+    x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=1).reshape(tokens, n_in)).to(torch.bfloat16).cuda()
+    view = op.TensorView(raw, dtype, n_in, n_out)
+    full = op.Weight(ctx, view)
+    y_full = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(full, x, y_full, tokens)
+    want_deq = O.dequant_blocks(dtype, raw).reshape(n_out, n_in)
+    world = 4
+    parts, acc = [], torch.zeros_like(y_full)
+    for rank in range(world):
+        wr = op.Weight(ctx, view, shard=(rank, world, op.SHARD_ROWS))
+        yr = torch.empty((tokens, n_out // world), dtype=torch.float32, device="cuda")
+        k.encode_quantized_matmul(wr, x, yr, tokens)
+        parts.append(yr)
+        assert np.array_equal(k.dequant(wr).cpu().numpy(), want_deq[rank * 16:(rank + 1) * 16])
+        wk = op.Weight(ctx, view, shard=(rank, world, op.SHARD_K))
+        ks = n_in // world
+        assert np.array_equal(k.dequant(wk).cpu().numpy(), want_deq[:, rank * ks:(rank + 1) * ks])
+        yk = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        k.encode_quantized_matmul(wk, x[:, rank * ks:(rank + 1) * ks].contiguous(), yk, tokens)
+        acc += yk
+    assert torch.equal(torch.cat(parts, dim=1), y_full)
+    assert H.rel_l2(acc.cpu().numpy(), y_full.cpu().numpy()) <= 1e-5
+
+
+def test_config1_full_size_q4k_gemv(gpu):
+    """y[1,27648] = x[1,5120] . W(Q4_K): every dequantised weight bit-exact, output within tolerance."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_in, n_out = 5120, 27648
+    wf = synth.normal_weights(n_out, n_in, seed=0, stream=4, device="cuda")
+    raw = synth.quantize_q4_k(wf)
+    x = synth.normal_activations(1, n_in, seed=0, device="cuda")
+    w = op.Weight(ctx, op.TensorView(raw, O.Q4_K, n_in, n_out))
+    raw_h = raw.cpu().numpy()
+    ow = O.TensorView(raw_h, O.Q4_K, n_in, n_out)
+    deq = k.dequant(w)
+    want = torch.from_numpy(O.dequant_tensor(ow))
+    assert torch.equal(deq.cpu().view(torch.int32), want.view(torch.int32))
+    y = torch.empty((1, n_out), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(w, x, y, 1)
+    ref = O.matmul(ow, x.float().cpu().numpy(), threads=O.host_threads())
+    assert H.rel_l2(y.cpu().numpy(), ref) <= REL_L2_TOL
+    # host-slice entry point (weights::matmul signature)
+    yh = op.matmul(ctx, w, x.float().cpu().numpy(), 1)
+    assert H.rel_l2(yh, ref) <= REL_L2_TOL
+    # linearity at full size: W(2a + b) == 2 W a + W b up to rounding
+    a, b = synth.normal_activations(2, n_in, seed=3, device="cuda")
+    ab = torch.stack([a, b, (2 * a.float() + b.float()).to(torch.bfloat16)])
+    y3 = torch.empty((3, n_out), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(w, ab, y3, 3)
+    lin = 2 * y3[0] + y3[1]
+    exact = (2 * a.float() + b.float())
+    y_exact = torch.empty((1, n_out), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(w, exact.reshape(1, -1).contiguous(), y_exact, 1)
+    assert H.rel_l2(lin.cpu().numpy(), y_exact[0].cpu().numpy()) <= 1e-4
+
+
+def test_misuse_returns_statuses(gpu):
+    op, ctx, k = gpu
+    raw = H.lcg_weights(O.Q4_K, 16, 1, seed=1)
+    with pytest.raises(op.MuserCudaError) as e:
+        op.Weight(ctx, op.TensorView(raw, 13, 256, 16))      # Q5_K: no projection kernel
+    assert e.value.status_name == "UNSUPPORTED_DTYPE"
+    with pytest.raises(op.MuserCudaError) as e:
+        op.Weight(ctx, op.TensorView(raw[:, :100], O.Q4_K, 256, 16))
+    assert e.value.status_name == "BAD_SHAPE"
+    w = op.Weight(ctx, op.TensorView(raw, O.Q4_K, 256, 16))
+    x = torch.zeros((65, 256), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((65, 16), dtype=torch.float32, device="cuda")
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_quantized_matmul(w, x, y, 65)
+    assert e.value.status_name == "BAD_SHAPE"
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_quantized_matmul(w, x.flatten()[1:257], y, 1)   # 2 bytes off a 16-byte boundary
+    assert e.value.status_name == "BAD_ALIGN"
+    with pytest.raises(op.MuserCudaError) as e:
+        op.Weight(ctx, op.TensorView(raw, O.Q4_K, 256, 16), shard=(0, 3, op.SHARD_ROWS))
+    assert e.value.status_name == "BAD_SHAPE"

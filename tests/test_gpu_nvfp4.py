@@ -1,0 +1,197 @@
+"""GPU parity of the NVFP4 path (quantizer, repack, block-scaled GEMM) against the CPU oracle and the
+vectors produced by the reference's own Python code."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-3  # outputs: relative L2 against the CPU lane's value before its final f16 rounding
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from muser_b200 import operator as op
+    ctx = op.Context(0, workspace_bytes=64 << 20)
+    yield op, ctx, op.CudaKernels(ctx)
+    ctx.close()
+
+
+def f16_bits_to_f32(a):
+    return a.view(np.float16).astype(np.float32)
+
+
+def test_activation_quantiser_is_bit_identical_to_reference_vectors(gpu, golden):
+    op, ctx, k = gpu
+    for tag in ("quant", "quant2", "w4a4"):
+        key = f"{tag}_input_f16_bits" if tag != "w4a4" else "w4a4_activation_f16_bits"
+        x = torch.from_numpy(f16_bits_to_f32(golden[key])).cuda()
+        isi = float(golden[f"{tag}_global_scale"] if tag != "w4a4" else golden["w4a4_act_global"])
+        packed, scales = k.quantize_nvfp4_activation(x, isi)
+        want_packed = golden[f"{tag}_packed"] if tag != "w4a4" else golden["w4a4_act_packed"]
+        assert np.array_equal(packed.cpu().numpy(), want_packed), tag
+        rows, n_in = x.shape
+        logical = op.unswizzle_scales(scales, rows, n_in).cpu().numpy()
+        op_, os_ = O.quantize_nvfp4_activation(x.cpu().numpy(), isi)
+        assert np.array_equal(logical, os_), tag
+        if tag != "w4a4":  # the reference's own swizzled plane, byte for byte where rows exist
+            ref = golden[f"{tag}_scales_swizzled"].reshape(-1)
+            assert np.array_equal(scales.cpu().numpy()[: ref.size], ref), tag
+
+
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_activation_quantiser_matches_oracle_on_random_and_edge_inputs(gpu, x_dtype):
+    op, ctx, k = gpu
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn((133, 320), generator=g) * torch.logspace(-6, 3, 320)[None, :]
+    x[5, :16] = 0.0
+    x[6, 16:32] = -0.0
+    x[7, 32] = 70000.0      # beyond f16: rounds to inf, scale saturates
+    x[8, 48:64] = 1e-8
+    x = x.to(x_dtype)
+    isi = 37.5
+    packed, scales = k.quantize_nvfp4_activation(x.cuda(), isi)
+    wp, ws = O.quantize_nvfp4_activation(x.float().numpy(), isi)
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    assert np.array_equal(op.unswizzle_scales(scales, 133, 320).cpu().numpy(), ws)
+
+
+def make_weight(op, ctx, n_out, n_in, seed, negative_scales=False):
+    from muser_b200 import synth
+    w = synth.normal_weights(n_out, n_in, seed=seed, stream=9)
+    packed, scales, scale2 = synth.nvfp4_weight(w)
+    packed, scales = packed.numpy().copy(), scales.numpy().copy()
+    if negative_scales:
+        scales[::3, ::5] |= 0x80  # signed E4M3 scale codes are legal in the stored format
+    return packed, scales, scale2
+
+
+def test_weight_repack_dequantises_bit_exactly(gpu, golden):
+    op, ctx, k = gpu
+    packed, scales, scale2 = make_weight(op, ctx, 37, 320, seed=2, negative_scales=True)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, 320, 37, scales, scale2, 100.0))
+    got = k.dequant(w).cpu().numpy()
+    want = O.dequant_nvfp4(packed, scales, scale2)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the reference Python decoder's vector
+    w2 = op.Weight(ctx, op.TensorView(np.tile(golden["codec_packed"], (1, 1)), O.NVFP4, 128, 9,
+                                      golden["codec_scales"], float(golden["codec_scale2"]), 1.0))
+    got2 = k.dequant(w2).cpu().numpy()
+    assert np.array_equal(got2.view(np.uint32), golden["codec_dequant"].view(np.uint32))
+    bad = scales.copy()
+    bad[3, 2] = 0x7F
+    with pytest.raises(op.MuserCudaError) as e:
+        op.Weight(ctx, op.TensorView(packed, O.NVFP4, 320, 37, bad, scale2, 100.0))
+    assert e.value.status_name == "NAN_SCALE"
+
+
+def test_w4a4_gemm_reproduces_the_reference_fixture(gpu, golden):
+    """32 x 128 x 128 fixture of scripts/gx10/vllm/test_exact_fp4_mm.py, expected values computed by its numpy half."""
+    op, ctx, k = gpu
+    isi = float(golden["w4a4_act_global"])
+    w = op.Weight(ctx, op.TensorView(golden["w4a4_w_packed"], O.NVFP4, 128, 128, golden["w4a4_w_scales_logical"],
+                                     float(golden["w4a4_weight_scale2"]), isi))
+    x = torch.from_numpy(f16_bits_to_f32(golden["w4a4_activation_f16_bits"])).cuda()
+    y = torch.full((32, 128), float("nan"), dtype=torch.float16, device="cuda")
+    k.encode_nvfp4_matmul(w, x, y, 32)
+    ctx.sync_status()
+    want = golden["w4a4_expected_f16_bits"].view(np.float16).astype(np.float32)
+    got = y.float().cpu().numpy()
+    assert H.rel_l2(got, want) <= REL_L2_TOL
+    # the integer lane is exact; an f32-accumulating tensor core may differ by an f16 ulp on a few cells
+    ulp = np.abs(got.astype(np.float16).view(np.int16).astype(np.int32) - want.astype(np.float16).view(np.int16).astype(np.int32))
+    assert ulp.max() <= 1 and (ulp > 0).mean() < 0.02
+
+
+@pytest.mark.parametrize("n_out,n_in,tokens", [(256, 256, 128), (37, 320, 7), (300, 1024, 130), (512, 2048, 300)])
+def test_w4a4_gemm_matches_cpu_lane(gpu, n_out, n_in, tokens):
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=n_out, negative_scales=True)
+    x = synth.normal_activations(tokens, n_in, seed=4)
+    isi = synth.activation_input_scale_inv(x)
+    ow = O.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi)
+    ref_f16, ref_f32 = O.matmul(ow, x.float().numpy(), threads=O.host_threads(), return_pre_round=True)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi))
+    for y_dtype, ref in ((torch.float32, ref_f32), (torch.float16, ref_f16), (torch.bfloat16, ref_f32)):
+        y = torch.full((tokens, n_out), float("nan"), dtype=y_dtype, device="cuda")
+        k.encode_nvfp4_matmul(w, x.cuda(), y, tokens)
+        ctx.sync_status()
+        tol = REL_L2_TOL if y_dtype != torch.bfloat16 else 4e-3  # bf16 output rounding alone is 2^-9
+        assert H.rel_l2(y.float().cpu().numpy(), ref) <= tol, (y_dtype, H.rel_l2(y.float().cpu().numpy(), ref))
+    # prequantised entry point + fused row scale and residual
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    rs = torch.linspace(0.5, 1.5, tokens, device="cuda")
+    res = torch.randn((tokens, n_out), device="cuda")
+    y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_prequant(w, xp, xs, y, tokens, row_scale=rs, residual=res)
+    ctx.sync_status()
+    want = ref_f32 * rs.cpu().numpy()[:, None] + res.cpu().numpy()
+    assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
+
+
+def test_nvfp4_tensor_parallel_shards(gpu):
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_out, n_in, tokens, world = 512, 1280, 40, 4   # 320 inputs per K shard: a ragged 256-value slab
+    packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=5)
+    x = synth.normal_activations(tokens, n_in, seed=6)
+    isi = synth.activation_input_scale_inv(x)
+    view = op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi)
+    full = op.Weight(ctx, view)
+    y_full = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_matmul(full, x.cuda(), y_full, tokens)
+    cols, acc = [], torch.zeros_like(y_full)
+    for rank in range(world):
+        wr = op.Weight(ctx, view, shard=(rank, world, op.SHARD_ROWS))
+        yr = torch.empty((tokens, n_out // world), dtype=torch.float32, device="cuda")
+        k.encode_nvfp4_matmul(wr, x.cuda(), yr, tokens)
+        cols.append(yr)
+        wk = op.Weight(ctx, view, shard=(rank, world, op.SHARD_K))
+        ks = n_in // world
+        yk = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        k.encode_nvfp4_matmul(wk, x[:, rank * ks:(rank + 1) * ks].contiguous().cuda(), yk, tokens)
+        acc += yk
+    ctx.sync_status()
+    assert torch.equal(torch.cat(cols, dim=1), y_full)
+    assert H.rel_l2(acc.cpu().numpy(), y_full.cpu().numpy()) <= 1e-5
+
+
+def test_prefill_shape_sampled_rows(gpu):
+    """M = 2048 on a real projection shape (attn_k: 5120 -> 1024), checked on 64 sampled token rows."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_in, n_out, tokens = 5120, 1024, 2048
+    w_f = synth.normal_weights(n_out, n_in, seed=0, stream=2, device="cuda")
+    packed, scales, scale2 = synth.nvfp4_weight(w_f)
+    x = synth.normal_activations(tokens, n_in, seed=0, device="cuda")
+    isi = synth.activation_input_scale_inv(x)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi))
+    y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_matmul(w, x, y, tokens)
+    ctx.sync_status()
+    rows = torch.randperm(tokens, generator=torch.Generator().manual_seed(0))[:64]
+    ow = O.TensorView(packed.cpu().numpy(), O.NVFP4, n_in, n_out, scales.cpu().numpy(), scale2, isi)
+    _, ref = O.matmul(ow, x[rows.cuda()].float().cpu().numpy(), threads=O.host_threads(), return_pre_round=True)
+    assert H.rel_l2(y[rows.cuda()].cpu().numpy(), ref) <= REL_L2_TOL
+
+
+def test_workspace_and_dtype_misuse(gpu):
+    op, ctx, k = gpu
+    packed, scales, scale2 = make_weight(op, ctx, 64, 256, seed=1)
+    w_only = op.Weight(ctx, op.TensorView(packed, O.NVFP4, 256, 64, scales, scale2, None))
+    x = torch.zeros((4, 256), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((4, 64), dtype=torch.float32, device="cuda")
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_nvfp4_matmul(w_only, x, y, 4)
+    assert e.value.status_name == "UNSUPPORTED_DTYPE"
+    small = op.Context(0, workspace_bytes=1024)
+    w = op.Weight(small, op.TensorView(packed, O.NVFP4, 256, 64, scales, scale2, 10.0))
+    with pytest.raises(op.MuserCudaError) as e:
+        op.CudaKernels(small).encode_nvfp4_matmul(w, x, y, 4)
+    assert e.value.status_name == "WORKSPACE_TOO_SMALL"
+    w.free()
+    small.close()
