@@ -178,6 +178,11 @@ muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muse
     ctx->workspace_bytes = workspace_bytes;
     e = cudaMalloc(&ctx->dev_status, 4 * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 4 * sizeof(int));
+    ctx->gemv_partial_bytes = 16u << 20;
+    ctx->gemv_counter_slots = 1u << 16;
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_partial, ctx->gemv_partial_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_counters, ctx->gemv_counter_slots * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counter_slots * sizeof(unsigned int));
     if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
@@ -195,6 +200,8 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaSetDevice(ctx->device);
     cudaFree(ctx->workspace);
     cudaFree(ctx->dev_status);
+    cudaFree(ctx->gemv_partial);
+    cudaFree(ctx->gemv_counters);
     cudaFree(ctx->dev_stage);
     if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);

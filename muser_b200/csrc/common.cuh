@@ -27,6 +27,10 @@ struct Ctx {
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
     int *dev_status = nullptr; // device-side give-up flags (bounded waits), read by sync_status
+    float *gemv_partial = nullptr;        // K-slice partial sums of the decode GEMV
+    size_t gemv_partial_bytes = 0;
+    unsigned int *gemv_counters = nullptr; // one arrival counter per 16-row tile, zero between launches
+    uint32_t gemv_counter_slots = 0;
     cudaStream_t copy_stream = nullptr;
     void *host_stage = nullptr; // pinned staging for matmul_host
     size_t host_stage_bytes = 0;
@@ -87,6 +91,8 @@ muser_cuda_status launch_dequant(Ctx *, const Weight *, float *out, cudaStream_t
 muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
                                        void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &,
                                        cudaStream_t);
+cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, void *y, uint32_t y_dtype,
+                               uint32_t tokens, const Epilogue &, cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
                                         float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t);
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,

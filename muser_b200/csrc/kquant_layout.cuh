@@ -1,19 +1,23 @@
 // Geometry of the repacked K-quant images, shared by the repack, dequant and matmul kernels.
 //
+// Lane (g, t) of a warp (g = lane / 4, t = lane % 4) owns rows g and g + 8 of the tile and, within each row,
+// WHOLE sub-blocks: Q4_K sub-blocks t and t + 4 (32 weights each), Q6_K sub-blocks t, t + 4, t + 8, t + 12
+// (16 weights each).  Its bytes sit at uint4 index (q * 32 + lane) of each plane, so one warp-wide 16-byte
+// load reads 512 contiguous bytes.
+//
 // Q4_K tile (16 rows x 256 inputs, 2304 bytes)
-//   [0, 2048)   uint4[4][32]: uint4 (q, lane) with lane = 4g + t, q = 2*rowsel + half, belongs to row
-//               g + 8*rowsel; its word wi holds sub-block j = 4*half + wi, elements 32j + 8t + i (i = 0..7),
-//               element i in nibble q4_nibble_pos(i).  That order puts elements (0,1), (2,3), (4,5), (6,7) in
-//               nibble pairs (s, s+4), so (word >> 4s) & 0x000F000F yields one packed pair per operation.
+//   [0, 2048)   uint4 (q, lane), q = 2*rowsel + hi: row g + 8*rowsel, sub-block t + 4*hi.  Word wi holds
+//               elements 8wi .. 8wi+7 of that sub-block, element i in nibble q4_nibble_pos(i): the order puts
+//               elements (0,1), (2,3), (4,5), (6,7) in nibble pairs (p, p+4), so (word >> 4p) & 0x000F000F
+//               yields one packed pair per operation.
 //   [2048,2304) 16 x the block's 16-byte header (d f16, dmin f16, 12 bytes of packed 6-bit scale/min).
 // Q6_K tile (3360 bytes)
-//   [0, 2048)   low nibbles: uint4 (q, lane), q = 2*rowsel + half; word wi holds sub-blocks 8*half + 2wi
-//               (low nibble of byte b) and 8*half + 2wi + 1 (high nibble of byte b), elements 4t + b.
-//   [2048,3072) high 2 bits: uint4 (rowsel, lane); word wi holds sub-blocks 4wi + s (s = 0..3): element
-//               4t + b in bits [8b + 2s, 8b + 2s + 1].
+//   [0, 2048)   low nibbles: uint4 (q, lane), q = 2*rowsel + half.  Word wi belongs to owned sub-block
+//               o = 2*half + wi/2 (sub-block t + 4o) and holds its elements 8h .. 8h+7, h = wi % 2: byte b
+//               carries element 8h + b in its low nibble and element 8h + 4 + b in its high nibble.
+//   [2048,3072) high 2 bits: uint4 (rowsel, lane); word o holds sub-block t + 4o: element 4x + b in bits
+//               [8b + 2x, 8b + 2x + 1].
 //   [3072,3328) 16 x sc[16] int8;  [3328,3360) 16 x d f16.
-// A lane (g, t) therefore owns, in both formats, the weights that the m16n8k16 A fragment assigns to it:
-// rows g and g + 8, MMA k-slots {2t, 2t+1, 2t+8, 2t+9}.
 #pragma once
 #include "common.cuh"
 

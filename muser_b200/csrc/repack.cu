@@ -27,12 +27,12 @@ __global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
         uint32_t q = u >> 7, lane = (u >> 2) & 31, wi = u & 3;
         uint32_t g = lane >> 2, t = lane & 3;
         uint32_t row = rt * 16 + g + 8 * (q >> 1);
-        uint32_t j = 4 * (q & 1) + wi;
+        uint32_t j = t + 4 * (q & 1);
         uint32_t word = 0;
         if (row < gm.n_out) {
             const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
             for (int i = 0; i < 8; ++i) {
-                uint32_t e = 32 * j + 8 * t + i;
+                uint32_t e = 32 * j + 8 * wi + i;
                 int64_t k = k_base + e;
                 if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) continue;
                 uint32_t grp = e >> 6, l = e & 63;
@@ -103,12 +103,12 @@ __global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
         uint32_t q = u >> 7, lane = (u >> 2) & 31, wi = u & 3;
         uint32_t g = lane >> 2, t = lane & 3;
         uint32_t row = rt * 16 + g + 8 * (q >> 1);
-        uint32_t sa = 8 * (q & 1) + 2 * wi; // even sub-block in the low nibbles, odd one in the high nibbles
+        uint32_t j = t + 4 * (2 * (q & 1) + (wi >> 1)), h = wi & 1;
         uint32_t word = 0;
         if (row < gm.n_out) {
             const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
             for (uint32_t b = 0; b < 4; ++b) {
-                uint32_t lo, hi2, ea = 16 * sa + 4 * t + b, eb = ea + 16;
+                uint32_t lo, hi2, ea = 16 * j + 8 * h + b, eb = ea + 4;
                 if (in_shard(ea)) {
                     q6_raw_value(blk, ea, &lo, &hi2);
                     word |= lo << (8 * b);
@@ -120,7 +120,7 @@ __global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
             }
         }
         reinterpret_cast<uint32_t *>(tile_ptr)[(q * 32 + lane) * 4 + wi] = word;
-    } else if (u < 768) { // high 2-bit plane: uint4 index rowsel*32+lane; word wi holds sub-blocks 4wi..4wi+3
+    } else if (u < 768) { // high 2-bit plane: uint4 index rowsel*32+lane; word wi holds sub-block t + 4wi
         uint32_t v = u - 512;
         uint32_t rowsel = v >> 7, lane = (v >> 2) & 31, wi = v & 3;
         uint32_t g = lane >> 2, t = lane & 3;
@@ -128,12 +128,12 @@ __global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
         uint32_t word = 0;
         if (row < gm.n_out) {
             const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
-            for (uint32_t s = 0; s < 4; ++s)
+            for (uint32_t x = 0; x < 4; ++x)
                 for (uint32_t b = 0; b < 4; ++b) {
-                    uint32_t lo, hi2, e = 16 * (4 * wi + s) + 4 * t + b;
+                    uint32_t lo, hi2, e = 16 * (t + 4 * wi) + 4 * x + b;
                     if (!in_shard(e)) continue;
                     q6_raw_value(blk, e, &lo, &hi2);
-                    word |= hi2 << (8 * b + 2 * s);
+                    word |= hi2 << (8 * b + 2 * x);
                 }
         }
         reinterpret_cast<uint32_t *>(tile_ptr + kQ6OffHi)[(rowsel * 32 + lane) * 4 + wi] = word;
@@ -228,8 +228,8 @@ __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__r
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * gm.nsb + sb) * kQ4TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
-    uint32_t j = e >> 5, t = (e >> 3) & 3, i = e & 7;
-    uint32_t q = rowsel * 2 + (j >> 2), lane = g * 4 + t, wi = j & 3;
+    uint32_t j = e >> 5, wi = (e >> 3) & 3, i = e & 7;
+    uint32_t q = rowsel * 2 + (j >> 2), lane = g * 4 + (j & 3);
     uint32_t word = reinterpret_cast<const uint32_t *>(tile)[(q * 32 + lane) * 4 + wi];
     uint32_t nib = (word >> (4 * q4_nibble_pos(i))) & 15u;
     const uint8_t *hdr = tile + 2048 + r * 16;
@@ -256,11 +256,11 @@ __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__r
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * gm.nsb + sb) * kQ6TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
-    uint32_t s = e >> 4, t = (e >> 2) & 3, b = e & 3, lane = g * 4 + t;
-    uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (s >> 3)) * 32 + lane) * 4 + ((s & 7) >> 1)];
-    uint32_t lo = (lo_word >> (8 * b + 4 * (s & 1))) & 15u;
-    uint32_t hi_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + (s >> 2)];
-    uint32_t hi2 = (hi_word >> (8 * b + 2 * (s & 3))) & 3u;
+    uint32_t s = e >> 4, el = e & 15, o = s >> 2, lane = g * 4 + (s & 3);
+    uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (o >> 1)) * 32 + lane) * 4 + (o & 1) * 2 + (el >> 3)];
+    uint32_t lo = (lo_word >> (8 * (el & 3) + 4 * ((el >> 2) & 1))) & 15u;
+    uint32_t hi_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + o];
+    uint32_t hi2 = (hi_word >> (8 * (el & 3) + 2 * (el >> 2))) & 3u;
     int qv = (int)(lo | (hi2 << 4)) - 32;
     float d = __half2float(reinterpret_cast<const __half *>(tile + kQ6OffD)[r]);
     int sc = reinterpret_cast<const int8_t *>(tile + kQ6OffSc)[r * 16 + s];
