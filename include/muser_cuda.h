@@ -176,6 +176,18 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx
                                                    void *y, uint32_t y_dtype, uint32_t tokens,
                                                    const muser_cuda_epilogue *epilogue, void *stream);
 
+/* No counterpart in the reference.  The same W4A4 projection as muser_cuda_nvfp4_matmul for callers that cannot
+ * allocate device memory: a driver that works out of arenas it sized once has no allocator to lend and, on the
+ * step path, may not stall on the device-wide lock that cudaMalloc / cudaFree take.  This call needs no context
+ * and allocates nothing: the quantized activations pass through a 2.25 MiB array that lives in the library image
+ * on every GPU that loads it.  `w` is a handle made earlier by muser_cuda_weight_repack*; x and y are the caller's.
+ * Limits: tokens <= 128, n_in <= 32768, else MUSER_CUDA_WORKSPACE_TOO_SMALL.  All calls on a device share that
+ * array, so calls that overlap on the GPU race: keep them on one stream or order them.  The first call on a device
+ * looks up the array's device address; make that call before any stream capture.  Failures leave their text in
+ * muser_cuda_last_error(NULL). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda_weight *w, const void *x, uint32_t x_dtype,
+                                                                void *y, uint32_t y_dtype, uint32_t tokens, void *stream);
+
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
  * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const float *x_host,

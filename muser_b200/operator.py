@@ -219,6 +219,15 @@ class CudaKernels:
         self.launches += 1
 
 
+def nvfp4_matmul_static(weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int) -> None:
+    """muser_cuda_nvfp4_matmul_static: the W4A4 projection without a context and without any allocation
+    (tokens <= 128, n_in <= 32768); scratch lives in the library image.  Enqueued on torch's current stream."""
+    st = _L.muser_cuda_nvfp4_matmul_static(weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
+                                           _TORCH_DTYPE[output.dtype], columns, _stream_ptr(input.device.index or 0))
+    if st != 0:
+        raise MuserCudaError(st, (_L.muser_cuda_last_error(None) or b"").decode())
+
+
 def matmul(ctx: Context, w: Weight, x: np.ndarray, n_tokens: int, out: np.ndarray | None = None) -> np.ndarray:
     """weights::matmul (weights.rs:398): host f32 slices in and out, the device path in between."""
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(n_tokens, w.n_in)
