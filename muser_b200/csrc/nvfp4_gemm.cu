@@ -5,7 +5,7 @@
 // (src/weights.rs:111-121, quant/nvfp4.rs:304-338): E2M1 codes of activations and weights, one E4M3 scale per
 // 16 values on each side, then (acc * weight_scale2) * (1 / input_scale_inv) in that order.
 //
-// Shape of the kernel: one CTA computes a 128-token x 256-row output tile.  Warp 0 streams 128-byte-swizzled
+// Shape of the kernel: persistent CTAs, one per SM, each walking 128-token x 256-row output tiles.  Warp 0 streams 128-byte-swizzled
 // K slabs (256 values) of both operands with TMA plus their scale factors with bulk copies through a
 // 4-stage shared-memory ring; warp 1 copies the scale factors into tensor memory (tcgen05.cp) and issues
 // tcgen05.mma kind::mxf4nvf4 (K = 64 per instruction) into a 128 x 256 f32 accumulator in tensor memory;
@@ -13,6 +13,8 @@
 // store.  Every mbarrier wait is bounded: on expiry the CTA records a code in the context's status word,
 // stops issuing work, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -26,6 +28,7 @@ constexpr int kSfaBytes = 4 * 512;               // 128 rows x 16 scales
 constexpr int kSfbBytes = 2 * 4 * 512;           // 256 rows x 16 scales
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+static_assert(kSmemBytes <= 227 * 1024, "stage ring exceeds the shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;              // 256 accumulator + 16 SFA + 32 SFB, rounded to a power of two
 constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -38,6 +41,7 @@ struct GemmArgs {
     const void *residual;
     int *status;
     uint32_t tokens, n_out, k_tiles, kt64; // kt64: 64-value blocks per row (one MMA and one scale chunk each)
+    uint32_t n_tiles;                      // 256-row tiles of the weight
     uint32_t y_dtype;
     float scale2, inv_input_scale;
 };
@@ -114,25 +118,80 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// One 32-column strip of one accumulator row: scale, fuse, convert, store (16-byte stores when the row allows).
+template <typename T>
+__device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T *res, uint32_t valid, bool vec_ok) {
+    if constexpr (sizeof(T) == 4) {
+        if (vec_ok && valid == 32) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                float4 q = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (res) {
+                    const float4 r = *reinterpret_cast<const float4 *>(res + i);
+                    q.x += r.x, q.y += r.y, q.z += r.z, q.w += r.w;
+                }
+                *reinterpret_cast<float4 *>(y + i) = q;
+            }
+            return;
+        }
+        for (uint32_t i = 0; i < valid; ++i) y[i] = v[i] + (res ? res[i] : 0.0f);
+    } else {
+        auto to_f = [](T h) { if constexpr (std::is_same<T, __half>::value) return __half2float(h); else return __bfloat162float(h); };
+        auto pack = [](float a, float b) -> uint32_t {
+            if constexpr (std::is_same<T, __half>::value) {
+                const __half2 h = __floats2half2_rn(a, b);
+                return *reinterpret_cast<const uint32_t *>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                return *reinterpret_cast<const uint32_t *>(&h);
+            }
+        };
+        if (vec_ok && valid == 32) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                float f[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = v[i + k];
+                if (res) {
+                    const uint4 r = *reinterpret_cast<const uint4 *>(res + i);
+                    const T *rt = reinterpret_cast<const T *>(&r);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) f[k] += to_f(rt[k]);
+                }
+                *reinterpret_cast<uint4 *>(y + i) = make_uint4(pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7]));
+            }
+            return;
+        }
+        for (uint32_t i = 0; i < valid; ++i) {
+            const float f = v[i] + (res ? to_f(res[i]) : 0.0f);
+            if constexpr (std::is_same<T, __half>::value) y[i] = __float2half_rn(f); else y[i] = __float2bfloat16_rn(f);
+        }
+    }
+}
+
+// Persistent: CTA b takes output tiles b, b + gridDim.x, ...; tile index -> (n tile, m tile) with m fastest, so the
+// CTAs that run side by side share one weight tile (read from HBM once, from L2 afterwards).
 __global__ void __launch_bounds__(192, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
     uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStages * kStageBytes);
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages), bar_acc = smem_u32(bars + 2 * kStages);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
+    const uint32_t bar_acc_full = smem_u32(bars + 2 * kStages), bar_acc_empty = smem_u32(bars + 2 * kStages + 1);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tile_m = blockIdx.y, tile_n = blockIdx.x;
+    const uint32_t m_tiles = (g.tokens + BM - 1) / BM, n_tiles_total = g.n_tiles * m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_acc, 1);
+        mbar_init(bar_acc_full, 1);
+        mbar_init(bar_acc_empty, 4); // one arrival per epilogue warp
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -149,38 +208,41 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
-            const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
-            const uint8_t *sfb0 = g.b_scales + (size_t)(2 * tile_n) * g.kt64 * 512;
-            const uint8_t *sfb1 = sfb0 + (size_t)g.kt64 * 512;
-            uint32_t issued = 0;
+            uint32_t it = 0, issued = 0; // k slabs issued so far, over all tiles
             bool ok = true;
-            for (uint32_t kt = 0; kt < g.k_tiles && ok; ++kt) {
-                const uint32_t s = kt % kStages, round = kt / kStages;
-                if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
-                if (!ok) break;
-                const uint32_t st = base + s * kStageBytes;
-                const uint32_t full = bar_full + 8 * s;
-                // the last slab may hold fewer than four 64-value blocks: the operand boxes are zero-filled
-                // past the row end, and only the scale chunks that exist are fetched
-                const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
-                mbar_expect_tx(full, kABytes + kBBytes + 3 * sf_bytes);
-                tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
-                tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
-                bulk_load(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
-                bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
-                bulk_load(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
-                issued = kt + 1;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
+                const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+                const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
+                const uint8_t *sfb0 = g.b_scales + (size_t)(2 * tile_n) * g.kt64 * 512;
+                const uint8_t *sfb1 = sfb0 + (size_t)g.kt64 * 512;
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kStages, round = it / kStages;
+                    if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    const uint32_t st = base + s * kStageBytes;
+                    const uint32_t full = bar_full + 8 * s;
+                    // the last slab may hold fewer than four 64-value blocks: the operand boxes are zero-filled
+                    // past the row end, and only the scale chunks that exist are fetched
+                    const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
+                    mbar_expect_tx(full, kABytes + kBBytes + 3 * sf_bytes);
+                    tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
+                    tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                    bulk_load(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
+                    bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
+                    bulk_load(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
+                    issued = it + 1;
+                }
             }
             if (!ok) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 101);
                 // let the copies already in flight land before the CTA's shared memory goes away
                 const uint32_t first = issued > kStages ? issued - kStages : 0;
-                for (uint32_t kt = first; kt < issued; ++kt) {
+                for (uint32_t k = first; k < issued; ++k) {
                     uint32_t done = 0;
                     for (uint32_t i = 0; i < kSpinLimit && !done; ++i)
                         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(done) : "r"(bar_full + 8 * (kt % kStages)), "r"((kt / kStages) & 1) : "memory");
+                                     : "=r"(done) : "r"(bar_full + 8 * (k % kStages)), "r"((k / kStages) & 1) : "memory");
                 }
             }
         }
@@ -189,45 +251,59 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (lane == 0) {
             // kind::mxf4nvf4: A and B E2M1 (format 1), K-major, UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, local = 0;
             bool ok = true;
-            for (uint32_t kt = 0; kt < g.k_tiles; ++kt) {
-                const uint32_t s = kt % kStages, round = kt / kStages;
-                ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t st = base + s * kStageBytes;
-                const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
-                const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
-                const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
-                for (uint32_t kb = 0; kb < nkb; ++kb) {
-                    tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(sfa + 512 * kb));
-                    tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(sfb + 512 * kb));
-                    tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
-                    // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
-                    mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb,
-                             (kt | kb) != 0);
+            for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++local) {
+                // the accumulator is free again once the epilogue warps have read the previous tile out of it
+                if (local > 0) {
+                    ok = mbar_wait(bar_acc_empty, (local - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                mma_commit(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kStages, round = it / kStages;
+                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = base + s * kStageBytes;
+                    const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
+                    const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
+                    const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
+                    for (uint32_t kb = 0; kb < nkb; ++kb) {
+                        tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(sfa + 512 * kb));
+                        tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(sfb + 512 * kb));
+                        tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                        // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
+                        mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb,
+                                 (kt | kb) != 0);
+                    }
+                    mma_commit(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
+                }
+                if (ok) mma_commit(bar_acc_full);
             }
-            if (ok) {
-                mma_commit(bar_acc);
-            } else {
+            if (!ok) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 102);
             }
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc, 0, abort_flag));
-        if (!ok && lane == 0) {
-            *abort_flag = 1;
-            atomicCAS(g.status + 1, 0, 103);
-        }
-        if (ok) {
+        const uint32_t quad = warp & 3; // the 32 accumulator lanes this warp may read
+        uint32_t local = 0;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
+            const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full, local & 1, abort_flag));
+            if (!ok) {
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicCAS(g.status + 1, 0, 103);
+                }
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t quad = warp & 3;                 // the 32 accumulator lanes this warp may read
             const uint32_t tok = tile_m * BM + quad * 32 + lane;
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
+            const bool vec_ok = (g.n_out & 7) == 0;
             for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 asm volatile(
@@ -240,43 +316,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(tmem + ((quad * 32) << 16) + c0));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c0 + 32 == BN) { // everything this warp needs is in registers: hand the accumulator back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
+                }
                 const uint32_t n0 = tile_n * BN + c0;
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
+                    const uint32_t valid = min(32u, g.n_out - n0);
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        // quant/nvfp4.rs:334-336: tensor scales applied one after the other
+                    for (int i = 0; i < 32; ++i) // quant/nvfp4.rs:334-336: tensor scales applied one after the other
                         v[i] = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), g.scale2), g.inv_input_scale) * rs;
-                    }
-                    const bool full = n0 + 32 <= g.n_out;
-                    if (g.y_dtype == MUSER_DTYPE_F32) {
-                        float *y = reinterpret_cast<float *>(g.y) + o;
-                        const float *res = g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr;
-                        if (full && ((g.n_out & 3) == 0)) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 q = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                                if (res) {
-                                    const float4 rr = *reinterpret_cast<const float4 *>(res + i);
-                                    q.x += rr.x, q.y += rr.y, q.z += rr.z, q.w += rr.w;
-                                }
-                                *reinterpret_cast<float4 *>(y + i) = q;
-                            }
-                        } else {
-                            for (int i = 0; i < 32 && n0 + i < g.n_out; ++i) y[i] = v[i] + (res ? res[i] : 0.0f);
-                        }
-                    } else if (g.y_dtype == MUSER_DTYPE_BF16) {
-                        __nv_bfloat16 *y = reinterpret_cast<__nv_bfloat16 *>(g.y) + o;
-                        const __nv_bfloat16 *res = g.residual ? reinterpret_cast<const __nv_bfloat16 *>(g.residual) + o : nullptr;
-                        for (int i = 0; i < 32 && n0 + i < g.n_out; ++i)
-                            y[i] = __float2bfloat16_rn(v[i] + (res ? __bfloat162float(res[i]) : 0.0f));
-                    } else {
-                        __half *y = reinterpret_cast<__half *>(g.y) + o;
-                        const __half *res = g.residual ? reinterpret_cast<const __half *>(g.residual) + o : nullptr;
-                        for (int i = 0; i < 32 && n0 + i < g.n_out; ++i)
-                            y[i] = __float2half_rn(v[i] + (res ? __half2float(res[i]) : 0.0f));
-                    }
+                    if (g.y_dtype == MUSER_DTYPE_F32)
+                        store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
+                                           g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
+                    else if (g.y_dtype == MUSER_DTYPE_BF16)
+                        store_strip<__nv_bfloat16>(v, reinterpret_cast<__nv_bfloat16 *>(g.y) + o,
+                                                   g.residual ? reinterpret_cast<const __nv_bfloat16 *>(g.residual) + o : nullptr, valid, vec_ok);
+                    else
+                        store_strip<__half>(v, reinterpret_cast<__half *>(g.y) + o,
+                                            g.residual ? reinterpret_cast<const __half *>(g.residual) + o : nullptr, valid, vec_ok);
                 }
             }
         }
@@ -357,7 +418,9 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.y_dtype = y_dtype;
     g.scale2 = w->scale2;
     g.inv_input_scale = 1.0f / w->input_scale_inv;
-    dim3 grid((unsigned)(w->n_out_pad / BN), (tokens + BM - 1) / BM);
+    g.n_tiles = (uint32_t)(w->n_out_pad / BN);
+    const uint32_t tiles = g.n_tiles * ((tokens + BM - 1) / BM);
+    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     nvfp4_gemm_kernel<<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;

@@ -38,6 +38,7 @@ struct DeviceSetup {
     bool ready = false;
     uint8_t *scratch = nullptr;
     int *status = nullptr;
+    int sm_count = 0;
 };
 constexpr int kMaxDevices = 64;
 DeviceSetup g_setup[kMaxDevices];
@@ -59,6 +60,13 @@ muser_cuda_status device_setup(int device, DeviceSetup **out) {
             g_create_error = std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e);
             return MUSER_CUDA_ERROR;
         }
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess || sms < 1) {
+            g_create_error = "cudaDeviceGetAttribute(multiProcessorCount) failed";
+            return MUSER_CUDA_ERROR;
+        }
+        s.sm_count = sms;
         s.scratch = reinterpret_cast<uint8_t *>(scratch);
         s.status = reinterpret_cast<int *>(status);
         s.ready = true;
@@ -103,6 +111,7 @@ extern "C" muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda_wei
     Ctx call; // plumbing for the launchers only: nothing in it is allocated
     call.device = w->device;
     call.dev_status = setup->status;
+    call.sm_count = setup->sm_count;
     uint8_t *packed = setup->scratch, *scales = setup->scratch + kStaticPackedBytes;
     st = launch_nvfp4_quantize(&call, x, x_dtype, tokens, w->n_in, w->input_scale_inv, packed, scales, (cudaStream_t)stream);
     if (st == MUSER_CUDA_OK)
