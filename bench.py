@@ -295,6 +295,46 @@ def run_gpu(args):
                "note": "muser_cuda_matmul_host per call: pinned staging, H2D of x, GEMV, D2H of y, synchronize"
                        + ("; rank 0's shard only" if world > 1 else "")}
 
+    # second half of the metric: NVFP4 prefill GEMM, M = 2048, the same layer's shapes (N = 1 only); not part of `value`
+    prefill = None
+    if rank == 0 and world == 1 and not args.no_prefill:
+        from muser_b200._lib import NVFP4
+        m = 2048
+        peak_fp4 = op.fp4_peak_tflops(ctx)
+        per, tot_fl, tot_s = {}, 0.0, 0.0
+        for i, (name, (k, n, _)) in enumerate(projs.items()):
+            wp, ws, s2 = synth.nvfp4_weight(synth.normal_weights(n, k, seed=0, stream=i, device=dev))
+            xa = synth.normal_activations(m, k, seed=0, stream=3000 + i, device=dev)
+            isi = synth.activation_input_scale_inv(xa)
+            wq = op.Weight(ctx, op.TensorView(wp, NVFP4, k, n, ws, s2, isi))
+            yq = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            xp, xs = kern.quantize_nvfp4_activation(xa, isi)
+            for _ in range(3):
+                kern.encode_nvfp4_prequant(wq, xp, xs, yq, m)
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            reps = 5
+            e0.record()
+            for _ in range(reps):
+                kern.encode_nvfp4_prequant(wq, xp, xs, yq, m)
+            e1.record()
+            for _ in range(reps):
+                kern.encode_nvfp4_matmul(wq, xa, yq, m)   # quantize + GEMM, as the operator is called
+            e2.record()
+            torch.cuda.synchronize()
+            ctx.sync_status()
+            t_gemm, t_full = e0.elapsed_time(e1) / reps * 1e-3, e1.elapsed_time(e2) / reps * 1e-3
+            fl = 2.0 * m * n * k
+            per[name] = {"gemm_tflops": round(fl / t_gemm / 1e12, 1), "with_quantize_tflops": round(fl / t_full / 1e12, 1)}
+            tot_fl, tot_s = tot_fl + fl, tot_s + t_gemm
+            wq.free()
+            del wp, ws, xa, yq, xp, xs
+        layer = tot_fl / tot_s / 1e12
+        prefill = {"workload": "nvfp4_prefill_gemm_layer_m2048", "unit": "TFLOP/s", "layer": round(layer, 1),
+                   "per_projection": per,
+                   "roofline": {"bound": "tensor", "achieved": round(layer, 1), "peak": round(peak_fp4, 1), "unit": "TFLOP/s",
+                                "frac": round(layer / peak_fp4, 4),
+                                "peak_kind": "measured here: muser_cuda_fp4_peak_probe (block-scaled FP4 MMAs, no memory traffic)"}}
+
     # CPU lane on this box's host cores, bounded sample (N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -337,6 +377,7 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "detail_us": detail,
+            "prefill": prefill,
         }
         print(json.dumps(line))
     if world > 1:
@@ -351,6 +392,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-lane baseline leg")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-projection timings")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the NVFP4 prefill GEMM section")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels one by one instead of as a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -188,6 +188,12 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx
 MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda_weight *w, const void *x, uint32_t x_dtype,
                                                                 void *y, uint32_t y_dtype, uint32_t tokens, void *stream);
 
+/* Measurement aid, no counterpart in the reference (its kernel bench prints TMAC/s without a ceiling,
+ * crates/muser-bench/src/m16.rs:755-774): enqueues a kernel in which every SM issues `iters` x 4 block-scaled FP4
+ * tensor-core instructions (the GEMM's, 128 x 256 x 64) with no memory traffic, and returns the flops it will have
+ * done.  Timing it gives the tensor-pipe ceiling that the prefill GEMM's roofline fraction is quoted against. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *ctx, uint32_t iters, double *flops, void *stream);
+
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
  * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const float *x_host,

@@ -22,7 +22,7 @@ EXPORTS = [
     "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
-    "muser_cuda_nvfp4_matmul_static",
+    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe",
 ]
 
 
@@ -78,6 +78,7 @@ def _load() -> C.CDLL:
         "muser_cuda_nvfp4_matmul_prequant": (i32, [vp, vp, vp, vp, vp, u32, u32, C.POINTER(Epilogue), vp]),
         "muser_cuda_matmul_host": (i32, [vp, vp, vp, u32, vp]),
         "muser_cuda_nvfp4_matmul_static": (i32, [vp, vp, u32, vp, u32, u32, vp]),
+        "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)  # AttributeError here means the library does not export what the header declares

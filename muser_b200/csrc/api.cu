@@ -396,6 +396,13 @@ muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_we
     return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
 }
 
+muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *c, uint32_t iters, double *flops, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !flops || iters == 0 || iters > (1u << 20)) return fail(ctx, MUSER_CUDA_BAD_ARG, "bad probe arguments");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_peak(ctx, iters, flops, (cudaStream_t)stream);
+}
+
 muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *c, const muser_cuda_weight *wp, const float *x_host,
                                          uint32_t tokens, float *y_host) {
     Ctx *ctx = reinterpret_cast<Ctx *>(c);

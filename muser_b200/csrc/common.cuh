@@ -97,6 +97,7 @@ muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, 
                                         float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t);
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
                                     void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t);
+muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);
 muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);
 void nvfp4_free_tensor_map(Weight *);
 

@@ -269,10 +269,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
                     const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
-                    for (uint32_t kb = 0; kb < nkb; ++kb) {
+                    auto copy_scales = [&](uint32_t kb) {
                         tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(sfa + 512 * kb));
                         tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(sfb + 512 * kb));
                         tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                    };
+                    // the scale copies of block kb + 1 are issued ahead of the MMA of block kb, so they can run under it
+                    copy_scales(0);
+                    for (uint32_t kb = 0; kb < nkb; ++kb) {
+                        if (kb + 1 < nkb) copy_scales(kb + 1);
                         // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
                         mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb,
                                  (kt | kb) != 0);
@@ -347,6 +352,66 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
+}
+
+// Tensor-pipe ceiling for this instruction: every SM issues `iters` x 4 block-scaled FP4 MMAs (128 x 256 x 64 each)
+// on whatever its shared and tensor memory hold, with no loads, no scale copies and no epilogue.  The time of this
+// kernel is the denominator for the GEMM's roofline fraction.
+__global__ void __launch_bounds__(192, 1) nvfp4_peak_kernel(uint32_t iters, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStageBytes);
+    const uint32_t bar_done = smem_u32(bars);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < kStageBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(aligned)[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+        mbar_init(bar_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    if (warp == 1 && lane == 0) {
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        const uint64_t da = operand_desc(base), db = operand_desc(base + kABytes);
+        // scale factors: one copy of zeroed chunks so that the accumulator stays finite
+        for (uint32_t kb = 0; kb < 4; ++kb) {
+            tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(base + kABytes + kBBytes));
+        }
+        for (uint32_t i = 0; i < iters; ++i)
+#pragma unroll
+            for (uint32_t kb = 0; kb < 4; ++kb)
+                mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb, (i | kb) != 0);
+        mma_commit(bar_done);
+        if (!mbar_wait(bar_done, 0, abort_flag)) atomicExch(status + 1, 104);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
+muser_cuda_status launch_nvfp4_peak(Ctx *ctx, uint32_t iters, double *flops, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes + 2048));
+        attr_set = true;
+    }
+    nvfp4_peak_kernel<<<ctx->sm_count, 192, kStageBytes + 2048, stream>>>(iters, ctx->dev_status);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    *flops = 2.0 * BM * BN * 64 * 4.0 * iters * ctx->sm_count;
+    return MUSER_CUDA_OK;
 }
 
 // ------------------------------------------------------------------------------------------ host side

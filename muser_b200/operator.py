@@ -219,6 +219,21 @@ class CudaKernels:
         self.launches += 1
 
 
+def fp4_peak_tflops(ctx: Context, iters: int = 20000, reps: int = 3) -> float:
+    """Dense block-scaled FP4 tensor throughput of this GPU (TFLOP/s), from muser_cuda_fp4_peak_probe."""
+    flops = C.c_double()
+    best = 0.0
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.check(_L.muser_cuda_fp4_peak_probe(ctx._h, iters, C.byref(flops), _stream_ptr(ctx.device)))
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    ctx.sync_status()
+    return best
+
+
 def nvfp4_matmul_static(weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int) -> None:
     """muser_cuda_nvfp4_matmul_static: the W4A4 projection without a context and without any allocation
     (tokens <= 128, n_in <= 32768); scratch lives in the library image.  Enqueued on torch's current stream."""
