@@ -379,9 +379,14 @@ def run_gpu(args):
             "detail_us": detail,
             "prefill": prefill,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the process group down: ranks finish at different times (rank 0 alone runs the
+        # detail, end-to-end and CPU legs), and a teardown that waits for a peer that is already gone never returns.
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
