@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MUSER_CUDA_ABI_VERSION 1u
+#define MUSER_CUDA_ABI_VERSION 2u
 
 #if defined(__GNUC__)
 #define MUSER_CUDA_API __attribute__((visibility("default")))
@@ -74,13 +74,17 @@ typedef struct muser_cuda_shard {
     uint32_t rank, world, axis;
 } muser_cuda_shard;
 
-/* Work fused behind a projection, reproducing src/reference.rs:59-80 (RMSNorm scale of the
- * input rows), :511-513 (silu(gate)*up) and :475-477,536-538 (residual add). */
+/* Work fused around a projection, reproducing src/reference.rs:59-80 (rms_norm, rms_norm_mul on the input
+ * rows), :511-513 (silu(gate)*up, through muser_cuda_ffn_gate_up_silu) and :475-477,536-538 (residual add). */
 typedef struct muser_cuda_epilogue {
-    const float *row_scale; /* [tokens] multiplies every output row (the 1/rms of a fused input norm), or NULL */
+    const float *row_scale; /* [tokens] multiplies every output row, or NULL */
     const void *residual;   /* [tokens][n_out] in y's dtype, added after scaling, or NULL */
-    uint32_t swiglu;        /* 1: weight rows interleave gate/up pairs; y is [tokens][n_out/2] = silu(gate)*up */
-    uint32_t reserved;
+    uint32_t swiglu;        /* must be 0: the fused SwiGLU takes two weights, see muser_cuda_ffn_gate_up_silu */
+    float norm_eps;         /* eps of the fused input norm (used when norm_weight is set) */
+    const float *norm_weight; /* [n_in] f32 on the device, or NULL.  Set: the projection reads
+                               * (x * 1/sqrt(mean(x^2) + norm_eps)) * norm_weight instead of x (rms_norm_mul,
+                               * reference.rs:73-80), computed inside the kernel that stages or quantizes x.  Not
+                               * available on K-sharded weights (a shard sees only part of the row). */
 } muser_cuda_epilogue;
 
 typedef struct muser_cuda_weight_info {
@@ -145,11 +149,17 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx
                                               uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                               const muser_cuda_epilogue *epilogue, void *stream);
 
-/* MetalKernels::encode_ffn_q4k_gate_up_silu_4r2s (src/metal/encode/ffn.rs:10-19):
- * y[t][j] = silu(Wgate_j . x_t) * (Wup_j . x_t), x read once. */
+/* MetalKernels::encode_ffn_q4k_gate_up_silu_4r2s (src/metal/encode/ffn.rs:10-19) and the CPU lane's
+ * silu_fast(gate) * up (src/reference.rs:511-513, quant/helpers.rs:72):
+ * y[t][j] = silu(Wgate_j . x_t) * (Wup_j . x_t), x read once, the two projections never written out.
+ * `epilogue` may be NULL; only its norm_weight / norm_eps are honoured (rms_norm_mul of the FFN input,
+ * reference.rs:489).  K-quant weights: 1 <= tokens <= 16.  NVFP4 weights (both with the same input_scale_inv): any token count; x is
+ * quantized into the context workspace once and one tensor-core GEMM computes both projections, each rounded
+ * to f16 as the W4A4 lane returns it (quant/nvfp4.rs:337) before the SwiGLU. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_ffn_gate_up_silu(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,
                                               const muser_cuda_weight *w_up, const void *x, uint32_t x_dtype,
-                                              void *y, uint32_t y_dtype, uint32_t tokens, void *stream);
+                                              void *y, uint32_t y_dtype, uint32_t tokens,
+                                              const muser_cuda_epilogue *epilogue, void *stream);
 
 /* quant::quantize_nvfp4_activation (src/quant/nvfp4.rs:221-238) with the scale layout of the
  * GB10 producer's quantizer (scripts/gx10/vllm/muser_vllm/exact_fp4_quant.py:149-162):
@@ -159,6 +169,13 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_quantize_nvfp4_activation(muser_cuda
                                                        uint32_t tokens, uint64_t n_in, float input_scale_inv,
                                                        uint8_t *packed, uint8_t *scales_swizzled, void *stream);
 MUSER_CUDA_API size_t muser_cuda_nvfp4_swizzled_scale_bytes(uint64_t rows, uint64_t n_in);
+/* The same quantizer behind a fused rms_norm_mul (src/reference.rs:59-80): each row is first scaled by
+ * 1/sqrt(mean(x^2) + norm_eps) and multiplied by norm_weight [n_in] (f32, device), in f32, inside the kernel.
+ * One call serves every projection that reads the normalized row (q, k, v; or gate and up). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_rmsnorm_quantize_nvfp4_activation(muser_cuda_ctx *ctx, const void *x, uint32_t x_dtype,
+                                                               uint32_t tokens, uint64_t n_in, const float *norm_weight,
+                                                               float norm_eps, float input_scale_inv, uint8_t *packed,
+                                                               uint8_t *scales_swizzled, void *stream);
 
 /* MetalKernels::encode_nvfp4_matmul with input_scale_inv = Some(..) (src/metal/encode/qkv.rs:128-227),
  * i.e. weights::matmul's W4A4 lane (src/weights.rs:111-121, quant/nvfp4.rs:304-338): quantizes x
@@ -175,6 +192,13 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx
                                                    const uint8_t *x_packed, const uint8_t *x_scales_swizzled,
                                                    void *y, uint32_t y_dtype, uint32_t tokens,
                                                    const muser_cuda_epilogue *epilogue, void *stream);
+
+/* muser_cuda_ffn_gate_up_silu for NVFP4 weights on activations quantized earlier (the pre-quantized form of
+ * qkv.rs:13-26 applied to the fused FFN front half). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,
+                                                             const muser_cuda_weight *w_up, const uint8_t *x_packed,
+                                                             const uint8_t *x_scales_swizzled, void *y, uint32_t y_dtype,
+                                                             uint32_t tokens, void *stream);
 
 /* No counterpart in the reference.  The same W4A4 projection as muser_cuda_nvfp4_matmul for callers that cannot
  * allocate device memory: a driver that works out of arenas it sized once has no allocator to lend and, on the

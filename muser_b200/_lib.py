@@ -22,7 +22,8 @@ EXPORTS = [
     "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
-    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe",
+    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
+    "muser_cuda_rmsnorm_quantize_nvfp4_activation",
 ]
 
 
@@ -31,7 +32,8 @@ class Shard(C.Structure):
 
 
 class Epilogue(C.Structure):
-    _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("reserved", C.c_uint32)]
+    _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("norm_eps", C.c_float),
+                ("norm_weight", C.c_void_p)]
 
 
 class WeightInfo(C.Structure):
@@ -71,7 +73,7 @@ def _load() -> C.CDLL:
         "muser_cuda_weight_info_get": (i32, [vp, C.POINTER(WeightInfo)]),
         "muser_cuda_dequant": (i32, [vp, vp, vp, vp]),
         "muser_cuda_quantized_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
-        "muser_cuda_ffn_gate_up_silu": (i32, [vp, vp, vp, vp, u32, vp, u32, u32, vp]),
+        "muser_cuda_ffn_gate_up_silu": (i32, [vp, vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
         "muser_cuda_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, f32, vp, vp, vp]),
         "muser_cuda_nvfp4_swizzled_scale_bytes": (C.c_size_t, [u64, u64]),
         "muser_cuda_nvfp4_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
@@ -79,6 +81,8 @@ def _load() -> C.CDLL:
         "muser_cuda_matmul_host": (i32, [vp, vp, vp, u32, vp]),
         "muser_cuda_nvfp4_matmul_static": (i32, [vp, vp, u32, vp, u32, u32, vp]),
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
+        "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
+        "muser_cuda_rmsnorm_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, vp, f32, f32, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)  # AttributeError here means the library does not export what the header declares

@@ -138,6 +138,23 @@ static muser_cuda_status check_io(Ctx *ctx, const Weight *w, const void *x, uint
     return MUSER_CUDA_OK;
 }
 
+// Public epilogue -> the launchers' form.  The fused input norm needs the whole input row, so it is refused on
+// K shards, and its weight vector must be readable with 16-byte loads.
+static muser_cuda_status take_epilogue(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e) {
+    if (!ep) return MUSER_CUDA_OK;
+    e->row_scale = ep->row_scale;
+    e->residual = ep->residual;
+    if (ep->norm_weight) {
+        if (w->shard.axis == MUSER_SHARD_K && w->shard.world > 1)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused input norm needs whole input rows; this weight is a K shard");
+        if (!aligned16(ep->norm_weight)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "norm_weight must be 16-byte aligned");
+        if (!(ep->norm_eps >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "norm_eps must be non-negative");
+        e->norm_weight = ep->norm_weight;
+        e->norm_eps = ep->norm_eps;
+    }
+    return MUSER_CUDA_OK;
+}
+
 } // namespace muser
 
 using namespace muser;
@@ -183,6 +200,8 @@ muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muse
     if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_partial, ctx->gemv_partial_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_counters, ctx->gemv_counter_slots * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counter_slots * sizeof(unsigned int));
+    ctx->norm_scratch_bytes = (size_t)64 * 32768 * sizeof(float); // 64 tokens x the widest row
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_scratch, ctx->norm_scratch_bytes);
     if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
@@ -202,6 +221,7 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->dev_status);
     cudaFree(ctx->gemv_partial);
     cudaFree(ctx->gemv_counters);
+    cudaFree(ctx->norm_scratch);
     cudaFree(ctx->dev_stage);
     if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
@@ -307,26 +327,81 @@ muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *c, const muser_cud
     if (tokens > 64) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "quantized_matmul serves 1..64 tokens per call");
     if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "use muser_cuda_ffn_gate_up_silu for the fused K-quant gate/up");
     Epilogue e;
-    if (ep) e.row_scale = ep->row_scale, e.residual = ep->residual;
+    st = take_epilogue(ctx, w, ep, &e);
+    if (st != MUSER_CUDA_OK) return st;
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_kquant_matmul(ctx, w, nullptr, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);
 }
 
+// The NVFP4 side of the fused gate/up call: both weights must quantize their input alike, because one set of
+// activation codes feeds both.
+static muser_cuda_status nvfp4_pair_checks(Ctx *ctx, const Weight *g, const Weight *u) {
+    if (!u) return fail(ctx, MUSER_CUDA_BAD_ARG, "null up weight");
+    if (g->dtype != MUSER_DTYPE_NVFP4_E2M1 || u->dtype != MUSER_DTYPE_NVFP4_E2M1)
+        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "gate and up must both be NVFP4");
+    if (g->n_in != u->n_in || g->n_out != u->n_out) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "gate and up geometry differ");
+    if (g->shard.axis == MUSER_SHARD_K || u->shard.axis == MUSER_SHARD_K)
+        return fail(ctx, MUSER_CUDA_BAD_SHAPE, "silu cannot be applied to K-sharded partial sums");
+    if (!g->has_input_scale_inv || !u->has_input_scale_inv)
+        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "the W4A4 lane needs input_scale_inv on both weights");
+    if (g->input_scale_inv != u->input_scale_inv)
+        return fail(ctx, MUSER_CUDA_BAD_ARG, "gate and up must share one input_scale_inv: they read the same quantized activations");
+    return MUSER_CUDA_OK;
+}
+
 muser_cuda_status muser_cuda_ffn_gate_up_silu(muser_cuda_ctx *c, const muser_cuda_weight *gp, const muser_cuda_weight *up,
                                               const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
-                                              uint32_t tokens, void *stream) {
+                                              uint32_t tokens, const muser_cuda_epilogue *ep, void *stream) {
     Ctx *ctx = reinterpret_cast<Ctx *>(c);
     const Weight *g = reinterpret_cast<const Weight *>(gp), *u = reinterpret_cast<const Weight *>(up);
-    muser_cuda_status st = check_io(ctx, g, x, x_dtype, y, y_dtype, tokens, false);
+    const bool fp4 = g && g->dtype == MUSER_DTYPE_NVFP4_E2M1;
+    muser_cuda_status st = check_io(ctx, g, x, x_dtype, y, y_dtype, tokens, fp4);
     if (st != MUSER_CUDA_OK) return st;
+    if (ep && (ep->row_scale || ep->residual || ep->swiglu))
+        return fail(ctx, MUSER_CUDA_BAD_ARG, "the fused gate/up call takes only the input-norm fields of the epilogue");
+    Epilogue e;
+    st = take_epilogue(ctx, g, ep, &e);
+    if (st != MUSER_CUDA_OK) return st;
+    if (fp4) {
+        st = nvfp4_pair_checks(ctx, g, u);
+        if (st != MUSER_CUDA_OK) return st;
+        const size_t tok_pad = ((size_t)tokens + 127) / 128 * 128;
+        const size_t packed_bytes = tok_pad * (g->n_in / 2);
+        const size_t scale_bytes = muser_cuda_nvfp4_swizzled_scale_bytes(tokens, g->n_in);
+        if (packed_bytes + scale_bytes > ctx->workspace_bytes)
+            return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL,
+                        "context workspace holds " + std::to_string(ctx->workspace_bytes) + " bytes, this call needs " +
+                            std::to_string(packed_bytes + scale_bytes));
+        uint8_t *xp = reinterpret_cast<uint8_t *>(ctx->workspace), *xs = xp + packed_bytes;
+        MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        st = launch_nvfp4_quantize(ctx, x, x_dtype, tokens, g->n_in, g->input_scale_inv, xp, xs, (cudaStream_t)stream,
+                                   e.norm_weight, e.norm_eps);
+        if (st != MUSER_CUDA_OK) return st;
+        return launch_nvfp4_gemm(ctx, g, xp, xs, y, y_dtype, tokens, Epilogue{}, (cudaStream_t)stream, u);
+    }
     if (!u) return fail(ctx, MUSER_CUDA_BAD_ARG, "null up weight");
-    if (!is_kquant(g->dtype) || g->dtype != u->dtype) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "gate and up must share one K-quant dtype");
+    if (!is_kquant(g->dtype) || g->dtype != u->dtype) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "gate and up must share one dtype (K-quant or NVFP4)");
     if (g->n_in != u->n_in || g->n_out != u->n_out || g->k_off != u->k_off || g->nsb != u->nsb)
         return fail(ctx, MUSER_CUDA_BAD_SHAPE, "gate and up geometry differ");
     if (g->shard.axis == MUSER_SHARD_K) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "silu cannot be applied to K-sharded partial sums");
-    if (tokens > 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused gate/up call serves 1..16 tokens");
+    if (tokens > 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused K-quant gate/up call serves 1..16 tokens");
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    return launch_kquant_matmul(ctx, g, u, x, x_dtype, y, y_dtype, tokens, Epilogue{}, (cudaStream_t)stream);
+    return launch_kquant_matmul(ctx, g, u, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muser_cuda_ctx *c, const muser_cuda_weight *gp,
+                                                             const muser_cuda_weight *up, const uint8_t *xp,
+                                                             const uint8_t *xs, void *y, uint32_t y_dtype,
+                                                             uint32_t tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *g = reinterpret_cast<const Weight *>(gp), *u = reinterpret_cast<const Weight *>(up);
+    muser_cuda_status st = check_io(ctx, g, xp, MUSER_DTYPE_BF16, y, y_dtype, tokens, true);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!xs || !aligned16(xs)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "activation scales must be 16-byte aligned");
+    st = nvfp4_pair_checks(ctx, g, u);
+    if (st != MUSER_CUDA_OK) return st;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_gemm(ctx, g, xp, xs, y, y_dtype, tokens, Epilogue{}, (cudaStream_t)stream, u);
 }
 
 size_t muser_cuda_nvfp4_swizzled_scale_bytes(uint64_t rows, uint64_t n_in) {
@@ -346,13 +421,27 @@ muser_cuda_status muser_cuda_quantize_nvfp4_activation(muser_cuda_ctx *c, const 
     return launch_nvfp4_quantize(ctx, x, x_dtype, tokens, n_in, isi, packed, scales, (cudaStream_t)stream);
 }
 
+muser_cuda_status muser_cuda_rmsnorm_quantize_nvfp4_activation(muser_cuda_ctx *c, const void *x, uint32_t x_dtype,
+                                                               uint32_t tokens, uint64_t n_in, const float *norm_weight,
+                                                               float norm_eps, float isi, uint8_t *packed,
+                                                               uint8_t *scales, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !x || !packed || !scales || !norm_weight) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (tokens == 0 || n_in == 0 || n_in % 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "NVFP4 rows are grouped by 16");
+    if (x_dtype != MUSER_DTYPE_F32 && x_dtype != MUSER_DTYPE_BF16) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "activations must be f32 or bf16");
+    if (!(std::isfinite(isi) && isi > 0.0f)) return fail(ctx, MUSER_CUDA_NAN_SCALE, "input_scale_inv must be finite and positive");
+    if (!(norm_eps >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "norm_eps must be non-negative");
+    if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(norm_weight))
+        return fail(ctx, MUSER_CUDA_BAD_ALIGN, "buffers must be 16-byte aligned");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_quantize(ctx, x, x_dtype, tokens, n_in, isi, packed, scales, (cudaStream_t)stream, norm_weight, norm_eps);
+}
+
 static muser_cuda_status nvfp4_checks(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e) {
     if (w->dtype != MUSER_DTYPE_NVFP4_E2M1) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "nvfp4_matmul takes NVFP4 weights");
     if (!w->has_input_scale_inv)
         return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "weight-only NVFP4 (no input_scale_inv) has no CUDA kernel yet");
-    if (ep && ep->swiglu && (w->n_out % 2)) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "swiglu needs an even n_out");
-    if (ep) e->row_scale = ep->row_scale, e->residual = ep->residual;
-    return MUSER_CUDA_OK;
+    return take_epilogue(ctx, w, ep, e);
 }
 
 muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx *c, const muser_cuda_weight *wp, const uint8_t *xp,
@@ -366,7 +455,8 @@ muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx *c, const muse
     Epilogue e;
     st = nvfp4_checks(ctx, w, ep, &e);
     if (st != MUSER_CUDA_OK) return st;
-    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "swiglu epilogue is not available on this entry point yet");
+    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "gate and up are two weights: use muser_cuda_ffn_gate_up_silu for the fused SwiGLU form");
+    if (e.norm_weight) return fail(ctx, MUSER_CUDA_BAD_ARG, "activations that are already quantized cannot be normalized: pass norm_weight to the quantizer");
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
 }
@@ -381,7 +471,7 @@ muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_we
     Epilogue e;
     st = nvfp4_checks(ctx, w, ep, &e);
     if (st != MUSER_CUDA_OK) return st;
-    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "swiglu epilogue is not available on this entry point yet");
+    if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "gate and up are two weights: use muser_cuda_ffn_gate_up_silu for the fused SwiGLU form");
     const size_t tok_pad = ((size_t)tokens + 127) / 128 * 128;
     const size_t packed_bytes = tok_pad * (w->n_in / 2);
     const size_t scale_bytes = muser_cuda_nvfp4_swizzled_scale_bytes(tokens, w->n_in);
@@ -391,7 +481,8 @@ muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_we
                         std::to_string(packed_bytes + scale_bytes));
     uint8_t *xp = reinterpret_cast<uint8_t *>(ctx->workspace), *xs = xp + packed_bytes;
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    st = launch_nvfp4_quantize(ctx, x, x_dtype, tokens, w->n_in, w->input_scale_inv, xp, xs, (cudaStream_t)stream);
+    st = launch_nvfp4_quantize(ctx, x, x_dtype, tokens, w->n_in, w->input_scale_inv, xp, xs, (cudaStream_t)stream,
+                               e.norm_weight, e.norm_eps);
     if (st != MUSER_CUDA_OK) return st;
     return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
 }

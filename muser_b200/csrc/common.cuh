@@ -31,6 +31,8 @@ struct Ctx {
     size_t gemv_partial_bytes = 0;
     unsigned int *gemv_counters = nullptr; // one arrival counter per 16-row tile, zero between launches
     uint32_t gemv_counter_slots = 0;
+    float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
+    size_t norm_scratch_bytes = 0;
     cudaStream_t copy_stream = nullptr;
     void *host_stage = nullptr; // pinned staging for matmul_host
     size_t host_stage_bytes = 0;
@@ -58,7 +60,8 @@ struct Weight {
     float input_scale_inv = 0.0f;
     bool has_input_scale_inv = false;
     uint64_t image_bytes = 0;
-    void *tmap_cache = nullptr; // CUtensorMap of `packed`, built at repack time
+    void *tmap_cache = nullptr; // CUtensorMap of `packed` with 256-row boxes, built at repack time
+    void *tmap_half = nullptr;  // the same image with 128-row boxes (fused gate/up form)
 };
 
 inline muser_cuda_status fail(Ctx *ctx, muser_cuda_status st, const std::string &msg) {
@@ -82,6 +85,8 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 struct Epilogue {
     const float *row_scale = nullptr;
     const void *residual = nullptr;
+    const float *norm_weight = nullptr; // fused input RMSNorm: x <- (x / rms(x)) * norm_weight before the projection
+    float norm_eps = 0.0f;
 };
 
 muser_cuda_status launch_repack_kquant(Ctx *, Weight *, const uint8_t *dev_blocks, cudaStream_t);
@@ -94,9 +99,13 @@ muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_u
 cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, void *y, uint32_t y_dtype,
                                uint32_t tokens, const Epilogue &, cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
-                                        float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t);
+                                        float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t,
+                                        const float *norm_weight = nullptr, float norm_eps = 0.0f);
+muser_cuda_status launch_rmsnorm_rows(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
+                                      const float *norm_weight, float norm_eps, float *out, cudaStream_t);
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
-                                    void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t);
+                                    void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t,
+                                    const Weight *w_up = nullptr);
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);
 muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);
 void nvfp4_free_tensor_map(Weight *);

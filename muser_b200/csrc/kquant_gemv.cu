@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "kquant_layout.cuh"
+#include "rmsnorm.cuh"
 
 namespace muser {
 
@@ -38,6 +39,8 @@ struct GemvArgs {
     void *y;
     const float *row_scale;
     const void *residual;
+    const float *norm_weight; // fused input RMSNorm (reference.rs:73-80), or null
+    float norm_eps;
     float *partial;          // [ksplit][images][tokens][n_out] partial sums (ksplit > 1)
     unsigned int *counters;  // [row_tiles] arrival counters, zero between launches
     int *status;             // context status words; [1] records a wait that gave up
@@ -91,7 +94,7 @@ template <> struct Fmt<MUSER_DTYPE_Q6_K> {
 // More tokens are NG groups of two, 1 KiB per group and tile.  Plus kSubs * tokens (scale, integer sum) pairs per tile.
 template <int DT, int MT, int NG>
 __device__ __forceinline__ void stage_activations(const GemvArgs &a, uint32_t sb_first, uint32_t n_tiles, uint4 *frag,
-                                                  float2 *meta) {
+                                                  float2 *meta, const float *inv_rms) {
     constexpr int BW = Fmt<DT>::kBlock, SUBS = Fmt<DT>::kSubs, PARTS = BW / 8; // threads per sub-block, 8 values each
     constexpr int V = MT == 1 ? BW / 4 : BW / 8;                               // MMAs that consume one sub-block
     constexpr int TOK = MT * NG;                                               // tokens, in NG groups of MT
@@ -113,6 +116,13 @@ __device__ __forceinline__ void stage_activations(const GemvArgs &a, uint32_t sb
             for (int i = 0; i < 4; ++i) {
                 v[2 * i] = __uint_as_float(w[i] << 16);
                 v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            if (a.norm_weight) { // (x * 1/rms) * weight, in that order
+                const float rs = inv_rms[tok];
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k)), w1 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k) + 1);
+                const float nw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], rs), nw[i]);
             }
         }
         float amax = 0.f;
@@ -411,16 +421,36 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_g
     if constexpr (DUAL) images[1] = a.image_up;
     uint8_t *ring = ring_base + (size_t)warp * kRing * kBytes;
     const uint32_t bar0 = smem_addr(bars + warp * kRing);
-    auto fetch = [&](uint32_t n) {
-        const uint32_t ri = n / per_row, rem = n % per_row;
-        const uint8_t *src = images[rem / n_tiles] + ((uint64_t)(first_row + ri * row_step) * a.nsb + sb_first + rem % n_tiles) * kBytes;
-        tile_fetch(smem_addr(ring + (size_t)(n % kRing) * kBytes), src, kBytes, bar0 + 8 * (n % kRing));
+    // the fetch cursor walks the stream with additions only: (tile in slice, image, row tile) -> tile index in the image
+    uint32_t f_tile = first_row * a.nsb + sb_first, f_tl = 0, f_im = 0;
+    auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, lane 0 issues the copy
+        const uint8_t *base = images[0];
+        if constexpr (DUAL) base = f_im ? images[1] : images[0];
+        if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot);
+        ++f_tile;
+        if (++f_tl == n_tiles) {
+            f_tl = 0;
+            if (DUAL && f_im == 0) {
+                f_im = 1;
+                f_tile -= n_tiles;
+            } else {
+                f_im = 0;
+                f_tile += row_step * a.nsb - n_tiles;
+            }
+        }
     };
     __syncthreads(); // barriers initialised
-    if (lane == 0)
-        for (uint32_t n = 0; n < kRing && n < total; ++n) fetch(n);
+    for (uint32_t i = 0; i < kRing && i < total; ++i) fetch_next(i);
 
-    stage_activations<DT, MT, NG>(a, sb_first, n_tiles, frag, meta);
+    __shared__ float norm_red[33], inv_rms[TOK];
+    if (a.norm_weight) { // every CTA needs the whole row's mean square, whatever its K slice
+        for (uint32_t tok = 0; tok < a.tokens; ++tok) {
+            const float r = block_inv_rms<false>(a.x + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red);
+            if (threadIdx.x == 0) inv_rms[tok] = r;
+        }
+        __syncthreads();
+    }
+    stage_activations<DT, MT, NG>(a, sb_first, n_tiles, frag, meta, inv_rms);
     __syncthreads();
 
     // which fragment entries this lane reads, relative to a tile's 1 KiB
@@ -437,14 +467,14 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_g
 #pragma unroll
             for (int gp = 0; gp < NG; ++gp) out[im][gp][0] = out[im][gp][1] = out[im][gp][2] = out[im][gp][3] = 0.f;
             for (uint32_t tl = 0; tl < n_tiles; ++tl, ++n) {
-                if (healthy && !tile_wait(bar0 + 8 * (n % kRing), (n / kRing) & 1)) {
+                if (healthy && !tile_wait(bar0 + 8 * (n & (kRing - 1)), (n / kRing) & 1)) {
                     healthy = false;
                     atomicExch(a.status + 1, 201);
                 }
                 if (healthy) {
-                    const Regs cur = load_regs(ring + (size_t)(n % kRing) * kBytes, lane, (Regs *)nullptr);
+                    const Regs cur = load_regs(ring + (n & (kRing - 1)) * kBytes, lane, (Regs *)nullptr);
                     __syncwarp(); // every lane has its copy: the slot may be refilled
-                    if (lane == 0 && n + kRing < total) fetch(n + kRing);
+                    if (n + kRing < total) fetch_next(n & (kRing - 1));
                     const uint4 *fb = feeds ? frag + (size_t)tl * 64 * NG + lane_entry : zero_block;
                     tile_compute<MT, NG>(cur, fb, feeds ? 64u : 0u, meta + (size_t)tl * SUBS * TOK, t, out[im]);
                 }
@@ -620,6 +650,8 @@ cudaError_t launch_kquant_gemv(Ctx *ctx, const Weight *w, const Weight *w_up, co
     a.y = y;
     a.row_scale = ep.row_scale;
     a.residual = ep.residual;
+    a.norm_weight = ep.norm_weight;
+    a.norm_eps = ep.norm_eps;
     a.partial = ctx->gemv_partial;
     a.counters = ctx->gemv_counters;
     a.status = ctx->dev_status;

@@ -475,6 +475,16 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
             return MUSER_CUDA_OK;
         }
     }
+    if (ep.norm_weight) {
+        // this kernel reads its activations as it goes, so the fused input norm runs as a pass of its own into
+        // the context's scratch rows (f32), which the projection then reads instead of x
+        const size_t need = (size_t)tokens * w->n_in * sizeof(float);
+        if (need > ctx->norm_scratch_bytes) return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL, "fused input norm: tokens x n_in exceeds the context's norm scratch");
+        muser_cuda_status st = launch_rmsnorm_rows(ctx, x, x_dtype, tokens, w->n_in, ep.norm_weight, ep.norm_eps, ctx->norm_scratch, stream);
+        if (st != MUSER_CUDA_OK) return st;
+        x = ctx->norm_scratch;
+        x_dtype = MUSER_DTYPE_F32;
+    }
     KqArgs a;
     a.image = w->image;
     a.image_up = w_up ? w_up->image : nullptr;

@@ -36,6 +36,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 struct GemmArgs {
     const uint8_t *a_scales; // activations, swizzled
     const uint8_t *b_scales; // weights, swizzled
+    const uint8_t *b2_scales; // second weight (up projection) of the fused gate/up form, else null
     void *y;
     const float *row_scale;
     const void *residual;
@@ -43,7 +44,7 @@ struct GemmArgs {
     uint32_t tokens, n_out, k_tiles, kt64; // kt64: 64-value blocks per row (one MMA and one scale chunk each)
     uint32_t n_tiles;                      // 256-row tiles of the weight
     uint32_t y_dtype;
-    float scale2, inv_input_scale;
+    float scale2, scale2_up, inv_input_scale;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -118,6 +119,20 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// 32 consecutive accumulator columns of this thread's lane (row) into registers; follow with tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // One 32-column strip of one accumulator row: scale, fuse, convert, store (16-byte stores when the row allows).
 template <typename T>
 __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T *res, uint32_t valid, bool vec_ok) {
@@ -171,8 +186,16 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 
 // Persistent: CTA b takes output tiles b, b + gridDim.x, ...; tile index -> (n tile, m tile) with m fastest, so the
 // CTAs that run side by side share one weight tile (read from HBM once, from L2 afterwards).
+//
+// DUAL is the fused FFN front half (reference: encode_ffn_q4k_gate_up_silu_4r2s, src/metal/encode/ffn.rs:10-36, and
+// reference.rs:511-513 on the CPU lane): the 256 accumulator columns of a tile are 128 rows of the gate weight next to
+// the same 128 rows of the up weight (map_b, map_b2: 128-row boxes), and the epilogue writes silu_fast(gate) * up,
+// each factor first rounded to f16 as the unfused W4A4 lane returns it (quant/nvfp4.rs:337).
+template <bool DUAL>
 __global__ void __launch_bounds__(192, 1)
-nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
+    constexpr uint32_t kTileRows = DUAL ? BN / 2 : BN; // output columns (weight rows) per tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
     uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -213,8 +236,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
                 const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
-                const uint8_t *sfb0 = g.b_scales + (size_t)(2 * tile_n) * g.kt64 * 512;
-                const uint8_t *sfb1 = sfb0 + (size_t)g.kt64 * 512;
+                const uint8_t *sfb0 = g.b_scales + (size_t)(DUAL ? tile_n : 2 * tile_n) * g.kt64 * 512;
+                const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
                     if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
@@ -226,7 +249,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
                     mbar_expect_tx(full, kABytes + kBBytes + 3 * sf_bytes);
                     tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
-                    tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                    if constexpr (DUAL) {
+                        tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
+                        tma_load_2d(st + kABytes + kBBytes / 2, &map_b2, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
+                    } else {
+                        tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                    }
                     bulk_load(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
                     bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
                     bulk_load(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
@@ -309,31 +337,32 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t tok = tile_m * BM + quad * 32 + lane;
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
             const bool vec_ok = (g.n_out & 7) == 0;
-            for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(tmem + ((quad * 32) << 16) + c0));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c0 + 32 == BN) { // everything this warp needs is in registers: hand the accumulator back
+            for (uint32_t c0 = 0; c0 < kTileRows; c0 += 32) {
+                uint32_t r[32], r_up[DUAL ? 32 : 1];
+                tmem_ld32(tmem + ((quad * 32) << 16) + c0, r);
+                if constexpr (DUAL) tmem_ld32(tmem + ((quad * 32) << 16) + kTileRows + c0, r_up);
+                tmem_ld_wait();
+                if (c0 + 32 == kTileRows) { // everything this warp needs is in registers: hand the accumulator back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
                 }
-                const uint32_t n0 = tile_n * BN + c0;
+                const uint32_t n0 = tile_n * kTileRows + c0;
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
                     const uint32_t valid = min(32u, g.n_out - n0);
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) // quant/nvfp4.rs:334-336: tensor scales applied one after the other
-                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), g.scale2), g.inv_input_scale) * rs;
+                    for (int i = 0; i < 32; ++i) { // quant/nvfp4.rs:334-336: tensor scales applied one after the other
+                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), g.scale2), g.inv_input_scale);
+                        if constexpr (DUAL) {
+                            const float gate = __half2float(__float2half_rn(v[i]));
+                            const float up = __half2float(__float2half_rn(
+                                __fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
+                            v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up; // silu_fast, quant/helpers.rs:72
+                        }
+                        v[i] *= rs;
+                    }
                     if (g.y_dtype == MUSER_DTYPE_F32)
                         store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
                                            g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
@@ -451,9 +480,16 @@ muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {
         return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the weight image");
     }
     w->tmap_cache = m;
+    CUtensorMap *half = new CUtensorMap; // 128-row boxes, for the fused gate/up form
+    if (!make_map(half, w->packed, w->n_out_pad, w->n_in / 2, BN / 2)) {
+        delete half;
+        return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the weight image (128-row boxes)");
+    }
+    w->tmap_half = half;
     static bool attr_set = false;
     if (!attr_set) {
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         attr_set = true;
     }
     return MUSER_CUDA_OK;
@@ -461,17 +497,21 @@ muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {
 
 void nvfp4_free_tensor_map(Weight *w) {
     delete reinterpret_cast<CUtensorMap *>(w->tmap_cache);
+    delete reinterpret_cast<CUtensorMap *>(w->tmap_half);
     w->tmap_cache = nullptr;
+    w->tmap_half = nullptr;
 }
 
 muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales, void *y,
-                                    uint32_t y_dtype, uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
+                                    uint32_t y_dtype, uint32_t tokens, const Epilogue &ep, cudaStream_t stream,
+                                    const Weight *w_up) {
     CUtensorMap map_a;
     if (!make_map(&map_a, x_packed, tokens, w->n_in / 2, BM))
         return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the activations");
     GemmArgs g;
     g.a_scales = x_scales;
     g.b_scales = w->scales;
+    g.b2_scales = w_up ? w_up->scales : nullptr;
     g.y = y;
     g.row_scale = ep.row_scale;
     g.residual = ep.residual;
@@ -482,11 +522,17 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.kt64 = (uint32_t)(w->n_in / 64);
     g.y_dtype = y_dtype;
     g.scale2 = w->scale2;
+    g.scale2_up = w_up ? w_up->scale2 : 0.0f;
     g.inv_input_scale = 1.0f / w->input_scale_inv;
-    g.n_tiles = (uint32_t)(w->n_out_pad / BN);
+    g.n_tiles = w_up ? (uint32_t)((w->n_out + BN / 2 - 1) / (BN / 2)) : (uint32_t)(w->n_out_pad / BN);
     const uint32_t tiles = g.n_tiles * ((tokens + BM - 1) / BM);
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
-    nvfp4_gemm_kernel<<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
+    if (w_up)
+        nvfp4_gemm_kernel<true><<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_half),
+                                                                   *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half), g);
+    else
+        nvfp4_gemm_kernel<false><<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache),
+                                                                    *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }

@@ -9,6 +9,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "rmsnorm.cuh"
 
 namespace muser {
 
@@ -31,6 +32,40 @@ __device__ __forceinline__ uint32_t e2m1_code(float r, float isi, float scale) {
     code += m >= __fmul_rn(scale, 3.5f);
     code += m > __fmul_rn(scale, 5.0f);
     return sign | code;
+}
+
+// Quantizes one group of 16 values: writes its 8 code bytes and returns its E4M3 scale code.
+__device__ __forceinline__ uint32_t quantize_group(float (&r)[16], float isi, uint8_t *codes) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        r[i] = __half2float(__float2half_rn(r[i]));
+        amax = fmaxf(amax, fabsf(r[i]));
+    }
+    const float target = fminf(__fmul_rn(__fmul_rn(amax, 1.0f / 6.0f), isi), 448.0f);
+    const uint32_t scale_code = __nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3) & 0x7Fu;
+    const float scale = e4m3_to_f32(scale_code);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        lo |= e2m1_code(r[i], isi, scale) << (4 * i);
+        hi |= e2m1_code(r[8 + i], isi, scale) << (4 * i);
+    }
+    *reinterpret_cast<uint2 *>(codes) = make_uint2(lo, hi);
+    return scale_code;
+}
+// Four neighbouring threads (groups 4q .. 4q+3 of one row) merge their scale bytes into one aligned 32-bit store.
+// Every lane of the warp calls this; lanes past the row's last group slot pass live = false.
+__device__ __forceinline__ void store_scale_quad(uint32_t scale_code, uint32_t row, uint32_t grp, uint32_t kt, uint8_t *scales,
+                                                 bool live = true) {
+    uint32_t word = scale_code;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 1) << 8;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 2) << 16;
+    word |= __shfl_down_sync(0xffffffffu, scale_code, 3) << 24;
+    if (live && (grp & 3) == 0) {
+        const size_t off = (size_t)(row / 128) * ((size_t)kt * 512) + (size_t)(grp / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4;
+        *reinterpret_cast<uint32_t *>(scales + off) = word;
+    }
 }
 
 // One thread per 16-value group; the four threads of a 64-value span merge their scale bytes into one
@@ -66,37 +101,91 @@ __global__ void nvfp4_quantize_kernel(const void *__restrict__ x, uint32_t token
                 }
             }
         }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            r[i] = __half2float(__float2half_rn(r[i]));
-            amax = fmaxf(amax, fabsf(r[i]));
-        }
-        const float target = fminf(__fmul_rn(__fmul_rn(amax, 1.0f / 6.0f), isi), 448.0f);
-        scale_code = __nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3) & 0x7Fu;
-        const float scale = e4m3_to_f32(scale_code);
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            lo |= e2m1_code(r[i], isi, scale) << (4 * i);
-            hi |= e2m1_code(r[8 + i], isi, scale) << (4 * i);
-        }
-        *reinterpret_cast<uint2 *>(packed + (size_t)row * (n_in / 2) + grp * 8) = make_uint2(lo, hi);
+        scale_code = quantize_group(r, isi, packed + (size_t)row * (n_in / 2) + grp * 8);
     }
-    uint32_t word = scale_code;
-    word |= __shfl_down_sync(0xffffffffu, scale_code, 1) << 8;
-    word |= __shfl_down_sync(0xffffffffu, scale_code, 2) << 16;
-    word |= __shfl_down_sync(0xffffffffu, scale_code, 3) << 24;
-    if ((grp & 3) == 0) {
-        const size_t off = (size_t)(row / 128) * ((size_t)kt * 512) + (size_t)(grp / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4;
-        *reinterpret_cast<uint32_t *>(scales + off) = word;
+    store_scale_quad(scale_code, row, grp, kt, scales);
+}
+
+// The same quantizer behind a fused input RMSNorm (reference.rs:73-80): one block per token row first adds the
+// row's squares, then quantizes (x * inv_rms) * w group by group.  Blocks of the padding rows only clear scales.
+template <bool XF32>
+__global__ void __launch_bounds__(256) nvfp4_norm_quantize_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in,
+                                                                  uint32_t kt, float isi, const float *__restrict__ norm_w,
+                                                                  float eps, uint8_t *__restrict__ packed,
+                                                                  uint8_t *__restrict__ scales) {
+    __shared__ float red[33];
+    const uint32_t row = blockIdx.x, groups_pad = kt * 4;
+    const void *xr = XF32 ? (const void *)(reinterpret_cast<const float *>(x) + (size_t)row * n_in)
+                          : (const void *)(reinterpret_cast<const __nv_bfloat16 *>(x) + (size_t)row * n_in);
+    float inv = 0.0f;
+    if (row < tokens) inv = block_inv_rms<XF32>(xr, n_in, eps, red); // uniform per block
+    for (uint32_t g0 = 0; g0 < groups_pad; g0 += blockDim.x) { // blockDim % 4 == 0: quads stay together
+        const uint32_t grp = g0 + threadIdx.x;
+        uint32_t scale_code = 0;
+        if (row < tokens && grp * 16 < n_in) {
+            float r[16], a[8], b[8];
+            load8<XF32>(xr, 2 * grp, a);
+            load8<XF32>(xr, 2 * grp + 1, b);
+            const float4 *wp = reinterpret_cast<const float4 *>(norm_w + grp * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 w = __ldg(wp + i);
+                const float *src = i < 2 ? a + 4 * i : b + 4 * (i - 2);
+                r[4 * i] = __fmul_rn(__fmul_rn(src[0], inv), w.x);
+                r[4 * i + 1] = __fmul_rn(__fmul_rn(src[1], inv), w.y);
+                r[4 * i + 2] = __fmul_rn(__fmul_rn(src[2], inv), w.z);
+                r[4 * i + 3] = __fmul_rn(__fmul_rn(src[3], inv), w.w);
+            }
+            scale_code = quantize_group(r, isi, packed + (size_t)row * (n_in / 2) + grp * 8);
+        }
+        store_scale_quad(scale_code, row, grp, kt, scales, grp < groups_pad);
     }
 }
 
+// Plain rows: out[t][k] = (x[t][k] * inv_rms_t) * w[k] in f32, for the kernels that read their activations as they go.
+template <bool XF32>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void *__restrict__ x, uint32_t n_in, const float *__restrict__ norm_w,
+                                                           float eps, float *__restrict__ out) {
+    __shared__ float red[33];
+    const uint32_t row = blockIdx.x;
+    const void *xr = XF32 ? (const void *)(reinterpret_cast<const float *>(x) + (size_t)row * n_in)
+                          : (const void *)(reinterpret_cast<const __nv_bfloat16 *>(x) + (size_t)row * n_in);
+    const float inv = block_inv_rms<XF32>(xr, n_in, eps, red);
+    for (uint32_t i = threadIdx.x; i < n_in / 8; i += blockDim.x) {
+        float v[8];
+        load8<XF32>(xr, i, v);
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i), w1 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i + 1);
+        float4 *o = reinterpret_cast<float4 *>(out + (size_t)row * n_in) + 2 * i;
+        o[0] = make_float4(__fmul_rn(__fmul_rn(v[0], inv), w0.x), __fmul_rn(__fmul_rn(v[1], inv), w0.y),
+                           __fmul_rn(__fmul_rn(v[2], inv), w0.z), __fmul_rn(__fmul_rn(v[3], inv), w0.w));
+        o[1] = make_float4(__fmul_rn(__fmul_rn(v[4], inv), w1.x), __fmul_rn(__fmul_rn(v[5], inv), w1.y),
+                           __fmul_rn(__fmul_rn(v[6], inv), w1.z), __fmul_rn(__fmul_rn(v[7], inv), w1.w));
+    }
+}
+
+muser_cuda_status launch_rmsnorm_rows(Ctx *ctx, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
+                                      const float *norm_weight, float norm_eps, float *out, cudaStream_t stream) {
+    if (x_dtype == MUSER_DTYPE_F32)
+        rmsnorm_rows_kernel<true><<<tokens, 256, 0, stream>>>(x, (uint32_t)n_in, norm_weight, norm_eps, out);
+    else
+        rmsnorm_rows_kernel<false><<<tokens, 256, 0, stream>>>(x, (uint32_t)n_in, norm_weight, norm_eps, out);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
+}
+
 muser_cuda_status launch_nvfp4_quantize(Ctx *ctx, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
-                                        float isi, uint8_t *packed, uint8_t *scales, cudaStream_t stream) {
+                                        float isi, uint8_t *packed, uint8_t *scales, cudaStream_t stream,
+                                        const float *norm_weight, float norm_eps) {
     const uint32_t kt = (uint32_t)((n_in + 63) / 64);
     const uint32_t tokens_pad = (tokens + 127) / 128 * 128;
+    if (norm_weight) {
+        if (x_dtype == MUSER_DTYPE_F32)
+            nvfp4_norm_quantize_kernel<true><<<tokens_pad, 256, 0, stream>>>(x, tokens, (uint32_t)n_in, kt, isi, norm_weight, norm_eps, packed, scales);
+        else
+            nvfp4_norm_quantize_kernel<false><<<tokens_pad, 256, 0, stream>>>(x, tokens, (uint32_t)n_in, kt, isi, norm_weight, norm_eps, packed, scales);
+        MUSER_CUDA_TRY(ctx, cudaGetLastError());
+        return MUSER_CUDA_OK;
+    }
     const uint64_t total = (uint64_t)tokens_pad * kt * 4;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (x_dtype == MUSER_DTYPE_F32)

@@ -150,11 +150,15 @@ def _row_bytes(dtype: int, n_in: int) -> int:
     raise MuserCudaError(4, f"dtype {dtype} has no CUDA projection kernel")
 
 
-def _epilogue(row_scale, residual):
-    if row_scale is None and residual is None:
+def _epilogue(row_scale=None, residual=None, norm_weight=None, norm_eps=0.0):
+    """muser_cuda_epilogue; `norm_weight` (f32 [n_in], device) fuses rms_norm_mul(x, eps, norm_weight) in front."""
+    if row_scale is None and residual is None and norm_weight is None:
         return None
+    if norm_weight is not None and norm_weight.dtype != torch.float32:
+        raise MuserCudaError(1, "norm_weight must be f32")
     return _lib.Epilogue(row_scale.data_ptr() if row_scale is not None else None,
-                         residual.data_ptr() if residual is not None else None, 0, 0)
+                         residual.data_ptr() if residual is not None else None, 0, float(norm_eps),
+                         norm_weight.data_ptr() if norm_weight is not None else None)
 
 
 class CudaKernels:
@@ -175,36 +179,56 @@ class CudaKernels:
         return out
 
     def encode_quantized_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, tokens: int,
-                                row_scale=None, residual=None) -> None:
+                                row_scale=None, residual=None, norm_weight=None, norm_eps=0.0) -> None:
         """y[t][r] = dot(W_r, x_t) for K-quant weights; input [tokens][n_in] f32|bf16, output [tokens][n_out] f32|bf16."""
-        ep = _epilogue(row_scale, residual)
+        ep = _epilogue(row_scale, residual, norm_weight, norm_eps)
         self.ctx.check(_L.muser_cuda_quantized_matmul(
             self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
             _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
     def encode_ffn_gate_up_silu(self, gate_w: Weight, up_w: Weight, input: torch.Tensor, output: torch.Tensor,
-                                tokens: int) -> None:
+                                tokens: int, norm_weight=None, norm_eps=0.0) -> None:
+        """output[t][j] = silu(gate_j . x_t) * (up_j . x_t); K-quant (tokens <= 16) or NVFP4 weights."""
+        ep = _epilogue(None, None, norm_weight, norm_eps)
         self.ctx.check(_L.muser_cuda_ffn_gate_up_silu(
             self.ctx._h, gate_w._h, up_w._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
-            _TORCH_DTYPE[output.dtype], tokens, _stream_ptr(self.ctx.device)))
+            _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
+        self.launches += 2 if gate_w.dtype == NVFP4 else 1
+
+    def encode_nvfp4_ffn_gate_up_silu_prequant(self, gate_w: Weight, up_w: Weight, packed: torch.Tensor,
+                                               scales: torch.Tensor, output: torch.Tensor, columns: int) -> None:
+        self.ctx.check(_L.muser_cuda_nvfp4_ffn_gate_up_silu_prequant(
+            self.ctx._h, gate_w._h, up_w._h, packed.data_ptr(), scales.data_ptr(), output.data_ptr(),
+            _TORCH_DTYPE[output.dtype], columns, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
-    def quantize_nvfp4_activation(self, input: torch.Tensor, input_scale_inv: float):
+    def quantize_nvfp4_activation(self, input: torch.Tensor, input_scale_inv: float, norm_weight=None, norm_eps=0.0,
+                                  out=None):
+        """(packed codes, swizzled scales) of `input`; with norm_weight, of rms_norm_mul(input, norm_eps, norm_weight).
+        `out` = (packed, scales) reuses earlier buffers."""
         tokens, n_in = input.shape
         dev = input.device
-        packed = torch.empty((tokens, n_in // 2), dtype=torch.uint8, device=dev)
-        scales = torch.empty((_L.muser_cuda_nvfp4_swizzled_scale_bytes(tokens, n_in),), dtype=torch.uint8, device=dev)
-        self.ctx.check(_L.muser_cuda_quantize_nvfp4_activation(
-            self.ctx._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, n_in, input_scale_inv, packed.data_ptr(),
-            scales.data_ptr(), _stream_ptr(self.ctx.device)))
+        if out is None:
+            packed = torch.empty((tokens, n_in // 2), dtype=torch.uint8, device=dev)
+            scales = torch.empty((_L.muser_cuda_nvfp4_swizzled_scale_bytes(tokens, n_in),), dtype=torch.uint8, device=dev)
+        else:
+            packed, scales = out
+        if norm_weight is not None:
+            self.ctx.check(_L.muser_cuda_rmsnorm_quantize_nvfp4_activation(
+                self.ctx._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, n_in, norm_weight.data_ptr(),
+                float(norm_eps), input_scale_inv, packed.data_ptr(), scales.data_ptr(), _stream_ptr(self.ctx.device)))
+        else:
+            self.ctx.check(_L.muser_cuda_quantize_nvfp4_activation(
+                self.ctx._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, n_in, input_scale_inv, packed.data_ptr(),
+                scales.data_ptr(), _stream_ptr(self.ctx.device)))
         self.launches += 1
         return packed, scales
 
     def encode_nvfp4_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int,
-                            row_scale=None, residual=None) -> None:
+                            row_scale=None, residual=None, norm_weight=None, norm_eps=0.0) -> None:
         """W4A4 lane: quantizes `input` with the weight's input_scale_inv, then the block-scaled GEMM."""
-        ep = _epilogue(row_scale, residual)
+        ep = _epilogue(row_scale, residual, norm_weight, norm_eps)
         self.ctx.check(_L.muser_cuda_nvfp4_matmul(
             self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
             _TORCH_DTYPE[output.dtype], columns, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))

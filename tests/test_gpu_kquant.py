@@ -107,6 +107,38 @@ def test_fused_gate_up_silu(gpu, dtype):
 
 
 @pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float32])
+def test_fused_input_rmsnorm(gpu, dtype, x_dtype):
+    """rms_norm_mul (reference.rs:59-80) fused in front of the projection: the decode kernel norms while it stages
+    the activations (bf16, few tokens), the skinny kernel behind a pass of its own; both against the CPU lane's
+    norm followed by weights::matmul."""
+    op, ctx, k = gpu
+    n_in, n_out, eps = 1024, 37, 1e-6
+    raw = H.lcg_weights(dtype, n_out, 4, seed=31)
+    raw_up = H.lcg_weights(dtype, n_out, 4, seed=32)
+    w, wu = (op.Weight(ctx, op.TensorView(r, dtype, n_in, n_out)) for r in (raw, raw_up))
+    nw = torch.linspace(0.5, 1.5, n_in)
+    for tokens in (1, 2, 5, 8, 19):
+        x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=tokens).reshape(tokens, n_in) * 3.0).to(x_dtype)
+        xn = O.rms_norm_mul(x.float().numpy(), eps, nw.numpy())
+        want = O.matmul(O.TensorView(raw, dtype, n_in, n_out), xn)
+        y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        k.encode_quantized_matmul(w, x.cuda(), y, tokens, norm_weight=nw.cuda(), norm_eps=eps)
+        assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, (tokens, H.rel_l2(y.cpu().numpy(), want))
+        if tokens <= 16:
+            want_ffn = O.silu_mul(want, O.matmul(O.TensorView(raw_up, dtype, n_in, n_out), xn))
+            k.encode_ffn_gate_up_silu(w, wu, x.cuda(), y, tokens, norm_weight=nw.cuda(), norm_eps=eps)
+            assert H.rel_l2(y.cpu().numpy(), want_ffn) <= REL_L2_TOL, tokens
+    ctx.sync_status()
+    # a K shard sees only part of the row: refused
+    wk = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out), shard=(0, 2, op.SHARD_K))
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_quantized_matmul(wk, torch.zeros((1, n_in // 2), dtype=x_dtype, device="cuda"),
+                                  torch.empty((1, n_out), dtype=torch.float32, device="cuda"), 1, norm_weight=nw.cuda())
+    assert e.value.status_name == "BAD_SHAPE"
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
 def test_tensor_parallel_shards(gpu, dtype):
     """Row shards concatenate to the unsharded result exactly; K shards sum to it within tolerance."""
     op, ctx, k = gpu

@@ -133,6 +133,75 @@ def test_w4a4_gemm_matches_cpu_lane(gpu, n_out, n_in, tokens):
     assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("n_out,n_in,tokens", [(128, 256, 128), (200, 320, 9), (700, 1024, 260)])
+def test_fused_gate_up_silu_matches_cpu_lane(gpu, n_out, n_in, tokens):
+    """silu_fast(gate) * up in one GEMM against the CPU lane's composition: two W4A4 matmuls (f16-rounded, as
+    quant/nvfp4.rs:337 returns them), then x / (1 + exp(-x)) * up in f32 (reference.rs:511-513)."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    gp, gs, g2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 1, negative_scales=True)
+    up, us, u2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 2)
+    x = synth.normal_activations(tokens, n_in, seed=9)
+    isi = synth.activation_input_scale_inv(x)
+    xf = x.float().numpy()
+    gate = O.matmul(O.TensorView(gp, O.NVFP4, n_in, n_out, gs, g2, isi), xf, threads=O.host_threads())
+    upv = O.matmul(O.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi), xf, threads=O.host_threads())
+    want = O.silu_mul(gate, upv)
+    wg = op.Weight(ctx, op.TensorView(gp, O.NVFP4, n_in, n_out, gs, g2, isi))
+    wu = op.Weight(ctx, op.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi))
+    for y_dtype, tol in ((torch.float32, REL_L2_TOL), (torch.bfloat16, 4e-3)):
+        y = torch.full((tokens, n_out), float("nan"), dtype=y_dtype, device="cuda")
+        k.encode_ffn_gate_up_silu(wg, wu, x.cuda(), y, tokens)
+        ctx.sync_status()
+        assert H.rel_l2(y.float().cpu().numpy(), want) <= tol, (y_dtype, H.rel_l2(y.float().cpu().numpy(), want))
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    y2 = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_ffn_gate_up_silu_prequant(wg, wu, xp, xs, y2, tokens)
+    ctx.sync_status()
+    assert H.rel_l2(y2.cpu().numpy(), want) <= REL_L2_TOL
+    # the two weights must quantize their input alike
+    other = op.Weight(ctx, op.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi * 2))
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_ffn_gate_up_silu(wg, other, x.cuda(), y2, tokens)
+    assert e.value.status_name == "BAD_ARG"
+
+
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_fused_input_rmsnorm(gpu, x_dtype):
+    """rms_norm_mul (reference.rs:59-80) fused into the activation quantizer.  The block adds the squares as a tree
+    where the CPU lane adds them front to back, so 1/rms can differ in its last bit: codes are compared by
+    mismatch count (a value sitting on a rounding boundary may fall the other way), outputs by relative L2."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_out, n_in, tokens, eps = 200, 1024, 70, 1e-6
+    packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=3)
+    x = (synth.normal_activations(tokens, n_in, seed=12).float() * 2.5).to(x_dtype)
+    nw = torch.linspace(0.25, 2.0, n_in)
+    xn = O.rms_norm_mul(x.float().numpy(), eps, nw.numpy())
+    isi = synth.activation_input_scale_inv(torch.from_numpy(xn))
+    want_p, want_s = O.quantize_nvfp4_activation(xn, isi)
+    got_p, got_s = k.quantize_nvfp4_activation(x.cuda(), isi, norm_weight=nw.cuda(), norm_eps=eps)
+    got_p, got_s = got_p.cpu().numpy(), op.unswizzle_scales(got_s, tokens, n_in).cpu().numpy()
+    differing = np.count_nonzero((got_p & 15) != (want_p & 15)) + np.count_nonzero((got_p >> 4) != (want_p >> 4))
+    assert differing <= 1e-3 * tokens * n_in, differing
+    assert np.count_nonzero(got_s != want_s) <= 1e-3 * want_s.size
+    ow = O.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi)
+    _, ref = O.matmul(ow, xn, threads=O.host_threads(), return_pre_round=True)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi))
+    y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_matmul(w, x.cuda(), y, tokens, norm_weight=nw.cuda(), norm_eps=eps)
+    ctx.sync_status()
+    assert H.rel_l2(y.cpu().numpy(), ref) <= REL_L2_TOL
+    # the fused FFN front half behind the same norm
+    up_p, up_s, up_2 = make_weight(op, ctx, n_out, n_in, seed=4)
+    wu = op.Weight(ctx, op.TensorView(up_p, O.NVFP4, n_in, n_out, up_s, up_2, isi))
+    gate = O.matmul(ow, xn, threads=O.host_threads())
+    upv = O.matmul(O.TensorView(up_p, O.NVFP4, n_in, n_out, up_s, up_2, isi), xn, threads=O.host_threads())
+    k.encode_ffn_gate_up_silu(w, wu, x.cuda(), y, tokens, norm_weight=nw.cuda(), norm_eps=eps)
+    ctx.sync_status()
+    assert H.rel_l2(y.cpu().numpy(), O.silu_mul(gate, upv)) <= 2 * REL_L2_TOL  # f16 boundaries of both factors can flip
+
+
 def test_nvfp4_tensor_parallel_shards(gpu):
     op, ctx, k = gpu
     from muser_b200 import synth
