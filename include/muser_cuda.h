@@ -116,6 +116,14 @@ MUSER_CUDA_API const char *muser_cuda_last_error(const muser_cuda_ctx *ctx);
  * synchronizes `stream` and folds asynchronous faults and device-side give-ups into a status. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, void *stream);
 
+/* No counterpart in the reference (its kernel choice is compiled in, src/metal/encode/qkv.rs:425-449).  Which kernel
+ * serves a K-quant call depends on the token count; these thresholds are the measured defaults and can be moved,
+ * e.g. to force one kernel in a test.  A value above 64 switches the tensor-core skinny kernel off. */
+#define MUSER_TUNE_TC_MIN_TOKENS_Q4_K 1u /* Q4_K calls with at least this many tokens take the tcgen05 kernel (default 12) */
+#define MUSER_TUNE_TC_MIN_TOKENS_Q6_K 2u /* likewise for Q6_K (default 5) */
+#define MUSER_TUNE_TC_MIN_ROWS 3u        /* ... if the weight has at least this many output rows (default 2048) */
+MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
+
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file
  * (src/weights.rs:171-373, src/decode.rs:148-161): takes the tensor exactly as stored
  * (K-quant: rows of blocks; NVFP4: packed E2M1 [n_out][n_in/2] plus E4M3FN scales

@@ -12,6 +12,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmuser_cuda.so"
 
 F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
 SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
+TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 
@@ -23,7 +24,7 @@ EXPORTS = [
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
     "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
-    "muser_cuda_rmsnorm_quantize_nvfp4_activation",
+    "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set",
 ]
 
 
@@ -82,6 +83,7 @@ def _load() -> C.CDLL:
         "muser_cuda_nvfp4_matmul_static": (i32, [vp, vp, u32, vp, u32, u32, vp]),
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
+        "muser_cuda_tuning_set": (i32, [vp, u32, u32]),
         "muser_cuda_rmsnorm_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, vp, f32, f32, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():

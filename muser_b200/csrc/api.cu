@@ -200,6 +200,8 @@ muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muse
     if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_partial, ctx->gemv_partial_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->gemv_counters, ctx->gemv_counter_slots * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counter_slots * sizeof(unsigned int));
+    ctx->tc_scratch_bytes = (size_t)64 * 32768 * 2 + (size_t)64 * 2048 * 2 + 4096; // f16 rows + sub-block sums, 64 tokens
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->tc_scratch, ctx->tc_scratch_bytes);
     ctx->norm_scratch_bytes = (size_t)64 * 32768 * sizeof(float); // 64 tokens x the widest row
     if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_scratch, ctx->norm_scratch_bytes);
     if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
@@ -222,6 +224,7 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->gemv_partial);
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->norm_scratch);
+    cudaFree(ctx->tc_scratch);
     cudaFree(ctx->dev_stage);
     if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
@@ -245,6 +248,17 @@ muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *c, void *stream) {
         return fail(ctx, MUSER_CUDA_TIMEOUT, "a device-side bounded wait gave up (code " + std::to_string(flags[1]) + ")");
     }
     return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_t value) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx) return MUSER_CUDA_BAD_ARG;
+    switch (key) {
+    case MUSER_TUNE_TC_MIN_TOKENS_Q4_K: ctx->tc_min_tokens[0] = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_TC_MIN_TOKENS_Q6_K: ctx->tc_min_tokens[1] = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_TC_MIN_ROWS: ctx->tc_min_rows = value; return MUSER_CUDA_OK;
+    default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
+    }
 }
 
 muser_cuda_status muser_cuda_weight_repack(muser_cuda_ctx *c, uint32_t t, const uint8_t *blocks, const uint8_t *scales,

@@ -31,6 +31,10 @@ struct Ctx {
     size_t gemv_partial_bytes = 0;
     unsigned int *gemv_counters = nullptr; // one arrival counter per 16-row tile, zero between launches
     uint32_t gemv_counter_slots = 0;
+    void *tc_scratch = nullptr;            // f16 activations + sub-block sums of the tensor-core K-quant kernel
+    size_t tc_scratch_bytes = 0;
+    uint32_t tc_min_tokens[2] = {12, 5};   // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
+    uint32_t tc_min_rows = 2048;           // and from how many output rows: measured crossovers)
     float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
     size_t norm_scratch_bytes = 0;
     cudaStream_t copy_stream = nullptr;
@@ -96,6 +100,8 @@ muser_cuda_status launch_dequant(Ctx *, const Weight *, float *out, cudaStream_t
 muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
                                        void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &,
                                        cudaStream_t);
+cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
+                             uint32_t tokens, const Epilogue &, cudaStream_t);
 cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, void *y, uint32_t y_dtype,
                                uint32_t tokens, const Epilogue &, cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,

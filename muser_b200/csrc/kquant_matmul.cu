@@ -467,8 +467,13 @@ static cudaError_t launch_tokens(const KqArgs &a, int warps, int sm_count, cudaS
 muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
                                        void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &ep,
                                        cudaStream_t stream) {
-    // the decode kernel (kquant_gemv.cu): measured faster up to 2 tokens for Q4_K and up to 8 for Q6_K
-    if (x_dtype == MUSER_DTYPE_BF16 && tokens <= (w->dtype == MUSER_DTYPE_Q6_K ? 8u : 2u)) {
+    // Measured crossovers on B200 (bf16 activations): the decode kernel (kquant_gemv.cu) up to 2 tokens for Q4_K and 4
+    // for Q6_K; the tcgen05 kernel (kquant_tc.cu) from 12 / 5 tokens when the weight has enough 128-row blocks to
+    // fill the GPU; this file's kernel in between, for f32 activations and for small weights.
+    const bool q6 = w->dtype == MUSER_DTYPE_Q6_K;
+    const bool tc_fits = !w_up && x_dtype == MUSER_DTYPE_BF16 && tokens >= ctx->tc_min_tokens[q6 ? 1 : 0] &&
+                         w->n_out >= ctx->tc_min_rows;
+    if (!tc_fits && x_dtype == MUSER_DTYPE_BF16 && tokens <= (q6 ? 4u : 2u)) {
         const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, y, y_dtype, tokens, ep, stream);
         if (ge != cudaErrorNotSupported) {
             MUSER_CUDA_TRY(ctx, ge);
@@ -476,14 +481,23 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
         }
     }
     if (ep.norm_weight) {
-        // this kernel reads its activations as it goes, so the fused input norm runs as a pass of its own into
-        // the context's scratch rows (f32), which the projection then reads instead of x
+        // the kernels below read their activations as they go, so the fused input norm runs as a pass of its own
+        // into the context's scratch rows (f32), which the projection then reads instead of x
         const size_t need = (size_t)tokens * w->n_in * sizeof(float);
         if (need > ctx->norm_scratch_bytes) return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL, "fused input norm: tokens x n_in exceeds the context's norm scratch");
         muser_cuda_status st = launch_rmsnorm_rows(ctx, x, x_dtype, tokens, w->n_in, ep.norm_weight, ep.norm_eps, ctx->norm_scratch, stream);
         if (st != MUSER_CUDA_OK) return st;
         x = ctx->norm_scratch;
         x_dtype = MUSER_DTYPE_F32;
+    }
+    if (tc_fits) { // (normalized bf16 rows reach it as f32 and are rounded to f16 there: 11 bits against bf16's 8)
+        Epilogue tail = ep;
+        tail.norm_weight = nullptr;
+        const cudaError_t te = launch_kquant_tc(ctx, w, x, x_dtype, y, y_dtype, tokens, tail, stream);
+        if (te != cudaErrorNotSupported) {
+            MUSER_CUDA_TRY(ctx, te);
+            return MUSER_CUDA_OK;
+        }
     }
     KqArgs a;
     a.image = w->image;

@@ -1,0 +1,656 @@
+// Skinny GEMM for Q4_K / Q6_K weights on the 5th-generation tensor cores: y[t][r] = dot(W_r, x_t), 3..64 tokens.
+//
+// Stands in for the batched routes of MetalKernels::encode_quantized_matmul and the speculative-verify batches of
+// encode_quantized_decode_group (crates/muser-engine/src/metal/encode/qkv.rs:234-281,414-449); on the CPU lane,
+// weights::matmul with quant::dot_q4_k_f32 / dot_q6_k_f32 (src/weights.rs:398-421).
+//
+// The weights stay in their 4.5 / 6.56-bit form in HBM and are read once, whatever the token count.  What goes to
+// the tensor cores is exact: the f16 operand built from a Q4_K weight is the INTEGER sc * q (6-bit scale times
+// 4-bit quant, at most 945), from a Q6_K weight sc * (q - 32) (at most 4096 in magnitude; f16 holds every such
+// product exactly up to 2048 and the even ones beyond), and the activations are the caller's bf16 values as f16.
+// The per-super-block factors d and dmin, which differ per row and per 256 inputs, cannot ride in the operands, so
+// the accumulator is drained once per 256 inputs: acc += d * sum(sc q x) - dmin * sum_j m_j X_j, with the second
+// sum (X_j = sum of the 32 activations of sub-block j, carried as an f16 head + remainder pair) done by one more
+// MMA.  This is the deferred order of quant/k_block.rs:178-240 and quant/k_block/q6.rs:90-141 with exact inner sums.
+//
+// One CTA per SM, persistent over (128-row block, K slice) items:
+//   warp 0      TMA: activation slabs (N tokens x 128 inputs, 128-byte swizzle) and the X_j pairs (32-byte swizzle)
+//   warp 1      tcgen05.mma kind::f16, M = 128 rows, N = tokens (16 / 32 / 64), K = 16; accumulators in tensor memory,
+//               two buffers so that the drain of one super-block column runs under the MMAs of the next
+//   warps 2-17  eight rows of one 16-row weight tile each: bulk copies global -> shared (two tiles in flight per warp),
+//               unpack to the f16 integers above, store into the swizzled A stage (three stages of 128 inputs)
+//   warps 18-21 drain: tcgen05.ld, scale by d / dmin (f32), keep N running sums per row in registers; at the end of
+//               an item add the K slices through the context scratch (last arriver sums in slice order) and store
+// Every wait is bounded; a wait that gives up records a code in the context's status word and the CTA winds down.
+#include <algorithm>
+#include <cmath>
+#include <type_traits>
+
+#include "common.cuh"
+#include "kquant_layout.cuh"
+#include "tcgen05.cuh"
+
+namespace muser {
+
+constexpr int kTcRows = 128;             // weight rows per block = MMA M
+constexpr int kTcStages = 2;             // A stages of 128 inputs each (the unpacked weights are the expensive bytes)
+constexpr int kTcABytes = kTcRows * 256; // 128 rows x 128 f16: two 64-column swizzle atoms of 16 KiB
+constexpr int kTcDequantWarps = 16;           // warp = (row tile of the block, upper / lower eight rows)
+constexpr int kTcThreads = 32 * (2 + kTcDequantWarps + 4);
+
+struct TcArgs {
+    const uint8_t *image;
+    void *y;
+    const float *row_scale;
+    const void *residual;
+    float *partial;         // [ksplit][tokens][n_out] partial sums (ksplit > 1)
+    unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
+    int *status;
+    uint32_t n_out, nsb, row_tiles, tokens, y_bf16, ksplit, items;
+};
+
+// The (item, super-block column) sequence of one CTA; every role walks the same sequence.
+struct TcWalk {
+    uint32_t item, rb, slice, k, k_end;
+    __device__ __forceinline__ void load(const TcArgs &a) {
+        if (item < a.items) {
+            rb = item / a.ksplit;
+            slice = item % a.ksplit;
+            k = a.nsb * slice / a.ksplit;
+            k_end = a.nsb * (slice + 1) / a.ksplit;
+        }
+    }
+    __device__ __forceinline__ void start(const TcArgs &a) {
+        item = blockIdx.x;
+        load(a);
+    }
+    __device__ __forceinline__ bool done(const TcArgs &a) const { return item >= a.items; }
+    __device__ __forceinline__ void next(const TcArgs &a) {
+        if (++k == k_end) {
+            item += gridDim.x;
+            load(a);
+        }
+    }
+};
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// K-major operand, 32 bytes (16 f16) per row, 32-byte swizzle, 8-row groups 256 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc32(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(256 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)6 << 61; // SWIZZLE_32B
+    return d;
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return (&v.x)[i]; } // compile-time i only
+
+// (byte `idx` of w) as an exact f16 pair (v, v): 0x6400 | v is 1024 + v
+__device__ __forceinline__ __half2 byte_pair(uint32_t w, uint32_t idx, float bias) {
+    const uint32_t m = __byte_perm(w, 0x64646464u, 0x4040u | idx | (idx << 8));
+    return __hsub2(u2h(m), __float2half2_rn(bias));
+}
+
+// ------------------------------------------------------------------------------------ Q4_K
+// What one unpacking warp holds of a tile: rows g (+ 8 * rowsel, rowsel fixed per warp), lane (g, t).
+// Its ring slot is [2 planes of 512 bytes: sub-blocks t, t + 4][8 row headers of 16 bytes].
+constexpr int kTcQ4Slot = 1024 + 128, kTcQ6Slot = 1024 + 512 + 128 + 16;
+struct TcQ4 {
+    uint4 q[2]; // [hi]: sub-block t + 4*hi
+    uint4 h;    // the row's header
+};
+struct TcQ4Hdr {
+    float d, dmin;
+    uint32_t sc[2], mn[2]; // 6-bit values as bytes: sub-blocks 0-3, 4-7 (quant/k_block.rs:22-31)
+};
+__device__ __forceinline__ TcQ4Hdr tc_q4_hdr(uint4 h) {
+    TcQ4Hdr s;
+    const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
+    s.d = __low2float(dd);
+    s.dmin = __high2float(dd);
+    s.sc[0] = h.y & 0x3F3F3F3Fu;
+    s.mn[0] = h.z & 0x3F3F3F3Fu;
+    s.sc[1] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+    s.mn[1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    return s;
+}
+__device__ __forceinline__ TcQ4 tc_load(const uint8_t *slot, int lane, TcQ4 *) {
+    TcQ4 r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(slot);
+    r.q[0] = q[lane];
+    r.q[1] = q[32 + lane];
+    r.h = reinterpret_cast<const uint4 *>(slot + 1024)[lane >> 2];
+    return r;
+}
+// Inputs 128*HALF .. +127 of row `row` (a multiple of 8 plus g) -> the A stage: sc * q as f16.
+template <int HALF>
+__device__ __forceinline__ void tc_unpack_half(const TcQ4 &r, const TcQ4Hdr &hd, uint32_t stage, uint32_t row, int g, int t) {
+    const __half2 sc = byte_pair(hd.sc[HALF], (uint32_t)t, 1024.0f);
+    const __half2 off = __hmul2(sc, __float2half2_rn(-1024.0f)); // exact: at most 63 * 1024
+    const uint32_t base = stage + (uint32_t)(t >> 1) * 16384u + (row >> 3) * 1024u + (row & 7) * 128u;
+    // Lanes t and t + 2 write the same 16-byte column of two different 16 KiB atoms, i.e. the same banks; the upper
+    // pair therefore walks its four words in the order 2, 3, 0, 1, which makes the warp's stores conflict-free.
+    const bool flip = t >= 2;
+    uint4 qv = r.q[HALF];
+    if (flip) qv = make_uint4(qv.z, qv.w, qv.x, qv.y);
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t w = word_of(qv, wi);
+        uint32_t o[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) { // nibbles p and p + 4 of the word are elements 2p, 2p + 1
+            const uint32_t e = ((w >> (4 * p)) & 0x000F000Fu) | 0x64006400u; // (1024 + q, 1024 + q')
+            o[p] = h2u(__hfma2(u2h(e), sc, off));                            // sc * q, exact
+        }
+        const uint32_t word = flip ? (uint32_t)(wi ^ 2) : (uint32_t)wi;      // which 8 elements of the sub-block these are
+        const uint32_t chunk = ((uint32_t)(t & 1) * 4 + word) ^ (uint32_t)g;
+        sts128(base + chunk * 16u, o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------ Q6_K
+// Ring slot: [2 low-nibble planes of 512 bytes][high-bit plane, 512][8 x sc[16] int8][8 x d f16].
+struct TcQ6 {
+    uint4 lo[2]; // [half]
+    uint4 hi;
+    uint4 sc;
+    float d;
+};
+__device__ __forceinline__ TcQ6 tc_load(const uint8_t *slot, int lane, TcQ6 *) {
+    TcQ6 r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(slot);
+    r.lo[0] = q[lane];
+    r.lo[1] = q[32 + lane];
+    r.hi = q[64 + lane];
+    r.sc = reinterpret_cast<const uint4 *>(slot + 1536)[lane >> 2];
+    r.d = __half2float(reinterpret_cast<const __half *>(slot + 1664)[lane >> 2]);
+    return r;
+}
+// elements 4x .. 4x+3 of one sub-block as bytes 0..63: low nibbles from `lo`, the two high bits from `hi`
+__device__ __forceinline__ uint32_t tc_q6_bytes(uint32_t lo, uint32_t hi, int x) {
+    const uint32_t n = ((x & 1) ? lo >> 4 : lo) & 0x0F0F0F0Fu;
+    const uint32_t h = x == 0 ? hi << 4 : x == 1 ? hi << 2 : x == 2 ? hi : hi >> 2;
+    return n | (h & 0x30303030u);
+}
+template <int HALF>
+__device__ __forceinline__ void tc_unpack_half(const TcQ6 &r, uint32_t stage, uint32_t row, int g, int t) {
+    const __half2 k1056 = __float2half2_rn(1056.0f);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) { // owned sub-block 2*HALF + u = sub-block t + 4*(2*HALF + u)
+        const uint32_t hw = word_of(r.hi, 2 * HALF + u), sw = word_of(r.sc, 2 * HALF + u);
+        const __half2 sc = byte_pair(sw ^ 0x80808080u, (uint32_t)t, 1152.0f); // int8 scale, exact
+        const uint32_t base = stage + (uint32_t)u * 16384u + (row >> 3) * 1024u + (row & 7) * 128u;
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) { // elements 8*h2 .. 8*h2 + 7 of the sub-block
+            const uint32_t lw = word_of(r.lo[HALF], 2 * u + h2);
+            const uint32_t b0 = tc_q6_bytes(lw, hw, 2 * h2), b1 = tc_q6_bytes(lw, hw, 2 * h2 + 1);
+            const uint32_t p0 = __byte_perm(b0, 0x64646464u, 0x4140u), p1 = __byte_perm(b0, 0x64646464u, 0x4342u);
+            const uint32_t p2 = __byte_perm(b1, 0x64646464u, 0x4140u), p3 = __byte_perm(b1, 0x64646464u, 0x4342u);
+            // (1024 + q) - 1056 = q - 32, exact; times the scale: exact up to 2048, nearest even beyond
+            const uint32_t o0 = h2u(__hmul2(__hsub2(u2h(p0), k1056), sc)), o1 = h2u(__hmul2(__hsub2(u2h(p1), k1056), sc));
+            const uint32_t o2 = h2u(__hmul2(__hsub2(u2h(p2), k1056), sc)), o3 = h2u(__hmul2(__hsub2(u2h(p3), k1056), sc));
+            const uint32_t chunk = (uint32_t)(2 * t + h2) ^ (uint32_t)g;
+            sts128(base + chunk * 16u, o0, o1, o2, o3);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ kernel
+template <int DT, int N>
+struct TcSmem {
+    static constexpr bool kQ4 = DT == MUSER_DTYPE_Q4_K;
+    static constexpr int kTile = kQ4 ? kQ4TileBytes : kQ6TileBytes, kSlot = kQ4 ? kTcQ4Slot : kTcQ6Slot;
+    // Raw tiles in flight per unpacking warp.  HBM latency times the stream's rate is ~55 KB per SM, and the warps
+    // run in step, so the rings are made as deep as shared memory allows: 72-105 KB of weights in flight per SM.
+    static constexpr int kRing = (!kQ4 && N == 64) ? 3 : 4;
+    static constexpr int kStagesB = N == 64 ? 3 : 4; // activation slabs come from L2 with ~1500 cycles of latency
+    static constexpr int kBBytes = N * 256;          // two atoms of N rows x 128 bytes
+    static constexpr int kMinA = kTcRows * 32, kMinB = N * 32 < 1024 ? 1024 : N * 32;
+    static constexpr int kOffB = kTcStages * kTcABytes;
+    static constexpr int kOffMinA = kOffB + kStagesB * kBBytes;
+    static constexpr int kOffMinB = kOffMinA + 2 * kMinA;
+    static constexpr int kOffRing = kOffMinB + 2 * kMinB;
+    static constexpr int kOffHdr = kOffRing + kTcDequantWarps * kRing * kSlot;
+    static constexpr int kOffBars = kOffHdr + 4 * kTcRows * 8;
+    static constexpr int kBars = 2 * kTcStages + 2 * kStagesB + 4 + kTcDequantWarps * kRing;
+    static constexpr int kBytes = kOffBars + kBars * 8 + 16 + 1024 /*alignment slack*/;
+    static_assert(kBytes <= 227 * 1024, "shared memory of one CTA exceeded");
+    static constexpr uint32_t kTmemCols = N >= 64 ? 512 : (N >= 32 ? 256 : 128); // two buffers of 3N columns
+};
+
+template <int DT, int N>
+__global__ void __launch_bounds__(kTcThreads, 1)
+kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_xs, const TcArgs a) {
+    using S = TcSmem<DT, N>;
+    constexpr bool Q4 = S::kQ4;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + S::kOffBars);
+    constexpr int kRing = S::kRing, kStagesB = S::kStagesB;
+    const uint32_t bar_full_a = smem_u32(bars), bar_empty_a = bar_full_a + 8 * kTcStages;
+    const uint32_t bar_full_b = bar_empty_a + 8 * kTcStages, bar_empty_b = bar_full_b + 8 * kStagesB;
+    const uint32_t bar_tmem_full = bar_empty_b + 8 * kStagesB, bar_tmem_empty = bar_tmem_full + 16, bar_ring = bar_tmem_empty + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + S::kBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float2 *hdr = reinterpret_cast<float2 *>(aligned + S::kOffHdr);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(bar_full_a + 8 * s, kTcDequantWarps);
+            mbar_init(bar_empty_a + 8 * s, 1);
+        }
+        for (int s = 0; s < kStagesB; ++s) {
+            mbar_init(bar_full_b + 8 * s, 1);
+            mbar_init(bar_empty_b + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_tmem_full + 8 * b, 1);
+            mbar_init(bar_tmem_empty + 8 * b, 4);
+        }
+        for (int i = 0; i < kTcDequantWarps * kRing; ++i) mbar_init(bar_ring + 8 * i, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(S::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- activation producer
+        if (lane == 0) {
+            TcWalk w;
+            w.start(a);
+            uint32_t hs = 0, tc = 0, issued = 0;
+            bool ok = true;
+            for (; !w.done(a) && ok; w.next(a), ++tc) {
+                for (uint32_t h = 0; h < 2; ++h, ++hs) {
+                    const uint32_t s = hs % kStagesB, round = hs / kStagesB;
+                    if (round > 0) ok = mbar_wait_relaxed(bar_empty_b + 8 * s, (round - 1) & 1, abort_flag, 32);
+                    if (!ok) break;
+                    const uint32_t full = bar_full_b + 8 * s, dst = base + S::kOffB + s * S::kBBytes;
+                    const bool with_sums = Q4 && h == 1;
+                    mbar_expect_tx(full, S::kBBytes + (with_sums ? N * 32 : 0));
+                    const int x0 = (int)((w.k * 256 + h * 128) * 2);
+                    tma_load_2d(dst, &map_x, x0, 0, full);
+                    tma_load_2d(dst + N * 128, &map_x, x0 + 128, 0, full);
+                    if (with_sums) tma_load_2d(base + S::kOffMinB + (tc & 1) * S::kMinB, &map_xs, (int)(w.k * 32), 0, full);
+                    issued = hs + 1;
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(a.status + 1, 301);
+                // let the copies already in flight land before the CTA's shared memory goes away
+                const uint32_t first = issued > (uint32_t)kStagesB ? issued - kStagesB : 0;
+                for (uint32_t k = first; k < issued; ++k) mbar_wait_alone(bar_full_b + 8 * (k % kStagesB), (k / kStagesB) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            // kind::f16: f32 accumulator (bit 4), A and B f16 (format 0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
+            TcWalk w;
+            w.start(a);
+            uint32_t hs = 0, tc = 0;
+            bool ok = true;
+            for (; !w.done(a) && ok; w.next(a), ++tc) {
+                const uint32_t buf = tc & 1, d_main = tmem + buf * 3 * N, d_min = d_main + 2 * N;
+                if (tc >= 2) { // the drain warps must have read this buffer's previous contents
+                    ok = mbar_wait(bar_tmem_empty + 8 * buf, ((tc >> 1) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                for (uint32_t h = 0; h < 2; ++h, ++hs) {
+                    const uint32_t s = hs % kTcStages, round = hs / kTcStages, s_b = hs % kStagesB, round_b = hs / kStagesB;
+                    ok = mbar_wait(bar_full_b + 8 * s_b, round_b & 1, abort_flag); if (ok) ok = mbar_wait(bar_full_a + 8 * s, round & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = base + s * kTcABytes, sb = base + S::kOffB + s_b * S::kBBytes;
+#pragma unroll
+                    for (uint32_t atom = 0; atom < 2; ++atom) {
+                        const uint64_t da = operand_desc(sa + atom * 16384u), db = operand_desc(sb + atom * (N * 128u));
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) // 16 values = 32 bytes along the swizzled 128-byte rows
+                            mma_f16(d_main + (kk & 1) * N, da + 2 * kk, db + 2 * kk, idesc, (h | atom | (kk >> 1)) != 0);
+                    }
+                    if (Q4 && h == 1)
+                        mma_f16(d_min, operand_desc32(base + S::kOffMinA + buf * S::kMinA),
+                                operand_desc32(base + S::kOffMinB + buf * S::kMinB), idesc, 0);
+                    mma_commit(bar_empty_a + 8 * s); // stages (and the sum buffers) reusable once these MMAs have read them
+                    mma_commit(bar_empty_b + 8 * s_b);
+                }
+                if (ok) mma_commit(bar_tmem_full + 8 * buf);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(a.status + 1, 302);
+            }
+        }
+    } else if (warp < 2 + kTcDequantWarps) {
+        // ---------------------------------------------------------------- weight unpackers
+        using Regs = typename std::conditional<Q4, TcQ4, TcQ6>::type;
+        const int dw = warp - 2, g = lane >> 2, t = lane & 3;
+        const uint32_t rsel = (uint32_t)dw & 1, row = (uint32_t)(dw >> 1) * 16 + g + 8 * rsel; // this lane's row of the block
+        uint8_t *ring = aligned + S::kOffRing + dw * kRing * S::kSlot;
+        const uint32_t rbar = bar_ring + 8 * dw * kRing;
+        auto fetch = [&](const TcWalk &x, uint32_t slot) { // this warp's eight rows of one tile: its planes and headers
+            if (lane == 0) {
+                const uint32_t rt = min(x.rb * (kTcRows / kTileRows) + (uint32_t)(dw >> 1), a.row_tiles - 1); // a short last block repeats its last tile
+                const uint8_t *src = a.image + ((uint64_t)rt * a.nsb + x.k) * S::kTile;
+                const uint32_t dst = smem_u32(ring) + slot * S::kSlot, bar = rbar + 8 * slot;
+                mbar_expect_tx(bar, S::kSlot);
+                bulk_load(dst, src + 1024 * rsel, 1024, bar);
+                if constexpr (Q4) {
+                    bulk_load(dst + 1024, src + 2048 + 128 * rsel, 128, bar);
+                } else {
+                    bulk_load(dst + 1024, src + kQ6OffHi + 512 * rsel, 512, bar);
+                    bulk_load(dst + 1536, src + kQ6OffSc + 128 * rsel, 128, bar);
+                    bulk_load(dst + 1664, src + kQ6OffD + 16 * rsel, 16, bar);
+                }
+            }
+        };
+        TcWalk w, f;
+        w.start(a);
+        f = w;
+        uint32_t fetched = 0;
+        for (; fetched < (uint32_t)kRing && !f.done(a); ++fetched, f.next(a)) fetch(f, fetched);
+        uint32_t n = 0, hs = 0;
+        bool ok = true;
+        // one half (128 inputs) of the tile in `cur` into its stage, then tell the MMA warp
+        auto half_step = [&](const Regs &cur, const TcQ4Hdr &hd, auto half_tag) {
+            constexpr int HALF = decltype(half_tag)::value;
+            const uint32_t s = hs % kTcStages, round = hs / kTcStages;
+            if (round > 0) ok = mbar_wait(bar_empty_a + 8 * s, (round - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            if constexpr (Q4) tc_unpack_half<HALF>(cur, hd, base + s * kTcABytes, row, g, t);
+            else tc_unpack_half<HALF>(cur, base + s * kTcABytes, row, g, t);
+            if constexpr (HALF == 1) {
+                if constexpr (Q4) {
+                    // min operand: 16 f16 per row, (m_j, m_j) for j = 0..7; lanes t = 0, 1 write the row's two 16-byte chunks
+                    if (t < 2) {
+                        const uint32_t mw = t ? hd.mn[1] : hd.mn[0];
+                        const uint32_t chunk = (uint32_t)t ^ ((row >> 2) & 1);
+                        sts128(base + S::kOffMinA + (n & 1) * S::kMinA + (row >> 3) * 256u + (row & 7) * 32u + chunk * 16u,
+                               h2u(byte_pair(mw, 0, 1024.0f)), h2u(byte_pair(mw, 1, 1024.0f)), h2u(byte_pair(mw, 2, 1024.0f)),
+                               h2u(byte_pair(mw, 3, 1024.0f)));
+                    }
+                    if (t == 2) hdr[(n & 3) * kTcRows + row] = make_float2(hd.d, hd.dmin);
+                } else {
+                    if (t == 2) hdr[(n & 3) * kTcRows + row] = make_float2(cur.d, 0.0f);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic stores -> visible to the MMA's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+            ++hs;
+        };
+        for (; !w.done(a) && ok; w.next(a), ++n) {
+            const uint32_t slot = n % kRing;
+            ok = mbar_wait(rbar + 8 * slot, (n / kRing) & 1, abort_flag);
+            if (!ok) break;
+            const Regs cur = tc_load(ring + slot * S::kSlot, lane, (Regs *)nullptr);
+            __syncwarp(); // every lane has its copy: the slot may be refilled
+            if (!f.done(a)) {
+                fetch(f, slot);
+                f.next(a);
+                ++fetched;
+            }
+            TcQ4Hdr hd{};
+            if constexpr (Q4) hd = tc_q4_hdr(cur.h);
+            half_step(cur, hd, std::integral_constant<int, 0>{});
+            if (ok) half_step(cur, hd, std::integral_constant<int, 1>{});
+        }
+        if (!ok && lane == 0) {
+            *abort_flag = 1;
+            atomicCAS(a.status + 1, 0, 303);
+        }
+        // copies still in flight into this warp's ring must land before the CTA's shared memory goes away
+        if (!ok)
+            for (uint32_t k = n; k < fetched; ++k) mbar_wait_alone(rbar + 8 * (k % kRing), (k / kRing) & 1);
+    } else {
+        // ---------------------------------------------------------------- drain (the last four warps)
+        const uint32_t quad = warp & 3, row_in_block = quad * 32 + lane;
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+        TcWalk w;
+        w.start(a);
+        uint32_t tc = 0;
+        while (!w.done(a)) {
+            const uint32_t buf = tc & 1;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_tmem_full + 8 * buf, (tc >> 1) & 1, abort_flag, 40));
+            if (!ok) {
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicCAS(a.status + 1, 0, 304);
+                }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float2 hd = hdr[(tc & 3) * kTcRows + row_in_block];
+            const uint32_t taddr = tmem + ((quad * 32) << 16) + buf * 3 * N;
+#pragma unroll
+            for (int c0 = 0; c0 < N; c0 += 16) {
+                uint32_t p[16], p2[16], m[16];
+                tmem_ld16(taddr + c0, p);
+                tmem_ld16(taddr + N + c0, p2);
+                if constexpr (Q4) tmem_ld16(taddr + 2 * N + c0, m);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    acc[c0 + i] = fmaf(hd.x, __uint_as_float(p[i]) + __uint_as_float(p2[i]), acc[c0 + i]);
+                    if constexpr (Q4) acc[c0 + i] = fmaf(-hd.y, __uint_as_float(m[i]), acc[c0 + i]);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+            const bool last = w.k + 1 == w.k_end;
+            const uint32_t rb = w.rb, slice = w.slice;
+            w.next(a);
+            ++tc;
+            if (!last) continue;
+
+            // ---- end of an item: meet the other K slices, then store
+            const uint32_t row = rb * kTcRows + row_in_block;
+            const bool live = row < a.n_out;
+            bool finish = true;
+            if (a.ksplit > 1) {
+                if (live)
+#pragma unroll
+                    for (int i = 0; i < N; ++i)
+                        if ((uint32_t)i < a.tokens) a.partial[((size_t)slice * a.tokens + i) * a.n_out + row] = acc[i];
+                __threadfence();
+                __syncwarp();
+                unsigned int seen = 0;
+                if (lane == 0) seen = atomicAdd(a.counters + rb * 4 + quad, 1u);
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                finish = seen == a.ksplit - 1;
+                if (finish) {
+                    if (lane == 0) a.counters[rb * 4 + quad] = 0; // ready for the next launch
+                    __threadfence();
+                    // slices in order (deterministic); sixteen independent loads in flight per step, not one
+#pragma unroll
+                    for (int c0 = 0; c0 < N; c0 += 16) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                        for (uint32_t sl = 0; sl < a.ksplit; ++sl) {
+                            float got[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const uint32_t i = min((uint32_t)(c0 + j), a.tokens - 1); // rows past `tokens` re-read the last one
+                                got[j] = __ldcg(a.partial + ((size_t)sl * a.tokens + i) * a.n_out + (live ? row : 0u));
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += got[j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[c0 + j] = v[j];
+                    }
+                }
+            }
+            if (finish && live) {
+#pragma unroll
+                for (int i = 0; i < N; ++i) {
+                    if ((uint32_t)i >= a.tokens) continue;
+                    float r = acc[i];
+                    const size_t o = (size_t)i * a.n_out + row;
+                    if (a.row_scale) r *= a.row_scale[i];
+                    if (a.y_bf16) {
+                        if (a.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.residual)[o]);
+                        reinterpret_cast<__nv_bfloat16 *>(a.y)[o] = __float2bfloat16_rn(r);
+                    } else {
+                        if (a.residual) r += reinterpret_cast<const float *>(a.residual)[o];
+                        reinterpret_cast<float *>(a.y)[o] = r;
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(S::kTmemCols) : "memory");
+}
+
+// Activations into the form the kernel reads: f16, N rows (rows past `tokens` zero), columns in the weight image's
+// tile coordinates (a K shard's first tile may start before the shard's first input: those columns are zero), and
+// per 32-input sub-block the sum of the f16 values as an f16 head + remainder pair.
+template <bool XF32>
+__global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in, uint32_t k_off,
+                                                                uint32_t nsb, __half *__restrict__ xh, __half *__restrict__ xs) {
+    const uint32_t tile = blockIdx.x, tok = blockIdx.y, i = threadIdx.x;
+    const int64_t k = (int64_t)tile * 256 + i - (int64_t)k_off;
+    float v = 0.0f;
+    if (tok < tokens && k >= 0 && k < (int64_t)n_in)
+        v = XF32 ? reinterpret_cast<const float *>(x)[(size_t)tok * n_in + k]
+                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(x)[(size_t)tok * n_in + k]);
+    v = fminf(fmaxf(v, -65504.0f), 65504.0f); // f16 range; NaN passes through
+    const __half hv = __float2half_rn(v);
+    xh[(size_t)tok * nsb * 256 + (size_t)tile * 256 + i] = hv;
+    float s = __half2float(hv);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((i & 31) == 0) {
+        const __half head = __float2half_rn(s);
+        const __half rest = __float2half_rn(s - __half2float(head));
+        __half *dst = xs + (size_t)tok * nsb * 16 + (size_t)tile * 16 + 2 * (i >> 5);
+        dst[0] = head;
+        dst[1] = rest;
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+// K slices: as many items as keep every SM busy to the end, with as few slices as that needs.
+static uint32_t tc_plan_split(uint32_t nsb, uint32_t row_blocks, int sm_count, uint32_t max_split) {
+    uint32_t best = 1;
+    double best_cost = 1e300;
+    for (uint32_t ks = 1; ks <= max_split && ks <= nsb && ks <= 32; ++ks) {
+        const double rounds = std::ceil((double)row_blocks * ks / sm_count);
+        const double cost = rounds * (std::ceil((double)nsb / ks) + 1.5) + (ks > 1 ? 1.0 : 0.0);
+        if (cost < best_cost * (1.0 - 1e-9)) best_cost = cost, best = ks;
+    }
+    return best;
+}
+
+template <int DT, int N>
+static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, const TcArgs &a, int grid, cudaStream_t stream) {
+    using S = TcSmem<DT, N>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kquant_tc_kernel<DT, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    kquant_tc_kernel<DT, N><<<grid, kTcThreads, S::kBytes, stream>>>(mx, mxs, a);
+    return cudaGetLastError();
+}
+
+// cudaErrorNotSupported: this shape is not served here (the caller falls back to the other kernels).
+cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
+                             uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
+    // (the caller sends f32 activations elsewhere: they would lose bits on their way to f16)
+    if (tokens > 64 || !ctx->tc_scratch) return cudaErrorNotSupported;
+    const uint32_t n = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+    const size_t xh_bytes = (size_t)n * w->nsb * 256 * sizeof(__half), xs_bytes = (size_t)n * w->nsb * 16 * sizeof(__half);
+    const size_t xs_off = (xh_bytes + 1023) & ~(size_t)1023;
+    if (xs_off + xs_bytes > ctx->tc_scratch_bytes) return cudaErrorNotSupported;
+    __half *xh = reinterpret_cast<__half *>(ctx->tc_scratch);
+    __half *xs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(ctx->tc_scratch) + xs_off);
+    const dim3 pgrid(w->nsb, n);
+    if (x_dtype == MUSER_DTYPE_F32)
+        kquant_tc_prepare_kernel<true><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
+    else
+        kquant_tc_prepare_kernel<false><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+
+    CUtensorMap mx, mxs;
+    if (!tma_make_map(&mx, xh, n, (uint64_t)w->nsb * 512, n, 128) || !tma_make_map(&mxs, xs, n, (uint64_t)w->nsb * 32, n, 32))
+        return cudaErrorInvalidValue;
+    TcArgs a;
+    a.image = w->image;
+    a.y = y;
+    a.row_scale = ep.row_scale;
+    a.residual = ep.residual;
+    a.partial = ctx->gemv_partial;
+    a.counters = ctx->gemv_counters;
+    a.status = ctx->dev_status;
+    a.n_out = (uint32_t)w->n_out;
+    a.nsb = w->nsb;
+    a.row_tiles = w->row_tiles;
+    a.tokens = tokens;
+    a.y_bf16 = y_dtype == MUSER_DTYPE_BF16;
+    const uint32_t row_blocks = (w->row_tiles + 7) / 8;
+    const size_t slice_bytes = (size_t)tokens * w->n_out * sizeof(float);
+    uint32_t max_split = (uint32_t)std::max<size_t>(1, ctx->gemv_partial_bytes / std::max<size_t>(1, slice_bytes));
+    if ((size_t)row_blocks * 4 > ctx->gemv_counter_slots) max_split = 1;
+    a.ksplit = tc_plan_split(w->nsb, row_blocks, ctx->sm_count, max_split);
+    a.items = row_blocks * a.ksplit;
+    const int grid = (int)std::min<uint32_t>(a.items, (uint32_t)ctx->sm_count);
+    if (w->dtype == MUSER_DTYPE_Q4_K)
+        return n == 16 ? tc_launch<MUSER_DTYPE_Q4_K, 16>(mx, mxs, a, grid, stream)
+             : n == 32 ? tc_launch<MUSER_DTYPE_Q4_K, 32>(mx, mxs, a, grid, stream)
+                       : tc_launch<MUSER_DTYPE_Q4_K, 64>(mx, mxs, a, grid, stream);
+    return n == 16 ? tc_launch<MUSER_DTYPE_Q6_K, 16>(mx, mxs, a, grid, stream)
+         : n == 32 ? tc_launch<MUSER_DTYPE_Q6_K, 32>(mx, mxs, a, grid, stream)
+                   : tc_launch<MUSER_DTYPE_Q6_K, 64>(mx, mxs, a, grid, stream);
+}
+
+} // namespace muser

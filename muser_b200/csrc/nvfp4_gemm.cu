@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace muser {
 
@@ -31,7 +32,6 @@ constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 25
 static_assert(kSmemBytes <= 227 * 1024, "stage ring exceeds the shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;              // 256 accumulator + 16 SFA + 32 SFB, rounded to a power of two
 constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct GemmArgs {
     const uint8_t *a_scales; // activations, swizzled
@@ -47,53 +47,6 @@ struct GemmArgs {
     float scale2, scale2_up, inv_input_scale;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait.  Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-// K-major operand tile, 128 bytes per row, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;            // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
-    d |= (uint64_t)1 << 46;            // descriptor version
-    d |= (uint64_t)2 << 61;            // SWIZZLE_128B
-    return d;
-}
 // Scale-factor chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -115,24 +68,6 @@ __device__ __forceinline__ void mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint6
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
         : "memory");
 }
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// 32 consecutive accumulator columns of this thread's lane (row) into registers; follow with tmem_ld_wait().
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
 // One 32-column strip of one accumulator row: scale, fuse, convert, store (16-byte stores when the row allows).
 template <typename T>
 __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T *res, uint32_t valid, bool vec_ok) {
@@ -460,17 +395,23 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// rows x (k/2 bytes), K contiguous; box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside.
-static bool make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+// rows x row_bytes, K contiguous; box = box_rows x box_bytes with the swizzle of the same width, zero fill outside.
+bool tma_make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint32_t box_bytes) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {row_bytes, rows};
     cuuint64_t strides[1] = {row_bytes};
-    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t box[2] = {box_bytes, box_rows};
     cuuint32_t elem[2] = {1, 1};
+    const CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                  : box_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    return tma_make_map(map, ptr, rows, row_bytes, box_rows, 128);
 }
 
 muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {

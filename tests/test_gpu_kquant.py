@@ -139,6 +139,45 @@ def test_fused_input_rmsnorm(gpu, dtype, x_dtype):
 
 
 @pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float32])
+def test_tensor_core_skinny_kernel(gpu, dtype, x_dtype):
+    """The tcgen05 kernel (exact integer f16 operands, per-super-block drain) forced for every token count it serves,
+    on shapes with a short last row block, one to many K slices, and the fused row scale / residual; then the same
+    calls with that kernel switched off, so the legacy skinny kernel stays covered."""
+    op, ctx, k = gpu
+    key = op.TUNE_TC_MIN_TOKENS_Q4_K if dtype == O.Q4_K else op.TUNE_TC_MIN_TOKENS_Q6_K
+    shapes = [(512, 13, 2), (1024, 37, 4), (2048, 300, 8)]
+    try:
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1)
+        for threshold in (1, 65):
+            ctx.tuning_set(key, threshold)
+            for n_in, n_out, blocks in shapes:
+                raw = H.lcg_weights(dtype, n_out, blocks, seed=n_out + dtype)
+                w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+                for tokens in (3, 9, 16, 17, 40, 64):
+                    x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=tokens).reshape(tokens, n_in)).to(x_dtype)
+                    want = O.matmul(O.TensorView(raw, dtype, n_in, n_out), x.float().numpy(), threads=O.host_threads())
+                    y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+                    k.encode_quantized_matmul(w, x.cuda(), y, tokens)
+                    ctx.sync_status()
+                    err = H.rel_l2(y.cpu().numpy(), want)
+                    assert err <= REL_L2_TOL, (threshold, n_in, n_out, tokens, err)
+                rs = torch.linspace(0.5, 2.0, 5, device="cuda")
+                res = torch.randn((5, n_out), device="cuda")
+                x = torch.from_numpy(H.lcg_activations(5 * n_in, seed=3).reshape(5, n_in)).to(x_dtype)
+                want = O.matmul(O.TensorView(raw, dtype, n_in, n_out), x.float().numpy())
+                y = torch.empty((5, n_out), dtype=torch.float32, device="cuda")
+                k.encode_quantized_matmul(w, x.cuda(), y, 5, row_scale=rs, residual=res)
+                assert H.rel_l2(y.cpu().numpy(), want * rs.cpu().numpy()[:, None] + res.cpu().numpy()) <= REL_L2_TOL
+                w.free()
+    finally:
+        ctx.tuning_set(op.TUNE_TC_MIN_TOKENS_Q4_K, 12)
+        ctx.tuning_set(op.TUNE_TC_MIN_TOKENS_Q6_K, 5)
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+    ctx.sync_status()
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
 def test_tensor_parallel_shards(gpu, dtype):
     """Row shards concatenate to the unsharded result exactly; K shards sum to it within tolerance."""
     op, ctx, k = gpu
