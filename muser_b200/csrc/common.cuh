@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 
 #include "../../include/muser_cuda.h"
 
@@ -82,6 +83,31 @@ extern thread_local std::string g_create_error;
             return ::muser::fail((ctx), MUSER_CUDA_ERROR,                                             \
                                  std::string(#expr) + ": " + cudaGetErrorString(e__));                \
     } while (0)
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may begin while the kernel before it in the
+// stream is still running.  It calls pdl_wait() before it touches anything an earlier kernel may have written (its
+// activations, the context's scratch and counters, its output); what it does before that (barrier set-up, the first
+// weight-tile copies: weights are constants) overlaps the predecessor's tail and hides the launch latency.
+// pdl_release() lets the next kernel start early in turn.  Both are no-ops for ordinary launches.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -441,6 +441,9 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_g
     };
     __syncthreads(); // barriers initialised
     for (uint32_t i = 0; i < kRing && i < total; ++i) fetch_next(i);
+    // the first weight tiles are on their way; everything from here on may depend on the kernel before this one
+    pdl_release();
+    pdl_wait();
 
     __shared__ float norm_red[33], inv_rms[TOK];
     if (a.norm_weight) { // every CTA needs the whole row's mean square, whatever its K slice
@@ -626,8 +629,7 @@ static cudaError_t launch_gemv(GemvArgs &a, Ctx *ctx, cudaStream_t stream) {
     a.ksplit = cache.plan.ksplit;
     a.groups = cache.groups;
     a.max_tiles = (a.nsb + a.ksplit - 1) / a.ksplit + 1;
-    kquant_gemv_kernel<DT, MT, NG, DUAL><<<cache.groups * a.ksplit, cache.plan.warps * 32, cache.smem, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kquant_gemv_kernel<DT, MT, NG, DUAL>, dim3(cache.groups * a.ksplit), dim3(cache.plan.warps * 32), cache.smem, stream, a);
 }
 
 template <int DT, bool DUAL>
