@@ -226,6 +226,11 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda
  * done.  Timing it gives the tensor-pipe ceiling that the prefill GEMM's roofline fraction is quoted against. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *ctx, uint32_t iters, double *flops, void *stream);
 
+/* Measurement aid, no counterpart in the reference.  Issue interval of the instruction the K-quant skinny kernel is
+ * built on: every SM issues iters x 4 tcgen05.mma kind::f16 (128 rows x n_cols x 16, n_cols in {16,32,64,128,256})
+ * back to back on resident operands; returns SM clock cycles per instruction.  Synchronizes the device. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *ctx, uint32_t n_cols, uint32_t iters, double *cycles_per_mma);
+
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
  * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const float *x_host,

@@ -508,6 +508,14 @@ muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *c, uint32_t iters, d
     return launch_nvfp4_peak(ctx, iters, flops, (cudaStream_t)stream);
 }
 
+muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *c, uint32_t n_cols, uint32_t iters, double *cycles_per_mma) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !cycles_per_mma || iters == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    MUSER_CUDA_TRY(ctx, cudaDeviceSynchronize()); // the probe borrows the split-K scratch
+    return launch_f16_mma_probe(ctx, n_cols, iters, cycles_per_mma);
+}
+
 muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *c, const muser_cuda_weight *wp, const float *x_host,
                                          uint32_t tokens, float *y_host) {
     Ctx *ctx = reinterpret_cast<Ctx *>(c);

@@ -576,6 +576,75 @@ __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__re
     }
 }
 
+// Issue-rate probe for the instruction this kernel is built on: one thread per SM issues `iters` x 4
+// tcgen05.mma kind::f16 (M = 128, K = 16, N columns) back to back on resident operands and one accumulator, and CTA 0
+// reports the cycles from the first issue to the completion of the last.
+template <int N>
+__global__ void __launch_bounds__(128, 1) f16_mma_probe_kernel(uint32_t iters, long long *out, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    constexpr int kOperands = 16384 + 32768; // A: 128 rows x 128 bytes, B: up to 256 rows x 128 bytes
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kOperands);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    for (uint32_t i = threadIdx.x; i < kOperands / 16; i += blockDim.x) reinterpret_cast<uint4 *>(aligned)[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(bars), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    const int warp = threadIdx.x >> 5;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 32) {
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
+        const uint64_t da = operand_desc(base), db = operand_desc(base + 16384);
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < iters; ++i)
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) mma_f16(tmem, da + 2 * kk, db + 2 * kk, idesc, (i | kk) != 0);
+        mma_commit(smem_u32(bars));
+        if (!mbar_wait(smem_u32(bars), 0, abort_flag)) atomicExch(status + 1, 305);
+        if (blockIdx.x == 0) out[0] = clock64() - t0;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+}
+
+muser_cuda_status launch_f16_mma_probe(Ctx *ctx, uint32_t n_cols, uint32_t iters, double *cycles_per_mma) {
+    constexpr int kSmem = 16384 + 32768 + 64 + 1024;
+    long long *out = reinterpret_cast<long long *>(ctx->gemv_partial); // scratch; the call synchronizes
+    auto run = [&](auto kernel) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return e;
+        kernel<<<ctx->sm_count, 128, kSmem>>>(iters, out, ctx->dev_status);
+        return cudaGetLastError();
+    };
+    cudaError_t e;
+    switch (n_cols) {
+    case 16: e = run(f16_mma_probe_kernel<16>); break;
+    case 32: e = run(f16_mma_probe_kernel<32>); break;
+    case 64: e = run(f16_mma_probe_kernel<64>); break;
+    case 128: e = run(f16_mma_probe_kernel<128>); break;
+    case 256: e = run(f16_mma_probe_kernel<256>); break;
+    default: return fail(ctx, MUSER_CUDA_BAD_ARG, "probe widths: 16, 32, 64, 128, 256");
+    }
+    MUSER_CUDA_TRY(ctx, e);
+    long long cycles = 0;
+    MUSER_CUDA_TRY(ctx, cudaMemcpy(&cycles, out, sizeof cycles, cudaMemcpyDeviceToHost));
+    *cycles_per_mma = (double)cycles / (4.0 * iters);
+    return MUSER_CUDA_OK;
+}
+
 // ------------------------------------------------------------------------------------------ host side
 // K slices: as many items as keep every SM busy to the end, with as few slices as that needs.
 static uint32_t tc_plan_split(uint32_t nsb, uint32_t row_blocks, int sm_count, uint32_t max_split) {

@@ -248,6 +248,8 @@ def main(argv=None) -> None:
     else:
         ctx = op.Context(0)
         print(f"dense block-scaled FP4 tensor peak: {op.fp4_peak_tflops(ctx):.1f} TFLOP/s")
+        for n in (16, 32, 64, 128, 256):
+            print(f"tcgen05.mma kind::f16, 128 x {n:3d} x 16, back to back: {op.f16_mma_cycles(ctx, n):.1f} cycles per instruction")
 
 
 if __name__ == "__main__":

@@ -263,6 +263,15 @@ def fp4_peak_tflops(ctx: Context, iters: int = 20000, reps: int = 3) -> float:
     return best
 
 
+def f16_mma_cycles(ctx: Context, n_cols: int, iters: int = 2000) -> float:
+    """SM cycles per tcgen05.mma kind::f16 (128 x n_cols x 16) issued back to back (muser_cuda_f16_mma_probe)."""
+    out = C.c_double()
+    ctx.check(_L.muser_cuda_f16_mma_probe(ctx._h, n_cols, iters, C.byref(out)))
+    ctx.check(_L.muser_cuda_f16_mma_probe(ctx._h, n_cols, iters, C.byref(out)))  # second run: warm
+    ctx.sync_status()
+    return out.value
+
+
 def nvfp4_matmul_static(weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int) -> None:
     """muser_cuda_nvfp4_matmul_static: the W4A4 projection without a context and without any allocation
     (tokens <= 128, n_in <= 32768); scratch lives in the library image.  Enqueued on torch's current stream."""
