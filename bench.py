@@ -54,6 +54,9 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+MEASURED_STEP_TRAFFIC_BYTES = 1262834688  # one GPU, one step, from the ncu capture named beside its use
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -89,7 +92,8 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({names[i] for s in self.samples for i in range(4) if len(s) > 2 + i and s[2 + i] == "Active"})
         return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(self.samples),
+                "window": "0.5 s of the same step replays right before the timed region, and the timed region"}
 
 
 # ----------------------------------------------------------------------------------- reference arm
@@ -204,11 +208,15 @@ def run_gpu(args):
         except Exception as exc:  # pragma: no cover - depends on the NCCL build
             print(f"graph capture unavailable ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
             torch.cuda.synchronize()
-    for _ in range(2):
-        run_step()
-    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
+        # The timed region can be a few milliseconds, less than one nvidia-smi query: the sampler therefore also
+        # covers ~0.5 s of the same replays immediately before it (same kernels, same load), all untimed.
+        lead = time.time()
+        while time.time() - lead < 0.5:
+            for _ in range(10):
+                run_step()
+            torch.cuda.synchronize()
         barrier()
         start.record()
         for _ in range(args.steps):
@@ -223,47 +231,20 @@ def run_gpu(args):
     total_bytes = step_bytes(2) * args.steps
     value = total_bytes / (ms * 1e-3) / 1e9
 
-    # per-call device times (secondary detail): each (projection, M) alone, as a graph of launches that alternate
-    # with the largest other tensor so that the weight never sits in L2; the other tensor's own time is subtracted
+    # per-call device times (secondary detail): each (projection, M) alone, launches rotating over enough copies of
+    # the weight that it never sits in L2, replayed as a CUDA graph (the per-kernel harness's measurement)
     detail = {}
     if rank == 0 and not args.no_detail:
-        def graph_us(calls, reps=5):
-            g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for c in calls:
-                    c()
-                torch.cuda.synchronize()
-                with torch.cuda.graph(g, stream=side):
-                    for c in calls:
-                        c()
-            torch.cuda.synchronize()
-            g.replay()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                g.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            return e0.elapsed_time(e1) * 1e3 / reps
-
-        def call(name, m):
-            return lambda: kern.encode_quantized_matmul(weights[name], x_dev[(name, m)], y_dev[(name, m)], m)
-
-        base = {o: graph_us([call(o, 1), call("ffn_up" if o != "ffn_up" else "ffn_gate", 1)] * 5) for o in ("ffn_down", "ffn_gate")}
+        from muser_b200 import microbench
         for name, (k, n, dt) in projs.items():
-            other = "ffn_down" if name not in ("ffn_down", "ffn_up") else "ffn_gate"
-            partner = "ffn_up" if other != "ffn_up" else "ffn_gate"
+            ws = microbench.weight_copies(ctx, views[name].raw, dt, k, n, shard=plan.shard(name))
             for m in TOKEN_COUNTS:
-                both = graph_us([call(name, m), call(other, 1)] * 5)
-                alone = graph_us([call(partner, 1), call(other, 1)] * 5)
-                if name == partner:
-                    us = both / 10
-                else:
-                    us = (both - alone) / 5 + base[other] / 10 if False else max(both - alone / 2, 0.0) / 5
+                us = microbench.kquant_call_seconds(ctx, kern, ws, x_dev[(name, m)], y_dev[(name, m)], m) * 1e6
                 kl, nl = weights[name].n_in, weights[name].n_out
                 b = nl * ((kl + 255) // 256) * KQ_BYTES_PER_256[dt] + m * kl * 2 + m * nl * 4
                 detail[f"{name}_m{m}"] = {"us": round(us, 2), "gbs": round(b / max(us, 1e-3) / 1e3, 1)}
+            for w in ws:
+                w.free()
 
     # end to end through the host-slice entry point (weights::matmul signature): f32 host x in, f32 host y out
     e2e = None
@@ -370,7 +351,10 @@ def run_gpu(args):
                        "launch": "one CUDA graph replay per step" if graphed else "plain launches",
                        "parallelism": f"tp{world}" if world > 1 else "single"},
             "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
-                         "traffic": None, "peak_kind": f"of {peak_kind}",
+                         # DRAM bytes of one step's launches under ncu (dram__bytes_read.sum + dram__bytes_write.sum,
+                         # profiles/bench_launch_list_decode_gemv_layer.md): 1.007 x the algorithmic bytes, no re-reads
+                         "traffic": MEASURED_STEP_TRAFFIC_BYTES if world == 1 else None, "traffic_per": "step (28 launches)",
+                         "algorithmic_bytes_per_step": step_bytes(2), "peak_kind": f"of {peak_kind}",
                          "kernel": "kquant_gemv_kernel / kquant_matmul_kernel (the 28 launches of a step; achieved = all their bytes / all their time)"},
             "cpu_baseline": cpu,
             "e2e": e2e,
@@ -392,7 +376,7 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-lane baseline leg")

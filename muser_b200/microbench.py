@@ -37,6 +37,38 @@ def _time(fn, reps: int) -> float:
     return e0.elapsed_time(e1) * 1e-3 / reps
 
 
+def kquant_call_seconds(ctx, kern, ws, x, y, m: int, graph: bool = True, reps: int = 5) -> float:
+    """Device seconds of one K-quant projection call at `m` tokens: launches rotate over the weight copies `ws`
+    (together larger than L2, so every launch streams its weights from HBM) and are replayed as one CUDA graph."""
+    copies = len(ws)
+    launches = max(20, copies)
+
+    def run():
+        for i in range(launches):
+            kern.encode_quantized_matmul(ws[i % copies], x, y, m)
+
+    run()
+    torch.cuda.synchronize()
+    fn = run
+    if graph:
+        g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                run()
+        torch.cuda.synchronize()
+        fn = g.replay
+    return _time(fn, reps) / launches
+
+
+def weight_copies(ctx, raw, dt: int, k: int, n: int, shard=None):
+    """Enough repacked copies of one tensor to exceed L2 (126 MB) when launches rotate over them."""
+    copies = max(2, min(24, (300 << 20) // raw.numel() + 1))
+    return [op.Weight(ctx, op.TensorView(raw, dt, k, n), shard=shard) for _ in range(copies)]
+
+
 def run_kquant(args) -> None:
     ctx = op.Context(0)
     kern = op.CudaKernels(ctx)
@@ -44,30 +76,11 @@ def run_kquant(args) -> None:
     for name in args.proj:
         k, n, dt = synth.LAYER_PROJECTIONS[name]
         raw = synth.quantize_kquant(synth.normal_weights(n, k, device="cuda"), dt)
-        copies = max(2, min(24, (300 << 20) // raw.numel() + 1))
-        ws = [op.Weight(ctx, op.TensorView(raw, dt, k, n)) for _ in range(copies)]
+        ws = weight_copies(ctx, raw, dt, k, n)
         for m in args.tokens:
             x = synth.normal_activations(m, k, device="cuda")
             y = torch.empty((m, n), dtype=torch.float32, device="cuda")
-            launches = max(20, copies)
-
-            def run():
-                for i in range(launches):
-                    kern.encode_quantized_matmul(ws[i % copies], x, y, m)
-
-            run()
-            torch.cuda.synchronize()
-            fn = run
-            if not args.no_graph:
-                g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-                with torch.cuda.stream(side):
-                    run()
-                    torch.cuda.synchronize()
-                    with torch.cuda.graph(g, stream=side):
-                        run()
-                torch.cuda.synchronize()
-                fn = g.replay
-            sec = _time(fn, args.reps) / launches
+            sec = kquant_call_seconds(ctx, kern, ws, x, y, m, graph=not args.no_graph, reps=args.reps)
             nbytes = raw.numel() + m * k * 2 + m * n * 4
             rel = float("nan")
             if args.check:
