@@ -46,29 +46,45 @@ struct TcArgs {
     float *partial;         // [ksplit][tokens][n_out] partial sums (ksplit > 1)
     unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
     int *status;
-    uint32_t n_out, nsb, row_tiles, tokens, y_bf16, ksplit, items;
+    uint32_t n_out, nsb, row_tiles, tokens, y_bf16;
+    uint32_t whole, ksplit, items; // items 0..whole-1: one row block each, all of K; then the other row blocks in ksplit slices
 };
 
 // The (item, super-block column) sequence of one CTA; every role walks the same sequence.
 struct TcWalk {
-    uint32_t item, rb, slice, k, k_end;
+    uint32_t item, rb, slice, k, k_begin, len, idx;
+    bool split;
     __device__ __forceinline__ void load(const TcArgs &a) {
-        if (item < a.items) {
-            rb = item / a.ksplit;
-            slice = item % a.ksplit;
-            k = a.nsb * slice / a.ksplit;
+        if (item >= a.items) return;
+        uint32_t k_end;
+        if (item < a.whole) {
+            rb = item, slice = 0, k_begin = 0, k_end = a.nsb, split = false;
+        } else {
+            const uint32_t j = item - a.whole;
+            rb = a.whole + j / a.ksplit;
+            slice = j % a.ksplit;
+            k_begin = a.nsb * slice / a.ksplit;
             k_end = a.nsb * (slice + 1) / a.ksplit;
+            split = a.ksplit > 1;
         }
+        // CTAs that work on the same columns at the same time would all ask L2 for the same activation lines: each
+        // starts its sweep at another column (the order of the f32 sums differs per row block, but is fixed)
+        len = k_end - k_begin;
+        idx = 0;
+        k = k_begin + blockIdx.x % len;
     }
     __device__ __forceinline__ void start(const TcArgs &a) {
         item = blockIdx.x;
         load(a);
     }
     __device__ __forceinline__ bool done(const TcArgs &a) const { return item >= a.items; }
+    __device__ __forceinline__ bool last_column() const { return idx + 1 == len; }
     __device__ __forceinline__ void next(const TcArgs &a) {
-        if (++k == k_end) {
+        if (++idx == len) {
             item += gridDim.x;
             load(a);
+        } else if (++k == k_begin + len) {
+            k = k_begin;
         }
     }
 };
@@ -235,11 +251,13 @@ struct TcSmem {
     static constexpr int kOffMinB = kOffMinA + 2 * kMinA;
     static constexpr int kOffRing = kOffMinB + 2 * kMinB;
     static constexpr int kOffHdr = kOffRing + kTcDequantWarps * kRing * kSlot;
-    static constexpr int kOffBars = kOffHdr + 4 * kTcRows * 8;
-    static constexpr int kBars = 2 * kTcStages + 2 * kStagesB + 4 + kTcDequantWarps * kRing;
+    static constexpr int kHdrDepth = 8;              // (d, dmin) per row of the last eight super-block columns
+    static constexpr int kOffBars = kOffHdr + kHdrDepth * kTcRows * 8;
+    static constexpr int kBufs = N == 64 ? 2 : 4;    // accumulator buffers of 3N columns in tensor memory
+    static constexpr int kBars = 2 * kTcStages + 2 * kStagesB + 2 * kBufs + kTcDequantWarps * kRing;
     static constexpr int kBytes = kOffBars + kBars * 8 + 16 + 1024 /*alignment slack*/;
     static_assert(kBytes <= 227 * 1024, "shared memory of one CTA exceeded");
-    static constexpr uint32_t kTmemCols = N >= 64 ? 512 : (N >= 32 ? 256 : 128); // two buffers of 3N columns
+    static constexpr uint32_t kTmemCols = N >= 32 ? 512 : 256; // kBufs buffers of 3N columns, rounded up to a power of two
 };
 
 template <int DT, int N>
@@ -254,7 +272,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     constexpr int kRing = S::kRing, kStagesB = S::kStagesB;
     const uint32_t bar_full_a = smem_u32(bars), bar_empty_a = bar_full_a + 8 * kTcStages;
     const uint32_t bar_full_b = bar_empty_a + 8 * kTcStages, bar_empty_b = bar_full_b + 8 * kStagesB;
-    const uint32_t bar_tmem_full = bar_empty_b + 8 * kStagesB, bar_tmem_empty = bar_tmem_full + 16, bar_ring = bar_tmem_empty + 16;
+    constexpr int kBufs = S::kBufs;
+    const uint32_t bar_tmem_full = bar_empty_b + 8 * kStagesB, bar_tmem_empty = bar_tmem_full + 8 * kBufs, bar_ring = bar_tmem_empty + 8 * kBufs;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + S::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float2 *hdr = reinterpret_cast<float2 *>(aligned + S::kOffHdr);
@@ -269,7 +288,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             mbar_init(bar_full_b + 8 * s, 1);
             mbar_init(bar_empty_b + 8 * s, 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kBufs; ++b) {
             mbar_init(bar_tmem_full + 8 * b, 1);
             mbar_init(bar_tmem_empty + 8 * b, 4);
         }
@@ -327,9 +346,9 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             uint32_t hs = 0, tc = 0;
             bool ok = true;
             for (; !w.done(a) && ok; w.next(a), ++tc) {
-                const uint32_t buf = tc & 1, d_main = tmem + buf * 3 * N, d_min = d_main + 2 * N;
-                if (tc >= 2) { // the drain warps must have read this buffer's previous contents
-                    ok = mbar_wait(bar_tmem_empty + 8 * buf, ((tc >> 1) - 1) & 1, abort_flag);
+                const uint32_t buf = tc % kBufs, d_main = tmem + buf * 3 * N, d_min = d_main + 2 * N;
+                if (tc >= (uint32_t)kBufs) { // the drain warps must have read this buffer's previous contents
+                    ok = mbar_wait(bar_tmem_empty + 8 * buf, ((tc / kBufs) - 1) & 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
@@ -347,8 +366,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             mma_f16(d_main + (kk & 1) * N, da + 2 * kk, db + 2 * kk, idesc, (h | atom | (kk >> 1)) != 0);
                     }
                     if (Q4 && h == 1)
-                        mma_f16(d_min, operand_desc32(base + S::kOffMinA + buf * S::kMinA),
-                                operand_desc32(base + S::kOffMinB + buf * S::kMinB), idesc, 0);
+                        mma_f16(d_min, operand_desc32(base + S::kOffMinA + (tc & 1) * S::kMinA),
+                                operand_desc32(base + S::kOffMinB + (tc & 1) * S::kMinB), idesc, 0);
                     mma_commit(bar_empty_a + 8 * s); // stages (and the sum buffers) reusable once these MMAs have read them
                     mma_commit(bar_empty_b + 8 * s_b);
                 }
@@ -408,9 +427,9 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                h2u(byte_pair(mw, 0, 1024.0f)), h2u(byte_pair(mw, 1, 1024.0f)), h2u(byte_pair(mw, 2, 1024.0f)),
                                h2u(byte_pair(mw, 3, 1024.0f)));
                     }
-                    if (t == 2) hdr[(n & 3) * kTcRows + row] = make_float2(hd.d, hd.dmin);
+                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(hd.d, hd.dmin);
                 } else {
-                    if (t == 2) hdr[(n & 3) * kTcRows + row] = make_float2(cur.d, 0.0f);
+                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(cur.d, 0.0f);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic stores -> visible to the MMA's reads
@@ -451,8 +470,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         w.start(a);
         uint32_t tc = 0;
         while (!w.done(a)) {
-            const uint32_t buf = tc & 1;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_tmem_full + 8 * buf, (tc >> 1) & 1, abort_flag, 40));
+            const uint32_t buf = tc % kBufs;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_tmem_full + 8 * buf, (tc / kBufs) & 1, abort_flag, 40));
             if (!ok) {
                 if (lane == 0) {
                     *abort_flag = 1;
@@ -461,7 +480,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float2 hd = hdr[(tc & 3) * kTcRows + row_in_block];
+            const float2 hd = hdr[(tc % S::kHdrDepth) * kTcRows + row_in_block];
             const uint32_t taddr = tmem + ((quad * 32) << 16) + buf * 3 * N;
 #pragma unroll
             for (int c0 = 0; c0 < N; c0 += 16) {
@@ -479,8 +498,9 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
-            const bool last = w.k + 1 == w.k_end;
+            const bool last = w.last_column();
             const uint32_t rb = w.rb, slice = w.slice;
+            const bool split = w.split;
             w.next(a);
             ++tc;
             if (!last) continue;
@@ -489,20 +509,21 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const uint32_t row = rb * kTcRows + row_in_block;
             const bool live = row < a.n_out;
             bool finish = true;
-            if (a.ksplit > 1) {
+            if (split) {
                 if (live)
 #pragma unroll
                     for (int i = 0; i < N; ++i)
                         if ((uint32_t)i < a.tokens) a.partial[((size_t)slice * a.tokens + i) * a.n_out + row] = acc[i];
-                __threadfence();
+                // Release / acquire through the counter: the warp barrier orders every lane's stores before lane 0's
+                // releasing add, and lane 0's acquire (handed on by the shuffle) before every lane's loads below.
                 __syncwarp();
                 unsigned int seen = 0;
-                if (lane == 0) seen = atomicAdd(a.counters + rb * 4 + quad, 1u);
+                if (lane == 0)
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.counters + rb * 4 + quad) : "memory");
                 seen = __shfl_sync(0xffffffffu, seen, 0);
                 finish = seen == a.ksplit - 1;
                 if (finish) {
                     if (lane == 0) a.counters[rb * 4 + quad] = 0; // ready for the next launch
-                    __threadfence();
                     // slices in order (deterministic); sixteen independent loads in flight per step, not one
 #pragma unroll
                     for (int c0 = 0; c0 < N; c0 += 16) {
@@ -646,16 +667,23 @@ muser_cuda_status launch_f16_mma_probe(Ctx *ctx, uint32_t n_cols, uint32_t iters
 }
 
 // ------------------------------------------------------------------------------------------ host side
-// K slices: as many items as keep every SM busy to the end, with as few slices as that needs.
-static uint32_t tc_plan_split(uint32_t nsb, uint32_t row_blocks, int sm_count, uint32_t max_split) {
-    uint32_t best = 1;
+// Items: as many whole row blocks as fill complete rounds over the SMs run unsplit (no exchange at their end); the
+// remaining row blocks are cut into K slices so that the last round keeps the SMs busy too.  An exchange costs about
+// as much as four super-block columns.
+struct TcPlan {
+    uint32_t whole, ksplit;
+};
+static TcPlan tc_plan(uint32_t nsb, uint32_t row_blocks, int sm_count, uint32_t max_split) {
+    TcPlan p{row_blocks / sm_count * sm_count, 1};
+    const uint32_t tail = row_blocks - p.whole;
+    if (tail == 0) return p;
     double best_cost = 1e300;
     for (uint32_t ks = 1; ks <= max_split && ks <= nsb && ks <= 32; ++ks) {
-        const double rounds = std::ceil((double)row_blocks * ks / sm_count);
-        const double cost = rounds * (std::ceil((double)nsb / ks) + 1.5) + (ks > 1 ? 1.0 : 0.0);
-        if (cost < best_cost * (1.0 - 1e-9)) best_cost = cost, best = ks;
+        const double rounds = std::ceil((double)tail * ks / sm_count);
+        const double cost = rounds * (std::ceil((double)nsb / ks) + (ks > 1 ? 4.0 : 0.0));
+        if (cost < best_cost * (1.0 - 1e-9)) best_cost = cost, p.ksplit = ks;
     }
-    return best;
+    return p;
 }
 
 template <int DT, int N>
@@ -710,8 +738,10 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     const size_t slice_bytes = (size_t)tokens * w->n_out * sizeof(float);
     uint32_t max_split = (uint32_t)std::max<size_t>(1, ctx->gemv_partial_bytes / std::max<size_t>(1, slice_bytes));
     if ((size_t)row_blocks * 4 > ctx->gemv_counter_slots) max_split = 1;
-    a.ksplit = tc_plan_split(w->nsb, row_blocks, ctx->sm_count, max_split);
-    a.items = row_blocks * a.ksplit;
+    const TcPlan plan = tc_plan(w->nsb, row_blocks, ctx->sm_count, max_split);
+    a.whole = plan.whole;
+    a.ksplit = plan.ksplit;
+    a.items = plan.whole + (row_blocks - plan.whole) * plan.ksplit;
     const int grid = (int)std::min<uint32_t>(a.items, (uint32_t)ctx->sm_count);
     if (w->dtype == MUSER_DTYPE_Q4_K)
         return n == 16 ? tc_launch<MUSER_DTYPE_Q4_K, 16>(mx, mxs, a, grid, stream)
