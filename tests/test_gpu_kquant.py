@@ -240,6 +240,33 @@ def test_config1_full_size_q4k_gemv(gpu):
     assert H.rel_l2(lin.cpu().numpy(), y_exact[0].cpu().numpy()) <= 1e-4
 
 
+@pytest.mark.parametrize("name", ["ffn_gate", "ffn_down"])
+def test_layer_shapes_every_kernel_sampled_rows_and_determinism(gpu, name):
+    """The layer's two big projections at full size, one token count per kernel and split-K regime (decode kernel,
+    legacy skinny kernel, tcgen05 kernel at 16 / 32 / 64 columns): 96 sampled output rows against the CPU lane, and
+    bit-identical results when the same call runs twice (the K slices are summed in a fixed order)."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_in, n_out, dtype = synth.LAYER_PROJECTIONS[name]
+    raw = synth.quantize_kquant(synth.normal_weights(n_out, n_in, seed=0, stream=11, device="cuda"), dtype)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    rows = np.sort(np.random.default_rng(5).choice(n_out, 96, replace=False))
+    sub = raw.cpu().numpy().reshape(n_out, -1)[rows].copy()
+    ow = O.TensorView(sub, dtype, n_in, len(rows))
+    for tokens in (1, 2, 4, 8, 12, 24, 64):
+        x = synth.normal_activations(tokens, n_in, seed=tokens, device="cuda")
+        y1 = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        y2 = torch.full_like(y1, float("nan"))
+        k.encode_quantized_matmul(w, x, y1, tokens)
+        k.encode_quantized_matmul(w, x, y2, tokens)
+        ctx.sync_status()
+        assert torch.equal(y1, y2), (name, tokens)
+        ref = O.matmul(ow, x.float().cpu().numpy(), threads=O.host_threads())
+        err = H.rel_l2(y1[:, torch.from_numpy(rows).cuda()].cpu().numpy(), ref)
+        assert err <= REL_L2_TOL, (name, tokens, err)
+    w.free()
+
+
 def test_misuse_returns_statuses(gpu):
     op, ctx, k = gpu
     raw = H.lcg_weights(O.Q4_K, 16, 1, seed=1)
