@@ -85,6 +85,9 @@ typedef struct muser_cuda_epilogue {
                                * (x * 1/sqrt(mean(x^2) + norm_eps)) * norm_weight instead of x (rms_norm_mul,
                                * reference.rs:73-80), computed inside the kernel that stages or quantizes x.  Not
                                * available on K-sharded weights (a shard sees only part of the row). */
+    float out_scale;          /* LM-head tail (src/reference.rs:559-570): every output is multiplied by out_scale
+                               * (0 is read as 1, so a zeroed struct changes nothing) ... */
+    float softcap;            /* ... and, when softcap > 0, becomes softcap * tanh(y / softcap); both before the residual */
 } muser_cuda_epilogue;
 
 typedef struct muser_cuda_weight_info {
@@ -156,6 +159,13 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_dequant(muser_cuda_ctx *ctx, const m
 MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
                                               uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                               const muser_cuda_epilogue *epilogue, void *stream);
+
+/* weights::matmul_rows (src/weights.rs:425-449): the projection restricted to a list of output rows, as the
+ * reference scores selected LM-head rows.  rows: n_rows row indices on the device (an index >= n_out yields NaN);
+ * y: f32 [tokens][n_rows].  K-quant weights, any token count. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx *ctx, const muser_cuda_weight *w,
+                                                   const uint32_t *rows, uint32_t n_rows, const void *x, uint32_t x_dtype,
+                                                   float *y, uint32_t tokens, void *stream);
 
 /* MetalKernels::encode_ffn_q4k_gate_up_silu_4r2s (src/metal/encode/ffn.rs:10-19) and the CPU lane's
  * silu_fast(gate) * up (src/reference.rs:511-513, quant/helpers.rs:72):

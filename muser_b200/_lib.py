@@ -24,7 +24,7 @@ EXPORTS = [
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
     "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
-    "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe",
+    "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
 ]
 
 
@@ -34,7 +34,7 @@ class Shard(C.Structure):
 
 class Epilogue(C.Structure):
     _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("norm_eps", C.c_float),
-                ("norm_weight", C.c_void_p)]
+                ("norm_weight", C.c_void_p), ("out_scale", C.c_float), ("softcap", C.c_float)]
 
 
 class WeightInfo(C.Structure):
@@ -84,6 +84,7 @@ def _load() -> C.CDLL:
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
         "muser_cuda_tuning_set": (i32, [vp, u32, u32]),
+        "muser_cuda_quantized_matmul_rows": (i32, [vp, vp, vp, u32, vp, u32, vp, u32, vp]),
         "muser_cuda_f16_mma_probe": (i32, [vp, u32, u32, C.POINTER(C.c_double)]),
         "muser_cuda_rmsnorm_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, vp, f32, f32, vp, vp, vp]),
     }

@@ -144,6 +144,9 @@ static muser_cuda_status take_epilogue(Ctx *ctx, const Weight *w, const muser_cu
     if (!ep) return MUSER_CUDA_OK;
     e->row_scale = ep->row_scale;
     e->residual = ep->residual;
+    if (!(ep->out_scale == ep->out_scale) || !(ep->softcap >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "out_scale / softcap must be numbers, softcap non-negative");
+    e->out_scale = ep->out_scale == 0.0f ? 1.0f : ep->out_scale;
+    e->softcap = ep->softcap;
     if (ep->norm_weight) {
         if (w->shard.axis == MUSER_SHARD_K && w->shard.world > 1)
             return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused input norm needs whole input rows; this weight is a K shard");
@@ -345,6 +348,19 @@ muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *c, const muser_cud
     if (st != MUSER_CUDA_OK) return st;
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_kquant_matmul(ctx, w, nullptr, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx *c, const muser_cuda_weight *wp, const uint32_t *rows,
+                                                   uint32_t n_rows, const void *x, uint32_t x_dtype, float *y,
+                                                   uint32_t tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    muser_cuda_status st = check_io(ctx, w, x, x_dtype, y, MUSER_DTYPE_F32, tokens, false);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!rows || n_rows == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "empty row list");
+    if (!is_kquant(w->dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "matmul_rows takes K-quant weights");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_kquant_rows(ctx, w, rows, n_rows, x, x_dtype, y, tokens, (cudaStream_t)stream);
 }
 
 // The NVFP4 side of the fused gate/up call: both weights must quantize their input alike, because one set of

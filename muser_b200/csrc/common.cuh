@@ -117,12 +117,24 @@ struct Epilogue {
     const void *residual = nullptr;
     const float *norm_weight = nullptr; // fused input RMSNorm: x <- (x / rms(x)) * norm_weight before the projection
     float norm_eps = 0.0f;
+    float out_scale = 1.0f;             // LM-head tail (reference.rs:559-570): y <- y * out_scale,
+    float softcap = 0.0f;               // then, if > 0, y <- softcap * tanh(y / softcap)
 };
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float logit_tail(float v, float out_scale, float softcap) {
+    v *= out_scale;
+    if (softcap > 0.0f) v = softcap * tanhf(v * __fdiv_rn(1.0f, softcap));
+    return v;
+}
+#endif
 
 muser_cuda_status launch_repack_kquant(Ctx *, Weight *, const uint8_t *dev_blocks, cudaStream_t);
 muser_cuda_status launch_repack_nvfp4(Ctx *, Weight *, const uint8_t *dev_packed, const uint8_t *dev_scales,
                                       cudaStream_t);
 muser_cuda_status launch_dequant(Ctx *, const Weight *, float *out, cudaStream_t);
+muser_cuda_status launch_kquant_rows(Ctx *, const Weight *w, const uint32_t *rows, uint32_t n_rows, const void *x,
+                                     uint32_t x_dtype, float *out, uint32_t tokens, cudaStream_t);
 muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
                                        void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &,
                                        cudaStream_t);

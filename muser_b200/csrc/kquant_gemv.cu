@@ -38,6 +38,7 @@ struct GemvArgs {
     const __nv_bfloat16 *x;
     void *y;
     const float *row_scale;
+    float out_scale, softcap; // LM-head tail
     const void *residual;
     const float *norm_weight; // fused input RMSNorm (reference.rs:73-80), or null
     float norm_eps;
@@ -540,6 +541,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_g
                 if constexpr (DUAL) r = __fdiv_rn(r, 1.0f + expf(-r)) * out[1][gp][c]; // silu_fast(gate) * up, quant/helpers.rs:72
                 const size_t o = (size_t)tok * a.n_out + row;
                 if (a.row_scale) r *= a.row_scale[tok];
+                r = logit_tail(r, a.out_scale, a.softcap);
                 if (a.y_bf16) {
                     if (a.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.residual)[o]);
                     reinterpret_cast<__nv_bfloat16 *>(a.y)[o] = __float2bfloat16_rn(r);
@@ -651,6 +653,8 @@ cudaError_t launch_kquant_gemv(Ctx *ctx, const Weight *w, const Weight *w_up, co
     a.x = reinterpret_cast<const __nv_bfloat16 *>(x);
     a.y = y;
     a.row_scale = ep.row_scale;
+    a.out_scale = ep.out_scale;
+    a.softcap = ep.softcap;
     a.residual = ep.residual;
     a.norm_weight = ep.norm_weight;
     a.norm_eps = ep.norm_eps;

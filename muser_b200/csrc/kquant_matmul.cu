@@ -31,6 +31,7 @@ struct KqArgs {
     const void *x;
     void *y;
     const float *row_scale;
+    float out_scale, softcap; // LM-head tail
     const void *residual;
     uint32_t n_out, n_in, nsb, k_off, tokens, y_bf16, row_tiles;
 };
@@ -420,6 +421,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) kquant_matmul_kernel(const KqA
                     if (row < a.n_out && tok < a.tokens) {
                         const size_t o = (size_t)tok * a.n_out + row;
                         if (a.row_scale) r *= a.row_scale[tok];
+                        r = logit_tail(r, a.out_scale, a.softcap);
                         if (a.y_bf16) {
                             if (a.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.residual)[o]);
                             reinterpret_cast<__nv_bfloat16 *>(a.y)[o] = __float2bfloat16_rn(r);
@@ -505,6 +507,8 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     a.x = x;
     a.y = y;
     a.row_scale = ep.row_scale;
+    a.out_scale = ep.out_scale;
+    a.softcap = ep.softcap;
     a.residual = ep.residual;
     a.n_out = (uint32_t)w->n_out;
     a.n_in = (uint32_t)w->n_in;

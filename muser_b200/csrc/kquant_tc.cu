@@ -42,6 +42,7 @@ struct TcArgs {
     const uint8_t *image;
     void *y;
     const float *row_scale;
+    float out_scale, softcap; // LM-head tail
     const void *residual;
     float *partial;         // [ksplit][tokens][n_out] partial sums (ksplit > 1)
     unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
@@ -552,6 +553,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     float r = acc[i];
                     const size_t o = (size_t)i * a.n_out + row;
                     if (a.row_scale) r *= a.row_scale[i];
+                    r = logit_tail(r, a.out_scale, a.softcap);
                     if (a.y_bf16) {
                         if (a.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.residual)[o]);
                         reinterpret_cast<__nv_bfloat16 *>(a.y)[o] = __float2bfloat16_rn(r);
@@ -725,6 +727,8 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     a.image = w->image;
     a.y = y;
     a.row_scale = ep.row_scale;
+    a.out_scale = ep.out_scale;
+    a.softcap = ep.softcap;
     a.residual = ep.residual;
     a.partial = ctx->gemv_partial;
     a.counters = ctx->gemv_counters;

@@ -39,6 +39,7 @@ struct GemmArgs {
     const uint8_t *b2_scales; // second weight (up projection) of the fused gate/up form, else null
     void *y;
     const float *row_scale;
+    float out_scale, softcap; // LM-head tail
     const void *residual;
     int *status;
     uint32_t tokens, n_out, k_tiles, kt64; // kt64: 64-value blocks per row (one MMA and one scale chunk each)
@@ -296,7 +297,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 __fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
                             v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up; // silu_fast, quant/helpers.rs:72
                         }
-                        v[i] *= rs;
+                        v[i] = logit_tail(v[i] * rs, g.out_scale, g.softcap);
                     }
                     if (g.y_dtype == MUSER_DTYPE_F32)
                         store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
@@ -455,6 +456,8 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.b2_scales = w_up ? w_up->scales : nullptr;
     g.y = y;
     g.row_scale = ep.row_scale;
+    g.out_scale = ep.out_scale;
+    g.softcap = ep.softcap;
     g.residual = ep.residual;
     g.status = ctx->dev_status;
     g.tokens = tokens;

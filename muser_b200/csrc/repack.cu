@@ -219,14 +219,10 @@ muser_cuda_status launch_repack_nvfp4(Ctx *ctx, Weight *w, const uint8_t *dev_pa
 }
 
 // ------------------------------------------------------------------------------ image -> f32
-// One thread per output element; reads the repacked image only.
-__global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
-    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
-    if (idx >= gm.n_out * gm.n_in) return;
-    uint32_t row = (uint32_t)(idx / gm.n_in);
-    uint64_t kk = idx % gm.n_in + gm.k_off; // position in the tile grid
+// One weight out of the repacked image: row `row`, position `kk` in the tile grid (input index + k_off).
+__device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
-    const uint8_t *tile = image + ((uint64_t)(row / 16) * gm.nsb + sb) * kQ4TileBytes;
+    const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ4TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t j = e >> 5, wi = (e >> 3) & 3, i = e & 7;
     uint32_t q = rowsel * 2 + (j >> 2), lane = g * 4 + (j & 3);
@@ -245,16 +241,12 @@ __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__r
         mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
     }
     float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
-    out[idx] = __fsub_rn(__fmul_rn(d1, (float)nib), m1); // k_block.rs:40-41
+    return __fsub_rn(__fmul_rn(d1, (float)nib), m1); // k_block.rs:40-41
 }
 
-__global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
-    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
-    if (idx >= gm.n_out * gm.n_in) return;
-    uint32_t row = (uint32_t)(idx / gm.n_in);
-    uint64_t kk = idx % gm.n_in + gm.k_off;
+__device__ __forceinline__ float q6k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
-    const uint8_t *tile = image + ((uint64_t)(row / 16) * gm.nsb + sb) * kQ6TileBytes;
+    const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ6TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t s = e >> 4, el = e & 15, o = s >> 2, lane = g * 4 + (s & 3);
     uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (o >> 1)) * 32 + lane) * 4 + (o & 1) * 2 + (el >> 3)];
@@ -264,7 +256,69 @@ __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__r
     int qv = (int)(lo | (hi2 << 4)) - 32;
     float d = __half2float(reinterpret_cast<const __half *>(tile + kQ6OffD)[r]);
     int sc = reinterpret_cast<const int8_t *>(tile + kQ6OffSc)[r * 16 + s];
-    out[idx] = __fmul_rn(__fmul_rn(d, (float)sc), (float)qv); // q6.rs:305-313
+    return __fmul_rn(__fmul_rn(d, (float)sc), (float)qv); // q6.rs:305-313
+}
+
+// One thread per output element; reads the repacked image only.
+__global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
+    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (idx >= gm.n_out * gm.n_in) return;
+    out[idx] = q4k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+}
+
+__global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
+    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (idx >= gm.n_out * gm.n_in) return;
+    out[idx] = q6k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+}
+
+// ------------------------------------------------------------------------------ selected rows
+// weights::matmul_rows (src/weights.rs:425-449): out[t][i] = dot(W_rows[i], x_t) for a list of output rows, the way
+// the reference scores a handful of LM-head rows.  One warp per listed row; lanes stride over the inputs, decode
+// each weight from the image and keep up to eight token sums; a butterfly adds the lanes (fixed order).
+template <bool Q4, bool XF32>
+__global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restrict__ image, KqGeom gm, const uint32_t *__restrict__ rows,
+                                                          uint32_t n_rows, const void *__restrict__ x, uint32_t tokens,
+                                                          float *__restrict__ out) {
+    const uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (i >= n_rows) return;
+    const uint32_t row = rows[i];
+    for (uint32_t t0 = 0; t0 < tokens; t0 += 8) {
+        const uint32_t nt = min(8u, tokens - t0);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (row < gm.n_out) {
+            for (uint64_t k = lane; k < gm.n_in; k += 32) {
+                const float w = Q4 ? q4k_weight(image, gm.nsb, row, k + gm.k_off) : q6k_weight(image, gm.nsb, row, k + gm.k_off);
+#pragma unroll
+                for (uint32_t t = 0; t < 8; ++t)
+                    if (t < nt) {
+                        const size_t xi = (size_t)(t0 + t) * gm.n_in + k;
+                        const float xv = XF32 ? reinterpret_cast<const float *>(x)[xi]
+                                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(x)[xi]);
+                        acc[t] = fmaf(w, xv, acc[t]);
+                    }
+            }
+        }
+#pragma unroll
+        for (uint32_t t = 0; t < 8; ++t) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+            if (lane == 0 && t < nt) out[(size_t)(t0 + t) * n_rows + i] = row < gm.n_out ? acc[t] : __int_as_float(0x7fc00000);
+        }
+    }
+}
+
+muser_cuda_status launch_kquant_rows(Ctx *ctx, const Weight *w, const uint32_t *rows, uint32_t n_rows, const void *x,
+                                     uint32_t x_dtype, float *out, uint32_t tokens, cudaStream_t stream) {
+    const unsigned blocks = (n_rows + 7) / 8;
+    const KqGeom gm = kq_geom(*w);
+    const bool q4 = w->dtype == MUSER_DTYPE_Q4_K, xf32 = x_dtype == MUSER_DTYPE_F32;
+    if (q4 && xf32) kquant_rows_kernel<true, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else if (q4) kquant_rows_kernel<true, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else if (xf32) kquant_rows_kernel<false, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else kquant_rows_kernel<false, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
 }
 
 __device__ __forceinline__ float e4m3_magnitude(uint32_t code) { // quant/nvfp4.rs:108-120, sign handled at repack

@@ -155,15 +155,16 @@ def _row_bytes(dtype: int, n_in: int) -> int:
     raise MuserCudaError(4, f"dtype {dtype} has no CUDA projection kernel")
 
 
-def _epilogue(row_scale=None, residual=None, norm_weight=None, norm_eps=0.0):
-    """muser_cuda_epilogue; `norm_weight` (f32 [n_in], device) fuses rms_norm_mul(x, eps, norm_weight) in front."""
-    if row_scale is None and residual is None and norm_weight is None:
+def _epilogue(row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0, softcap=0.0):
+    """muser_cuda_epilogue; `norm_weight` (f32 [n_in], device) fuses rms_norm_mul(x, eps, norm_weight) in front,
+    `out_scale` / `softcap` the LM-head tail y <- softcap * tanh(y * out_scale / softcap) behind."""
+    if row_scale is None and residual is None and norm_weight is None and out_scale == 1.0 and softcap == 0.0:
         return None
     if norm_weight is not None and norm_weight.dtype != torch.float32:
         raise MuserCudaError(1, "norm_weight must be f32")
     return _lib.Epilogue(row_scale.data_ptr() if row_scale is not None else None,
                          residual.data_ptr() if residual is not None else None, 0, float(norm_eps),
-                         norm_weight.data_ptr() if norm_weight is not None else None)
+                         norm_weight.data_ptr() if norm_weight is not None else None, float(out_scale), float(softcap))
 
 
 class CudaKernels:
@@ -184,12 +185,21 @@ class CudaKernels:
         return out
 
     def encode_quantized_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, tokens: int,
-                                row_scale=None, residual=None, norm_weight=None, norm_eps=0.0) -> None:
+                                row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0,
+                                softcap=0.0) -> None:
         """y[t][r] = dot(W_r, x_t) for K-quant weights; input [tokens][n_in] f32|bf16, output [tokens][n_out] f32|bf16."""
-        ep = _epilogue(row_scale, residual, norm_weight, norm_eps)
+        ep = _epilogue(row_scale, residual, norm_weight, norm_eps, out_scale, softcap)
         self.ctx.check(_L.muser_cuda_quantized_matmul(
             self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
             _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+    def encode_quantized_matmul_rows(self, weights: Weight, rows: torch.Tensor, input: torch.Tensor, output: torch.Tensor,
+                                     tokens: int) -> None:
+        """weights::matmul_rows: output[t][i] = dot(W_rows[i], x_t); rows int32/uint32 on the device, output f32."""
+        self.ctx.check(_L.muser_cuda_quantized_matmul_rows(
+            self.ctx._h, weights._h, rows.data_ptr(), rows.numel(), input.data_ptr(), _TORCH_DTYPE[input.dtype],
+            output.data_ptr(), tokens, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
     def encode_ffn_gate_up_silu(self, gate_w: Weight, up_w: Weight, input: torch.Tensor, output: torch.Tensor,
@@ -231,9 +241,10 @@ class CudaKernels:
         return packed, scales
 
     def encode_nvfp4_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, columns: int,
-                            row_scale=None, residual=None, norm_weight=None, norm_eps=0.0) -> None:
+                            row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0,
+                            softcap=0.0) -> None:
         """W4A4 lane: quantizes `input` with the weight's input_scale_inv, then the block-scaled GEMM."""
-        ep = _epilogue(row_scale, residual, norm_weight, norm_eps)
+        ep = _epilogue(row_scale, residual, norm_weight, norm_eps, out_scale, softcap)
         self.ctx.check(_L.muser_cuda_nvfp4_matmul(
             self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
             _TORCH_DTYPE[output.dtype], columns, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))

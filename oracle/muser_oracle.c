@@ -774,6 +774,35 @@ ORACLE_API void oracle_rms_norm_mul(float *x, size_t rows, size_t dim, float eps
     }
 }
 
+/* reference.rs:559-570: logits *= logit_scale; then, if the cap is positive, cap * tanh(logit / cap) */
+ORACLE_API void oracle_logit_tail(float *logits, size_t n, float logit_scale, float softcap) {
+    for (size_t i = 0; i < n; ++i) logits[i] *= logit_scale;
+    if (softcap > 0.0f) {
+        float inv = 1.0f / softcap;
+        for (size_t i = 0; i < n; ++i) logits[i] = softcap * tanhf(logits[i] * inv);
+    }
+}
+
+/* weights.rs:425-449 matmul_rows: the same dot_row as matmul, over the listed rows only; out is [n_tokens][n_rows] */
+ORACLE_API int oracle_matmul_rows(const oracle_tensor_view *w, const float *x, size_t n_tokens, const size_t *rows,
+                                  size_t n_rows, float *out) {
+    size_t rb = oracle_row_bytes(w->dtype, w->n_in);
+    for (size_t i = 0; i < n_rows; ++i) {
+        if (rows[i] >= w->n_out) return 1;
+        oracle_tensor_view one = *w;
+        one.raw = w->raw + rows[i] * rb;
+        one.n_out = 1;
+        if (w->block_scales) one.block_scales = w->block_scales + rows[i] * (w->n_in / 16);
+        for (size_t t = 0; t < n_tokens; ++t) {
+            float v;
+            int rc = oracle_matmul(&one, x + t * w->n_in, 1, &v, NULL, 1, 1);
+            if (rc) return rc;
+            out[t * n_rows + i] = v;
+        }
+    }
+    return 0;
+}
+
 /* reference.rs:511-513: silu_fast(gate) * up */
 ORACLE_API void oracle_silu_mul(const float *gate, const float *up, float *out, size_t n) {
     for (size_t i = 0; i < n; ++i) out[i] = oracle_silu_fast(gate[i]) * up[i];

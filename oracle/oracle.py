@@ -102,6 +102,10 @@ def lib() -> C.CDLL:
         L.oracle_rms_norm_mul.argtypes = [f32p, C.c_size_t, C.c_size_t, C.c_float, f32p]
         L.oracle_silu_mul.restype = None
         L.oracle_silu_mul.argtypes = [f32p, f32p, f32p, C.c_size_t]
+        L.oracle_logit_tail.restype = None
+        L.oracle_logit_tail.argtypes = [f32p, C.c_size_t, C.c_float, C.c_float]
+        L.oracle_matmul_rows.restype = C.c_int
+        L.oracle_matmul_rows.argtypes = [C.POINTER(_TensorView), f32p, C.c_size_t, C.c_void_p, C.c_size_t, f32p]
     return _lib
 
 
@@ -291,6 +295,24 @@ def rms_norm_mul(x, eps: float, w=None) -> np.ndarray:
     wv = None if w is None else _f32(w)
     lib().oracle_rms_norm_mul(_p(x), rows, dim, eps, 0 if wv is None else _p(wv))
     return x
+
+
+def logit_tail(logits, logit_scale: float, softcap: float) -> np.ndarray:
+    """reference.rs:559-570: logits * logit_scale, then softcap * tanh(. / softcap) when softcap > 0."""
+    out = _f32(logits).copy()
+    lib().oracle_logit_tail(_p(out), out.size, logit_scale, softcap)
+    return out
+
+
+def matmul_rows(w: "TensorView", x, rows) -> np.ndarray:
+    """weights.rs `matmul_rows`: out [T][len(rows)]."""
+    x = _f32(x).reshape(-1, w.n_in)
+    idx = np.ascontiguousarray(rows, dtype=np.uint64)
+    out = np.empty((x.shape[0], idx.size), dtype=np.float32)
+    v = w._c()
+    if lib().oracle_matmul_rows(C.byref(v), _p(x), x.shape[0], idx.ctypes.data, idx.size, _p(out)) != 0:
+        raise ValueError("oracle_matmul_rows rejected a row index, the shapes or the dtype")
+    return out
 
 
 def silu_mul(gate, up) -> np.ndarray:

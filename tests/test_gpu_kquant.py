@@ -267,6 +267,43 @@ def test_layer_shapes_every_kernel_sampled_rows_and_determinism(gpu, name):
     w.free()
 
 
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_lm_head_tail_and_selected_rows(gpu, dtype):
+    """The LM-head end of the path (reference.rs:559-570, weights.rs:425-449): logit scale and tanh soft cap fused
+    behind the projection in every K-quant kernel, and the projection restricted to a list of rows."""
+    op, ctx, k = gpu
+    n_in, n_out, scale, cap = 1024, 300, 0.0625, 30.0
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=55)
+    ow = O.TensorView(raw, dtype, n_in, n_out)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1)
+    try:
+        for tokens in (1, 3, 7, 20):  # decode kernel, legacy skinny kernel, tcgen05 kernel
+            x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=tokens).reshape(tokens, n_in) * 40.0).to(torch.bfloat16)
+            want = O.logit_tail(O.matmul(ow, x.float().numpy()), scale, cap)
+            assert np.abs(want).max() > 0.5 * cap  # the cap is actually exercised
+            y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+            k.encode_quantized_matmul(w, x.cuda(), y, tokens, out_scale=scale, softcap=cap)
+            assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, tokens
+            k.encode_quantized_matmul(w, x.cuda(), y, tokens, out_scale=scale)
+            assert H.rel_l2(y.cpu().numpy(), O.logit_tail(O.matmul(ow, x.float().numpy()), scale, 0.0)) <= REL_L2_TOL
+    finally:
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+    rows = np.array([299, 0, 17, 17, 128, 255, 16], dtype=np.int32)
+    for x_dtype in (torch.bfloat16, torch.float32):
+        x = torch.from_numpy(H.lcg_activations(11 * n_in, seed=9).reshape(11, n_in)).to(x_dtype)
+        y = torch.full((11, len(rows)), float("nan"), dtype=torch.float32, device="cuda")
+        k.encode_quantized_matmul_rows(w, torch.from_numpy(rows).cuda(), x.cuda(), y, 11)
+        want = O.matmul_rows(ow, x.float().numpy(), rows)
+        assert np.array_equal(want, O.matmul(ow, x.float().numpy())[:, rows])
+        assert H.rel_l2(y.cpu().numpy(), want) <= 1e-5, x_dtype
+    bad = torch.tensor([5, n_out], dtype=torch.int32, device="cuda")  # an index past the last row reads nothing
+    y = torch.zeros((1, 2), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul_rows(w, bad, torch.ones((1, n_in), dtype=torch.float32, device="cuda"), y, 1)
+    assert torch.isfinite(y[0, 0]) and torch.isnan(y[0, 1])
+    ctx.sync_status()
+
+
 def test_misuse_returns_statuses(gpu):
     op, ctx, k = gpu
     raw = H.lcg_weights(O.Q4_K, 16, 1, seed=1)

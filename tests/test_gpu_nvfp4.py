@@ -131,6 +131,11 @@ def test_w4a4_gemm_matches_cpu_lane(gpu, n_out, n_in, tokens):
     ctx.sync_status()
     want = ref_f32 * rs.cpu().numpy()[:, None] + res.cpu().numpy()
     assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
+    # LM-head tail (reference.rs:559-570) behind the GEMM
+    big = float(1.0 / np.abs(ref_f32).max()) * 60.0
+    k.encode_nvfp4_matmul(w, x.cuda(), y, tokens, out_scale=big, softcap=30.0)
+    ctx.sync_status()
+    assert H.rel_l2(y.cpu().numpy(), O.logit_tail(ref_f32, big, 30.0)) <= REL_L2_TOL
 
 
 @pytest.mark.parametrize("n_out,n_in,tokens", [(128, 256, 128), (200, 320, 9), (700, 1024, 260)])

@@ -106,3 +106,22 @@ def test_rms_norm_and_silu_follow_reference_formulas():
     u = np.asarray([2.0, 0.5], dtype=np.float32)
     got = O.silu_mul(g, u)
     assert np.allclose(got, g / (1 + np.exp(-g)) * u, rtol=1e-6)
+
+
+def test_matmul_rows_and_logit_tail_follow_the_reference():
+    """weights.rs:425-449 (`matmul_rows` is `matmul` over the listed rows, same dot_row) and reference.rs:559-570."""
+    rng = np.random.default_rng(3)
+    for dtype in (O.Q4_K, O.Q6_K):
+        raw = H.lcg_weights(dtype, 21, 2, seed=5 + dtype)
+        w = O.TensorView(raw, dtype, 512, 21)
+        x = rng.standard_normal((3, 512)).astype(np.float32)
+        rows = [20, 0, 7, 7]
+        assert np.array_equal(O.matmul_rows(w, x, rows), O.matmul(w, x)[:, rows])
+        with pytest.raises(ValueError):
+            O.matmul_rows(w, x, [21])
+    logits = np.array([0.0, 1.0, -2.5, 90.0, -1e4], dtype=np.float32)
+    scaled = O.logit_tail(logits, 0.5, 0.0)
+    assert np.array_equal(scaled, logits * np.float32(0.5))
+    capped = O.logit_tail(logits, 0.5, 30.0)
+    want = 30.0 * np.tanh(logits.astype(np.float64) * 0.5 / 30.0)
+    assert np.allclose(capped, want, rtol=1e-6, atol=1e-6) and np.all(np.abs(capped) <= 30.0)
