@@ -140,8 +140,8 @@ muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_u
                                        cudaStream_t);
 cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
                              uint32_t tokens, const Epilogue &, cudaStream_t);
-cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, void *y, uint32_t y_dtype,
-                               uint32_t tokens, const Epilogue &, cudaStream_t);
+cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype, void *y,
+                               uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
                                         float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t,
                                         const float *norm_weight = nullptr, float norm_eps = 0.0f);

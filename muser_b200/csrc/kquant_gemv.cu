@@ -35,7 +35,7 @@ namespace muser {
 struct GemvArgs {
     const uint8_t *image;
     const uint8_t *image_up; // second weight of the fused gate/up call, else null
-    const __nv_bfloat16 *x;
+    const void *x;           // [tokens][n_in], bf16 or (x_f32) f32
     void *y;
     const float *row_scale;
     float out_scale, softcap; // LM-head tail
@@ -45,7 +45,7 @@ struct GemvArgs {
     float *partial;          // [ksplit][images][tokens][n_out] partial sums (ksplit > 1)
     unsigned int *counters;  // [row_tiles] arrival counters, zero between launches
     int *status;             // context status words; [1] records a wait that gave up
-    uint32_t n_out, n_in, nsb, k_off, tokens, y_bf16, row_tiles, ksplit, groups, max_tiles;
+    uint32_t n_out, n_in, nsb, k_off, tokens, y_bf16, x_f32, row_tiles, ksplit, groups, max_tiles;
 };
 
 constexpr int kRing = 2;                 // weight tiles in flight per warp
@@ -111,13 +111,8 @@ __device__ __forceinline__ void stage_activations(const GemvArgs &a, uint32_t sb
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
         const int64_t k = (int64_t)(sb_first + tile) * 256 - (int64_t)a.k_off + j * BW + part * 8;
         if (live && tok < a.tokens && (uint64_t)k < a.n_in) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(a.x + (size_t)tok * a.n_in + k));
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                v[2 * i] = __uint_as_float(w[i] << 16);
-                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-            }
+            if (a.x_f32) load8<true>(reinterpret_cast<const float *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
+            else load8<false>(reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
             if (a.norm_weight) { // (x * 1/rms) * weight, in that order
                 const float rs = inv_rms[tok];
                 const float4 w0 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k)), w1 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k) + 1);
@@ -449,7 +444,8 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_g
     __shared__ float norm_red[33], inv_rms[TOK];
     if (a.norm_weight) { // every CTA needs the whole row's mean square, whatever its K slice
         for (uint32_t tok = 0; tok < a.tokens; ++tok) {
-            const float r = block_inv_rms<false>(a.x + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red);
+            const float r = a.x_f32 ? block_inv_rms<true>(reinterpret_cast<const float *>(a.x) + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red)
+                                    : block_inv_rms<false>(reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red);
             if (threadIdx.x == 0) inv_rms[tok] = r;
         }
         __syncthreads();
@@ -644,13 +640,14 @@ static cudaError_t launch_gemv_tokens(GemvArgs &a, Ctx *ctx, cudaStream_t stream
 
 // 1 to 8 tokens of bf16 activations.  Returns cudaErrorNotSupported when the shape does not fit this kernel
 // (the caller then takes the general one).
-cudaError_t launch_kquant_gemv(Ctx *ctx, const Weight *w, const Weight *w_up, const void *x, void *y, uint32_t y_dtype,
-                               uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
+cudaError_t launch_kquant_gemv(Ctx *ctx, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype, void *y,
+                               uint32_t y_dtype, uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
     if (tokens > 8 || w->nsb > 2048) return cudaErrorNotSupported;
     GemvArgs a;
     a.image = w->image;
     a.image_up = w_up ? w_up->image : nullptr;
-    a.x = reinterpret_cast<const __nv_bfloat16 *>(x);
+    a.x = x;
+    a.x_f32 = x_dtype == MUSER_DTYPE_F32;
     a.y = y;
     a.row_scale = ep.row_scale;
     a.out_scale = ep.out_scale;

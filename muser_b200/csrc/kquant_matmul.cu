@@ -475,8 +475,8 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     const bool q6 = w->dtype == MUSER_DTYPE_Q6_K;
     const bool tc_fits = !w_up && x_dtype == MUSER_DTYPE_BF16 && tokens >= ctx->tc_min_tokens[q6 ? 1 : 0] &&
                          w->n_out >= ctx->tc_min_rows;
-    if (!tc_fits && x_dtype == MUSER_DTYPE_BF16 && tokens <= (q6 ? 4u : 2u)) {
-        const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, y, y_dtype, tokens, ep, stream);
+    if (!tc_fits && tokens <= (q6 ? 4u : 2u)) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
+        const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, x_dtype, y, y_dtype, tokens, ep, stream);
         if (ge != cudaErrorNotSupported) {
             MUSER_CUDA_TRY(ctx, ge);
             return MUSER_CUDA_OK;
