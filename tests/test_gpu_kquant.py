@@ -268,6 +268,23 @@ def test_layer_shapes_every_kernel_sampled_rows_and_determinism(gpu, name):
 
 
 @pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_host_slice_entry_point_repeated_calls(gpu, dtype):
+    """weights::matmul's signature (host f32 slices in and out).  From its second call per (weight, token count) the
+    entry point replays a recorded graph: every call must still see its own input and fill its own output."""
+    op, ctx, k = gpu
+    n_in, n_out = 1024, 80
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=61)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    ow = O.TensorView(raw, dtype, n_in, n_out)
+    for tokens in (1, 5, 70):  # 70: two chunks of at most 64 tokens
+        for call in range(4):
+            x = H.lcg_activations(tokens * n_in, seed=10 * tokens + call).reshape(tokens, n_in).astype(np.float32)
+            y = op.matmul(ctx, w, x, tokens)
+            assert H.rel_l2(y, O.matmul(ow, x)) <= REL_L2_TOL, (tokens, call)
+    w.free()
+
+
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
 def test_lm_head_tail_and_selected_rows(gpu, dtype):
     """The LM-head end of the path (reference.rs:559-570, weights.rs:425-449): logit scale and tanh soft cap fused
     behind the projection in every K-quant kernel, and the projection restricted to a list of rows."""
