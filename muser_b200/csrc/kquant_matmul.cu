@@ -20,6 +20,8 @@
 // and the scale epilogue runs half as often.  Each warp first passes its tile through shared memory to regroup
 // the stored words (every lane owns whole sub-blocks, kquant_layout.cuh) so that every lane holds a quarter of
 // every sub-block, the operand order of a sub-block-at-a-time MMA.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kquant_layout.cuh"
 
@@ -473,8 +475,12 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     // for Q6_K; the tcgen05 kernel (kquant_tc.cu) from 12 / 5 tokens when the weight has enough 128-row blocks to
     // fill the GPU; this file's kernel in between, for f32 activations and for small weights.
     const bool q6 = w->dtype == MUSER_DTYPE_Q6_K;
-    const bool tc_fits = !w_up && x_dtype == MUSER_DTYPE_BF16 && tokens >= ctx->tc_min_tokens[q6 ? 1 : 0] &&
-                         w->n_out >= ctx->tc_min_rows;
+    // (f32 activations cost the legacy kernel a second MMA pass, so the tensor-core kernel takes over earlier;
+    //  it carries them as f16 head + remainder column pairs, hence at most 32 tokens)
+    const bool xf32_in = x_dtype == MUSER_DTYPE_F32;
+    const uint32_t tc_set = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
+    const uint32_t tc_from = (xf32_in && tc_set <= 64) ? std::min(tc_set, 5u) : tc_set;
+    const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32_in ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
     if (!tc_fits && tokens <= (q6 ? 4u : 2u)) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
         const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, x_dtype, y, y_dtype, tokens, ep, stream);
         if (ge != cudaErrorNotSupported) {
@@ -492,7 +498,7 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
         x = ctx->norm_scratch;
         x_dtype = MUSER_DTYPE_F32;
     }
-    if (tc_fits) { // (normalized bf16 rows reach it as f32 and are rounded to f16 there: 11 bits against bf16's 8)
+    if (tc_fits) {
         Epilogue tail = ep;
         tail.norm_weight = nullptr;
         const cudaError_t te = launch_kquant_tc(ctx, w, x, x_dtype, y, y_dtype, tokens, tail, stream);

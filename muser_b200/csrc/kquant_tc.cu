@@ -48,6 +48,7 @@ struct TcArgs {
     unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
     int *status;
     uint32_t n_out, nsb, row_tiles, tokens, y_bf16;
+    uint32_t fold;          // f32 activations travel as f16 head + remainder in columns i and i + N/2: add the pairs
     uint32_t whole, ksplit, items; // items 0..whole-1: one row block each, all of K; then the other row blocks in ksplit slices
 };
 
@@ -507,6 +508,9 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (!last) continue;
 
             // ---- end of an item: meet the other K slices, then store
+            if (a.fold)
+#pragma unroll
+                for (int i = 0; i < N / 2; ++i) acc[i] += acc[i + N / 2];
             const uint32_t row = rb * kTcRows + row_in_block;
             const bool live = row < a.n_out;
             bool finish = true;
@@ -577,23 +581,27 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // per 32-input sub-block the sum of the f16 values as an f16 head + remainder pair.
 template <bool XF32>
 __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in, uint32_t k_off,
-                                                                uint32_t nsb, __half *__restrict__ xh, __half *__restrict__ xs) {
-    const uint32_t tile = blockIdx.x, tok = blockIdx.y, i = threadIdx.x;
+                                                                uint32_t nsb, uint32_t half, __half *__restrict__ xh, __half *__restrict__ xs) {
+    // bf16 activations are exact in f16: output row = token.  f32 activations are carried exactly (to 22 bits) as an
+    // f16 head in row t and the remainder in row `half` + t; the kernel adds the two columns at the end.
+    const uint32_t tile = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
+    const uint32_t tok = XF32 ? r % half : r, part = XF32 ? r / half : 0;
     const int64_t k = (int64_t)tile * 256 + i - (int64_t)k_off;
     float v = 0.0f;
     if (tok < tokens && k >= 0 && k < (int64_t)n_in)
         v = XF32 ? reinterpret_cast<const float *>(x)[(size_t)tok * n_in + k]
                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(x)[(size_t)tok * n_in + k]);
     v = fminf(fmaxf(v, -65504.0f), 65504.0f); // f16 range; NaN passes through
-    const __half hv = __float2half_rn(v);
-    xh[(size_t)tok * nsb * 256 + (size_t)tile * 256 + i] = hv;
+    __half hv = __float2half_rn(v);
+    if (part) hv = __float2half_rn(v - __half2float(hv));
+    xh[(size_t)r * nsb * 256 + (size_t)tile * 256 + i] = hv;
     float s = __half2float(hv);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if ((i & 31) == 0) {
         const __half head = __float2half_rn(s);
         const __half rest = __float2half_rn(s - __half2float(head));
-        __half *dst = xs + (size_t)tok * nsb * 16 + (size_t)tile * 16 + 2 * (i >> 5);
+        __half *dst = xs + (size_t)r * nsb * 16 + (size_t)tile * 16 + 2 * (i >> 5);
         dst[0] = head;
         dst[1] = rest;
     }
@@ -704,19 +712,20 @@ static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, cons
 // cudaErrorNotSupported: this shape is not served here (the caller falls back to the other kernels).
 cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
                              uint32_t tokens, const Epilogue &ep, cudaStream_t stream) {
-    // (the caller sends f32 activations elsewhere: they would lose bits on their way to f16)
-    if (tokens > 64 || !ctx->tc_scratch) return cudaErrorNotSupported;
-    const uint32_t n = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+    const bool xf32 = x_dtype == MUSER_DTYPE_F32;
+    const uint32_t cols = xf32 ? 2 * tokens : tokens; // f32 activations take two columns each (f16 head + remainder)
+    if (cols > 64 || !ctx->tc_scratch) return cudaErrorNotSupported;
+    const uint32_t n = cols <= 16 ? 16 : (cols <= 32 ? 32 : 64);
     const size_t xh_bytes = (size_t)n * w->nsb * 256 * sizeof(__half), xs_bytes = (size_t)n * w->nsb * 16 * sizeof(__half);
     const size_t xs_off = (xh_bytes + 1023) & ~(size_t)1023;
     if (xs_off + xs_bytes > ctx->tc_scratch_bytes) return cudaErrorNotSupported;
     __half *xh = reinterpret_cast<__half *>(ctx->tc_scratch);
     __half *xs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(ctx->tc_scratch) + xs_off);
     const dim3 pgrid(w->nsb, n);
-    if (x_dtype == MUSER_DTYPE_F32)
-        kquant_tc_prepare_kernel<true><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
+    if (xf32)
+        kquant_tc_prepare_kernel<true><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, n / 2, xh, xs);
     else
-        kquant_tc_prepare_kernel<false><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
+        kquant_tc_prepare_kernel<false><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, n / 2, xh, xs);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
 
@@ -738,6 +747,7 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     a.row_tiles = w->row_tiles;
     a.tokens = tokens;
     a.y_bf16 = y_dtype == MUSER_DTYPE_BF16;
+    a.fold = xf32 ? 1u : 0u;
     const uint32_t row_blocks = (w->row_tiles + 7) / 8;
     const size_t slice_bytes = (size_t)tokens * w->n_out * sizeof(float);
     uint32_t max_split = (uint32_t)std::max<size_t>(1, ctx->gemv_partial_bytes / std::max<size_t>(1, slice_bytes));
