@@ -9,7 +9,7 @@
 // K slabs (256 values) of both operands with TMA plus their scale factors with bulk copies through a
 // 4-stage shared-memory ring; warp 1 copies the scale factors into tensor memory (tcgen05.cp) and issues
 // tcgen05.mma kind::mxf4nvf4 (K = 64 per instruction) into a 128 x 256 f32 accumulator in tensor memory;
-// warps 2-5 read the accumulator back (tcgen05.ld), apply the two tensor scales and the fused epilogue, and
+// warps 2-9 read the accumulator back (tcgen05.ld), apply the two tensor scales and the fused epilogue, and
 // store.  Every mbarrier wait is bounded: on expiry the CTA records a code in the context's status word,
 // stops issuing work, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
 #include <cuda.h>
@@ -128,7 +128,7 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 // the same 128 rows of the up weight (map_b, map_b2: 128-row boxes), and the epilogue writes silu_fast(gate) * up,
 // each factor first rounded to f16 as the unfused W4A4 lane returns it (quant/nvfp4.rs:337).
 template <bool DUAL>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
     constexpr uint32_t kTileRows = DUAL ? BN / 2 : BN; // output columns (weight rows) per tile
@@ -150,7 +150,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc_full, 1);
-        mbar_init(bar_acc_empty, 4); // one arrival per epilogue warp
+        mbar_init(bar_acc_empty, 8); // one arrival per epilogue warp
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -256,8 +256,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const uint32_t quad = warp & 3; // the 32 accumulator lanes this warp may read
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        // Eight warps: two per 32-lane quarter of the accumulator, one for each half of the tile's output columns.
+        // The MMA warp cannot start the next tile before the last tcgen05.ld of this one (there is room for one
+        // accumulator only), so the read-out is kept short: half the columns per warp, and the next strip's load is
+        // in flight while the current one is scaled and stored.
+        const uint32_t quad = warp & 3;                 // the 32 accumulator lanes this warp may read
+        const uint32_t part = (uint32_t)(warp - 2) >> 2; // which half of the output columns
+        constexpr uint32_t kOutCols = DUAL ? BN / 2 : BN, kPartCols = kOutCols / 2;
+        const bool tail = g.out_scale != 1.0f || g.softcap > 0.0f; // LM-head tail: off the common path
         uint32_t local = 0;
         for (uint32_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
             const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
@@ -273,32 +280,41 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t tok = tile_m * BM + quad * 32 + lane;
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
             const bool vec_ok = (g.n_out & 7) == 0;
-            for (uint32_t c0 = 0; c0 < kTileRows; c0 += 32) {
-                uint32_t r[32], r_up[DUAL ? 32 : 1];
-                tmem_ld32(tmem + ((quad * 32) << 16) + c0, r);
-                if constexpr (DUAL) tmem_ld32(tmem + ((quad * 32) << 16) + kTileRows + c0, r_up);
+            const uint32_t lane_base = tmem + ((quad * 32) << 16), col0 = part * kPartCols;
+            uint32_t r[2][32], r_up[DUAL ? 32 : 1];
+            tmem_ld32(lane_base + col0, r[0]);
+#pragma unroll
+            for (uint32_t s = 0; s < kPartCols / 32; ++s) {
+                const uint32_t c0 = col0 + 32 * s;
+                uint32_t(&cur)[32] = r[s & 1];
+                if constexpr (DUAL) tmem_ld32(lane_base + kOutCols + c0, r_up);
                 tmem_ld_wait();
-                if (c0 + 32 == kTileRows) { // everything this warp needs is in registers: hand the accumulator back
+                if (s + 1 < kPartCols / 32) {
+                    tmem_ld32(lane_base + c0 + 32, r[(s + 1) & 1]); // in flight under this strip's arithmetic and stores
+                } else { // everything this warp needs is in registers: hand the accumulator back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
                 }
-                const uint32_t n0 = tile_n * kTileRows + c0;
+                const uint32_t n0 = tile_n * kOutCols + c0;
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
                     const uint32_t valid = min(32u, g.n_out - n0);
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) { // quant/nvfp4.rs:334-336: tensor scales applied one after the other
-                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), g.scale2), g.inv_input_scale);
+                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(cur[i]), g.scale2), g.inv_input_scale);
                         if constexpr (DUAL) {
                             const float gate = __half2float(__float2half_rn(v[i]));
                             const float up = __half2float(__float2half_rn(
                                 __fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
                             v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up; // silu_fast, quant/helpers.rs:72
                         }
-                        v[i] = logit_tail(v[i] * rs, g.out_scale, g.softcap);
+                        v[i] *= rs;
                     }
+                    if (tail)
+#pragma unroll 1
+                        for (int i = 0; i < 32; ++i) v[i] = logit_tail(v[i], g.out_scale, g.softcap);
                     if (g.y_dtype == MUSER_DTYPE_F32)
                         store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
                                            g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
@@ -472,10 +488,10 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     const uint32_t tiles = g.n_tiles * ((tokens + BM - 1) / BM);
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     if (w_up)
-        nvfp4_gemm_kernel<true><<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_half),
+        nvfp4_gemm_kernel<true><<<grid, 320, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_half),
                                                                    *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half), g);
     else
-        nvfp4_gemm_kernel<false><<<grid, 192, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache),
+        nvfp4_gemm_kernel<false><<<grid, 320, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache),
                                                                     *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
