@@ -376,7 +376,9 @@ __device__ __forceinline__ void tile_compute(const Q6Regs &r, const uint4 *fb, u
 }
 
 // ------------------------------------------------------------------------------------ kernel
-constexpr int kGemvMaxWarps = 16;
+// Warps per CTA at most: 14 where two CTAs share an SM (448 threads x 2 leave 72 registers a thread, which is what the
+// one- and two-token loops need to stay out of local memory), 16 for the token-group variants (one CTA per SM).
+constexpr int gemv_max_warps(int ng) { return ng > 1 ? 16 : 14; }
 
 template <int DT> struct RegsOf;
 template <> struct RegsOf<MUSER_DTYPE_Q4_K> { using type = Q4Regs; };
@@ -388,7 +390,7 @@ template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
 // synchronisation after the staging.  With more than one slice, a warp drops its 16 x MT partial sums into the
 // scratch buffer and bumps the row tile's counter; the warp that finds the counter full adds the slices in order.
 template <int DT, int MT, int NG, bool DUAL>
-__global__ void __launch_bounds__(kGemvMaxWarps * 32, (NG > 1 ? 1 : 2)) kquant_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(gemv_max_warps(NG) * 32, (NG > 1 ? 1 : 2)) kquant_gemv_kernel(const GemvArgs a) {
     using Regs = typename RegsOf<DT>::type;
     constexpr int SUBS = Fmt<DT>::kSubs, kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = MT * NG;
     extern __shared__ uint4 dyn[];
@@ -571,11 +573,11 @@ static GemvPlan plan_split(uint32_t nsb, uint32_t row_tiles, int sm_count, int t
     GemvPlan best{2, 1};
     double best_cost = 1e300;
     for (int ks = 1; ks <= 16 && (uint32_t)ks <= nsb; ++ks)
-        for (int w = 2; w <= kGemvMaxWarps; w += 2) {
+        for (int w = 2; w <= gemv_max_warps(frag_kib); w += 2) {
             const size_t smem = gemv_smem_bytes(nsb, ks, w, tile_bytes, meta_bytes_per_tile, frag_kib);
             if (smem > 220u * 1024) continue;
             int ctas = (int)((227u * 1024) / (smem + 1024));
-            ctas = std::min(ctas, std::max(1, (frag_kib > 1 ? 16 : 32) / w)); // 64 (128) registers a thread
+            ctas = std::min(ctas, std::max(1, (frag_kib > 1 ? 16 : 28) / w)); // 72 (128) registers a thread
             const double tiles = std::ceil((double)nsb / ks);
             const double cta_count = std::ceil((double)row_tiles / w) * ks;           // one row tile per warp and round
             const double ctas_on_sm = std::ceil(cta_count / sm_count);                // the busiest SM

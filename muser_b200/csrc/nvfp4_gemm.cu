@@ -85,7 +85,9 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
             }
             return;
         }
-        for (uint32_t i = 0; i < valid; ++i) y[i] = v[i] + (res ? res[i] : 0.0f);
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) // (unrolled with a predicate: a run-time index would push v[] out of registers)
+            if (i < valid) y[i] = v[i] + (res ? res[i] : 0.0f);
     } else {
         auto to_f = [](T h) { if constexpr (std::is_same<T, __half>::value) return __half2float(h); else return __bfloat162float(h); };
         auto pack = [](float a, float b) -> uint32_t {
@@ -113,7 +115,9 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
             }
             return;
         }
-        for (uint32_t i = 0; i < valid; ++i) {
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) {
+            if (i >= valid) continue;
             const float f = v[i] + (res ? to_f(res[i]) : 0.0f);
             if constexpr (std::is_same<T, __half>::value) y[i] = __float2half_rn(f); else y[i] = __float2bfloat16_rn(f);
         }
@@ -127,7 +131,8 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 // reference.rs:511-513 on the CPU lane): the 256 accumulator columns of a tile are 128 rows of the gate weight next to
 // the same 128 rows of the up weight (map_b, map_b2: 128-row boxes), and the epilogue writes silu_fast(gate) * up,
 // each factor first rounded to f16 as the unfused W4A4 lane returns it (quant/nvfp4.rs:337).
-template <bool DUAL>
+// TAIL compiles the LM-head tail (logit scale, tanh soft cap) into the epilogue; the common instantiation has none of it.
+template <bool DUAL, bool TAIL>
 __global__ void __launch_bounds__(320, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
@@ -264,7 +269,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t quad = warp & 3;                 // the 32 accumulator lanes this warp may read
         const uint32_t part = (uint32_t)(warp - 2) >> 2; // which half of the output columns
         constexpr uint32_t kOutCols = DUAL ? BN / 2 : BN, kPartCols = kOutCols / 2;
-        const bool tail = g.out_scale != 1.0f || g.softcap > 0.0f; // LM-head tail: off the common path
         uint32_t local = 0;
         for (uint32_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
             const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
@@ -311,10 +315,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up; // silu_fast, quant/helpers.rs:72
                         }
                         v[i] *= rs;
+                        if constexpr (TAIL) v[i] = logit_tail(v[i], g.out_scale, g.softcap);
                     }
-                    if (tail)
-#pragma unroll 1
-                        for (int i = 0; i < 32; ++i) v[i] = logit_tail(v[i], g.out_scale, g.softcap);
                     if (g.y_dtype == MUSER_DTYPE_F32)
                         store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
                                            g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
@@ -446,8 +448,9 @@ muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {
     w->tmap_half = half;
     static bool attr_set = false;
     if (!attr_set) {
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         attr_set = true;
     }
     return MUSER_CUDA_OK;
@@ -487,12 +490,15 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.n_tiles = w_up ? (uint32_t)((w->n_out + BN / 2 - 1) / (BN / 2)) : (uint32_t)(w->n_out_pad / BN);
     const uint32_t tiles = g.n_tiles * ((tokens + BM - 1) / BM);
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(w_up ? w->tmap_half : w->tmap_cache);
+    const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
+    const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
     if (w_up)
-        nvfp4_gemm_kernel<true><<<grid, 320, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_half),
-                                                                   *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half), g);
+        nvfp4_gemm_kernel<true, false><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
+    else if (tail)
+        nvfp4_gemm_kernel<false, true><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g);
     else
-        nvfp4_gemm_kernel<false><<<grid, 320, kSmemBytes, stream>>>(map_a, *reinterpret_cast<const CUtensorMap *>(w->tmap_cache),
-                                                                    *reinterpret_cast<const CUtensorMap *>(w->tmap_cache), g);
+        nvfp4_gemm_kernel<false, false><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
