@@ -19,7 +19,7 @@
 //               two buffers so that the drain of one super-block column runs under the MMAs of the next
 //   warps 2-17  eight rows of one 16-row weight tile each: bulk copies global -> shared (two tiles in flight per warp),
 //               unpack to the f16 integers above, store into the swizzled A stage (three stages of 128 inputs)
-//   warps 18-21 drain: tcgen05.ld, scale by d / dmin (f32), keep N running sums per row in registers; at the end of
+//   warps 18-..  drain (four warps; eight at N = 64, 32 token columns each, so that the running sums stay in registers): tcgen05.ld, scale by d / dmin (f32), keep N running sums per row in registers; at the end of
 //               an item add the K slices through the context scratch (last arriver sums in slice order) and store
 // Every wait is bounded; a wait that gives up records a code in the context's status word and the CTA winds down.
 #include <algorithm>
@@ -36,7 +36,6 @@ constexpr int kTcRows = 128;             // weight rows per block = MMA M
 constexpr int kTcStages = 2;             // A stages of 128 inputs each (the unpacked weights are the expensive bytes)
 constexpr int kTcABytes = kTcRows * 256; // 128 rows x 128 f16: two 64-column swizzle atoms of 16 KiB
 constexpr int kTcDequantWarps = 16;           // warp = (row tile of the block, upper / lower eight rows)
-constexpr int kTcThreads = 32 * (2 + kTcDequantWarps + 4);
 
 struct TcArgs {
     const uint8_t *image;
@@ -48,7 +47,7 @@ struct TcArgs {
     unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
     int *status;
     uint32_t n_out, nsb, row_tiles, tokens, y_bf16;
-    uint32_t fold;          // f32 activations travel as f16 head + remainder in columns i and i + N/2: add the pairs
+    uint32_t fold;          // f32 activations travel as f16 head + remainder in columns 2t and 2t + 1: add the pairs
     uint32_t whole, ksplit, items; // items 0..whole-1: one row block each, all of K; then the other row blocks in ksplit slices
 };
 
@@ -255,15 +254,19 @@ struct TcSmem {
     static constexpr int kOffHdr = kOffRing + kTcDequantWarps * kRing * kSlot;
     static constexpr int kHdrDepth = 8;              // (d, dmin) per row of the last eight super-block columns
     static constexpr int kOffBars = kOffHdr + kHdrDepth * kTcRows * 8;
-    static constexpr int kBufs = N == 64 ? 2 : 4;    // accumulator buffers of 3N columns in tensor memory
+    static constexpr int kBufs = 4;                  // accumulator buffers in tensor memory, each kAcc main parts + the min part
+    static constexpr int kAcc = N <= 32 ? 2 : 1;     // two main accumulators taken in turn where the columns allow (measured faster)
+    static constexpr int kBufCols = (kAcc + 1) * N;
+    static constexpr int kDrainWarps = N >= 32 ? 8 : 4, kDrainCols = N / (kDrainWarps / 4);
+    static constexpr int kThreads = 32 * (2 + kTcDequantWarps + kDrainWarps);
     static constexpr int kBars = 2 * kTcStages + 2 * kStagesB + 2 * kBufs + kTcDequantWarps * kRing;
     static constexpr int kBytes = kOffBars + kBars * 8 + 16 + 1024 /*alignment slack*/;
     static_assert(kBytes <= 227 * 1024, "shared memory of one CTA exceeded");
-    static constexpr uint32_t kTmemCols = N >= 32 ? 512 : 256; // kBufs buffers of 3N columns, rounded up to a power of two
+    static constexpr uint32_t kTmemCols = N == 16 ? 256 : 512; // kBufs x kBufCols = 192 / 384 / 512, rounded up to a power of two
 };
 
 template <int DT, int N>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__((TcSmem<DT, N>::kThreads), 1)
 kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_xs, const TcArgs a) {
     using S = TcSmem<DT, N>;
     constexpr bool Q4 = S::kQ4;
@@ -292,7 +295,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         for (int b = 0; b < kBufs; ++b) {
             mbar_init(bar_tmem_full + 8 * b, 1);
-            mbar_init(bar_tmem_empty + 8 * b, 4);
+            mbar_init(bar_tmem_empty + 8 * b, S::kDrainWarps);
         }
         for (int i = 0; i < kTcDequantWarps * kRing; ++i) mbar_init(bar_ring + 8 * i, 1);
         *abort_flag = 0;
@@ -348,7 +351,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             uint32_t hs = 0, tc = 0;
             bool ok = true;
             for (; !w.done(a) && ok; w.next(a), ++tc) {
-                const uint32_t buf = tc % kBufs, d_main = tmem + buf * 3 * N, d_min = d_main + 2 * N;
+                const uint32_t buf = tc % kBufs, d_main = tmem + buf * S::kBufCols, d_min = d_main + S::kAcc * N;
                 if (tc >= (uint32_t)kBufs) { // the drain warps must have read this buffer's previous contents
                     ok = mbar_wait(bar_tmem_empty + 8 * buf, ((tc / kBufs) - 1) & 1, abort_flag);
                     if (!ok) break;
@@ -365,7 +368,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         const uint64_t da = operand_desc(sa + atom * 16384u), db = operand_desc(sb + atom * (N * 128u));
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; ++kk) // 16 values = 32 bytes along the swizzled 128-byte rows
-                            mma_f16(d_main + (kk & 1) * N, da + 2 * kk, db + 2 * kk, idesc, (h | atom | (kk >> 1)) != 0);
+                            mma_f16(d_main + (S::kAcc == 2 ? (kk & 1) * N : 0), da + 2 * kk, db + 2 * kk, idesc,
+                                    (h | atom | (S::kAcc == 2 ? kk >> 1 : kk)) != 0);
                     }
                     if (Q4 && h == 1)
                         mma_f16(d_min, operand_desc32(base + S::kOffMinA + (tc & 1) * S::kMinA),
@@ -463,11 +467,15 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (!ok)
             for (uint32_t k = n; k < fetched; ++k) mbar_wait_alone(rbar + 8 * (k % kRing), (k / kRing) & 1);
     } else {
-        // ---------------------------------------------------------------- drain (the last four warps)
-        const uint32_t quad = warp & 3, row_in_block = quad * 32 + lane;
-        float acc[N];
+        // ---------------------------------------------------------------- drain (the last 4 or 8 warps)
+        constexpr int C = S::kDrainCols;                                          // token columns of this warp
+        const uint32_t quad = warp & 3, row_in_block = quad * 32 + lane;          // its 32 accumulator lanes = rows
+        const uint32_t part = (uint32_t)(warp - 2 - kTcDequantWarps) >> 2, col0 = part * C;
+        // f32 activations occupy column pairs (2t, 2t + 1): after folding, this warp holds tokens col0/2 .. col0/2 + C/2 - 1
+        const uint32_t tok0 = a.fold ? col0 / 2 : col0, n_tok = a.fold ? C / 2 : C;
+        float acc[C];
 #pragma unroll
-        for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < C; ++i) acc[i] = 0.0f;
         TcWalk w;
         w.start(a);
         uint32_t tc = 0;
@@ -483,17 +491,19 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float2 hd = hdr[(tc % S::kHdrDepth) * kTcRows + row_in_block];
-            const uint32_t taddr = tmem + ((quad * 32) << 16) + buf * 3 * N;
+            const uint32_t taddr = tmem + ((quad * 32) << 16) + buf * S::kBufCols + col0;
 #pragma unroll
-            for (int c0 = 0; c0 < N; c0 += 16) {
-                uint32_t p[16], p2[16], m[16];
+            for (int c0 = 0; c0 < C; c0 += 16) {
+                uint32_t p[16], p2[S::kAcc == 2 ? 16 : 1], m[16];
                 tmem_ld16(taddr + c0, p);
-                tmem_ld16(taddr + N + c0, p2);
-                if constexpr (Q4) tmem_ld16(taddr + 2 * N + c0, m);
+                if constexpr (S::kAcc == 2) tmem_ld16(taddr + N + c0, p2);
+                if constexpr (Q4) tmem_ld16(taddr + S::kAcc * N + c0, m);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    acc[c0 + i] = fmaf(hd.x, __uint_as_float(p[i]) + __uint_as_float(p2[i]), acc[c0 + i]);
+                    float main = __uint_as_float(p[i]);
+                    if constexpr (S::kAcc == 2) main += __uint_as_float(p2[i]);
+                    acc[c0 + i] = fmaf(hd.x, main, acc[c0 + i]);
                     if constexpr (Q4) acc[c0 + i] = fmaf(-hd.y, __uint_as_float(m[i]), acc[c0 + i]);
                 }
             }
@@ -510,28 +520,28 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // ---- end of an item: meet the other K slices, then store
             if (a.fold)
 #pragma unroll
-                for (int i = 0; i < N / 2; ++i) acc[i] += acc[i + N / 2];
+                for (int i = 0; i < C / 2; ++i) acc[i] = acc[2 * i] + acc[2 * i + 1];
             const uint32_t row = rb * kTcRows + row_in_block;
             const bool live = row < a.n_out;
             bool finish = true;
             if (split) {
                 if (live)
 #pragma unroll
-                    for (int i = 0; i < N; ++i)
-                        if ((uint32_t)i < a.tokens) a.partial[((size_t)slice * a.tokens + i) * a.n_out + row] = acc[i];
+                    for (int i = 0; i < C; ++i)
+                        if ((uint32_t)i < n_tok && tok0 + i < a.tokens) a.partial[((size_t)slice * a.tokens + tok0 + i) * a.n_out + row] = acc[i];
                 // Release / acquire through the counter: the warp barrier orders every lane's stores before lane 0's
                 // releasing add, and lane 0's acquire (handed on by the shuffle) before every lane's loads below.
                 __syncwarp();
                 unsigned int seen = 0;
-                if (lane == 0)
-                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.counters + rb * 4 + quad) : "memory");
+                unsigned int *counter = a.counters + (rb * 4 + quad) * 2 + part;
+                if (lane == 0) asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(counter) : "memory");
                 seen = __shfl_sync(0xffffffffu, seen, 0);
                 finish = seen == a.ksplit - 1;
                 if (finish) {
-                    if (lane == 0) a.counters[rb * 4 + quad] = 0; // ready for the next launch
+                    if (lane == 0) *counter = 0; // ready for the next launch
                     // slices in order (deterministic); sixteen independent loads in flight per step, not one
 #pragma unroll
-                    for (int c0 = 0; c0 < N; c0 += 16) {
+                    for (int c0 = 0; c0 < C; c0 += 16) {
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.0f;
@@ -539,8 +549,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             float got[16];
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
-                                const uint32_t i = min((uint32_t)(c0 + j), a.tokens - 1); // rows past `tokens` re-read the last one
-                                got[j] = __ldcg(a.partial + ((size_t)sl * a.tokens + i) * a.n_out + (live ? row : 0u));
+                                const uint32_t t = min(tok0 + (uint32_t)(c0 + j), a.tokens - 1); // past `tokens`: re-read the last one
+                                got[j] = __ldcg(a.partial + ((size_t)sl * a.tokens + t) * a.n_out + (live ? row : 0u));
                             }
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] += got[j];
@@ -552,11 +562,12 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
             if (finish && live) {
 #pragma unroll
-                for (int i = 0; i < N; ++i) {
-                    if ((uint32_t)i >= a.tokens) continue;
+                for (int i = 0; i < C; ++i) {
+                    const uint32_t t = tok0 + i;
+                    if ((uint32_t)i >= n_tok || t >= a.tokens) continue;
                     float r = acc[i];
-                    const size_t o = (size_t)i * a.n_out + row;
-                    if (a.row_scale) r *= a.row_scale[i];
+                    const size_t o = (size_t)t * a.n_out + row;
+                    if (a.row_scale) r *= a.row_scale[t];
                     r = logit_tail(r, a.out_scale, a.softcap);
                     if (a.y_bf16) {
                         if (a.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.residual)[o]);
@@ -568,7 +579,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             }
 #pragma unroll
-            for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < C; ++i) acc[i] = 0.0f;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -581,11 +592,11 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // per 32-input sub-block the sum of the f16 values as an f16 head + remainder pair.
 template <bool XF32>
 __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in, uint32_t k_off,
-                                                                uint32_t nsb, uint32_t half, __half *__restrict__ xh, __half *__restrict__ xs) {
+                                                                uint32_t nsb, __half *__restrict__ xh, __half *__restrict__ xs) {
     // bf16 activations are exact in f16: output row = token.  f32 activations are carried exactly (to 22 bits) as an
-    // f16 head in row t and the remainder in row `half` + t; the kernel adds the two columns at the end.
+    // f16 head in row 2t and the remainder in row 2t + 1; the kernel adds the two columns at the end.
     const uint32_t tile = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
-    const uint32_t tok = XF32 ? r % half : r, part = XF32 ? r / half : 0;
+    const uint32_t tok = XF32 ? r >> 1 : r, part = XF32 ? r & 1 : 0;
     const int64_t k = (int64_t)tile * 256 + i - (int64_t)k_off;
     float v = 0.0f;
     if (tok < tokens && k >= 0 && k < (int64_t)n_in)
@@ -705,7 +716,7 @@ static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, cons
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    kquant_tc_kernel<DT, N><<<grid, kTcThreads, S::kBytes, stream>>>(mx, mxs, a);
+    kquant_tc_kernel<DT, N><<<grid, S::kThreads, S::kBytes, stream>>>(mx, mxs, a);
     return cudaGetLastError();
 }
 
@@ -723,9 +734,9 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     __half *xs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(ctx->tc_scratch) + xs_off);
     const dim3 pgrid(w->nsb, n);
     if (xf32)
-        kquant_tc_prepare_kernel<true><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, n / 2, xh, xs);
+        kquant_tc_prepare_kernel<true><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
     else
-        kquant_tc_prepare_kernel<false><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, n / 2, xh, xs);
+        kquant_tc_prepare_kernel<false><<<pgrid, 256, 0, stream>>>(x, tokens, (uint32_t)w->n_in, w->k_off, w->nsb, xh, xs);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
 
@@ -751,7 +762,7 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     const uint32_t row_blocks = (w->row_tiles + 7) / 8;
     const size_t slice_bytes = (size_t)tokens * w->n_out * sizeof(float);
     uint32_t max_split = (uint32_t)std::max<size_t>(1, ctx->gemv_partial_bytes / std::max<size_t>(1, slice_bytes));
-    if ((size_t)row_blocks * 4 > ctx->gemv_counter_slots) max_split = 1;
+    if ((size_t)row_blocks * 8 > ctx->gemv_counter_slots) max_split = 1;
     const TcPlan plan = tc_plan(w->nsb, row_blocks, ctx->sm_count, max_split);
     a.whole = plan.whole;
     a.ksplit = plan.ksplit;
