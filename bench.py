@@ -310,8 +310,52 @@ def run_gpu(args):
             wq.free()
             del wp, ws, xa, yq, xp, xs
         layer = tot_fl / tot_s / 1e12
+
+        fused = {}
+        try:
+            # fused variants: q|k|v as one weight (rows concatenated, one quantized input), gate|up with SwiGLU in the epilogue
+            def timed(fn, reps=5):
+                for _ in range(2):
+                    fn()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                for _ in range(reps):
+                    fn()
+                t1.record()
+                torch.cuda.synchronize()
+                ctx.sync_status()
+                return t0.elapsed_time(t1) / reps * 1e-3
+
+            names = list(projs)
+            k_h = projs["attn_q"][0]
+            xa = synth.normal_activations(m, k_h, seed=0, stream=3100, device=dev)
+            isi = synth.activation_input_scale_inv(xa)
+            xp, xs = kern.quantize_nvfp4_activation(xa, isi)
+            parts = [synth.nvfp4_weight(synth.normal_weights(projs[nm][1], k_h, seed=0, stream=names.index(nm), device=dev))
+                     for nm in ("attn_q", "attn_k", "attn_v")]
+            n_qkv = sum(projs[nm][1] for nm in ("attn_q", "attn_k", "attn_v"))
+            # one tensor scale for the concatenation: the synthetic weights share a distribution, so the first one's serves
+            w_qkv = op.Weight(ctx, op.TensorView(torch.cat([p[0] for p in parts]), NVFP4, k_h, n_qkv,
+                                                 torch.cat([p[1] for p in parts]), parts[0][2], isi))
+            y_qkv = torch.empty((m, n_qkv), dtype=torch.bfloat16, device=dev)
+            t = timed(lambda: kern.encode_nvfp4_prequant(w_qkv, xp, xs, y_qkv, m))
+            fused["attn_q|k|v"] = {"gemm_tflops": round(2.0 * m * n_qkv * k_h / t / 1e12, 1)}
+            w_qkv.free()
+            n_f = projs["ffn_gate"][1]
+            gu = [synth.nvfp4_weight(synth.normal_weights(n_f, k_h, seed=0, stream=names.index(nm), device=dev)) for nm in ("ffn_gate", "ffn_up")]
+            w_g, w_u = (op.Weight(ctx, op.TensorView(p[0], NVFP4, k_h, n_f, p[1], p[2], isi)) for p in gu)
+            y_f = torch.empty((m, n_f), dtype=torch.bfloat16, device=dev)
+            t = timed(lambda: kern.encode_nvfp4_ffn_gate_up_silu_prequant(w_g, w_u, xp, xs, y_f, m))
+            fused["ffn_gate|up+swiglu"] = {"gemm_tflops": round(2.0 * m * 2 * n_f * k_h / t / 1e12, 1)}
+            w_g.free()
+            w_u.free()
+            del parts, gu, y_qkv, y_f, xa, xp, xs
+
+        except Exception as exc:  # the secondary section must never cost the headline line
+            fused = {"error": f"{type(exc).__name__}: {exc}"}
+
         prefill = {"workload": "nvfp4_prefill_gemm_layer_m2048", "unit": "TFLOP/s", "layer": round(layer, 1),
-                   "per_projection": per,
+                   "per_projection": per, "fused": fused,
                    "roofline": {"bound": "tensor", "achieved": round(layer, 1), "peak": round(peak_fp4, 1), "unit": "TFLOP/s",
                                 "frac": round(layer / peak_fp4, 4),
                                 "peak_kind": "measured here: muser_cuda_fp4_peak_probe (block-scaled FP4 MMAs, no memory traffic)"}}
@@ -355,7 +399,7 @@ def run_gpu(args):
                          # profiles/bench_launch_list_decode_gemv_layer.md): 1.007 x the algorithmic bytes, no re-reads
                          "traffic": MEASURED_STEP_TRAFFIC_BYTES if world == 1 else None, "traffic_per": "step (28 launches)",
                          "algorithmic_bytes_per_step": step_bytes(2), "peak_kind": f"of {peak_kind}",
-                         "kernel": "kquant_gemv_kernel / kquant_matmul_kernel (the 28 launches of a step; achieved = all their bytes / all their time)"},
+                         "kernel": "kquant_gemv_kernel / kquant_matmul_kernel / kquant_tc_kernel (the 28 launches of a step; achieved = all their bytes / all their time)"},
             "cpu_baseline": cpu,
             "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,

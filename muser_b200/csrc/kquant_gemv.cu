@@ -505,15 +505,15 @@ __global__ void __launch_bounds__(gemv_max_warps(NG) * 32, (NG > 1 ? 1 : 2)) kqu
                                 a.partial[(((size_t)slice * kImages + im) * TOK + tok) * a.n_out + row] = out[im][gp][c];
                         }
             }
-            __threadfence();
+            // Release / acquire through the counter: the warp barrier orders every lane's stores before lane 0's
+            // releasing add, and lane 0's acquire (handed on by the shuffle) before every lane's loads below.
             __syncwarp();
             unsigned int seen = 0;
-            if (lane == 0) seen = atomicAdd(a.counters + rt, 1u);
+            if (lane == 0) asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.counters + rt) : "memory");
             seen = __shfl_sync(0xffffffffu, seen, 0);
             finish = seen == a.ksplit - 1;
             if (finish) {
                 if (lane == 0) a.counters[rt] = 0; // ready for the next launch
-                __threadfence();
 #pragma unroll
                 for (int im = 0; im < kImages; ++im)
 #pragma unroll
