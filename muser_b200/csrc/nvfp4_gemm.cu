@@ -31,7 +31,7 @@ constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 static_assert(kSmemBytes <= 227 * 1024, "stage ring exceeds the shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;              // 256 accumulator + 16 SFA + 32 SFB, rounded to a power of two
-constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
+constexpr uint32_t kSfCol = 256, kSfBufCols = 48; // two scale buffers of 16 (SFA) + 32 (SFB) columns behind the accumulator
 
 struct GemmArgs {
     const uint8_t *a_scales; // activations, swizzled
@@ -133,7 +133,7 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 // each factor first rounded to f16 as the unfused W4A4 lane returns it (quant/nvfp4.rs:337).
 // TAIL compiles the LM-head tail (logit scale, tanh soft cap) into the epilogue; the common instantiation has none of it.
 template <bool DUAL, bool TAIL>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
     constexpr uint32_t kTileRows = DUAL ? BN / 2 : BN; // output columns (weight rows) per tile
@@ -143,7 +143,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStages * kStageBytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
     const uint32_t bar_acc_full = smem_u32(bars + 2 * kStages), bar_acc_empty = smem_u32(bars + 2 * kStages + 1);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2);
+    const uint32_t bar_sf_full = smem_u32(bars + 2 * kStages + 2), bar_sf_empty = smem_u32(bars + 2 * kStages + 4);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 6);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,6 +157,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         mbar_init(bar_acc_full, 1);
         mbar_init(bar_acc_empty, 8); // one arrival per epilogue warp
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_sf_full + 8 * b, 1);
+            mbar_init(bar_sf_empty + 8 * b, 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -236,21 +241,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes;
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
-                    const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
-                    auto copy_scales = [&](uint32_t kb) {
-                        tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(sfa + 512 * kb));
-                        tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(sfb + 512 * kb));
-                        tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
-                    };
-                    // the scale copies of block kb + 1 are issued ahead of the MMA of block kb, so they can run under it
-                    copy_scales(0);
-                    for (uint32_t kb = 0; kb < nkb; ++kb) {
-                        if (kb + 1 < nkb) copy_scales(kb + 1);
-                        // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
-                        mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb,
-                                 (kt | kb) != 0);
-                    }
+                    // the scale factors of this slab were copied into tensor memory by the copier warp
+                    const uint32_t buf = it & 1, sf = tmem + kSfCol + buf * kSfBufCols;
+                    ok = mbar_wait(bar_sf_full + 8 * buf, (it >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (uint32_t kb = 0; kb < nkb; ++kb) // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
+                        mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
+                    mma_commit(bar_sf_empty + 8 * buf);
                     mma_commit(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
                 }
                 if (ok) mma_commit(bar_acc_full);
@@ -258,6 +257,35 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (!ok) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 102);
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------------------------------------------------------- scale copier
+        // tcgen05.cp of the slab's scale factors into one of two tensor-memory buffers, issued by a thread of its
+        // own: in the MMA thread's instruction stream the twelve copies of a slab took as long as its four MMAs.
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kStages, round = it / kStages, buf = it & 1;
+                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                    if (ok && it >= 2) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it >> 1) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = base + s * kStageBytes, sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
+                    const uint32_t sf = tmem + kSfCol + buf * kSfBufCols, nkb = min(4u, g.kt64 - 4 * kt);
+                    for (uint32_t kb = 0; kb < nkb; ++kb) {
+                        tmem_cp_scales(sf + 4 * kb, scale_desc(sfa + 512 * kb));
+                        tmem_cp_scales(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
+                        tmem_cp_scales(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                    }
+                    mma_commit(bar_sf_full + 8 * buf);
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(g.status + 1, 0, 105);
             }
         }
     } else {
@@ -369,14 +397,14 @@ __global__ void __launch_bounds__(192, 1) nvfp4_peak_kernel(uint32_t iters, int 
         const uint64_t da = operand_desc(base), db = operand_desc(base + kABytes);
         // scale factors: one copy of zeroed chunks so that the accumulator stays finite
         for (uint32_t kb = 0; kb < 4; ++kb) {
-            tmem_cp_scales(tmem + kSfaCol + 4 * kb, scale_desc(base + kABytes + kBBytes));
-            tmem_cp_scales(tmem + kSfbCol + 8 * kb, scale_desc(base + kABytes + kBBytes));
-            tmem_cp_scales(tmem + kSfbCol + 8 * kb + 4, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales(tmem + kSfCol + 4 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales(tmem + kSfCol + 16 + 8 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales(tmem + kSfCol + 16 + 8 * kb + 4, scale_desc(base + kABytes + kBBytes));
         }
         for (uint32_t i = 0; i < iters; ++i)
 #pragma unroll
             for (uint32_t kb = 0; kb < 4; ++kb)
-                mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfaCol + 4 * kb, tmem + kSfbCol + 8 * kb, (i | kb) != 0);
+                mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfCol + 4 * kb, tmem + kSfCol + 16 + 8 * kb, (i | kb) != 0);
         mma_commit(bar_done);
         if (!mbar_wait(bar_done, 0, abort_flag)) atomicExch(status + 1, 104);
     }
@@ -494,11 +522,11 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
     const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
     if (w_up)
-        nvfp4_gemm_kernel<true, false><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
+        nvfp4_gemm_kernel<true, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
     else if (tail)
-        nvfp4_gemm_kernel<false, true><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+        nvfp4_gemm_kernel<false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
     else
-        nvfp4_gemm_kernel<false, false><<<grid, 320, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+        nvfp4_gemm_kernel<false, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
