@@ -31,7 +31,7 @@ constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 static_assert(kSmemBytes <= 227 * 1024, "stage ring exceeds the shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;              // 256 accumulator + 16 SFA + 32 SFB, rounded to a power of two
-constexpr uint32_t kSfCol = 256, kSfBufCols = 48; // two scale buffers of 16 (SFA) + 32 (SFB) columns behind the accumulator
+constexpr uint32_t kSfCol = 256, kSfBufCols = 48, kSfBufs = 4; // scale buffers of 16 (SFA) + 32 (SFB) columns behind the accumulator
 
 struct GemmArgs {
     const uint8_t *a_scales; // activations, swizzled
@@ -143,8 +143,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStages * kStageBytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
     const uint32_t bar_acc_full = smem_u32(bars + 2 * kStages), bar_acc_empty = smem_u32(bars + 2 * kStages + 1);
-    const uint32_t bar_sf_full = smem_u32(bars + 2 * kStages + 2), bar_sf_empty = smem_u32(bars + 2 * kStages + 4);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 6);
+    const uint32_t bar_sf_full = smem_u32(bars + 2 * kStages + 2), bar_sf_empty = smem_u32(bars + 2 * kStages + 2 + kSfBufs);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 + 2 * kSfBufs);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -157,7 +157,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         mbar_init(bar_acc_full, 1);
         mbar_init(bar_acc_empty, 8); // one arrival per epilogue warp
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < (int)kSfBufs; ++b) {
             mbar_init(bar_sf_full + 8 * b, 1);
             mbar_init(bar_sf_empty + 8 * b, 1);
         }
@@ -243,8 +243,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
                     // the scale factors of this slab were copied into tensor memory by the copier warp
-                    const uint32_t buf = it & 1, sf = tmem + kSfCol + buf * kSfBufCols;
-                    ok = mbar_wait(bar_sf_full + 8 * buf, (it >> 1) & 1, abort_flag);
+                    const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
+                    ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb) // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
@@ -268,9 +268,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % kStages, round = it / kStages, buf = it & 1;
+                    const uint32_t s = it % kStages, round = it / kStages, buf = it % kSfBufs;
                     ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
-                    if (ok && it >= 2) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it >> 1) - 1) & 1, abort_flag);
+                    if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes, sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
