@@ -16,11 +16,13 @@
 // One CTA per SM, persistent over (128-row block, K slice) items:
 //   warp 0      TMA: activation slabs (N tokens x 128 inputs, 128-byte swizzle) and the X_j pairs (32-byte swizzle)
 //   warp 1      tcgen05.mma kind::f16, M = 128 rows, N = tokens (16 / 32 / 64), K = 16; accumulators in tensor memory,
-//               two buffers so that the drain of one super-block column runs under the MMAs of the next
-//   warps 2-17  eight rows of one 16-row weight tile each: bulk copies global -> shared (two tiles in flight per warp),
-//               unpack to the f16 integers above, store into the swizzled A stage (three stages of 128 inputs)
-//   warps 18-..  drain (four warps; eight at N = 64, 32 token columns each, so that the running sums stay in registers): tcgen05.ld, scale by d / dmin (f32), keep N running sums per row in registers; at the end of
-//               an item add the K slices through the context scratch (last arriver sums in slice order) and store
+//               four buffers so that the drain of one super-block column runs under the MMAs of the next ones
+//   warps 2-17  eight rows of one 16-row weight tile each: bulk copies global -> shared (three or four tiles in flight
+//               per warp), unpack to the f16 integers above, store into the swizzled A stage (two stages of 128 inputs)
+//   warps 18-.. drain (four warps; eight from 32 token columns on, half the columns each, so that the running sums
+//               stay in registers): tcgen05.ld, scale by d / dmin (f32), keep the running sums per row in registers;
+//               at the end of an item add the K slices through the context scratch (last arriver sums in slice
+//               order) and store
 // Every wait is bounded; a wait that gives up records a code in the context's status word and the CTA winds down.
 #include <algorithm>
 #include <cmath>
@@ -44,7 +46,7 @@ struct TcArgs {
     float out_scale, softcap; // LM-head tail
     const void *residual;
     float *partial;         // [ksplit][tokens][n_out] partial sums (ksplit > 1)
-    unsigned int *counters; // [row_blocks * 4] arrival counters, zero between launches
+    unsigned int *counters; // [row_blocks * 8] arrival counters (row quarter x column half), zero between launches
     int *status;
     uint32_t n_out, nsb, row_tiles, tokens, y_bf16;
     uint32_t fold;          // f32 activations travel as f16 head + remainder in columns 2t and 2t + 1: add the pairs
