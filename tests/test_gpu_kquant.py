@@ -205,6 +205,27 @@ def test_tensor_parallel_shards(gpu, dtype):
         acc += yk
     assert torch.equal(torch.cat(parts, dim=1), y_full)
     assert H.rel_l2(acc.cpu().numpy(), y_full.cpu().numpy()) <= 1e-5
+    # the same K shards (first tile starts before the shard's first input on odd ranks) through the tcgen05 kernel,
+    # bf16 and f32 activations, against the CPU lane on the whole tensor
+    ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1)
+    key = op.TUNE_TC_MIN_TOKENS_Q4_K if dtype == O.Q4_K else op.TUNE_TC_MIN_TOKENS_Q6_K
+    ctx.tuning_set(key, 1)
+    try:
+        ow = O.TensorView(raw, dtype, n_in, n_out)
+        for x_dtype, toks in ((torch.bfloat16, 20), (torch.float32, 9)):
+            xs = torch.from_numpy(H.lcg_activations(toks * n_in, seed=toks).reshape(toks, n_in)).to(x_dtype).cuda()
+            want = O.matmul(ow, xs.float().cpu().numpy())
+            acc = torch.zeros((toks, n_out), dtype=torch.float32, device="cuda")
+            for rank in range(world):
+                wk = op.Weight(ctx, view, shard=(rank, world, op.SHARD_K))
+                yk = torch.empty((toks, n_out), dtype=torch.float32, device="cuda")
+                k.encode_quantized_matmul(wk, xs[:, rank * ks:(rank + 1) * ks].contiguous(), yk, toks)
+                acc += yk
+            ctx.sync_status()
+            assert H.rel_l2(acc.cpu().numpy(), want) <= REL_L2_TOL, x_dtype
+    finally:
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+        ctx.tuning_set(key, 12 if dtype == O.Q4_K else 5)
 
 
 def test_config1_full_size_q4k_gemv(gpu):
