@@ -125,6 +125,9 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_TC_MIN_TOKENS_Q4_K 1u /* Q4_K calls with at least this many tokens take the tcgen05 kernel (default 12) */
 #define MUSER_TUNE_TC_MIN_TOKENS_Q6_K 2u /* likewise for Q6_K (default 5) */
 #define MUSER_TUNE_TC_MIN_ROWS 3u        /* ... if the weight has at least this many output rows (default 2048) */
+#define MUSER_TUNE_GEMV_MAX_TOKENS_Q4_K 4u /* Q4_K calls with at most this many tokens take the decode GEMV (default 2, at most 8) */
+#define MUSER_TUNE_GEMV_MAX_TOKENS_Q6_K 5u /* likewise for Q6_K (default 4) */
+#define MUSER_TUNE_MATMUL_WARPS 6u       /* warps that split K in a CTA of the general skinny kernel, 1-8 (default 0: chosen per weight) */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file

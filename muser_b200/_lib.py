@@ -13,6 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmuser_cuda.so"
 F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
 SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
 TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
+TUNE_GEMV_MAX_TOKENS_Q4_K, TUNE_GEMV_MAX_TOKENS_Q6_K, TUNE_MATMUL_WARPS = 4, 5, 6
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 

@@ -260,6 +260,12 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
     case MUSER_TUNE_TC_MIN_TOKENS_Q4_K: ctx->tc_min_tokens[0] = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_TC_MIN_TOKENS_Q6_K: ctx->tc_min_tokens[1] = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_TC_MIN_ROWS: ctx->tc_min_rows = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_GEMV_MAX_TOKENS_Q4_K: ctx->gemv_max_tokens[0] = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_GEMV_MAX_TOKENS_Q6_K: ctx->gemv_max_tokens[1] = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_MATMUL_WARPS:
+        if (value > 8) return fail(ctx, MUSER_CUDA_BAD_ARG, "at most 8 warps");
+        ctx->matmul_warps = value;
+        return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
 }

@@ -36,6 +36,8 @@ struct Ctx {
     size_t tc_scratch_bytes = 0;
     uint32_t tc_min_tokens[2] = {12, 5};   // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
     uint32_t tc_min_rows = 2048;           // and from how many output rows: measured crossovers)
+    uint32_t matmul_warps = 0;             // 0: the general skinny kernel picks its warps per CTA from the weight's shape
+    uint32_t gemv_max_tokens[2] = {2, 4};  // up to how many tokens Q4_K / Q6_K calls take the decode GEMV
     float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
     size_t norm_scratch_bytes = 0;
     cudaStream_t copy_stream = nullptr;

@@ -441,15 +441,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32) kquant_matmul_kernel(const KqA
 
 template <int DT, int MT, int NT, bool XF32, bool DUAL>
 static cudaError_t launch_one(const KqArgs &a, int warps, int sm_count, cudaStream_t stream) {
-    static int ctas_per_sm = 0; // occupancy of this instantiation at full CTA width, queried once
-    if (ctas_per_sm == 0) {
+    static int ctas_per_sm[kMaxWarps + 1] = {}; // occupancy of this instantiation per CTA width, queried once each
+    if (ctas_per_sm[warps] == 0) {
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-            &n, kquant_matmul_kernel<DT, MT, NT, XF32, DUAL>, kMaxWarps * 32, 0);
+            &n, kquant_matmul_kernel<DT, MT, NT, XF32, DUAL>, warps * 32, 0);
         if (e != cudaSuccess) return e;
-        ctas_per_sm = n > 0 ? n : 1;
+        ctas_per_sm[warps] = n > 0 ? n : 1;
     }
-    const uint32_t resident = (uint32_t)(ctas_per_sm * (kMaxWarps / warps) * sm_count);
+    const uint32_t resident = (uint32_t)(ctas_per_sm[warps] * sm_count);
     dim3 grid(a.row_tiles < resident ? a.row_tiles : resident), block(warps * 32);
     kquant_matmul_kernel<DT, MT, NT, XF32, DUAL><<<grid, block, 0, stream>>>(a);
     return cudaGetLastError();
@@ -481,7 +481,7 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     const uint32_t tc_set = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
     const uint32_t tc_from = (xf32_in && tc_set <= 64) ? std::min(tc_set, 5u) : tc_set;
     const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32_in ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
-    if (!tc_fits && tokens <= (q6 ? 4u : 2u)) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
+    if (!tc_fits && tokens <= ctx->gemv_max_tokens[q6 ? 1 : 0]) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
         const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, x_dtype, y, y_dtype, tokens, ep, stream);
         if (ge != cudaErrorNotSupported) {
             MUSER_CUDA_TRY(ctx, ge);
@@ -524,7 +524,19 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     a.y_bf16 = y_dtype == MUSER_DTYPE_BF16;
     a.row_tiles = w->row_tiles;
     const bool xf32 = x_dtype == MUSER_DTYPE_F32, dual = w_up != nullptr;
-    const int warps = w->nsb >= 8 ? 8 : (w->nsb >= 4 ? 4 : (w->nsb >= 2 ? 2 : 1));
+    // Warps that split K inside a CTA.  A warp pays about two tiles' worth of start-up (its first load, its share of
+    // the CTA's reduction) per row tile, so with row tiles to spare the cheapest split is the one with the smallest
+    // warps x (longest K run + 2): 4 warps x 5 tiles for K = 5120 took 35 us where 8 warps x 3 took 42 (ffn_gate,
+    // 4 tokens).  A weight with few row tiles needs all 8 warps to keep the SMs' load queues full.
+    int warps = w->nsb >= 8 ? 8 : (w->nsb >= 4 ? 4 : (w->nsb >= 2 ? 2 : 1));
+    if (w->nsb >= 8 && w->row_tiles >= 2u * (uint32_t)ctx->sm_count) {
+        uint32_t best = ~0u;
+        for (int c = 4; c <= kMaxWarps; ++c) {
+            const uint32_t cost = (uint32_t)c * ((w->nsb + c - 1) / c + 2);
+            if (cost < best) best = cost, warps = c;
+        }
+    }
+    if (ctx->matmul_warps) warps = (int)std::min(ctx->matmul_warps, w->nsb);
     const int sms = ctx->sm_count;
     cudaError_t e;
     if (w->dtype == MUSER_DTYPE_Q4_K) {

@@ -22,8 +22,9 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, TUNE_TC_MIN_ROWS,
-                   TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
+from ._lib import (BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, TUNE_GEMV_MAX_TOKENS_Q4_K,
+                   TUNE_GEMV_MAX_TOKENS_Q6_K, TUNE_MATMUL_WARPS, TUNE_TC_MIN_ROWS, TUNE_TC_MIN_TOKENS_Q4_K,
+                   TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
 
 _L = _lib.lib
 _TORCH_DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -68,7 +69,7 @@ class Context:
         self.check(_L.muser_cuda_sync_status(self._h, _stream_ptr(self.device)))
 
     def tuning_set(self, key: int, value: int) -> None:
-        """muser_cuda_tuning_set: move a kernel-choice threshold (TUNE_TC_MIN_TOKENS_*)."""
+        """muser_cuda_tuning_set: move a kernel-choice threshold (the TUNE_* keys)."""
         self.check(_L.muser_cuda_tuning_set(self._h, key, value))
 
     def close(self) -> None:

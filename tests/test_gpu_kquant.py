@@ -228,6 +228,44 @@ def test_tensor_parallel_shards(gpu, dtype):
         ctx.tuning_set(key, 12 if dtype == O.Q4_K else 5)
 
 
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_every_kernel_choice_on_the_same_calls(gpu, dtype):
+    """The dispatcher's thresholds moved both ways: the decode GEMV for every token count it can take (1 to 8, all
+    its token-group variants) and the general skinny kernel with 1 to 8 warps splitting K, bf16 and f32
+    activations, against the CPU lane; a fixed choice must also give identical bits on a repeated call."""
+    op, ctx, k = gpu
+    n_in, n_out = 2560, 5000          # 10 K tiles (not divisible by most warp counts), a short last row tile
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=123 + dtype)
+    ow = O.TensorView(raw, dtype, n_in, n_out)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    gemv_key = op.TUNE_GEMV_MAX_TOKENS_Q4_K if dtype == O.Q4_K else op.TUNE_GEMV_MAX_TOKENS_Q6_K
+    tc_key = op.TUNE_TC_MIN_TOKENS_Q4_K if dtype == O.Q4_K else op.TUNE_TC_MIN_TOKENS_Q6_K
+    try:
+        ctx.tuning_set(tc_key, 65)
+        for x_dtype in (torch.bfloat16, torch.float32):
+            for tokens in (1, 2, 3, 4, 5, 7, 8):
+                x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=40 + tokens).reshape(tokens, n_in)).to(x_dtype).cuda()
+                want = O.matmul(ow, x.float().cpu().numpy())
+                choices = [(8, 0)] + [(0, warps) for warps in (1, 2, 3, 4, 5, 6, 7, 8)]
+                for gemv_max, warps in choices if tokens in (3, 8) else choices[:1] + choices[4:5]:
+                    ctx.tuning_set(gemv_key, gemv_max)
+                    ctx.tuning_set(op.TUNE_MATMUL_WARPS, warps)
+                    y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+                    k.encode_quantized_matmul(w, x, y, tokens)
+                    again = torch.empty_like(y)
+                    k.encode_quantized_matmul(w, x, again, tokens)
+                    ctx.sync_status()
+                    assert torch.equal(y, again), (x_dtype, tokens, gemv_max, warps)
+                    assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, (x_dtype, tokens, gemv_max, warps)
+        with pytest.raises(op.MuserCudaError):
+            ctx.tuning_set(op.TUNE_MATMUL_WARPS, 9)
+    finally:
+        ctx.tuning_set(gemv_key, 2 if dtype == O.Q4_K else 4)
+        ctx.tuning_set(op.TUNE_MATMUL_WARPS, 0)
+        ctx.tuning_set(tc_key, 12 if dtype == O.Q4_K else 5)
+        w.free()
+
+
 def test_config1_full_size_q4k_gemv(gpu):
     """y[1,27648] = x[1,5120] . W(Q4_K): every dequantised weight bit-exact, output within tolerance."""
     op, ctx, k = gpu
