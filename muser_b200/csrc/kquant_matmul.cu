@@ -481,7 +481,11 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     const uint32_t tc_set = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
     const uint32_t tc_from = (xf32_in && tc_set <= 64) ? std::min(tc_set, 5u) : tc_set;
     const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32_in ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
-    if (!tc_fits && tokens <= ctx->gemv_max_tokens[q6 ? 1 : 0]) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
+    // (a weight of few row tiles cannot fill the GEMV's rings: attn_k / attn_v of 1024 rows take 7.3 / 9.9 us in the
+    //  general kernel at 2 / 4 tokens of bf16, 9.3 / 14.9 us in the GEMV)
+    uint32_t gemv_max = ctx->gemv_max_tokens[q6 ? 1 : 0];
+    if (!xf32_in && w->row_tiles < (uint32_t)ctx->sm_count) gemv_max = std::min(gemv_max, q6 ? 2u : 1u);
+    if (!tc_fits && tokens <= gemv_max) { // bf16 or f32 activations: either becomes 15-bit fixed point per sub-block
         const cudaError_t ge = launch_kquant_gemv(ctx, w, w_up, x, x_dtype, y, y_dtype, tokens, ep, stream);
         if (ge != cudaErrorNotSupported) {
             MUSER_CUDA_TRY(ctx, ge);
