@@ -27,7 +27,9 @@ import torch
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    ref = Path(sys.argv[1])
     sys.path.insert(0, str(ref / "scripts"))
     sys.path.insert(0, str(ref / "scripts" / "gx10" / "vllm"))
     import nvfp4_codec
