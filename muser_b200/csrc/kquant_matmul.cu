@@ -479,7 +479,11 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     //  it carries them as f16 head + remainder column pairs, hence at most 32 tokens)
     const bool xf32_in = x_dtype == MUSER_DTYPE_F32;
     const uint32_t tc_set = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
-    const uint32_t tc_from = (xf32_in && tc_set <= 64) ? std::min(tc_set, 5u) : tc_set;
+    uint32_t tc_from = (xf32_in && tc_set <= 64) ? std::min(tc_set, 5u) : tc_set;
+    // (a Q4_K weight with fewer than 8 row tiles per SM gives the tcgen05 kernel too few 128-row blocks: on attn_q,
+    //  5120 rows, the general kernel takes 17.7 us up to 16 tokens of bf16 against 21.8; a threshold set below the
+    //  default is a caller's explicit choice and stands)
+    if (!q6 && !xf32_in && tc_from >= 12 && tc_from <= 16 && w->row_tiles < 8u * (uint32_t)ctx->sm_count) tc_from = 17;
     const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32_in ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
     // (a weight of few row tiles cannot fill the GEMV's rings: attn_k / attn_v of 1024 rows take 7.3 / 9.9 us in the
     //  general kernel at 2 / 4 tokens of bf16, 9.3 / 14.9 us in the GEMV)
