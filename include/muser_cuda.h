@@ -78,7 +78,10 @@ typedef struct muser_cuda_shard {
  * rows), :511-513 (silu(gate)*up, through muser_cuda_ffn_gate_up_silu) and :475-477,536-538 (residual add). */
 typedef struct muser_cuda_epilogue {
     const float *row_scale; /* [tokens] multiplies every output row, or NULL */
-    const void *residual;   /* [tokens][n_out] in y's dtype, added after scaling, or NULL */
+    const void *residual;   /* [tokens][n_out] in y's dtype, added after scaling, or NULL.  On a K-sharded weight the
+                             * outputs are partial sums that the ranks add afterwards: pass the residual on ONE rank
+                             * only (the others NULL), or it is added `world` times.  For the same reason softcap
+                             * is refused on K shards (MUSER_CUDA_BAD_SHAPE). */
     uint32_t swiglu;        /* must be 0: the fused SwiGLU takes two weights, see muser_cuda_ffn_gate_up_silu */
     float norm_eps;         /* eps of the fused input norm (used when norm_weight is set) */
     const float *norm_weight; /* [n_in] f32 on the device, or NULL.  Set: the projection reads
@@ -232,6 +235,10 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muse
  * muser_cuda_last_error(NULL). */
 MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda_weight *w, const void *x, uint32_t x_dtype,
                                                                 void *y, uint32_t y_dtype, uint32_t tokens, void *stream);
+/* No counterpart in the reference.  muser_cuda_sync_status for the call above, which has no context: synchronizes
+ * `stream` on `device` and reports MUSER_CUDA_TIMEOUT if a bounded wait inside one of that path's kernels gave up
+ * since the last check (the output of such a call is incomplete), then clears the record.  Allocates nothing. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_static_sync_status(int device, void *stream);
 
 /* Measurement aid, no counterpart in the reference (its kernel bench prints TMAC/s without a ceiling,
  * crates/muser-bench/src/m16.rs:755-774): enqueues a kernel in which every SM issues `iters` x 4 block-scaled FP4
@@ -243,6 +250,12 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *ctx, 
  * built on: every SM issues iters x 4 tcgen05.mma kind::f16 (128 rows x n_cols x 16, n_cols in {16,32,64,128,256})
  * back to back on resident operands; returns SM clock cycles per instruction.  Synchronizes the device. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *ctx, uint32_t n_cols, uint32_t iters, double *cycles_per_mma);
+
+/* Test aid, no counterpart in the reference.  Runs the give-up path of the kernels' bounded waits on its own: one
+ * thread polls a barrier that nobody arrives at `polls` times (1..65536), records a give-up code as the kernels do
+ * and returns.  The next muser_cuda_sync_status on the context reports MUSER_CUDA_TIMEOUT once; the context stays
+ * usable. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_wait_probe(muser_cuda_ctx *ctx, uint32_t polls, void *stream);
 
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
  * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */

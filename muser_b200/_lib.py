@@ -26,6 +26,7 @@ EXPORTS = [
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
     "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
+    "muser_cuda_static_sync_status", "muser_cuda_wait_probe",
 ]
 
 
@@ -87,6 +88,8 @@ def _load() -> C.CDLL:
         "muser_cuda_tuning_set": (i32, [vp, u32, u32]),
         "muser_cuda_quantized_matmul_rows": (i32, [vp, vp, vp, u32, vp, u32, vp, u32, vp]),
         "muser_cuda_f16_mma_probe": (i32, [vp, u32, u32, C.POINTER(C.c_double)]),
+        "muser_cuda_static_sync_status": (i32, [i32, vp]),
+        "muser_cuda_wait_probe": (i32, [vp, u32, vp]),
         "muser_cuda_rmsnorm_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, vp, f32, f32, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():

@@ -1,13 +1,38 @@
 // C ABI of the library: argument validation, handle lifetime, dispatch.  See include/muser_cuda.h.
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <new>
 
 #include "common.cuh"
 #include "kquant_layout.cuh"
+#include "tcgen05.cuh"
 
 namespace muser {
 thread_local std::string g_create_error;
+
+cudaError_t ensure_dynamic_smem(const void *kernel, int device, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> set;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = set[{kernel, device}];
+    if (bytes <= have) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) have = bytes;
+    return e;
+}
+
+// The give-up path of the kernels' bounded waits, run on its own: one thread waits on a barrier that nobody will
+// ever arrive at, for `polls` polls, then records code 901 the way the kernels record theirs and returns.  Nothing
+// hangs and nothing faults; muser_cuda_sync_status must then report MUSER_CUDA_TIMEOUT once.
+__global__ void wait_probe_kernel(uint32_t polls, int *status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, polls)) atomicExch(status + 1, 901);
+}
 
 static bool is_kquant(uint32_t t) { return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q6_K; }
 
@@ -147,6 +172,8 @@ static muser_cuda_status take_epilogue(Ctx *ctx, const Weight *w, const muser_cu
     if (!(ep->out_scale == ep->out_scale) || !(ep->softcap >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "out_scale / softcap must be numbers, softcap non-negative");
     e->out_scale = ep->out_scale == 0.0f ? 1.0f : ep->out_scale;
     e->softcap = ep->softcap;
+    if (ep->softcap > 0.0f && w->shard.axis == MUSER_SHARD_K && w->shard.world > 1)
+        return fail(ctx, MUSER_CUDA_BAD_SHAPE, "softcap is not linear: it cannot be applied to a K shard's partial sums");
     if (ep->norm_weight) {
         if (w->shard.axis == MUSER_SHARD_K && w->shard.world > 1)
             return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the fused input norm needs whole input rows; this weight is a K shard");
@@ -528,6 +555,15 @@ muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *c, uint32_t iters, d
     if (!ctx || !flops || iters == 0 || iters > (1u << 20)) return fail(ctx, MUSER_CUDA_BAD_ARG, "bad probe arguments");
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_nvfp4_peak(ctx, iters, flops, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_wait_probe(muser_cuda_ctx *c, uint32_t polls, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || polls == 0 || polls > (1u << 16)) return fail(ctx, MUSER_CUDA_BAD_ARG, "polls must be 1..65536");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    wait_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(polls, ctx->dev_status);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
 }
 
 muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *c, uint32_t n_cols, uint32_t iters, double *cycles_per_mma) {

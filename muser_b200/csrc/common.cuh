@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 #include <utility>
 
@@ -112,6 +113,18 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 #endif
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Launch set-up that CUDA keeps per device.  A process may hold contexts on several GPUs and drive them from several
+// host threads, so nothing of it lives in unguarded function-local statics.
+constexpr int kMaxDevices = 64;
+// Raises cudaFuncAttributeMaxDynamicSharedMemorySize of `kernel` on `device` (which must be current) to at least
+// `bytes`; remembers what it set per (kernel, device) under a lock, so repeated calls cost a table lookup.
+cudaError_t ensure_dynamic_smem(const void *kernel, int device, size_t bytes);
+// One slot per device for a launcher's cached plan; lock() before touching a slot.
+template <typename T> struct PerDevice {
+    std::mutex mu;
+    T slot[kMaxDevices];
+};
 
 // ---- launchers implemented in the .cu files ---------------------------------------------------
 struct Epilogue {

@@ -600,31 +600,34 @@ static cudaError_t launch_gemv(GemvArgs &a, Ctx *ctx, cudaStream_t stream) {
         size_t smem = 0;
         uint32_t groups = 0;
     };
-    static Cached cache; // last geometry of this instantiation
-    static size_t smem_set = 0;
-    if (cache.nsb != a.nsb || cache.row_tiles != a.row_tiles || cache.n_out != a.n_out) {
-        GemvPlan p = plan_split(a.nsb, a.row_tiles, ctx->sm_count, Fmt<DT>::kTileBytes, kMeta, NG);
-        const size_t images = DUAL ? 2 : 1;
-        while (p.ksplit > 1 && (size_t)p.ksplit * images * MT * NG * a.n_out * sizeof(float) > ctx->gemv_partial_bytes) --p.ksplit;
-        if (a.row_tiles > ctx->gemv_counter_slots) p.ksplit = 1;
-        const size_t smem = gemv_smem_bytes(a.nsb, p.ksplit, p.warps, Fmt<DT>::kTileBytes, kMeta, NG);
-        if (smem > smem_set) {
-            cudaError_t e = cudaFuncSetAttribute(kquant_gemv_kernel<DT, MT, NG, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static PerDevice<Cached> cached; // last geometry of this instantiation, per device
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return cudaErrorInvalidDevice;
+    Cached cache;
+    {
+        std::lock_guard<std::mutex> lock(cached.mu);
+        Cached &slot = cached.slot[ctx->device];
+        if (slot.nsb != a.nsb || slot.row_tiles != a.row_tiles || slot.n_out != a.n_out) {
+            GemvPlan p = plan_split(a.nsb, a.row_tiles, ctx->sm_count, Fmt<DT>::kTileBytes, kMeta, NG);
+            const size_t images = DUAL ? 2 : 1;
+            while (p.ksplit > 1 && (size_t)p.ksplit * images * MT * NG * a.n_out * sizeof(float) > ctx->gemv_partial_bytes) --p.ksplit;
+            if (a.row_tiles > ctx->gemv_counter_slots) p.ksplit = 1;
+            const size_t smem = gemv_smem_bytes(a.nsb, p.ksplit, p.warps, Fmt<DT>::kTileBytes, kMeta, NG);
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_gemv_kernel<DT, MT, NG, DUAL>), ctx->device, smem);
             if (e != cudaSuccess) return e;
-            smem_set = smem;
+            int per_sm = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_gemv_kernel<DT, MT, NG, DUAL>, p.warps * 32, smem);
+            if (e != cudaSuccess) return e;
+            if (per_sm < 1) return cudaErrorInvalidConfiguration;
+            // CTAs per slice: all that fit at once, but no more than there are row tiles for their warps
+            uint32_t groups = std::max(1u, (uint32_t)per_sm * ctx->sm_count / p.ksplit);
+            const uint32_t wanted = (a.row_tiles + p.warps - 1) / p.warps;
+            if (groups > wanted) groups = wanted;
+            const uint32_t rounds = (wanted + groups - 1) / groups;
+            groups = (wanted + rounds - 1) / rounds;
+            slot.nsb = a.nsb, slot.row_tiles = a.row_tiles, slot.n_out = a.n_out;
+            slot.plan = p, slot.smem = smem, slot.groups = groups;
         }
-        int per_sm = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_gemv_kernel<DT, MT, NG, DUAL>, p.warps * 32, smem);
-        if (e != cudaSuccess) return e;
-        if (per_sm < 1) return cudaErrorInvalidConfiguration;
-        // CTAs per slice: all that fit at once, but no more than there are row tiles for their warps
-        uint32_t groups = std::max(1u, (uint32_t)per_sm * ctx->sm_count / p.ksplit);
-        const uint32_t wanted = (a.row_tiles + p.warps - 1) / p.warps;
-        if (groups > wanted) groups = wanted;
-        const uint32_t rounds = (wanted + groups - 1) / groups;
-        groups = (wanted + rounds - 1) / rounds;
-        cache.nsb = a.nsb, cache.row_tiles = a.row_tiles, cache.n_out = a.n_out;
-        cache.plan = p, cache.smem = smem, cache.groups = groups;
+        cache = slot;
     }
     a.ksplit = cache.plan.ksplit;
     a.groups = cache.groups;

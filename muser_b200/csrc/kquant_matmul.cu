@@ -440,30 +440,39 @@ __global__ void __launch_bounds__(kMaxWarps * 32) kquant_matmul_kernel(const KqA
 }
 
 template <int DT, int MT, int NT, bool XF32, bool DUAL>
-static cudaError_t launch_one(const KqArgs &a, int warps, int sm_count, cudaStream_t stream) {
-    static int ctas_per_sm[kMaxWarps + 1] = {}; // occupancy of this instantiation per CTA width, queried once each
-    if (ctas_per_sm[warps] == 0) {
-        int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-            &n, kquant_matmul_kernel<DT, MT, NT, XF32, DUAL>, warps * 32, 0);
-        if (e != cudaSuccess) return e;
-        ctas_per_sm[warps] = n > 0 ? n : 1;
+static cudaError_t launch_one(const KqArgs &a, int warps, int device, int sm_count, cudaStream_t stream) {
+    struct Occ {
+        int ctas_per_sm[kMaxWarps + 1] = {}; // occupancy of this instantiation per CTA width, queried once each
+    };
+    static PerDevice<Occ> occ;
+    int per_sm;
+    {
+        std::lock_guard<std::mutex> lock(occ.mu);
+        int &slot = occ.slot[device].ctas_per_sm[warps];
+        if (slot == 0) {
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, kquant_matmul_kernel<DT, MT, NT, XF32, DUAL>, warps * 32, 0);
+            if (e != cudaSuccess) return e;
+            slot = n > 0 ? n : 1;
+        }
+        per_sm = slot;
     }
-    const uint32_t resident = (uint32_t)(ctas_per_sm[warps] * sm_count);
+    const uint32_t resident = (uint32_t)(per_sm * sm_count);
     dim3 grid(a.row_tiles < resident ? a.row_tiles : resident), block(warps * 32);
     kquant_matmul_kernel<DT, MT, NT, XF32, DUAL><<<grid, block, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int DT, bool XF32, bool DUAL>
-static cudaError_t launch_tokens(const KqArgs &a, int warps, int sm_count, cudaStream_t stream) {
+static cudaError_t launch_tokens(const KqArgs &a, int warps, int device, int sm_count, cudaStream_t stream) {
     const uint32_t m = a.tokens;
-    if (m <= 4) return launch_one<DT, 4, 1, XF32, DUAL>(a, warps, sm_count, stream);
-    if (m <= 8) return launch_one<DT, 8, 1, XF32, DUAL>(a, warps, sm_count, stream);
-    if (m <= 16) return launch_one<DT, 8, 2, XF32, DUAL>(a, warps, sm_count, stream);
+    if (m <= 4) return launch_one<DT, 4, 1, XF32, DUAL>(a, warps, device, sm_count, stream);
+    if (m <= 8) return launch_one<DT, 8, 1, XF32, DUAL>(a, warps, device, sm_count, stream);
+    if (m <= 16) return launch_one<DT, 8, 2, XF32, DUAL>(a, warps, device, sm_count, stream);
     if constexpr (!DUAL) {
-        if (m <= 32) return launch_one<DT, 8, 4, XF32, false>(a, warps, sm_count, stream);
-        return launch_one<DT, 8, 8, XF32, false>(a, warps, sm_count, stream);
+        if (m <= 32) return launch_one<DT, 8, 4, XF32, false>(a, warps, device, sm_count, stream);
+        return launch_one<DT, 8, 8, XF32, false>(a, warps, device, sm_count, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -548,15 +557,15 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     const int sms = ctx->sm_count;
     cudaError_t e;
     if (w->dtype == MUSER_DTYPE_Q4_K) {
-        if (dual) e = xf32 ? launch_tokens<MUSER_DTYPE_Q4_K, true, true>(a, warps, sms, stream)
-                           : launch_tokens<MUSER_DTYPE_Q4_K, false, true>(a, warps, sms, stream);
-        else e = xf32 ? launch_tokens<MUSER_DTYPE_Q4_K, true, false>(a, warps, sms, stream)
-                      : launch_tokens<MUSER_DTYPE_Q4_K, false, false>(a, warps, sms, stream);
+        if (dual) e = xf32 ? launch_tokens<MUSER_DTYPE_Q4_K, true, true>(a, warps, ctx->device, sms, stream)
+                           : launch_tokens<MUSER_DTYPE_Q4_K, false, true>(a, warps, ctx->device, sms, stream);
+        else e = xf32 ? launch_tokens<MUSER_DTYPE_Q4_K, true, false>(a, warps, ctx->device, sms, stream)
+                      : launch_tokens<MUSER_DTYPE_Q4_K, false, false>(a, warps, ctx->device, sms, stream);
     } else {
-        if (dual) e = xf32 ? launch_tokens<MUSER_DTYPE_Q6_K, true, true>(a, warps, sms, stream)
-                           : launch_tokens<MUSER_DTYPE_Q6_K, false, true>(a, warps, sms, stream);
-        else e = xf32 ? launch_tokens<MUSER_DTYPE_Q6_K, true, false>(a, warps, sms, stream)
-                      : launch_tokens<MUSER_DTYPE_Q6_K, false, false>(a, warps, sms, stream);
+        if (dual) e = xf32 ? launch_tokens<MUSER_DTYPE_Q6_K, true, true>(a, warps, ctx->device, sms, stream)
+                           : launch_tokens<MUSER_DTYPE_Q6_K, false, true>(a, warps, ctx->device, sms, stream);
+        else e = xf32 ? launch_tokens<MUSER_DTYPE_Q6_K, true, false>(a, warps, ctx->device, sms, stream)
+                      : launch_tokens<MUSER_DTYPE_Q6_K, false, false>(a, warps, ctx->device, sms, stream);
     }
     MUSER_CUDA_TRY(ctx, e);
     return MUSER_CUDA_OK;

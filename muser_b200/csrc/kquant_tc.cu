@@ -595,8 +595,11 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 template <bool XF32>
 __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in, uint32_t k_off,
                                                                 uint32_t nsb, __half *__restrict__ xh, __half *__restrict__ xs) {
-    // bf16 activations are exact in f16: output row = token.  f32 activations are carried exactly (to 22 bits) as an
-    // f16 head in row 2t and the remainder in row 2t + 1; the kernel adds the two columns at the end.
+    // Output row = token.  bf16 activations inside f16's range (2^-14 <= |x| <= 65504, which covers normalized
+    // hidden states) are exact in f16; larger magnitudes are clamped to 65504 and smaller ones lose bits, so for such
+    // inputs this kernel's result differs from the exact kernels that serve lower token counts.  f32 activations
+    // are carried (to 22 bits, same range) as an f16 head in row 2t and the remainder in row 2t + 1; the kernel
+    // adds the two columns at the end.
     const uint32_t tile = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
     const uint32_t tok = XF32 ? r >> 1 : r, part = XF32 ? r & 1 : 0;
     const int64_t k = (int64_t)tile * 256 + i - (int64_t)k_off;
@@ -710,14 +713,10 @@ static TcPlan tc_plan(uint32_t nsb, uint32_t row_blocks, int sm_count, uint32_t 
 }
 
 template <int DT, int N>
-static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, const TcArgs &a, int grid, cudaStream_t stream) {
+static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, const TcArgs &a, int device, int grid, cudaStream_t stream) {
     using S = TcSmem<DT, N>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kquant_tc_kernel<DT, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    const cudaError_t ae = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_tc_kernel<DT, N>), device, S::kBytes);
+    if (ae != cudaSuccess) return ae;
     kquant_tc_kernel<DT, N><<<grid, S::kThreads, S::kBytes, stream>>>(mx, mxs, a);
     return cudaGetLastError();
 }
@@ -771,12 +770,12 @@ cudaError_t launch_kquant_tc(Ctx *ctx, const Weight *w, const void *x, uint32_t 
     a.items = plan.whole + (row_blocks - plan.whole) * plan.ksplit;
     const int grid = (int)std::min<uint32_t>(a.items, (uint32_t)ctx->sm_count);
     if (w->dtype == MUSER_DTYPE_Q4_K)
-        return n == 16 ? tc_launch<MUSER_DTYPE_Q4_K, 16>(mx, mxs, a, grid, stream)
-             : n == 32 ? tc_launch<MUSER_DTYPE_Q4_K, 32>(mx, mxs, a, grid, stream)
-                       : tc_launch<MUSER_DTYPE_Q4_K, 64>(mx, mxs, a, grid, stream);
-    return n == 16 ? tc_launch<MUSER_DTYPE_Q6_K, 16>(mx, mxs, a, grid, stream)
-         : n == 32 ? tc_launch<MUSER_DTYPE_Q6_K, 32>(mx, mxs, a, grid, stream)
-                   : tc_launch<MUSER_DTYPE_Q6_K, 64>(mx, mxs, a, grid, stream);
+        return n == 16 ? tc_launch<MUSER_DTYPE_Q4_K, 16>(mx, mxs, a, ctx->device, grid, stream)
+             : n == 32 ? tc_launch<MUSER_DTYPE_Q4_K, 32>(mx, mxs, a, ctx->device, grid, stream)
+                       : tc_launch<MUSER_DTYPE_Q4_K, 64>(mx, mxs, a, ctx->device, grid, stream);
+    return n == 16 ? tc_launch<MUSER_DTYPE_Q6_K, 16>(mx, mxs, a, ctx->device, grid, stream)
+         : n == 32 ? tc_launch<MUSER_DTYPE_Q6_K, 32>(mx, mxs, a, ctx->device, grid, stream)
+                   : tc_launch<MUSER_DTYPE_Q6_K, 64>(mx, mxs, a, ctx->device, grid, stream);
 }
 
 } // namespace muser

@@ -414,11 +414,7 @@ __global__ void __launch_bounds__(192, 1) nvfp4_peak_kernel(uint32_t iters, int 
 }
 
 muser_cuda_status launch_nvfp4_peak(Ctx *ctx, uint32_t iters, double *flops, cudaStream_t stream) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes + 2048));
-        attr_set = true;
-    }
+    MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_peak_kernel), ctx->device, kStageBytes + 2048));
     nvfp4_peak_kernel<<<ctx->sm_count, 192, kStageBytes + 2048, stream>>>(iters, ctx->dev_status);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     *flops = 2.0 * BM * BN * 64 * 4.0 * iters * ctx->sm_count;
@@ -474,13 +470,6 @@ muser_cuda_status nvfp4_build_tensor_map(Ctx *ctx, Weight *w) {
         return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the weight image (128-row boxes)");
     }
     w->tmap_half = half;
-    static bool attr_set = false;
-    if (!attr_set) {
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        MUSER_CUDA_TRY(ctx, cudaFuncSetAttribute(nvfp4_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        attr_set = true;
-    }
     return MUSER_CUDA_OK;
 }
 
@@ -521,6 +510,11 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(w_up ? w->tmap_half : w->tmap_cache);
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
     const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
+    // (the attribute is per device: set where the launch happens, with the launching context's device current)
+    const void *kfn = w_up ? reinterpret_cast<const void *>(nvfp4_gemm_kernel<true, false>)
+                      : tail ? reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, true>)
+                             : reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, false>);
+    MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(kfn, ctx->device, kSmemBytes));
     if (w_up)
         nvfp4_gemm_kernel<true, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
     else if (tail)

@@ -119,3 +119,22 @@ extern "C" muser_cuda_status muser_cuda_nvfp4_matmul_static(const muser_cuda_wei
     if (st != MUSER_CUDA_OK) g_create_error = call.last_error;
     return st;
 }
+
+// The static path's muser_cuda_sync_status: it has no context, so the give-up word of its kernels' bounded waits
+// lives beside the scratch array and is read here.
+extern "C" muser_cuda_status muser_cuda_static_sync_status(int device, void *stream) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return refuse(MUSER_CUDA_ERROR, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    DeviceSetup *setup = nullptr;
+    muser_cuda_status st = device_setup(device, &setup);
+    if (st != MUSER_CUDA_OK) return st;
+    int flags[4] = {0, 0, 0, 0};
+    e = cudaMemcpyAsync(flags, setup->status, sizeof(flags), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return refuse(MUSER_CUDA_ERROR, std::string("static status read: ") + cudaGetErrorString(e));
+    if (flags[1]) {
+        cudaMemsetAsync(setup->status, 0, sizeof(flags), (cudaStream_t)stream);
+        return refuse(MUSER_CUDA_TIMEOUT, "a device-side bounded wait gave up on the static-scratch path (code " + std::to_string(flags[1]) + ")");
+    }
+    return MUSER_CUDA_OK;
+}

@@ -293,6 +293,13 @@ def nvfp4_matmul_static(weights: Weight, input: torch.Tensor, output: torch.Tens
         raise MuserCudaError(st, (_L.muser_cuda_last_error(None) or b"").decode())
 
 
+def static_sync_status(device: int = 0) -> None:
+    """muser_cuda_static_sync_status: the bounded-wait report of the context-free entry point above."""
+    st = _L.muser_cuda_static_sync_status(device, _stream_ptr(device))
+    if st != 0:
+        raise MuserCudaError(st, (_L.muser_cuda_last_error(None) or b"").decode())
+
+
 def matmul(ctx: Context, w: Weight, x: np.ndarray, n_tokens: int, out: np.ndarray | None = None) -> np.ndarray:
     """weights::matmul (weights.rs:398): host f32 slices in and out, the device path in between."""
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(n_tokens, w.n_in)

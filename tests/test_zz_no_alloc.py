@@ -29,13 +29,19 @@ def test_static_scratch_entry_point_matches_context_entry_point_twice():
     isi = synth.activation_input_scale_inv(x_all)
     w = op.Weight(ctx, op.TensorView(wq.numpy(), O.NVFP4, n_in, n_out, ws.numpy(), scale2, isi))
     ow = O.TensorView(wq.numpy(), O.NVFP4, n_in, n_out, ws.numpy(), scale2, isi)
+    calls = 0
     for tokens, y_dtype in ((128, torch.float32), (37, torch.float16)):   # two calls in a row, the second smaller
         x = x_all[:tokens].contiguous().cuda()
         want = torch.full((tokens, n_out), float("nan"), dtype=y_dtype, device="cuda")
         k.encode_nvfp4_matmul(w, x, want, tokens)
         got = torch.full((tokens, n_out), float("nan"), dtype=y_dtype, device="cuda")
-        op.nvfp4_matmul_static(w, x, got, tokens)
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        op.nvfp4_matmul_static(w, x, got, tokens)
+        op.static_sync_status(0)   # synchronizes; raises if a bounded wait inside the call gave up
+        if calls:                  # (the first call on a device may still load the kernels' code)
+            assert torch.cuda.mem_get_info()[0] == free_before, "the static entry point must not allocate device memory"
+        calls += 1
         assert torch.equal(got.view(torch.int16 if y_dtype == torch.float16 else torch.int32),
                            want.view(torch.int16 if y_dtype == torch.float16 else torch.int32))
         ref_f16, ref_f32 = O.matmul(ow, x.float().cpu().numpy(), threads=O.host_threads(), return_pre_round=True)
