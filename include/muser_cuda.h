@@ -131,6 +131,10 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_GEMV_MAX_TOKENS_Q4_K 4u /* Q4_K calls with at most this many tokens take the decode GEMV (default 2, at most 8) */
 #define MUSER_TUNE_GEMV_MAX_TOKENS_Q6_K 5u /* likewise for Q6_K (default 4) */
 #define MUSER_TUNE_MATMUL_WARPS 6u       /* warps that split K in a CTA of the general skinny kernel, 1-8 (default 0: chosen per weight) */
+#define MUSER_TUNE_KQUANT_LAYOUT 7u      /* image layout built by later weight_repack calls: 0 whole sub-blocks per lane, 1 column layout (decode kernel) */
+#define MUSER_TUNE_DECODE_WARPS 8u       /* decode kernel: warps per CTA (0: cost model) */
+#define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: cost model) */
+#define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: cost model) */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file

@@ -86,6 +86,7 @@ static muser_cuda_status repack_common(Ctx *ctx, uint32_t dtype, const uint8_t *
     if (!w) return fail(ctx, MUSER_CUDA_ERROR, "out of host memory");
     w->dtype = dtype;
     w->device = ctx->device;
+    w->layout = is_kquant(dtype) ? ctx->kq_layout : 0;
     muser_cuda_status st = validate_shard(ctx, dtype, n_in, n_out, shard, w);
     auto bail = [&](muser_cuda_status s) {
         muser_cuda_weight_free(reinterpret_cast<muser_cuda_weight *>(w));
@@ -293,6 +294,13 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
         if (value > 8) return fail(ctx, MUSER_CUDA_BAD_ARG, "at most 8 warps");
         ctx->matmul_warps = value;
         return MUSER_CUDA_OK;
+    case MUSER_TUNE_KQUANT_LAYOUT:
+        if (value > 1) return fail(ctx, MUSER_CUDA_BAD_ARG, "layout is 0 or 1");
+        ctx->kq_layout = value;
+        return MUSER_CUDA_OK;
+    case MUSER_TUNE_DECODE_WARPS: ctx->dec_warps = value & ~1u; return MUSER_CUDA_OK;
+    case MUSER_TUNE_DECODE_KSPLIT: ctx->dec_ksplit = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_DECODE_RING: ctx->dec_ring = value; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
 }

@@ -1,0 +1,697 @@
+// Decode / small-batch projection for Q4_K and Q6_K weights, 1 to 16 tokens: y[t][r] = dot(W_r, x_t), for up to
+// four projections of the same input in one launch.
+//
+// Stands in for MetalKernels::encode_quantized_matmul at decode (crates/muser-engine/src/metal/encode/qkv.rs:425-449),
+// encode_quantized_decode_group (qkv.rs:234-281: up to four sequences per dispatch), the one-barrier-interval dispatch
+// of the projections that read the same hidden state (src/decode.rs:5569-5598) and encode_ffn_q4k_gate_up_silu_4r2s
+// (src/metal/encode/ffn.rs:10-36); on the CPU lane, weights::matmul with quant::dot_q4_k_f32 / dot_q6_k_f32
+// (src/weights.rs:398-421) in the deferred-scale order of quant/k_block.rs:178-240 and quant/k_block/q6.rs:90-141.
+//
+// HBM-bound by design: every weight byte is read once, as one bulk copy per 16-row x 256-input tile into a private
+// ring of the warp that consumes it.  The arithmetic is integer until the last step:
+//   - activations become 15-bit fixed point per token and 256-input tile (x ~ sx * (128 hi + lo), two int8 planes,
+//     |error| <= amax(tile) * 2^-15), once per CTA, parked in shared memory in tensor-core fragment order;
+//   - the 4-bit (6-bit) quants go straight from the tile into int8 mma.sync fragments: the image is laid out so that
+//     a lane already owns its fragment's bytes (kquant_layout.cuh, "column" layout);
+//   - one MMA multiplies a whole sub-block (32 weights of 16 rows for Q4_K, 16 for Q6_K) with a group of four
+//     tokens: the eight fragment columns are (token, plane) pairs, so a lane ends up with the high- and low-plane
+//     sums of ITS token for rows g and g + 8 and no value ever crosses lanes;
+//   - the sub-block scale (6-bit, or int8 for Q6_K) is applied to the integer sums with integer multiply-adds, the
+//     Q4_K min term is an integer dot product of the 6-bit mins with the tile's per-sub-block activation sums, and
+//     only the per-256 factors d, dmin and sx are applied in f32, once per tile.
+// Work is cut into (row tile, K slice) items; a CTA keeps one K slice (it stages only that part of the
+// activations), its warps take row tiles in turn and never synchronise after the staging.  With more than one
+// slice the partial sums meet in the context's scratch and the last arriver adds them in slice order
+// (deterministic).  Every wait on a copy barrier is bounded.
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+#include "kquant_layout.cuh"
+#include "rmsnorm.cuh"
+
+namespace muser {
+
+constexpr int kDecMaxJobs = 4;
+constexpr uint32_t kDecWaitLimit = 1u << 22; // polls before a wait gives up
+
+struct DecJob {
+    const uint8_t *image;
+    const uint8_t *image_up; // second weight of the fused gate/up call, else null
+    void *y;
+    const float *row_scale;
+    const void *residual;
+    float out_scale, softcap; // LM-head tail
+    uint32_t dtype, n_out, row_tiles, y_bf16;
+    uint32_t cta0;     // first CTA of this job in the grid
+    uint32_t groups;   // CTAs per K slice
+    uint32_t counter0; // first arrival counter of this job (one per row tile)
+    uint32_t partial0; // first float of this job's partial sums in the scratch
+};
+
+struct DecArgs {
+    DecJob job[kDecMaxJobs];
+    uint32_t n_jobs;
+    const void *x;            // [tokens][n_in], bf16 or (x_f32) f32
+    const float *norm_weight; // fused input RMSNorm (reference.rs:73-80), or null
+    float norm_eps;
+    float *partial;
+    unsigned int *counters; // zero between launches
+    int *status;            // context status words; [1] records a wait that gave up
+    uint32_t n_in, nsb, k_off, tokens, x_f32, ksplit, max_tiles, ring /* tiles in flight per warp: 2 or 4 */;
+};
+
+namespace dec {
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tile_fetch(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool tile_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kDecWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// 16 rows x 32 inputs (Q4_K sub-block): unsigned 4-bit weights as bytes times signed activation bytes
+__device__ __forceinline__ void imma32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// 16 rows x 16 inputs (Q6_K sub-block): signed bytes 4 * (q - 32) times signed activation bytes
+__device__ __forceinline__ void imma16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+__device__ __forceinline__ uint32_t gw(const uint4 &v, int i) { return (&v.x)[i]; } // compile-time i only
+__device__ __forceinline__ int ubyte(uint32_t w, int i) { return (int)__byte_perm(w, 0u, 0x4440u | (uint32_t)i); }
+__device__ __forceinline__ int sbyte(uint32_t w, int i) { // sign-extended byte i: a selector nibble of 8 + i replicates that byte's sign bit
+    const uint32_t s = 8u | (uint32_t)i;
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"((s << 12) | (s << 8) | (s << 4) | (uint32_t)i));
+    return r;
+}
+
+template <int DT> struct Fmt;
+template <> struct Fmt<MUSER_DTYPE_Q4_K> { static constexpr int kTileBytes = kQ4TileBytes; };
+template <> struct Fmt<MUSER_DTYPE_Q6_K> { static constexpr int kTileBytes = kQ6TileBytes; };
+
+constexpr int kFragU4 = 128; // uint4 of B fragments per (tile, token group): 4 fragment quads x 32 lanes
+constexpr int kMetaU4 = 3;   // uint4 per (tile, token): sx, then the eight sub-block sums of a Q4_K tile
+
+// ------------------------------------------------------------------------------------ activation staging
+// One warp turns one (tile, token) into fragment bytes: lane l holds inputs 8l .. 8l+7 of the tile.
+//   Q4_K: sub-block j = l / 4, quarter tq = l % 4; the lane's eight values are exactly what fragment lane (., tq)
+//         feeds for that sub-block: b0 = elements (0, 4, 1, 5) of its eight (the order in which the low nibbles of a
+//         weight word come out), b1 = elements (2, 6, 3, 7).  Entry (tile, group, j / 2, column, tq) is a uint4
+//         (b0_j, b1_j, b0_j+1, b1_j+1) for even j; the column is 2 * (token % 4) + plane.
+//   Q6_K: sub-block s = l / 2; the lane's values are the bytes of fragment lanes 2 * (l % 2) and 2 * (l % 2) + 1.
+//         Entry (tile, group, s / 4, column, t) is a uint4 over sub-blocks 4 * (s / 4) .. + 3.
+template <int DT, int NG>
+__device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint32_t n_tiles, uint4 *frag, uint4 *meta, const float *inv_rms) {
+    constexpr int TOK = 4 * NG;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    uint32_t *fw = reinterpret_cast<uint32_t *>(frag), *mw = reinterpret_cast<uint32_t *>(meta);
+    for (uint32_t task = warp; task < n_tiles * TOK; task += warps) {
+        const uint32_t tile = task / TOK, tok = task % TOK, gp = tok >> 2, t4 = tok & 3;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        const int64_t k = (int64_t)(sb_first + tile) * 256 - (int64_t)a.k_off + 8 * lane;
+        if (tok < a.tokens && (uint64_t)k < a.n_in) { // a negative k wraps to a huge value
+            if (a.x_f32) load8<true>(reinterpret_cast<const float *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
+            else load8<false>(reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
+            if (a.norm_weight) { // (x * 1/rms) * weight, in that order
+                const float rs = inv_rms[tok];
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k)), w1 = __ldg(reinterpret_cast<const float4 *>(a.norm_weight + k) + 1);
+                const float nw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], rs), nw[i]);
+            }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const bool usable = amax > 0.f && amax < 3.0e38f; // an all-zero or non-finite tile contributes nothing
+        const float inv = usable ? __fdiv_rn(16383.0f, amax) : 0.f;
+        int xi[8], sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            xi[i] = __float2int_rn(v[i] * inv);
+            sum += xi[i];
+        }
+        auto pack = [&](int e0, int e1, int e2, int e3, uint32_t &hi, uint32_t &lo) {
+            const int e[4] = {e0, e1, e2, e3};
+            hi = lo = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                hi |= (uint32_t)((xi[e[b]] >> 7) & 0xFF) << (8 * b);
+                lo |= (uint32_t)(xi[e[b]] & 127) << (8 * b);
+            }
+        };
+        const float sx = usable ? __fdiv_rn(amax, 16383.0f) : 0.f;
+        uint32_t *mrow = mw + (size_t)(tile * TOK + tok) * (kMetaU4 * 4);
+        uint32_t *fbase = fw + (size_t)(tile * NG + gp) * (kFragU4 * 4);
+        if constexpr (DT == MUSER_DTYPE_Q4_K) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const uint32_t j = lane >> 2, tq = lane & 3;
+            uint32_t h0, l0, h1, l1;
+            pack(0, 4, 1, 5, h0, l0);
+            pack(2, 6, 3, 7, h1, l1);
+            uint32_t *e = fbase + (((j >> 1) * 32 + (2 * t4) * 4 + tq) * 4 + (j & 1) * 2);
+            *reinterpret_cast<uint2 *>(e) = make_uint2(h0, h1);      // column 2 * t4: high plane
+            *reinterpret_cast<uint2 *>(e + 16) = make_uint2(l0, l1); // column 2 * t4 + 1: low plane
+            if (tq == 0) mrow[1 + j] = (uint32_t)sum;
+            if (lane == 0) mrow[0] = __float_as_uint(sx);
+        } else {
+            const uint32_t s = lane >> 1, t = 2 * (lane & 1);
+            uint32_t h0, l0, h1, l1;
+            pack(0, 1, 2, 3, h0, l0);
+            pack(4, 5, 6, 7, h1, l1);
+            uint32_t *e = fbase + (((s >> 2) * 32 + (2 * t4) * 4 + t) * 4 + (s & 3));
+            e[0] = h0, e[4] = h1;   // fragment lanes t and t + 1 of the high-plane column
+            e[16] = l0, e[20] = l1; // and of the low-plane column
+            if (lane == 0) mrow[0] = __float_as_uint(sx * 0.25f); // the fragment bytes are 4 * (q - 32)
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ Q4_K tile
+struct Q4Regs {
+    uint4 q[4]; // [2*rowsel + half]: row g + 8*rowsel, word jj = sub-block 4*half + jj, this lane's eight elements
+    uint4 ha, hb;
+};
+__device__ __forceinline__ Q4Regs load_regs(const uint8_t *tile, int lane, Q4Regs *) { // tile: shared memory
+    Q4Regs r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(tile);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = q[32 * i + lane];
+    const uint4 *h = reinterpret_cast<const uint4 *>(tile + 2048);
+    r.ha = h[lane >> 2];
+    r.hb = h[(lane >> 2) + 8];
+    return r;
+}
+struct Q4Hdr {
+    float d, dmin;
+    uint32_t sc[2], mn[2]; // 6-bit values as bytes: sub-blocks 0-3, 4-7 (quant/k_block.rs:22-31)
+};
+__device__ __forceinline__ Q4Hdr q4_hdr(uint4 h) {
+    Q4Hdr s;
+    const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
+    s.d = __low2float(dd);
+    s.dmin = __high2float(dd);
+    s.sc[0] = h.y & 0x3F3F3F3Fu;
+    s.mn[0] = h.z & 0x3F3F3F3Fu;
+    s.sc[1] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+    s.mn[1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    return s;
+}
+
+// out[gp][0 / 1]: row g / g + 8, token 4 * gp + t.  fb: this lane's fragment entries of the tile; mt: the tile's meta.
+template <int NG>
+__device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+    const Q4Hdr ha = q4_hdr(r.ha), hb = q4_hdr(r.hb);
+    int acc[NG][4];
+#pragma unroll
+    for (int gp = 0; gp < NG; ++gp) acc[gp][0] = acc[gp][1] = acc[gp][2] = acc[gp][3] = 0;
+#pragma unroll
+    for (int jp = 0; jp < 4; ++jp) {
+        uint4 b[NG];
+#pragma unroll
+        for (int gp = 0; gp < NG; ++gp) b[gp] = fb[(gp * 4 + jp) * 32];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int j = 2 * jp + e;
+            const uint32_t wa = gw(r.q[j >> 2], j & 3), wb = gw(r.q[2 + (j >> 2)], j & 3);
+            const uint32_t a0 = wa & 0x0F0F0F0Fu, a2 = (wa >> 4) & 0x0F0F0F0Fu;
+            const uint32_t a1 = wb & 0x0F0F0F0Fu, a3 = (wb >> 4) & 0x0F0F0F0Fu;
+            const int sa = ubyte(ha.sc[j >> 2], j & 3), sb = ubyte(hb.sc[j >> 2], j & 3);
+#pragma unroll
+            for (int gp = 0; gp < NG; ++gp) {
+                int d[4];
+                imma32(d, a0, a1, a2, a3, e ? b[gp].z : b[gp].x, e ? b[gp].w : b[gp].y);
+                acc[gp][0] += sa * d[0];
+                acc[gp][1] += sa * d[1];
+                acc[gp][2] += sb * d[2];
+                acc[gp][3] += sb * d[3];
+            }
+        }
+    }
+    int ma[8], mb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ma[j] = ubyte(ha.mn[j >> 2], j & 3), mb[j] = ubyte(hb.mn[j >> 2], j & 3);
+#pragma unroll
+    for (int gp = 0; gp < NG; ++gp) {
+        const uint4 *m = mt + (gp * 4 + t) * kMetaU4;
+        const uint4 m0 = m[0], m1 = m[1], m2 = m[2];
+        const int s[8] = {(int)m0.y, (int)m0.z, (int)m0.w, (int)m1.x, (int)m1.y, (int)m1.z, (int)m1.w, (int)m2.x};
+        int mina = 0, minb = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mina += ma[j] * s[j], minb += mb[j] * s[j];
+        const float sx = __uint_as_float(m0.x);
+        const float pa = fmaf(128.0f, (float)acc[gp][0], (float)acc[gp][1]), pb = fmaf(128.0f, (float)acc[gp][2], (float)acc[gp][3]);
+        out[gp][0] = fmaf(sx, fmaf(-ha.dmin, (float)mina, ha.d * pa), out[gp][0]);
+        out[gp][1] = fmaf(sx, fmaf(-hb.dmin, (float)minb, hb.d * pb), out[gp][1]);
+    }
+}
+
+// ------------------------------------------------------------------------------------ Q6_K tile
+struct Q6Regs {
+    uint4 top[4]; // [2*rowsel + half]
+    uint4 low[2]; // [rowsel]
+    uint4 sa, sb;
+    float da, db;
+};
+__device__ __forceinline__ Q6Regs load_regs(const uint8_t *tile, int lane, Q6Regs *) { // tile: shared memory
+    Q6Regs r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(tile);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.top[i] = q[32 * i + lane];
+    const uint4 *h = reinterpret_cast<const uint4 *>(tile + kQ6OffHi);
+    r.low[0] = h[lane];
+    r.low[1] = h[32 + lane];
+    const uint4 *s = reinterpret_cast<const uint4 *>(tile + kQ6OffSc);
+    r.sa = s[lane >> 2];
+    r.sb = s[(lane >> 2) + 8];
+    const __half *d = reinterpret_cast<const __half *>(tile + kQ6OffD);
+    r.da = __half2float(d[lane >> 2]);
+    r.db = __half2float(d[(lane >> 2) + 8]);
+    return r;
+}
+// the signed bytes 4 * (q - 32) of this lane's four elements of sub-block s, row selector rs
+template <int S>
+__device__ __forceinline__ uint32_t q6_bytes(const Q6Regs &r, int rs) {
+    const uint32_t tw = gw(r.top[2 * rs + (S >> 3)], (S & 7) >> 1), lw = gw(r.low[rs], S >> 2);
+    const uint32_t top = (S & 1) ? tw : tw << 4;
+    constexpr int x = S & 3;
+    const uint32_t low = x == 0 ? lw << 2 : x == 1 ? lw : x == 2 ? lw >> 2 : lw >> 4;
+    return (top & 0xF0F0F0F0u) | (low & 0x0C0C0C0Cu);
+}
+
+template <int NG, int S>
+__device__ __forceinline__ void q6_sub_block(const Q6Regs &r, const uint4 (&b)[NG], int (&acc)[NG][4]) {
+    const uint32_t a0 = q6_bytes<S>(r, 0), a1 = q6_bytes<S>(r, 1);
+    const int sa = sbyte(gw(r.sa, S >> 2), S & 3), sb = sbyte(gw(r.sb, S >> 2), S & 3);
+#pragma unroll
+    for (int gp = 0; gp < NG; ++gp) {
+        int d[4];
+        imma16(d, a0, a1, gw(b[gp], S & 3));
+        acc[gp][0] += sa * d[0];
+        acc[gp][1] += sa * d[1];
+        acc[gp][2] += sb * d[2];
+        acc[gp][3] += sb * d[3];
+    }
+}
+
+template <int NG>
+__device__ __forceinline__ void tile_compute(const Q6Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+    int acc[NG][4];
+#pragma unroll
+    for (int gp = 0; gp < NG; ++gp) acc[gp][0] = acc[gp][1] = acc[gp][2] = acc[gp][3] = 0;
+#define MUSER_Q6_QUAD(Q)                                                     \
+    {                                                                        \
+        uint4 b[NG];                                                         \
+        _Pragma("unroll") for (int gp = 0; gp < NG; ++gp) b[gp] = fb[(gp * 4 + (Q)) * 32]; \
+        q6_sub_block<NG, 4 * (Q) + 0>(r, b, acc);                            \
+        q6_sub_block<NG, 4 * (Q) + 1>(r, b, acc);                            \
+        q6_sub_block<NG, 4 * (Q) + 2>(r, b, acc);                            \
+        q6_sub_block<NG, 4 * (Q) + 3>(r, b, acc);                            \
+    }
+    MUSER_Q6_QUAD(0)
+    MUSER_Q6_QUAD(1)
+    MUSER_Q6_QUAD(2)
+    MUSER_Q6_QUAD(3)
+#undef MUSER_Q6_QUAD
+#pragma unroll
+    for (int gp = 0; gp < NG; ++gp) {
+        const float sx = __uint_as_float(mt[(gp * 4 + t) * kMetaU4].x); // includes the 1/4 of the fragment bytes
+        const float pa = fmaf(128.0f, (float)acc[gp][0], (float)acc[gp][1]), pb = fmaf(128.0f, (float)acc[gp][2], (float)acc[gp][3]);
+        out[gp][0] = fmaf(sx * r.da, pa, out[gp][0]);
+        out[gp][1] = fmaf(sx * r.db, pb, out[gp][1]);
+    }
+}
+
+template <int DT> struct RegsOf;
+template <> struct RegsOf<MUSER_DTYPE_Q4_K> { using type = Q4Regs; };
+template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
+
+// ------------------------------------------------------------------------------------ one CTA's work
+// Warp w of CTA group G takes row tiles G * warps + w, + groups * warps, ... and streams the K slice's tiles of each
+// through its own ring.
+template <int DT, int NG, bool DUAL>
+__device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
+    using Regs = typename RegsOf<DT>::type;
+    constexpr int kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = 4 * NG;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sb_first = a.nsb * slice / a.ksplit, sb_last = a.nsb * (slice + 1) / a.ksplit, n_tiles = sb_last - sb_first;
+    const uint32_t ring_n = a.ring, ring_mask = a.ring - 1, ring_shift = a.ring == 4 ? 2 : 1;
+
+    uint4 *frag = dyn;                                                  // max_tiles x NG x 2 KiB
+    uint4 *meta = frag + (size_t)a.max_tiles * NG * kFragU4;            // max_tiles x TOK x 48 bytes
+    uint8_t *ring_base = reinterpret_cast<uint8_t *>(meta + (size_t)a.max_tiles * TOK * kMetaU4);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_base + (size_t)warps * ring_n * kQ6TileBytes); // sized for the larger tile
+    if (threadIdx.x < (unsigned)(warps * ring_n))
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bars + threadIdx.x)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+
+    // this warp's tiles, over all its row tiles, form one stream: n -> (row tile, image, tile); start it before staging
+    const uint32_t first_row = group * warps + warp, row_step = jb.groups * warps;
+    const uint32_t my_rows = jb.row_tiles > first_row ? (jb.row_tiles - first_row + row_step - 1) / row_step : 0;
+    const uint32_t per_row = n_tiles * kImages, total = per_row * my_rows;
+    uint8_t *ring = ring_base + (size_t)warp * ring_n * kBytes;
+    const uint32_t bar0 = smem_addr(bars + warp * ring_n);
+    uint32_t f_tile = first_row * a.nsb + sb_first, f_tl = 0, f_im = 0;
+    auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, lane 0 issues the copy
+        const uint8_t *base = jb.image;
+        if constexpr (DUAL) base = f_im ? jb.image_up : jb.image;
+        if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot);
+        ++f_tile;
+        if (++f_tl == n_tiles) {
+            f_tl = 0;
+            if (DUAL && f_im == 0) {
+                f_im = 1;
+                f_tile -= n_tiles;
+            } else {
+                f_im = 0;
+                f_tile += row_step * a.nsb - n_tiles;
+            }
+        }
+    };
+    __syncthreads(); // barriers initialised
+    for (uint32_t i = 0; i < ring_n && i < total; ++i) fetch_next(i);
+    // the first weight tiles are on their way; everything from here on may depend on the kernel before this one
+    pdl_release();
+    pdl_wait();
+
+    __shared__ float norm_red[33];
+    if (a.norm_weight) { // every CTA needs the whole row's mean square, whatever its K slice
+        for (uint32_t tok = 0; tok < a.tokens; ++tok) {
+            const float r = a.x_f32 ? block_inv_rms<true>(reinterpret_cast<const float *>(a.x) + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red)
+                                    : block_inv_rms<false>(reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)tok * a.n_in, a.n_in, a.norm_eps, norm_red);
+            if (threadIdx.x == 0) inv_rms[tok] = r;
+        }
+        __syncthreads();
+    }
+    stage<DT, NG>(a, sb_first, n_tiles, frag, meta, inv_rms);
+    __syncthreads();
+
+    uint32_t n = 0;
+    bool healthy = true;
+    for (uint32_t rt = first_row; rt < jb.row_tiles; rt += row_step) {
+        float out[kImages][NG][2];
+#pragma unroll
+        for (int im = 0; im < kImages; ++im) {
+#pragma unroll
+            for (int gp = 0; gp < NG; ++gp) out[im][gp][0] = out[im][gp][1] = 0.f;
+            for (uint32_t tl = 0; tl < n_tiles; ++tl, ++n) {
+                const uint32_t slot = n & ring_mask;
+                if (healthy && !tile_wait(bar0 + 8 * slot, (n >> ring_shift) & 1)) {
+                    healthy = false;
+                    atomicExch(a.status + 1, 211);
+                }
+                if (healthy) {
+                    const Regs cur = load_regs(ring + slot * kBytes, lane, (Regs *)nullptr);
+                    __syncwarp(); // every lane has its copy: the slot may be refilled
+                    if (n + ring_n < total) fetch_next(slot);
+                    tile_compute<NG>(cur, frag + (size_t)tl * NG * kFragU4 + lane, meta + (size_t)tl * TOK * kMetaU4, t, out[im]);
+                }
+            }
+        }
+        // this lane now holds, per group gp: [0] -> row g, [1] -> row g + 8, token 4 * gp + t
+        bool finish = true;
+        if (a.ksplit > 1) {
+#pragma unroll
+            for (int im = 0; im < kImages; ++im)
+#pragma unroll
+                for (int gp = 0; gp < NG; ++gp)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint32_t row = rt * 16 + g + 8 * c, tok = 4 * gp + t;
+                        if (row < jb.n_out && tok < a.tokens)
+                            a.partial[jb.partial0 + (((size_t)slice * kImages + im) * TOK + tok) * jb.n_out + row] = out[im][gp][c];
+                    }
+            // Release / acquire through the counter: the warp barrier orders every lane's stores before lane 0's
+            // releasing add, and lane 0's acquire (handed on by the shuffle) before every lane's loads below.
+            __syncwarp();
+            unsigned int seen = 0;
+            if (lane == 0) asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.counters + jb.counter0 + rt) : "memory");
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            finish = seen == a.ksplit - 1;
+            if (finish) {
+                if (lane == 0) a.counters[jb.counter0 + rt] = 0; // ready for the next launch
+#pragma unroll
+                for (int im = 0; im < kImages; ++im)
+#pragma unroll
+                    for (int gp = 0; gp < NG; ++gp)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const uint32_t row = rt * 16 + g + 8 * c, tok = 4 * gp + t;
+                            float sum = 0.f;
+                            if (row < jb.n_out && tok < a.tokens)
+                                for (uint32_t sl = 0; sl < a.ksplit; ++sl)
+                                    sum += __ldcg(a.partial + jb.partial0 + (((size_t)sl * kImages + im) * TOK + tok) * jb.n_out + row);
+                            out[im][gp][c] = sum;
+                        }
+            }
+        }
+        if (finish) {
+#pragma unroll
+            for (int gp = 0; gp < NG; ++gp)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t row = rt * 16 + g + 8 * c, tok = 4 * gp + t;
+                    if (row >= jb.n_out || tok >= a.tokens) continue;
+                    float r = out[0][gp][c];
+                    if constexpr (DUAL) r = __fdiv_rn(r, 1.0f + expf(-r)) * out[1][gp][c]; // silu_fast(gate) * up, quant/helpers.rs:72
+                    const size_t o = (size_t)tok * jb.n_out + row;
+                    if (jb.row_scale) r *= jb.row_scale[tok];
+                    r = logit_tail(r, jb.out_scale, jb.softcap);
+                    if (jb.y_bf16) {
+                        if (jb.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(jb.residual)[o]);
+                        reinterpret_cast<__nv_bfloat16 *>(jb.y)[o] = __float2bfloat16_rn(r);
+                    } else {
+                        if (jb.residual) r += reinterpret_cast<const float *>(jb.residual)[o];
+                        reinterpret_cast<float *>(jb.y)[o] = r;
+                    }
+                }
+        }
+    }
+}
+
+constexpr int max_warps(int ng) { return ng > 1 ? 16 : 14; }
+
+} // namespace dec
+
+// blockIdx.x -> (job, CTA group, K slice): a job's CTAs are contiguous, group-major.
+template <int NG, bool DUAL>
+__global__ void __launch_bounds__(dec::max_warps(NG) * 32, (NG > 1 ? 1 : 2)) kquant_decode_kernel(const __grid_constant__ DecArgs a) {
+    extern __shared__ uint4 dec_dyn[];
+    __shared__ float inv_rms[4 * NG];
+    uint32_t ji = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < kDecMaxJobs; ++i)
+        if (i < a.n_jobs && blockIdx.x >= a.job[i].cta0) ji = i;
+    const DecJob &jb = a.job[ji];
+    const uint32_t local = blockIdx.x - jb.cta0, slice = local % a.ksplit, group = local / a.ksplit;
+    if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+    else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+}
+
+// ------------------------------------------------------------------------------------ host side
+namespace {
+
+struct DecPlan {
+    int warps, ksplit, ring;
+};
+
+size_t dec_smem_bytes(uint32_t nsb, int ksplit, int warps, int ring, int ng) {
+    const uint32_t max_tiles = (nsb + ksplit - 1) / ksplit + 1;
+    return (size_t)max_tiles * ng * (dec::kFragU4 * 16 + 4 * dec::kMetaU4 * 16) + (size_t)warps * ring * (kQ6TileBytes + 8) + 16;
+}
+
+// K slices, warps per CTA and ring depth from a small cost model: a tile costs `per_tile` issue slots of its warp,
+// a scheduler retires about 0.12 instructions per clock per resident warp up to ~0.9, and an SM cannot take tiles
+// faster than HBM delivers them.  As many busy warps per SM as fit, spread evenly over the SMs, and slices only as
+// far as that needs, because every slice costs a trip through the scratch buffer and a staging pass per CTA.
+DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6) {
+    DecPlan best{2, 1, 2};
+    double best_cost = 1e300;
+    const double instr = (q6 ? 330.0 : 260.0) + (ng - 1) * (q6 ? 130.0 : 110.0); // issue slots per tile
+    const double hbm_cycles = q6 ? 150.0 : 105.0;                                 // per tile and SM at full HBM rate
+    for (int ring = 2; ring <= 4; ring += 2)
+        for (int ks = 1; ks <= 16 && (uint32_t)ks <= nsb; ++ks)
+            for (int w = 2; w <= dec::max_warps(ng); w += 2) {
+                const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng);
+                if (smem > 220u * 1024) continue;
+                int ctas = (int)((227u * 1024) / (smem + 1024));
+                ctas = std::min(ctas, std::max(1, (ng > 1 ? 16 : 28) / w)); // 128 (72) registers a thread
+                const double tiles = std::ceil((double)nsb / ks);
+                const double wanted = std::ceil((double)row_tiles / w);                   // CTAs per slice if every warp took one row tile
+                const double groups = std::min(wanted, std::floor((double)ctas * sm_count / ks));
+                if (groups < 1.0) continue;
+                const double rows_per_warp = std::ceil(wanted / groups);
+                const double ctas_on_sm = std::ceil(groups * ks / sm_count);              // the busiest SM
+                const double busy = ctas_on_sm * w;                                       // warps at work there
+                const double ipc = std::min(3.0, 0.11 * busy * (ring == 4 ? 1.1 : 1.0));  // SM-wide
+                const double per_tile = std::max(hbm_cycles, instr / ipc);                // SM cycles per tile
+                const double staging = ctas_on_sm * tiles * ng * 45.0 + 1500.0;           // per SM, before the first tile
+                const double per_item = 400.0 + (ks > 1 ? 1500.0 : 0.0);                  // epilogue latency, scratch round trip
+                const double cost = busy * rows_per_warp * tiles * per_tile + rows_per_warp * per_item + staging;
+                if (cost < best_cost * (1.0 - 1e-9)) best_cost = cost, best = DecPlan{w, ks, ring};
+            }
+    return best;
+}
+
+template <int NG, bool DUAL>
+cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t stream) {
+    struct Cached {
+        uint32_t nsb = 0, rows[kDecMaxJobs] = {0, 0, 0, 0}, n_jobs = 0;
+        bool q6 = false;
+        DecPlan plan{1, 1, 2};
+        size_t smem = 0;
+        uint32_t groups[kDecMaxJobs] = {0, 0, 0, 0};
+        uint32_t forced_w = 0, forced_k = 0, forced_r = 0;
+    };
+    static PerDevice<Cached> cached; // last geometry of this instantiation, per device
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return cudaErrorInvalidDevice;
+    Cached cache;
+    {
+        std::lock_guard<std::mutex> lock(cached.mu);
+        Cached &slot = cached.slot[ctx->device];
+        bool same = slot.nsb == a.nsb && slot.n_jobs == a.n_jobs && slot.forced_w == (uint32_t)forced.warps &&
+                    slot.forced_k == (uint32_t)forced.ksplit && slot.forced_r == (uint32_t)forced.ring;
+        bool q6 = false;
+        uint32_t total_tiles = 0;
+        size_t out_floats = 0;
+        for (uint32_t i = 0; i < a.n_jobs; ++i) {
+            same = same && slot.rows[i] == a.job[i].row_tiles;
+            q6 = q6 || a.job[i].dtype == MUSER_DTYPE_Q6_K;
+            total_tiles += a.job[i].row_tiles;
+            out_floats += (size_t)(DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
+        }
+        same = same && slot.q6 == q6;
+        if (!same) {
+            DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, q6);
+            if (forced.warps) p.warps = std::min(forced.warps, dec::max_warps(NG));
+            if (forced.ksplit) p.ksplit = (int)std::min<uint32_t>((uint32_t)forced.ksplit, a.nsb);
+            if (forced.ring) p.ring = forced.ring >= 4 ? 4 : 2;
+            while (p.ksplit > 1 && (size_t)p.ksplit * out_floats * sizeof(float) > ctx->gemv_partial_bytes) --p.ksplit;
+            if (total_tiles > ctx->gemv_counter_slots) p.ksplit = 1;
+            size_t smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+            while (smem > 226u * 1024 && p.ring > 2) p.ring = 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+            while (smem > 226u * 1024 && (uint32_t)p.ksplit < a.nsb &&
+                   (size_t)(p.ksplit + 1) * out_floats * sizeof(float) <= ctx->gemv_partial_bytes && total_tiles <= ctx->gemv_counter_slots)
+                ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+            while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+            if (smem > 226u * 1024) return cudaErrorNotSupported;
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL>), ctx->device, smem);
+            if (e != cudaSuccess) return e;
+            int per_sm = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL>, p.warps * 32, smem);
+            if (e != cudaSuccess) return e;
+            if (per_sm < 1) return cudaErrorInvalidConfiguration;
+            // CTAs per slice over all jobs: all that fit at once, but no more than there are row tiles for their warps
+            uint32_t wanted = 0;
+            for (uint32_t i = 0; i < a.n_jobs; ++i) wanted += (a.job[i].row_tiles + p.warps - 1) / p.warps;
+            const uint32_t resident = std::max(1u, (uint32_t)per_sm * ctx->sm_count / p.ksplit);
+            const uint32_t rounds = (wanted + resident - 1) / resident;
+            slot = Cached{};
+            for (uint32_t i = 0; i < a.n_jobs; ++i) {
+                const uint32_t w_i = (a.job[i].row_tiles + p.warps - 1) / p.warps;
+                slot.groups[i] = std::max(1u, (w_i + rounds - 1) / rounds);
+                slot.rows[i] = a.job[i].row_tiles;
+            }
+            slot.nsb = a.nsb, slot.n_jobs = a.n_jobs, slot.q6 = q6;
+            slot.plan = p, slot.smem = smem;
+            slot.forced_w = forced.warps, slot.forced_k = forced.ksplit, slot.forced_r = forced.ring;
+        }
+        cache = slot;
+    }
+    a.ksplit = cache.plan.ksplit;
+    a.ring = cache.plan.ring;
+    a.max_tiles = (a.nsb + a.ksplit - 1) / a.ksplit + 1;
+    uint32_t cta = 0, counter = 0;
+    size_t partial = 0;
+    for (uint32_t i = 0; i < a.n_jobs; ++i) {
+        a.job[i].cta0 = cta;
+        a.job[i].groups = cache.groups[i];
+        a.job[i].counter0 = counter;
+        a.job[i].partial0 = (uint32_t)partial;
+        cta += cache.groups[i] * a.ksplit;
+        counter += a.job[i].row_tiles;
+        partial += (size_t)a.ksplit * (DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
+    }
+    return launch_pdl(kquant_decode_kernel<NG, DUAL>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
+}
+
+} // namespace
+
+// Up to four column-layout K-quant weights of one n_in (and one K shard geometry) applied to the same 1..16 tokens.
+// w_up: the fused gate/up form (one job).  Returns cudaErrorNotSupported when the shape does not fit this kernel.
+cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
+                                 uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
+                                 const Epilogue *ep, cudaStream_t stream) {
+    if (n_jobs == 0 || n_jobs > (uint32_t)kDecMaxJobs || tokens == 0 || tokens > 16 || w[0]->nsb > 4096) return cudaErrorNotSupported;
+    DecArgs a;
+    a.n_jobs = n_jobs;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        if (w[i]->layout != 1 || w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off || w[i]->n_in != w[0]->n_in) return cudaErrorNotSupported;
+        DecJob &j = a.job[i];
+        j.image = w[i]->image;
+        j.image_up = w_up ? w_up->image : nullptr;
+        j.y = y[i];
+        j.row_scale = ep[i].row_scale;
+        j.residual = ep[i].residual;
+        j.out_scale = ep[i].out_scale;
+        j.softcap = ep[i].softcap;
+        j.dtype = w[i]->dtype;
+        j.n_out = (uint32_t)w[i]->n_out;
+        j.row_tiles = w[i]->row_tiles;
+        j.y_bf16 = y_dtype[i] == MUSER_DTYPE_BF16;
+        j.cta0 = j.groups = j.counter0 = j.partial0 = 0;
+    }
+    for (uint32_t i = n_jobs; i < (uint32_t)kDecMaxJobs; ++i) a.job[i] = a.job[0];
+    a.x = x;
+    a.x_f32 = x_dtype == MUSER_DTYPE_F32;
+    a.norm_weight = ep[0].norm_weight;
+    a.norm_eps = ep[0].norm_eps;
+    a.partial = ctx->gemv_partial;
+    a.counters = ctx->gemv_counters;
+    a.status = ctx->dev_status;
+    a.n_in = (uint32_t)w[0]->n_in;
+    a.nsb = w[0]->nsb;
+    a.k_off = w[0]->k_off;
+    a.tokens = tokens;
+    a.ksplit = 1, a.max_tiles = 0, a.ring = 2;
+    const DecPlan forced{(int)ctx->dec_warps, (int)ctx->dec_ksplit, (int)ctx->dec_ring};
+    const uint32_t ng = (tokens + 3) / 4;
+    if (w_up) {
+        if (n_jobs != 1) return cudaErrorNotSupported;
+        switch (ng) {
+        case 1: return dec_launch<1, true>(a, ctx, forced, stream);
+        case 2: return dec_launch<2, true>(a, ctx, forced, stream);
+        case 3: return dec_launch<3, true>(a, ctx, forced, stream);
+        default: return dec_launch<4, true>(a, ctx, forced, stream);
+        }
+    }
+    switch (ng) {
+    case 1: return dec_launch<1, false>(a, ctx, forced, stream);
+    case 2: return dec_launch<2, false>(a, ctx, forced, stream);
+    case 3: return dec_launch<3, false>(a, ctx, forced, stream);
+    default: return dec_launch<4, false>(a, ctx, forced, stream);
+    }
+}
+
+} // namespace muser

@@ -18,6 +18,25 @@
 //   [2048,3072) high 2 bits: uint4 (rowsel, lane); word o holds sub-block t + 4o: element 4x + b in bits
 //               [8b + 2x, 8b + 2x + 1].
 //   [3072,3328) 16 x sc[16] int8;  [3328,3360) 16 x d f16.
+//
+// ---- The "column" layout (Weight::layout == 1), read by the decode kernel (kquant_decode.cu) ----
+// Here a lane owns a QUARTER of EVERY sub-block of its two rows, which is what a tensor-core fragment of a
+// sub-block-at-a-time product wants: lane (g, t) supplies rows g and g + 8 and 8 (Q4_K) or 4 (Q6_K) consecutive
+// elements of each sub-block, so no regrouping is needed between the load and the MMA.
+//
+// Q4_K tile (2304 bytes)
+//   [0, 2048)   uint4 (u, lane), u = 2*rowsel + half: row g + 8*rowsel, sub-blocks 4*half .. 4*half + 3.  Word jj
+//               holds elements 8t .. 8t+7 of sub-block 4*half + jj, element i in nibble q4_nibble_pos(i): the low
+//               nibbles of bytes 0..3 are elements 8t + (0, 4, 1, 5), the high nibbles 8t + (2, 6, 3, 7).
+//   [2048,2304) 16 x the block's 16-byte header, as above.
+// Q6_K tile (3360 bytes).  A weight is stored as v = (q - 32) & 63 (six-bit two's complement), split into its top
+// four bits T = v >> 2 and low two bits L = v & 3, so that (T << 4) | (L << 2) is the signed byte 4 * (q - 32).
+//   [0, 2048)   T plane: uint4 (u, lane), u = 2*rowsel + half: row g + 8*rowsel, sub-blocks 8*half .. 8*half + 7.
+//               Word wi: byte b carries element 4t + b of sub-block 8*half + 2*wi in its low nibble and of
+//               sub-block 8*half + 2*wi + 1 in its high nibble.
+//   [2048,3072) L plane: uint4 (rowsel, lane); word v covers sub-blocks 4v .. 4v+3: bits [2x, 2x+1] of byte b are
+//               L of element 4t + b of sub-block 4v + x.
+//   [3072,3328) 16 x sc[16] int8;  [3328,3360) 16 x d f16.
 #pragma once
 #include "common.cuh"
 

@@ -483,6 +483,23 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
     // Measured crossovers on B200 (bf16 activations): the decode kernel (kquant_gemv.cu) up to 2 tokens for Q4_K and 4
     // for Q6_K; the tcgen05 kernel (kquant_tc.cu) from 12 / 5 tokens when the weight has enough 128-row blocks to
     // fill the GPU; this file's kernel in between, for f32 activations and for small weights.
+    if (w->layout == 1) {
+        // column-layout images are read by the decode kernel: up to 16 tokens a launch, more in chunks of 16
+        if (w_up && w_up->layout != 1) return fail(ctx, MUSER_CUDA_BAD_ARG, "gate and up images differ in layout");
+        const size_t xb = x_dtype == MUSER_DTYPE_F32 ? 4 : 2, yb = y_dtype == MUSER_DTYPE_BF16 ? 2 : 4;
+        for (uint32_t t0 = 0; t0 < tokens; t0 += 16) {
+            const uint32_t n = std::min(16u, tokens - t0);
+            Epilogue e = ep;
+            if (e.row_scale) e.row_scale += t0;
+            if (e.residual) e.residual = reinterpret_cast<const uint8_t *>(e.residual) + (size_t)t0 * w->n_out * yb;
+            void *yc = reinterpret_cast<uint8_t *>(y) + (size_t)t0 * w->n_out * yb;
+            const cudaError_t de = launch_kquant_decode(ctx, &w, w_up, 1, reinterpret_cast<const uint8_t *>(x) + (size_t)t0 * w->n_in * xb,
+                                                        x_dtype, &yc, &y_dtype, n, &e, stream);
+            if (de == cudaErrorNotSupported) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "this shape does not fit the decode kernel");
+            MUSER_CUDA_TRY(ctx, de);
+        }
+        return MUSER_CUDA_OK;
+    }
     const bool q6 = w->dtype == MUSER_DTYPE_Q6_K;
     // (f32 activations cost the legacy kernel a second MMA pass, so the tensor-core kernel takes over earlier;
     //  it carries them as f16 head + remainder column pairs, hence at most 32 tokens)

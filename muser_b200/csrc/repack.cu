@@ -161,9 +161,148 @@ __global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
     }
 }
 
+// ------------------------------------------------------------------------------ column layout (layout 1)
+// The same tensors in the layout of the decode kernel: a lane owns a quarter of every sub-block (kquant_layout.cuh).
+__global__ void repack_q4k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
+    const uint64_t units_per_tile = 512 + 16;
+    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)gm.row_tiles * gm.nsb * units_per_tile) return;
+    uint64_t tile = idx / units_per_tile;
+    uint32_t unit = (uint32_t)(idx % units_per_tile);
+    uint32_t rt = (uint32_t)(tile / gm.nsb), sb = (uint32_t)(tile % gm.nsb);
+    uint8_t *tile_ptr = image + tile * kQ4TileBytes;
+    uint64_t sb_global = gm.k0 / 256 + sb;
+    int64_t k_base = (int64_t)sb_global * 256;
+    if (unit < 512) {
+        uint32_t u = unit >> 7, lane = (unit >> 2) & 31, jj = unit & 3;
+        uint32_t g = lane >> 2, t = lane & 3;
+        uint32_t row = rt * 16 + g + 8 * (u >> 1), j = 4 * (u & 1) + jj;
+        uint32_t word = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
+            for (int i = 0; i < 8; ++i) {
+                uint32_t e = 32 * j + 8 * t + i;
+                int64_t k = k_base + e;
+                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) continue;
+                uint32_t grp = e >> 6, l = e & 63;
+                uint8_t byte = blk[16 + 32 * grp + (l & 31)];
+                uint32_t nib = l < 32 ? (byte & 15u) : (byte >> 4);
+                word |= nib << (4 * q4_nibble_pos(i));
+            }
+        }
+        reinterpret_cast<uint32_t *>(tile_ptr)[(u * 32 + lane) * 4 + jj] = word;
+    } else {
+        uint32_t r = unit - 512, row = rt * 16 + r;
+        uint8_t hdr[16];
+        for (int i = 0; i < 16; ++i) hdr[i] = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
+            const uint8_t *sp = blk + 4;
+            uint8_t sc[8], mn[8];
+            for (int j = 0; j < 8; ++j) {
+                if (j < 4) {
+                    sc[j] = sp[j] & 63;
+                    mn[j] = sp[j + 4] & 63;
+                } else {
+                    sc[j] = (uint8_t)((sp[j + 4] & 15) | ((sp[j - 4] >> 6) << 4));
+                    mn[j] = (uint8_t)((sp[j + 4] >> 4) | ((sp[j] >> 6) << 4));
+                }
+                int64_t k = k_base + 32 * j; // a sub-block outside the shard contributes nothing
+                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) sc[j] = mn[j] = 0;
+            }
+            hdr[0] = blk[0], hdr[1] = blk[1], hdr[2] = blk[2], hdr[3] = blk[3];
+            for (int j = 0; j < 4; ++j) {
+                hdr[4 + j] = (uint8_t)(sc[j] | ((sc[j + 4] >> 4) << 6));
+                hdr[8 + j] = (uint8_t)(mn[j] | ((mn[j + 4] >> 4) << 6));
+                hdr[12 + j] = (uint8_t)((sc[j + 4] & 15) | ((mn[j + 4] & 15) << 4));
+            }
+        }
+        uint4 v;
+        memcpy(&v, hdr, 16);
+        reinterpret_cast<uint4 *>(tile_ptr + 2048)[r] = v;
+    }
+}
+
+__global__ void repack_q6k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
+    const uint64_t units_per_tile = 512 + 256 + 16 + 1;
+    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)gm.row_tiles * gm.nsb * units_per_tile) return;
+    uint64_t tile = idx / units_per_tile;
+    uint32_t unit = (uint32_t)(idx % units_per_tile);
+    uint32_t rt = (uint32_t)(tile / gm.nsb), sb = (uint32_t)(tile % gm.nsb);
+    uint8_t *tile_ptr = image + tile * kQ6TileBytes;
+    uint64_t sb_global = gm.k0 / 256 + sb;
+    int64_t k_base = (int64_t)sb_global * 256;
+    // six-bit two's complement of q - 32 for element e of the block, 0 outside this shard
+    auto v6 = [&](const uint8_t *blk, uint32_t e) -> uint32_t {
+        int64_t k = k_base + e;
+        if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) return 0u;
+        uint32_t lo, hi2;
+        return q6_raw_value(blk, e, &lo, &hi2) ^ 32u;
+    };
+    if (unit < 512) { // T plane
+        uint32_t u = unit >> 7, lane = (unit >> 2) & 31, wi = unit & 3;
+        uint32_t g = lane >> 2, t = lane & 3;
+        uint32_t row = rt * 16 + g + 8 * (u >> 1), s0 = 8 * (u & 1) + 2 * wi;
+        uint32_t word = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
+            for (uint32_t b = 0; b < 4; ++b) {
+                word |= (v6(blk, 16 * s0 + 4 * t + b) >> 2) << (8 * b);
+                word |= (v6(blk, 16 * (s0 + 1) + 4 * t + b) >> 2) << (8 * b + 4);
+            }
+        }
+        reinterpret_cast<uint32_t *>(tile_ptr)[(u * 32 + lane) * 4 + wi] = word;
+    } else if (unit < 768) { // L plane
+        uint32_t v = unit - 512;
+        uint32_t rowsel = v >> 7, lane = (v >> 2) & 31, wv = v & 3;
+        uint32_t g = lane >> 2, t = lane & 3;
+        uint32_t row = rt * 16 + g + 8 * rowsel;
+        uint32_t word = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
+            for (uint32_t x = 0; x < 4; ++x)
+                for (uint32_t b = 0; b < 4; ++b) word |= (v6(blk, 16 * (4 * wv + x) + 4 * t + b) & 3u) << (8 * b + 2 * x);
+        }
+        reinterpret_cast<uint32_t *>(tile_ptr + kQ6OffHi)[(rowsel * 32 + lane) * 4 + wv] = word;
+    } else if (unit < 784) {
+        uint32_t r = unit - 768, row = rt * 16 + r;
+        uint8_t sc[16];
+        for (int i = 0; i < 16; ++i) sc[i] = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
+            for (uint32_t s2 = 0; s2 < 16; ++s2) {
+                int64_t k = k_base + 16 * s2;
+                sc[s2] = (k >= (int64_t)gm.k0 && k < (int64_t)(gm.k0 + gm.n_in)) ? blk[192 + s2] : 0;
+            }
+        }
+        uint4 v;
+        memcpy(&v, sc, 16);
+        reinterpret_cast<uint4 *>(tile_ptr + kQ6OffSc)[r] = v;
+    } else {
+        for (uint32_t r = 0; r < 16; ++r) {
+            uint32_t row = rt * 16 + r;
+            uint16_t d = 0;
+            if (row < gm.n_out) {
+                const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
+                d = (uint16_t)(blk[208] | (blk[209] << 8));
+            }
+            reinterpret_cast<uint16_t *>(tile_ptr + kQ6OffD)[r] = d;
+        }
+    }
+}
+
 muser_cuda_status launch_repack_kquant(Ctx *ctx, Weight *w, const uint8_t *dev_blocks, cudaStream_t stream) {
     KqGeom gm = kq_geom(*w);
     uint64_t tiles = (uint64_t)gm.row_tiles * gm.nsb;
+    if (w->layout == 1) {
+        if (w->dtype == MUSER_DTYPE_Q4_K)
+            repack_q4k_col_kernel<<<(unsigned)((tiles * 528 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
+        else
+            repack_q6k_col_kernel<<<(unsigned)((tiles * 785 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
+        MUSER_CUDA_TRY(ctx, cudaGetLastError());
+        return MUSER_CUDA_OK;
+    }
     if (w->dtype == MUSER_DTYPE_Q4_K) {
         uint64_t total = tiles * 528;
         repack_q4k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
@@ -220,13 +359,16 @@ muser_cuda_status launch_repack_nvfp4(Ctx *ctx, Weight *w, const uint8_t *dev_pa
 
 // ------------------------------------------------------------------------------ image -> f32
 // One weight out of the repacked image: row `row`, position `kk` in the tile grid (input index + k_off).
+template <int LAYOUT>
 __device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ4TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t j = e >> 5, wi = (e >> 3) & 3, i = e & 7;
-    uint32_t q = rowsel * 2 + (j >> 2), lane = g * 4 + (j & 3);
-    uint32_t word = reinterpret_cast<const uint32_t *>(tile)[(q * 32 + lane) * 4 + wi];
+    uint32_t q = rowsel * 2 + (j >> 2);
+    // layout 0: lane (g, j % 4) holds the sub-block, word = 8-element group; layout 1: lane (g, group), word = j % 4
+    uint32_t word = LAYOUT == 0 ? reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + (j & 3)) * 4 + wi]
+                                : reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + wi) * 4 + (j & 3)];
     uint32_t nib = (word >> (4 * q4_nibble_pos(i))) & 15u;
     const uint8_t *hdr = tile + 2048 + r * 16;
     float d = __half2float(*reinterpret_cast<const __half *>(hdr));
@@ -244,39 +386,53 @@ __device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, u
     return __fsub_rn(__fmul_rn(d1, (float)nib), m1); // k_block.rs:40-41
 }
 
+template <int LAYOUT>
 __device__ __forceinline__ float q6k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ6TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
-    uint32_t s = e >> 4, el = e & 15, o = s >> 2, lane = g * 4 + (s & 3);
-    uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (o >> 1)) * 32 + lane) * 4 + (o & 1) * 2 + (el >> 3)];
-    uint32_t lo = (lo_word >> (8 * (el & 3) + 4 * ((el >> 2) & 1))) & 15u;
-    uint32_t hi_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + o];
-    uint32_t hi2 = (hi_word >> (8 * (el & 3) + 2 * (el >> 2))) & 3u;
-    int qv = (int)(lo | (hi2 << 4)) - 32;
+    uint32_t s = e >> 4, el = e & 15;
+    int qv;
+    if constexpr (LAYOUT == 0) {
+        uint32_t o = s >> 2, lane = g * 4 + (s & 3);
+        uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (o >> 1)) * 32 + lane) * 4 + (o & 1) * 2 + (el >> 3)];
+        uint32_t lo = (lo_word >> (8 * (el & 3) + 4 * ((el >> 2) & 1))) & 15u;
+        uint32_t hi_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + o];
+        uint32_t hi2 = (hi_word >> (8 * (el & 3) + 2 * (el >> 2))) & 3u;
+        qv = (int)(lo | (hi2 << 4)) - 32;
+    } else {
+        uint32_t lane = g * 4 + (el >> 2), b = el & 3;
+        uint32_t t_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (s >> 3)) * 32 + lane) * 4 + ((s & 7) >> 1)];
+        uint32_t top = (t_word >> (8 * b + 4 * (s & 1))) & 15u;
+        uint32_t l_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + (s >> 2)];
+        uint32_t low = (l_word >> (8 * b + 2 * (s & 3))) & 3u;
+        qv = (int)(((top << 2) | low) ^ 32u) - 32; // the image holds (q - 32) & 63
+    }
     float d = __half2float(reinterpret_cast<const __half *>(tile + kQ6OffD)[r]);
     int sc = reinterpret_cast<const int8_t *>(tile + kQ6OffSc)[r * 16 + s];
     return __fmul_rn(__fmul_rn(d, (float)sc), (float)qv); // q6.rs:305-313
 }
 
 // One thread per output element; reads the repacked image only.
+template <int LAYOUT>
 __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= gm.n_out * gm.n_in) return;
-    out[idx] = q4k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+    out[idx] = q4k_weight<LAYOUT>(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
 }
 
+template <int LAYOUT>
 __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= gm.n_out * gm.n_in) return;
-    out[idx] = q6k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+    out[idx] = q6k_weight<LAYOUT>(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
 }
 
 // ------------------------------------------------------------------------------ selected rows
 // weights::matmul_rows (src/weights.rs:425-449): out[t][i] = dot(W_rows[i], x_t) for a list of output rows, the way
 // the reference scores a handful of LM-head rows.  One warp per listed row; lanes stride over the inputs, decode
 // each weight from the image and keep up to eight token sums; a butterfly adds the lanes (fixed order).
-template <bool Q4, bool XF32>
+template <bool Q4, bool XF32, int LAYOUT>
 __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restrict__ image, KqGeom gm, const uint32_t *__restrict__ rows,
                                                           uint32_t n_rows, const void *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ out) {
@@ -288,7 +444,7 @@ __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restr
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (row < gm.n_out) {
             for (uint64_t k = lane; k < gm.n_in; k += 32) {
-                const float w = Q4 ? q4k_weight(image, gm.nsb, row, k + gm.k_off) : q6k_weight(image, gm.nsb, row, k + gm.k_off);
+                const float w = Q4 ? q4k_weight<LAYOUT>(image, gm.nsb, row, k + gm.k_off) : q6k_weight<LAYOUT>(image, gm.nsb, row, k + gm.k_off);
 #pragma unroll
                 for (uint32_t t = 0; t < 8; ++t)
                     if (t < nt) {
@@ -313,10 +469,16 @@ muser_cuda_status launch_kquant_rows(Ctx *ctx, const Weight *w, const uint32_t *
     const unsigned blocks = (n_rows + 7) / 8;
     const KqGeom gm = kq_geom(*w);
     const bool q4 = w->dtype == MUSER_DTYPE_Q4_K, xf32 = x_dtype == MUSER_DTYPE_F32;
-    if (q4 && xf32) kquant_rows_kernel<true, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else if (q4) kquant_rows_kernel<true, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else if (xf32) kquant_rows_kernel<false, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else kquant_rows_kernel<false, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+#define MUSER_ROWS_LAUNCH(Q4_, XF32_)                                                                                        \
+    do {                                                                                                                      \
+        if (w->layout == 1) kquant_rows_kernel<Q4_, XF32_, 1><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out); \
+        else kquant_rows_kernel<Q4_, XF32_, 0><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);       \
+    } while (0)
+    if (q4 && xf32) MUSER_ROWS_LAUNCH(true, true);
+    else if (q4) MUSER_ROWS_LAUNCH(true, false);
+    else if (xf32) MUSER_ROWS_LAUNCH(false, true);
+    else MUSER_ROWS_LAUNCH(false, false);
+#undef MUSER_ROWS_LAUNCH
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
@@ -349,9 +511,11 @@ muser_cuda_status launch_dequant(Ctx *ctx, const Weight *w, float *out, cudaStre
         dequant_nvfp4_kernel<<<blocks, 256, 0, stream>>>(w->packed, w->scales, out, w->n_out, w->n_in,
                                                          (uint32_t)((w->n_in + 63) / 64), w->scale2);
     } else if (w->dtype == MUSER_DTYPE_Q4_K) {
-        dequant_q4k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        if (w->layout == 1) dequant_q4k_kernel<1><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        else dequant_q4k_kernel<0><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     } else {
-        dequant_q6k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        if (w->layout == 1) dequant_q6k_kernel<1><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        else dequant_q6k_kernel<0><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     }
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
