@@ -123,18 +123,16 @@ MUSER_CUDA_API const char *muser_cuda_last_error(const muser_cuda_ctx *ctx);
 MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, void *stream);
 
 /* No counterpart in the reference (its kernel choice is compiled in, src/metal/encode/qkv.rs:425-449).  Which kernel
- * serves a K-quant call depends on the token count; these thresholds are the measured defaults and can be moved,
- * e.g. to force one kernel in a test.  A value above 64 switches the tensor-core skinny kernel off. */
-#define MUSER_TUNE_TC_MIN_TOKENS_Q4_K 1u /* Q4_K calls with at least this many tokens take the tcgen05 kernel (default 12) */
-#define MUSER_TUNE_TC_MIN_TOKENS_Q6_K 2u /* likewise for Q6_K (default 5) */
+ * serves a K-quant call depends on the token count: up to 16 tokens the decode kernel, from 17 the tcgen05 skinny
+ * kernel where the weight is large enough.  The thresholds and the decode kernel's launch plan can be moved, e.g. to
+ * force one kernel in a test.  A TC_MIN_TOKENS value above 64 switches the tensor-core skinny kernel off. */
+#define MUSER_TUNE_TC_MIN_TOKENS_Q4_K 1u /* Q4_K calls with at least this many tokens take the tcgen05 kernel (default 17) */
+#define MUSER_TUNE_TC_MIN_TOKENS_Q6_K 2u /* likewise for Q6_K (default 17) */
 #define MUSER_TUNE_TC_MIN_ROWS 3u        /* ... if the weight has at least this many output rows (default 2048) */
-#define MUSER_TUNE_GEMV_MAX_TOKENS_Q4_K 4u /* Q4_K calls with at most this many tokens take the decode GEMV (default 2, at most 8) */
-#define MUSER_TUNE_GEMV_MAX_TOKENS_Q6_K 5u /* likewise for Q6_K (default 4) */
-#define MUSER_TUNE_MATMUL_WARPS 6u       /* warps that split K in a CTA of the general skinny kernel, 1-8 (default 0: chosen per weight) */
-#define MUSER_TUNE_KQUANT_LAYOUT 7u      /* image layout built by later weight_repack calls: 0 whole sub-blocks per lane, 1 column layout (decode kernel) */
-#define MUSER_TUNE_DECODE_WARPS 8u       /* decode kernel: warps per CTA (0: cost model) */
-#define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: cost model) */
-#define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: cost model) */
+#define MUSER_TUNE_DECODE_WARPS 8u       /* decode kernel: warps per CTA, even (0: from its cost model) */
+#define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: from its cost model) */
+#define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: from its cost model) */
+#define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 262144; 0: always NCCL) */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file
@@ -165,10 +163,29 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_dequant(muser_cuda_ctx *ctx, const m
 /* MetalKernels::encode_quantized_matmul (src/metal/encode/qkv.rs:414-424) and its CPU twin
  * weights::matmul (src/weights.rs:398-421) for K-quant weights: y[t][r] = dot(W_r, x_t).
  * x_dtype is F32 or BF16, y_dtype F32 or BF16; 1 <= tokens <= 64 (decode, decode groups as in
- * encode_quantized_decode_group qkv.rs:234-244, and speculative-verify batches). */
+ * encode_quantized_decode_group qkv.rs:234-244, and speculative-verify batches).  Activations are taken as 15-bit
+ * fixed point per 256 inputs up to 16 tokens (error <= amax * 2^-15 per input) and as f16 beyond. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
                                               uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                               const muser_cuda_epilogue *epilogue, void *stream);
+
+/* The projections that read the same activations, in ONE launch: the reference dispatches q, k, v (and gate) of a
+ * decode step inside one barrier interval (src/decode.rs:5569-5598) and groups up to four sequences per dispatch
+ * (MetalKernels::encode_quantized_decode_group, src/metal/encode/qkv.rs:234-281).  1 <= n_items <= 4 K-quant weights of
+ * one n_in (and, when K-sharded, one shard geometry), Q4_K and Q6_K may mix; 1 <= tokens <= 16; each item has its own
+ * output and epilogue, but the fused input norm (norm_weight / norm_eps) must be the same in all of them (or absent
+ * in all), since x is staged once.  Results equal n_items calls of muser_cuda_quantized_matmul up to the order in
+ * which the f32 partial sums of the K slices are added (the launch plan depends on the group's total size). */
+typedef struct muser_cuda_group_item {
+    const muser_cuda_weight *w;
+    void *y;                             /* [tokens][w.n_out] */
+    uint32_t y_dtype;                    /* F32 or BF16 */
+    uint32_t reserved;                   /* 0 */
+    const muser_cuda_epilogue *epilogue; /* or NULL */
+} muser_cuda_group_item;
+MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul_group(muser_cuda_ctx *ctx, const muser_cuda_group_item *items,
+                                                    uint32_t n_items, const void *x, uint32_t x_dtype, uint32_t tokens,
+                                                    void *stream);
 
 /* weights::matmul_rows (src/weights.rs:425-449): the projection restricted to a list of output rows, as the
  * reference scores selected LM-head rows.  rows: n_rows row indices on the device (an index >= n_out yields NaN);
@@ -261,10 +278,39 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *ctx, u
  * usable. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_wait_probe(muser_cuda_ctx *ctx, uint32_t polls, void *stream);
 
+/* Tensor parallelism.  The reference has none (scripts/gx10/vllm/muser_vllm/connector.py:119-120 refuses it), so
+ * these have no counterpart there.  One process per GPU of one box; a context gets a communicator either from an
+ * id that rank 0 made and the host carried to the other ranks (comm_init: every rank calls it, it blocks until all
+ * have), or from an NCCL communicator the host already owns (comm_attach; `nccl_comm` is an ncclComm_t).  NCCL is
+ * looked up at run time (libnccl.so.2); MUSER_CUDA_NCCL_ERROR reports its absence or a failed call.  At most 8 ranks
+ * get the one-shot path; the set-up call synchronizes `stream`. */
+#define MUSER_CUDA_COMM_ID_BYTES 128u
+MUSER_CUDA_API muser_cuda_status muser_cuda_comm_unique_id(uint8_t *out, size_t out_bytes);
+MUSER_CUDA_API muser_cuda_status muser_cuda_ctx_comm_init(muser_cuda_ctx *ctx, const uint8_t *id, uint32_t rank, uint32_t world, void *stream);
+MUSER_CUDA_API muser_cuda_status muser_cuda_ctx_comm_attach(muser_cuda_ctx *ctx, void *nccl_comm, uint32_t rank, uint32_t world, void *stream);
+/* 1 when the context's communicator has its peer buffers mapped (CUDA IPC) and small payloads avoid NCCL. */
+MUSER_CUDA_API int muser_cuda_ctx_comm_has_oneshot(const muser_cuda_ctx *ctx);
+/* The all-reduce(sum) after a row-parallel projection (o_proj, down_proj), in place on `buf` (count elements of F32,
+ * F16 or BF16), enqueued on `stream`; every rank must make the same calls in the same order.  f32 payloads up to
+ * 256 KiB (a decode step's [tokens][hidden] partial sums) take a one-shot exchange over peer memory: each rank stores
+ * its values into every rank's buffer over NVLink, raises a flag there, waits (bounded: a give-up is reported by
+ * muser_cuda_sync_status as MUSER_CUDA_TIMEOUT and leaves `buf` as it was) and adds the copies in rank order, so all
+ * ranks end with identical bits.  Larger payloads and 16-bit types go to ncclAllReduce on the same stream. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_all_reduce(muser_cuda_ctx *ctx, void *buf, uint64_t count, uint32_t dtype, void *stream);
+
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.
  * Copies x up, runs the device path for w's dtype, copies y back and synchronizes. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const float *x_host,
                                          uint32_t tokens, float *y_host);
+
+/* The same with the wait left to the caller, the way the reference's drivers encode a whole step into one command
+ * buffer and wait once (src/decode.rs:5448-5460, src/metal/context.rs:149-211): the copy of x up, the projection and
+ * the copy of y back are enqueued on `stream` and the call returns.  x_host and y_host must stay valid until the
+ * stream has been synchronized (muser_cuda_sync_status does that and also rewinds the context's staging arena); with
+ * pinned host memory the copies overlap the host's next calls.  The arena (64 MiB, allocated on first use) is the
+ * only allocation; a step that outgrows it makes the call wait for the stream once and start the arena over. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *ctx, const muser_cuda_weight *w,
+                                                 const float *x_host, uint32_t tokens, float *y_host, void *stream);
 
 #ifdef __cplusplus
 }

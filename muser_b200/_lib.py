@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmuser_cuda.so"
 F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
 SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
 TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
-TUNE_GEMV_MAX_TOKENS_Q4_K, TUNE_GEMV_MAX_TOKENS_Q6_K, TUNE_MATMUL_WARPS = 4, 5, 6
+TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES = 8, 9, 10, 11
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 
@@ -26,7 +26,9 @@ EXPORTS = [
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
     "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
-    "muser_cuda_static_sync_status", "muser_cuda_wait_probe",
+    "muser_cuda_static_sync_status", "muser_cuda_wait_probe", "muser_cuda_quantized_matmul_group",
+    "muser_cuda_matmul_host_enqueue", "muser_cuda_comm_unique_id", "muser_cuda_ctx_comm_init", "muser_cuda_ctx_comm_attach",
+    "muser_cuda_ctx_comm_has_oneshot", "muser_cuda_all_reduce",
 ]
 
 
@@ -37,6 +39,11 @@ class Shard(C.Structure):
 class Epilogue(C.Structure):
     _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("norm_eps", C.c_float),
                 ("norm_weight", C.c_void_p), ("out_scale", C.c_float), ("softcap", C.c_float)]
+
+
+class GroupItem(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_uint32), ("reserved", C.c_uint32),
+                ("epilogue", C.POINTER(Epilogue))]
 
 
 class WeightInfo(C.Structure):
@@ -82,6 +89,12 @@ def _load() -> C.CDLL:
         "muser_cuda_nvfp4_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
         "muser_cuda_nvfp4_matmul_prequant": (i32, [vp, vp, vp, vp, vp, u32, u32, C.POINTER(Epilogue), vp]),
         "muser_cuda_matmul_host": (i32, [vp, vp, vp, u32, vp]),
+        "muser_cuda_matmul_host_enqueue": (i32, [vp, vp, vp, u32, vp, vp]),
+        "muser_cuda_comm_unique_id": (i32, [vp, C.c_size_t]),
+        "muser_cuda_ctx_comm_init": (i32, [vp, vp, u32, u32, vp]),
+        "muser_cuda_ctx_comm_attach": (i32, [vp, vp, u32, u32, vp]),
+        "muser_cuda_ctx_comm_has_oneshot": (i32, [vp]),
+        "muser_cuda_all_reduce": (i32, [vp, vp, u64, u32, vp]),
         "muser_cuda_nvfp4_matmul_static": (i32, [vp, vp, u32, vp, u32, u32, vp]),
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
@@ -90,6 +103,7 @@ def _load() -> C.CDLL:
         "muser_cuda_f16_mma_probe": (i32, [vp, u32, u32, C.POINTER(C.c_double)]),
         "muser_cuda_static_sync_status": (i32, [i32, vp]),
         "muser_cuda_wait_probe": (i32, [vp, u32, vp]),
+        "muser_cuda_quantized_matmul_group": (i32, [vp, C.POINTER(GroupItem), u32, vp, u32, u32, vp]),
         "muser_cuda_rmsnorm_quantize_nvfp4_activation": (i32, [vp, vp, u32, u32, u64, vp, f32, f32, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():

@@ -86,7 +86,6 @@ static muser_cuda_status repack_common(Ctx *ctx, uint32_t dtype, const uint8_t *
     if (!w) return fail(ctx, MUSER_CUDA_ERROR, "out of host memory");
     w->dtype = dtype;
     w->device = ctx->device;
-    w->layout = is_kquant(dtype) ? ctx->kq_layout : 0;
     muser_cuda_status st = validate_shard(ctx, dtype, n_in, n_out, shard, w);
     auto bail = [&](muser_cuda_status s) {
         muser_cuda_weight_free(reinterpret_cast<muser_cuda_weight *>(w));
@@ -250,6 +249,7 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     Ctx *ctx = reinterpret_cast<Ctx *>(c);
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    comm_destroy(ctx);
     cudaFree(ctx->workspace);
     cudaFree(ctx->dev_status);
     cudaFree(ctx->gemv_partial);
@@ -257,6 +257,7 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->norm_scratch);
     cudaFree(ctx->tc_scratch);
     cudaFree(ctx->dev_stage);
+    cudaFree(ctx->arena);
     if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     delete ctx;
@@ -274,6 +275,7 @@ muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *c, void *stream) {
     int flags[4] = {0, 0, 0, 0};
     MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(flags, ctx->dev_status, sizeof(flags), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     MUSER_CUDA_TRY(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    ctx->arena_used = 0; // everything enqueued through matmul_host_enqueue on this stream has finished
     if (flags[1]) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(flags), (cudaStream_t)stream);
         return fail(ctx, MUSER_CUDA_TIMEOUT, "a device-side bounded wait gave up (code " + std::to_string(flags[1]) + ")");
@@ -288,19 +290,10 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
     case MUSER_TUNE_TC_MIN_TOKENS_Q4_K: ctx->tc_min_tokens[0] = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_TC_MIN_TOKENS_Q6_K: ctx->tc_min_tokens[1] = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_TC_MIN_ROWS: ctx->tc_min_rows = value; return MUSER_CUDA_OK;
-    case MUSER_TUNE_GEMV_MAX_TOKENS_Q4_K: ctx->gemv_max_tokens[0] = value; return MUSER_CUDA_OK;
-    case MUSER_TUNE_GEMV_MAX_TOKENS_Q6_K: ctx->gemv_max_tokens[1] = value; return MUSER_CUDA_OK;
-    case MUSER_TUNE_MATMUL_WARPS:
-        if (value > 8) return fail(ctx, MUSER_CUDA_BAD_ARG, "at most 8 warps");
-        ctx->matmul_warps = value;
-        return MUSER_CUDA_OK;
-    case MUSER_TUNE_KQUANT_LAYOUT:
-        if (value > 1) return fail(ctx, MUSER_CUDA_BAD_ARG, "layout is 0 or 1");
-        ctx->kq_layout = value;
-        return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_WARPS: ctx->dec_warps = value & ~1u; return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_KSPLIT: ctx->dec_ksplit = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_RING: ctx->dec_ring = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
 }
@@ -389,6 +382,43 @@ muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *c, const muser_cud
     if (st != MUSER_CUDA_OK) return st;
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_kquant_matmul(ctx, w, nullptr, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_quantized_matmul_group(muser_cuda_ctx *c, const muser_cuda_group_item *items, uint32_t n_items,
+                                                    const void *x, uint32_t x_dtype, uint32_t tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !items || n_items == 0 || n_items > 4) return fail(ctx, MUSER_CUDA_BAD_ARG, "a group holds 1..4 projections");
+    if (tokens > 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "a grouped launch serves 1..16 tokens");
+    const Weight *w[4];
+    void *y[4];
+    uint32_t yd[4];
+    Epilogue e[4];
+    for (uint32_t i = 0; i < n_items; ++i) {
+        w[i] = reinterpret_cast<const Weight *>(items[i].w);
+        y[i] = items[i].y;
+        yd[i] = items[i].y_dtype;
+        muser_cuda_status st = check_io(ctx, w[i], x, x_dtype, y[i], yd[i], tokens, false);
+        if (st != MUSER_CUDA_OK) return st;
+        if (!is_kquant(w[i]->dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "grouped launches take K-quant weights");
+        if (items[i].epilogue && items[i].epilogue->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "use muser_cuda_ffn_gate_up_silu for the fused gate/up");
+        st = take_epilogue(ctx, w[i], items[i].epilogue, &e[i]);
+        if (st != MUSER_CUDA_OK) return st;
+        if (w[i]->n_in != w[0]->n_in || w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the projections of a group must share n_in and the K shard geometry");
+        if (e[i].norm_weight != e[0].norm_weight || e[i].norm_eps != e[0].norm_eps)
+            return fail(ctx, MUSER_CUDA_BAD_ARG, "the projections of a group share one input, so they must share the fused input norm");
+    }
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const cudaError_t de = launch_kquant_decode(ctx, w, nullptr, n_items, x, x_dtype, y, yd, tokens, e, (cudaStream_t)stream);
+    if (de != cudaErrorNotSupported) {
+        MUSER_CUDA_TRY(ctx, de);
+        return MUSER_CUDA_OK;
+    }
+    for (uint32_t i = 0; i < n_items; ++i) { // shapes the grouped kernel does not take: one launch each
+        const muser_cuda_status st = launch_kquant_matmul(ctx, w[i], nullptr, x, x_dtype, y[i], yd[i], tokens, e[i], (cudaStream_t)stream);
+        if (st != MUSER_CUDA_OK) return st;
+    }
+    return MUSER_CUDA_OK;
 }
 
 muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx *c, const muser_cuda_weight *wp, const uint32_t *rows,
@@ -580,6 +610,46 @@ muser_cuda_status muser_cuda_f16_mma_probe(muser_cuda_ctx *c, uint32_t n_cols, u
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     MUSER_CUDA_TRY(ctx, cudaDeviceSynchronize()); // the probe borrows the split-K scratch
     return launch_f16_mma_probe(ctx, n_cols, iters, cycles_per_mma);
+}
+
+muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *c, const muser_cuda_weight *wp, const float *x_host,
+                                                 uint32_t tokens, float *y_host, void *stream_) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    cudaStream_t s = (cudaStream_t)stream_;
+    if (!ctx || !w || !x_host || !y_host || tokens == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)tokens * w->n_in * 4, yb = (size_t)tokens * w->n_out * 4;
+    const size_t need = (xb + 255) / 256 * 256 + (yb + 255) / 256 * 256;
+    if (ctx->arena_used + need > ctx->arena_bytes) {
+        // out of staging: wait for what is in flight, then start over (and grow, for a call larger than the arena)
+        MUSER_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+        ctx->arena_used = 0;
+        if (need > ctx->arena_bytes) {
+            cudaFree(ctx->arena);
+            ctx->arena = nullptr;
+            ctx->arena_bytes = 0;
+            const size_t want = need > ((size_t)64 << 20) ? need : ((size_t)64 << 20);
+            MUSER_CUDA_TRY(ctx, cudaMalloc(&ctx->arena, want));
+            ctx->arena_bytes = want;
+        }
+    }
+    uint8_t *dx = reinterpret_cast<uint8_t *>(ctx->arena) + ctx->arena_used, *dy = dx + (xb + 255) / 256 * 256;
+    ctx->arena_used += need;
+    MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(dx, x_host, xb, cudaMemcpyHostToDevice, s));
+    muser_cuda_status st = MUSER_CUDA_OK;
+    if (w->dtype == MUSER_DTYPE_NVFP4_E2M1) {
+        st = muser_cuda_nvfp4_matmul(c, wp, dx, MUSER_DTYPE_F32, dy, MUSER_DTYPE_F32, tokens, nullptr, s);
+    } else {
+        for (uint32_t t0 = 0; t0 < tokens && st == MUSER_CUDA_OK; t0 += 64) {
+            const uint32_t n = tokens - t0 < 64 ? tokens - t0 : 64;
+            st = muser_cuda_quantized_matmul(c, wp, dx + (size_t)t0 * w->n_in * 4, MUSER_DTYPE_F32,
+                                             dy + (size_t)t0 * w->n_out * 4, MUSER_DTYPE_F32, n, nullptr, s);
+        }
+    }
+    if (st != MUSER_CUDA_OK) return st;
+    MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(y_host, dy, yb, cudaMemcpyDeviceToHost, s));
+    return MUSER_CUDA_OK;
 }
 
 muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *c, const muser_cuda_weight *wp, const float *x_host,

@@ -35,11 +35,8 @@ struct Ctx {
     uint32_t gemv_counter_slots = 0;
     void *tc_scratch = nullptr;            // f16 activations + sub-block sums of the tensor-core K-quant kernel
     size_t tc_scratch_bytes = 0;
-    uint32_t tc_min_tokens[2] = {12, 5};   // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
-    uint32_t tc_min_rows = 2048;           // and from how many output rows: measured crossovers)
-    uint32_t matmul_warps = 0;             // 0: the general skinny kernel picks its warps per CTA from the weight's shape
-    uint32_t gemv_max_tokens[2] = {2, 4};  // up to how many tokens Q4_K / Q6_K calls take the decode GEMV
-    uint32_t kq_layout = 0;                // image layout that muser_cuda_weight_repack builds for K-quant weights
+    uint32_t tc_min_tokens[2] = {17, 17};  // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
+    uint32_t tc_min_rows = 2048;           // and from how many output rows); fewer tokens take the decode kernel
     uint32_t dec_warps = 0, dec_ksplit = 0, dec_ring = 0; // decode kernel plan overrides (0: from its cost model)
     float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
     size_t norm_scratch_bytes = 0;
@@ -48,8 +45,14 @@ struct Ctx {
     size_t host_stage_bytes = 0;
     void *dev_stage = nullptr;
     size_t dev_stage_bytes = 0;
+    void *arena = nullptr; // device staging of matmul_host_enqueue: bumped per call, rewound by sync_status
+    size_t arena_bytes = 0, arena_used = 0;
+    void *comm = nullptr;                      // tensor-parallel communicator (collective.cu), or null
+    uint32_t oneshot_max_bytes = 256u << 10;   // all-reduce payloads up to this size take the one-shot peer exchange
     std::string last_error;
 };
+
+void comm_destroy(Ctx *ctx);
 
 struct Weight {
     uint32_t dtype = 0;
@@ -62,7 +65,6 @@ struct Weight {
     uint32_t row_tiles = 0;   // ceil(n_out / 16)
     uint32_t nsb = 0;         // super-block tiles per row tile
     uint32_t k_off = 0;       // elements of the first tile that precede this shard's first input
-    uint32_t layout = 0;      // 0: lanes own whole sub-blocks, 1: lanes own a quarter of every sub-block (kquant_layout.cuh)
     // NVFP4
     uint8_t *packed = nullptr; // [n_out_pad][n_in/2]
     uint8_t *scales = nullptr; // swizzled [n_out_pad/128][ceil(n_in/64)][32][4][4], unsigned magnitudes
@@ -161,8 +163,6 @@ cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_d
 cudaError_t launch_kquant_decode(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
                                  const Epilogue *ep, cudaStream_t);
-cudaError_t launch_kquant_gemv(Ctx *, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype, void *y,
-                               uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
                                         float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t,
                                         const float *norm_weight = nullptr, float norm_eps = 0.0f);

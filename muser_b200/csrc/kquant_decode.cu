@@ -12,7 +12,7 @@
 //   - activations become 15-bit fixed point per token and 256-input tile (x ~ sx * (128 hi + lo), two int8 planes,
 //     |error| <= amax(tile) * 2^-15), once per CTA, parked in shared memory in tensor-core fragment order;
 //   - the 4-bit (6-bit) quants go straight from the tile into int8 mma.sync fragments: the image is laid out so that
-//     a lane already owns its fragment's bytes (kquant_layout.cuh, "column" layout);
+//     a lane already owns its fragment's bytes (kquant_layout.cuh);
 //   - one MMA multiplies a whole sub-block (32 weights of 16 rows for Q4_K, 16 for Q6_K) with a group of four
 //     tokens: the eight fragment columns are (token, plane) pairs, so a lane ends up with the high- and low-plane
 //     sums of ITS token for rows g and g + 8 and no value ever crosses lanes;
@@ -104,7 +104,7 @@ template <> struct Fmt<MUSER_DTYPE_Q4_K> { static constexpr int kTileBytes = kQ4
 template <> struct Fmt<MUSER_DTYPE_Q6_K> { static constexpr int kTileBytes = kQ6TileBytes; };
 
 constexpr int kFragU4 = 128; // uint4 of B fragments per (tile, token group): 4 fragment quads x 32 lanes
-constexpr int kMetaU4 = 3;   // uint4 per (tile, token): sx, then the eight sub-block sums of a Q4_K tile
+constexpr int kMetaU4 = 2;   // uint4 per (tile, token): sx, then (Q4_K) the eight sub-block sums as three byte planes
 
 // ------------------------------------------------------------------------------------ activation staging
 // One warp turns one (tile, token) into fragment bytes: lane l holds inputs 8l .. 8l+7 of the tile.
@@ -119,13 +119,15 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
     constexpr int TOK = 4 * NG;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     uint32_t *fw = reinterpret_cast<uint32_t *>(frag), *mw = reinterpret_cast<uint32_t *>(meta);
-    for (uint32_t task = warp; task < n_tiles * TOK; task += warps) {
-        const uint32_t tile = task / TOK, tok = task % TOK, gp = tok >> 2, t4 = tok & 3;
-        float v[8];
+    // one task = one (tile, token); a warp takes tasks warp, warp + warps, ... and fetches the next task's inputs
+    // before it works on the current one (the loads come from L2 and would otherwise be paid once per task in turn)
+    auto fetch = [&](uint32_t task, float (&v)[8]) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        if (task >= n_tiles * a.tokens) return;
+        const uint32_t tile = task / a.tokens, tok = task % a.tokens;
         const int64_t k = (int64_t)(sb_first + tile) * 256 - (int64_t)a.k_off + 8 * lane;
-        if (tok < a.tokens && (uint64_t)k < a.n_in) { // a negative k wraps to a huge value
+        if ((uint64_t)k < a.n_in) { // a negative k wraps to a huge value
             if (a.x_f32) load8<true>(reinterpret_cast<const float *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
             else load8<false>(reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)tok * a.n_in + k, 0, v);
             if (a.norm_weight) { // (x * 1/rms) * weight, in that order
@@ -136,6 +138,23 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
                 for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], rs), nw[i]);
             }
         }
+    };
+    // columns of tokens that do not exist are zero; meta entries of such tokens are never used for a stored result
+    if (a.tokens < (uint32_t)TOK) {
+        const uint32_t per_tile = NG * kFragU4;
+        for (uint32_t i = threadIdx.x; i < n_tiles * per_tile; i += blockDim.x) {
+            const uint32_t col = (i % 32) >> 2, tok = 4 * ((i % per_tile) / kFragU4) + (col >> 1); // entry (quad, column, t)
+            if (tok >= a.tokens) frag[i] = make_uint4(0, 0, 0, 0);
+        }
+        for (uint32_t i = threadIdx.x; i < n_tiles * TOK * kMetaU4; i += blockDim.x)
+            if ((i / kMetaU4) % TOK >= a.tokens) meta[i] = make_uint4(0, 0, 0, 0);
+    }
+    const uint32_t n_tasks = n_tiles * a.tokens; // task -> (tile, token < tokens)
+    float v[8], nxt[8];
+    fetch(warp, v);
+    for (uint32_t task = warp; task < n_tasks; task += warps) {
+        const uint32_t tile = task / a.tokens, tok = task % a.tokens, gp = tok >> 2, t4 = tok & 3;
+        fetch(task + warps, nxt);
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -171,7 +190,14 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
             uint32_t *e = fbase + (((j >> 1) * 32 + (2 * t4) * 4 + tq) * 4 + (j & 1) * 2);
             *reinterpret_cast<uint2 *>(e) = make_uint2(h0, h1);      // column 2 * t4: high plane
             *reinterpret_cast<uint2 *>(e + 16) = make_uint2(l0, l1); // column 2 * t4 + 1: low plane
-            if (tq == 0) mrow[1 + j] = (uint32_t)sum;
+            // the sub-block's integer sum S (|S| <= 2^19) as three byte planes, S = 2^14 s2 + 2^7 s1 + s0 with s0, s1 in
+            // 0..127 and s2 signed, so that four sub-blocks' worth multiply a word of 6-bit mins in one dp4a each
+            if (tq == 0) {
+                uint8_t *mb = reinterpret_cast<uint8_t *>(mrow + 1);
+                mb[j] = (uint8_t)(sum & 127);
+                mb[8 + j] = (uint8_t)((sum >> 7) & 127);
+                mb[16 + j] = (uint8_t)((sum >> 14) & 0xFF);
+            }
             if (lane == 0) mrow[0] = __float_as_uint(sx);
         } else {
             const uint32_t s = lane >> 1, t = 2 * (lane & 1);
@@ -183,6 +209,8 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
             e[16] = l0, e[20] = l1; // and of the low-plane column
             if (lane == 0) mrow[0] = __float_as_uint(sx * 0.25f); // the fragment bytes are 4 * (q - 32)
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = nxt[i];
     }
 }
 
@@ -247,17 +275,15 @@ __device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, c
             }
         }
     }
-    int ma[8], mb[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ma[j] = ubyte(ha.mn[j >> 2], j & 3), mb[j] = ubyte(hb.mn[j >> 2], j & 3);
 #pragma unroll
     for (int gp = 0; gp < NG; ++gp) {
         const uint4 *m = mt + (gp * 4 + t) * kMetaU4;
-        const uint4 m0 = m[0], m1 = m[1], m2 = m[2];
-        const int s[8] = {(int)m0.y, (int)m0.z, (int)m0.w, (int)m1.x, (int)m1.y, (int)m1.z, (int)m1.w, (int)m2.x};
-        int mina = 0, minb = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mina += ma[j] * s[j], minb += mb[j] * s[j];
+        const uint4 m0 = m[0], m1 = m[1];
+        // sum_j min_j S_j with S_j = 2^14 s2 + 2^7 s1 + s0: planes (m0.y, m0.z), (m0.w, m1.x), (m1.y, m1.z)
+        auto dot8 = [](const uint32_t (&mn)[2], uint32_t p0, uint32_t p1) { return __dp4a((int)mn[0], (int)p0, __dp4a((int)mn[1], (int)p1, 0)); };
+        const int a0 = dot8(ha.mn, m0.y, m0.z), a1 = dot8(ha.mn, m0.w, m1.x), a2 = dot8(ha.mn, m1.y, m1.z);
+        const int b0 = dot8(hb.mn, m0.y, m0.z), b1 = dot8(hb.mn, m0.w, m1.x), b2 = dot8(hb.mn, m1.y, m1.z);
+        const int mina = (a2 << 14) + (a1 << 7) + a0, minb = (b2 << 14) + (b1 << 7) + b0;
         const float sx = __uint_as_float(m0.x);
         const float pa = fmaf(128.0f, (float)acc[gp][0], (float)acc[gp][1]), pb = fmaf(128.0f, (float)acc[gp][2], (float)acc[gp][3]);
         out[gp][0] = fmaf(sx, fmaf(-ha.dmin, (float)mina, ha.d * pa), out[gp][0]);
@@ -490,13 +516,16 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     }
 }
 
-constexpr int max_warps(int ng) { return ng > 1 ? 16 : 14; }
+// Threads and CTAs per SM by token groups: one group runs two CTAs of 14 warps an SM (72 registers a thread), two
+// groups two CTAs of 12 warps (80 registers), more groups one CTA of 16 warps.
+constexpr int max_warps(int ng) { return ng == 1 ? 14 : ng == 2 ? 12 : 16; }
+constexpr int ctas_per_sm(int ng) { return ng <= 2 ? 2 : 1; }
 
 } // namespace dec
 
 // blockIdx.x -> (job, CTA group, K slice): a job's CTAs are contiguous, group-major.
 template <int NG, bool DUAL>
-__global__ void __launch_bounds__(dec::max_warps(NG) * 32, (NG > 1 ? 1 : 2)) kquant_decode_kernel(const __grid_constant__ DecArgs a) {
+__global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG)) kquant_decode_kernel(const __grid_constant__ DecArgs a) {
     extern __shared__ uint4 dec_dyn[];
     __shared__ float inv_rms[4 * NG];
     uint32_t ji = 0;
@@ -536,7 +565,7 @@ DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6
                 const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng);
                 if (smem > 220u * 1024) continue;
                 int ctas = (int)((227u * 1024) / (smem + 1024));
-                ctas = std::min(ctas, std::max(1, (ng > 1 ? 16 : 28) / w)); // 128 (72) registers a thread
+                ctas = std::min(ctas, std::max(1, dec::max_warps(ng) * dec::ctas_per_sm(ng) / w)); // the register file
                 const double tiles = std::ceil((double)nsb / ks);
                 const double wanted = std::ceil((double)row_tiles / w);                   // CTAs per slice if every warp took one row tile
                 const double groups = std::min(wanted, std::floor((double)ctas * sm_count / ks));
@@ -638,7 +667,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
 
 } // namespace
 
-// Up to four column-layout K-quant weights of one n_in (and one K shard geometry) applied to the same 1..16 tokens.
+// Up to four K-quant weights of one n_in (and one K shard geometry) applied to the same 1..16 tokens.
 // w_up: the fused gate/up form (one job).  Returns cudaErrorNotSupported when the shape does not fit this kernel.
 cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
@@ -647,7 +676,7 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     DecArgs a;
     a.n_jobs = n_jobs;
     for (uint32_t i = 0; i < n_jobs; ++i) {
-        if (w[i]->layout != 1 || w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off || w[i]->n_in != w[0]->n_in) return cudaErrorNotSupported;
+        if (w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off || w[i]->n_in != w[0]->n_in) return cudaErrorNotSupported;
         DecJob &j = a.job[i];
         j.image = w[i]->image;
         j.image_up = w_up ? w_up->image : nullptr;
@@ -692,6 +721,55 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     case 3: return dec_launch<3, false>(a, ctx, forced, stream);
     default: return dec_launch<4, false>(a, ctx, forced, stream);
     }
+}
+
+// ------------------------------------------------------------------------------------ dispatch
+// Which kernel serves a K-quant call (bf16 or f32 activations alike): up to 16 tokens the decode kernel above; from
+// 17 tokens the tcgen05 kernel (kquant_tc.cu) when the weight has enough 128-row blocks to fill the GPU and the token
+// count fits its columns (64, or 32 for f32 activations, which travel as f16 head + remainder pairs); everything else
+// in chunks of 16 tokens through the decode kernel.  The thresholds can be moved through muser_cuda_tuning_set.
+muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *w_up, const void *x, uint32_t x_dtype,
+                                       void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &ep,
+                                       cudaStream_t stream) {
+    const bool q6 = w->dtype == MUSER_DTYPE_Q6_K, xf32 = x_dtype == MUSER_DTYPE_F32;
+    const uint32_t tc_from = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
+    const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32 ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
+    if (tc_fits) {
+        const void *xin = x;
+        uint32_t xin_dtype = x_dtype;
+        if (ep.norm_weight) {
+            // the tensor-core kernel reads its activations through TMA, so the fused input norm runs as a pass of its
+            // own into the context's scratch rows (f32), which the projection then reads instead of x
+            const size_t need = (size_t)tokens * w->n_in * sizeof(float);
+            if (need > ctx->norm_scratch_bytes) return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL, "fused input norm: tokens x n_in exceeds the context's norm scratch");
+            muser_cuda_status st = launch_rmsnorm_rows(ctx, x, x_dtype, tokens, w->n_in, ep.norm_weight, ep.norm_eps, ctx->norm_scratch, stream);
+            if (st != MUSER_CUDA_OK) return st;
+            xin = ctx->norm_scratch;
+            xin_dtype = MUSER_DTYPE_F32;
+        }
+        if (xin_dtype != MUSER_DTYPE_F32 || tokens <= 32) {
+            Epilogue tail = ep;
+            tail.norm_weight = nullptr;
+            const cudaError_t te = launch_kquant_tc(ctx, w, xin, xin_dtype, y, y_dtype, tokens, tail, stream);
+            if (te != cudaErrorNotSupported) {
+                MUSER_CUDA_TRY(ctx, te);
+                return MUSER_CUDA_OK;
+            }
+        }
+    }
+    const size_t xb = xf32 ? 4 : 2, yb = y_dtype == MUSER_DTYPE_BF16 ? 2 : 4;
+    for (uint32_t t0 = 0; t0 < tokens; t0 += 16) {
+        const uint32_t n = std::min(16u, tokens - t0);
+        Epilogue e = ep;
+        if (e.row_scale) e.row_scale += t0;
+        if (e.residual) e.residual = reinterpret_cast<const uint8_t *>(e.residual) + (size_t)t0 * w->n_out * yb;
+        void *yc = reinterpret_cast<uint8_t *>(y) + (size_t)t0 * w->n_out * yb;
+        const cudaError_t de = launch_kquant_decode(ctx, &w, w_up, 1, reinterpret_cast<const uint8_t *>(x) + (size_t)t0 * w->n_in * xb,
+                                                    x_dtype, &yc, &y_dtype, n, &e, stream);
+        if (de == cudaErrorNotSupported) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "this shape does not fit the decode kernel");
+        MUSER_CUDA_TRY(ctx, de);
+    }
+    return MUSER_CUDA_OK;
 }
 
 } // namespace muser

@@ -136,10 +136,10 @@ __device__ __forceinline__ __half2 byte_pair(uint32_t w, uint32_t idx, float bia
 
 // ------------------------------------------------------------------------------------ Q4_K
 // What one unpacking warp holds of a tile: rows g (+ 8 * rowsel, rowsel fixed per warp), lane (g, t).
-// Its ring slot is [2 planes of 512 bytes: sub-blocks t, t + 4][8 row headers of 16 bytes].
+// Its ring slot is [2 planes of 512 bytes: sub-blocks 0-3 and 4-7, this lane's eight elements of each][8 row headers].
 constexpr int kTcQ4Slot = 1024 + 128, kTcQ6Slot = 1024 + 512 + 128 + 16;
 struct TcQ4 {
-    uint4 q[2]; // [hi]: sub-block t + 4*hi
+    uint4 q[2]; // [half]: word jj = sub-block 4*half + jj, elements 8t .. 8t+7
     uint4 h;    // the row's header
 };
 struct TcQ4Hdr {
@@ -166,18 +166,22 @@ __device__ __forceinline__ TcQ4 tc_load(const uint8_t *slot, int lane, TcQ4 *) {
     return r;
 }
 // Inputs 128*HALF .. +127 of row `row` (a multiple of 8 plus g) -> the A stage: sc * q as f16.
+// Column layout (kquant_layout.cuh): word jj of r.q[HALF] holds elements 8t .. 8t+7 of sub-block 4*HALF + jj, i.e.
+// the 16-byte chunk 4*jj + t of the row's 128 inputs: atom jj / 2, chunk (jj % 2) * 4 + t inside it.
 template <int HALF>
 __device__ __forceinline__ void tc_unpack_half(const TcQ4 &r, const TcQ4Hdr &hd, uint32_t stage, uint32_t row, int g, int t) {
-    const __half2 sc = byte_pair(hd.sc[HALF], (uint32_t)t, 1024.0f);
-    const __half2 off = __hmul2(sc, __float2half2_rn(-1024.0f)); // exact: at most 63 * 1024
-    const uint32_t base = stage + (uint32_t)(t >> 1) * 16384u + (row >> 3) * 1024u + (row & 7) * 128u;
-    // Lanes t and t + 2 write the same 16-byte column of two different 16 KiB atoms, i.e. the same banks; the upper
-    // pair therefore walks its four words in the order 2, 3, 0, 1, which makes the warp's stores conflict-free.
-    const bool flip = t >= 2;
+    const uint32_t base = stage + (row >> 3) * 1024u + (row & 7) * 128u;
+    // In one store instruction the lanes of rows g and g + 1 would write the same four chunks of two rows, i.e. the
+    // same banks; odd rows therefore take their words in the order 1, 0, 3, 2, which puts them in the other half of
+    // the 128-byte row and makes the warp's stores conflict-free.
+    const uint32_t odd = (uint32_t)g & 1u;
     uint4 qv = r.q[HALF];
-    if (flip) qv = make_uint4(qv.z, qv.w, qv.x, qv.y);
+    if (odd) qv = make_uint4(qv.y, qv.x, qv.w, qv.z);
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t jj = (uint32_t)wi ^ odd; // sub-block 4*HALF + jj
+        const __half2 sc = byte_pair(hd.sc[HALF], jj, 1024.0f);
+        const __half2 off = __hmul2(sc, __float2half2_rn(-1024.0f)); // exact: at most 63 * 1024
         const uint32_t w = word_of(qv, wi);
         uint32_t o[4];
 #pragma unroll
@@ -185,14 +189,13 @@ __device__ __forceinline__ void tc_unpack_half(const TcQ4 &r, const TcQ4Hdr &hd,
             const uint32_t e = ((w >> (4 * p)) & 0x000F000Fu) | 0x64006400u; // (1024 + q, 1024 + q')
             o[p] = h2u(__hfma2(u2h(e), sc, off));                            // sc * q, exact
         }
-        const uint32_t word = flip ? (uint32_t)(wi ^ 2) : (uint32_t)wi;      // which 8 elements of the sub-block these are
-        const uint32_t chunk = ((uint32_t)(t & 1) * 4 + word) ^ (uint32_t)g;
-        sts128(base + chunk * 16u, o[0], o[1], o[2], o[3]);
+        const uint32_t chunk = ((jj & 1u) * 4u + (uint32_t)t) ^ (uint32_t)g;
+        sts128(base + (jj >> 1) * 16384u + chunk * 16u, o[0], o[1], o[2], o[3]);
     }
 }
 
 // ------------------------------------------------------------------------------------ Q6_K
-// Ring slot: [2 low-nibble planes of 512 bytes][high-bit plane, 512][8 x sc[16] int8][8 x d f16].
+// Ring slot: [2 top-nibble planes of 512 bytes][low-two-bits plane, 512][8 x sc[16] int8][8 x d f16].
 struct TcQ6 {
     uint4 lo[2]; // [half]
     uint4 hi;
@@ -209,32 +212,30 @@ __device__ __forceinline__ TcQ6 tc_load(const uint8_t *slot, int lane, TcQ6 *) {
     r.d = __half2float(reinterpret_cast<const __half *>(slot + 1664)[lane >> 2]);
     return r;
 }
-// elements 4x .. 4x+3 of one sub-block as bytes 0..63: low nibbles from `lo`, the two high bits from `hi`
-__device__ __forceinline__ uint32_t tc_q6_bytes(uint32_t lo, uint32_t hi, int x) {
-    const uint32_t n = ((x & 1) ? lo >> 4 : lo) & 0x0F0F0F0Fu;
-    const uint32_t h = x == 0 ? hi << 4 : x == 1 ? hi << 2 : x == 2 ? hi : hi >> 2;
-    return n | (h & 0x30303030u);
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+// Column layout: the lane holds elements 4t .. 4t+3 of every sub-block of its row, stored as (q - 32) & 63 split
+// into a top-nibble plane (r.lo) and a low-two-bits plane (r.hi); (T << 4) | (L << 2) is the signed byte 4 (q - 32).
+// What goes to the A stage is 4 * sc * (q - 32) as f16 (the factor 4 is a shift of the exponent, so the products are
+// as exact as sc * (q - 32) itself); the drain's d carries the 1/4.
 template <int HALF>
 __device__ __forceinline__ void tc_unpack_half(const TcQ6 &r, uint32_t stage, uint32_t row, int g, int t) {
-    const __half2 k1056 = __float2half2_rn(1056.0f);
+    const __half2 k1152 = __float2half2_rn(1152.0f);
+    const uint32_t base = stage + (row >> 3) * 1024u + (row & 7) * 128u + (uint32_t)(t & 1) * 8u;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) { // owned sub-block 2*HALF + u = sub-block t + 4*(2*HALF + u)
-        const uint32_t hw = word_of(r.hi, 2 * HALF + u), sw = word_of(r.sc, 2 * HALF + u);
-        const __half2 sc = byte_pair(sw ^ 0x80808080u, (uint32_t)t, 1152.0f); // int8 scale, exact
-        const uint32_t base = stage + (uint32_t)u * 16384u + (row >> 3) * 1024u + (row & 7) * 128u;
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) { // elements 8*h2 .. 8*h2 + 7 of the sub-block
-            const uint32_t lw = word_of(r.lo[HALF], 2 * u + h2);
-            const uint32_t b0 = tc_q6_bytes(lw, hw, 2 * h2), b1 = tc_q6_bytes(lw, hw, 2 * h2 + 1);
-            const uint32_t p0 = __byte_perm(b0, 0x64646464u, 0x4140u), p1 = __byte_perm(b0, 0x64646464u, 0x4342u);
-            const uint32_t p2 = __byte_perm(b1, 0x64646464u, 0x4140u), p3 = __byte_perm(b1, 0x64646464u, 0x4342u);
-            // (1024 + q) - 1056 = q - 32, exact; times the scale: exact up to 2048, nearest even beyond
-            const uint32_t o0 = h2u(__hmul2(__hsub2(u2h(p0), k1056), sc)), o1 = h2u(__hmul2(__hsub2(u2h(p1), k1056), sc));
-            const uint32_t o2 = h2u(__hmul2(__hsub2(u2h(p2), k1056), sc)), o3 = h2u(__hmul2(__hsub2(u2h(p3), k1056), sc));
-            const uint32_t chunk = (uint32_t)(2 * t + h2) ^ (uint32_t)g;
-            sts128(base + chunk * 16u, o0, o1, o2, o3);
-        }
+    for (int sl = 0; sl < 8; ++sl) { // sub-block 8*HALF + sl: inputs 16*sl + 4t .. + 3 of the half
+        constexpr int kX[4] = {2, 0, -2, -4};
+        const uint32_t tw = word_of(r.lo[HALF], sl >> 1), lw = word_of(r.hi, 2 * HALF + (sl >> 2));
+        const uint32_t top = (sl & 1) ? tw : tw << 4;
+        const int sh = kX[sl & 3];
+        const uint32_t low = sh > 0 ? lw << sh : lw >> (-sh);
+        const uint32_t b = ((top & 0xF0F0F0F0u) | (low & 0x0C0C0C0Cu)) ^ 0x80808080u; // bytes 4 (q - 32) + 128
+        const __half2 sc = byte_pair(word_of(r.sc, 2 * HALF + (sl >> 2)) ^ 0x80808080u, (uint32_t)(sl & 3), 1152.0f); // int8 scale, exact
+        const uint32_t p0 = __byte_perm(b, 0x64646464u, 0x4140u), p1 = __byte_perm(b, 0x64646464u, 0x4342u);
+        const uint32_t o0 = h2u(__hmul2(__hsub2(u2h(p0), k1152), sc)), o1 = h2u(__hmul2(__hsub2(u2h(p1), k1152), sc));
+        const uint32_t chunk = (uint32_t)(2 * (sl & 3) + (t >> 1)) ^ (uint32_t)g;
+        sts64(base + (uint32_t)(sl >> 2) * 16384u + chunk * 16u, o0, o1);
     }
 }
 
@@ -437,7 +438,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                     if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(hd.d, hd.dmin);
                 } else {
-                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(cur.d, 0.0f);
+                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(0.25f * cur.d, 0.0f); // the A operand is 4 sc (q - 32)
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic stores -> visible to the MMA's reads

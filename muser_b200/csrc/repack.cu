@@ -8,74 +8,8 @@
 
 namespace muser {
 
-// ------------------------------------------------------------------------------ Q4_K repack
-// One thread builds one 32-bit word of the nibble plane (8 weights of one row and sub-block), or
-// one scale header.
-__global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
-    const uint64_t words_per_tile = 512, units_per_tile = 512 + 16;
-    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
-    uint64_t total = (uint64_t)gm.row_tiles * gm.nsb * units_per_tile;
-    if (idx >= total) return;
-    uint64_t tile = idx / units_per_tile;
-    uint32_t u = (uint32_t)(idx % units_per_tile);
-    uint32_t rt = (uint32_t)(tile / gm.nsb), sb = (uint32_t)(tile % gm.nsb);
-    uint8_t *tile_ptr = image + tile * kQ4TileBytes;
-    // global super-block index and the element range of this shard inside it
-    uint64_t sb_global = gm.k0 / 256 + sb;
-    int64_t k_base = (int64_t)sb_global * 256; // global k of element 0 of this tile
-    if (u < words_per_tile) {
-        uint32_t q = u >> 7, lane = (u >> 2) & 31, wi = u & 3;
-        uint32_t g = lane >> 2, t = lane & 3;
-        uint32_t row = rt * 16 + g + 8 * (q >> 1);
-        uint32_t j = t + 4 * (q & 1);
-        uint32_t word = 0;
-        if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
-            for (int i = 0; i < 8; ++i) {
-                uint32_t e = 32 * j + 8 * wi + i;
-                int64_t k = k_base + e;
-                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) continue;
-                uint32_t grp = e >> 6, l = e & 63;
-                uint8_t byte = blk[16 + 32 * grp + (l & 31)];
-                uint32_t nib = l < 32 ? (byte & 15u) : (byte >> 4);
-                word |= nib << (4 * q4_nibble_pos(i));
-            }
-        }
-        reinterpret_cast<uint32_t *>(tile_ptr)[(q * 32 + lane) * 4 + wi] = word;
-    } else {
-        uint32_t r = u - words_per_tile;
-        uint32_t row = rt * 16 + r;
-        uint8_t hdr[16];
-        for (int i = 0; i < 16; ++i) hdr[i] = 0;
-        if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
-            const uint8_t *s = blk + 4;
-            uint8_t sc[8], mn[8];
-            for (int j = 0; j < 8; ++j) {
-                if (j < 4) {
-                    sc[j] = s[j] & 63;
-                    mn[j] = s[j + 4] & 63;
-                } else {
-                    sc[j] = (uint8_t)((s[j + 4] & 15) | ((s[j - 4] >> 6) << 4));
-                    mn[j] = (uint8_t)((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
-                }
-                int64_t k = k_base + 32 * j; // a sub-block outside the shard contributes nothing
-                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) sc[j] = mn[j] = 0;
-            }
-            hdr[0] = blk[0], hdr[1] = blk[1], hdr[2] = blk[2], hdr[3] = blk[3];
-            for (int j = 0; j < 4; ++j) {
-                hdr[4 + j] = (uint8_t)(sc[j] | ((sc[j + 4] >> 4) << 6));
-                hdr[8 + j] = (uint8_t)(mn[j] | ((mn[j + 4] >> 4) << 6));
-                hdr[12 + j] = (uint8_t)((sc[j + 4] & 15) | ((mn[j + 4] & 15) << 4));
-            }
-        }
-        uint4 v;
-        memcpy(&v, hdr, 16);
-        reinterpret_cast<uint4 *>(tile_ptr + 2048)[r] = v;
-    }
-}
-
-// ------------------------------------------------------------------------------ Q6_K repack
+// ------------------------------------------------------------------------------ K-quant repack
+// One thread builds one 32-bit word of a quant plane (8 weights of one row), or one scale header.
 __device__ __forceinline__ uint32_t q6_raw_value(const uint8_t *blk, uint32_t e, uint32_t *lo, uint32_t *hi2) {
     uint32_t h = e >> 7, r = e & 127, c = r >> 5, l = r & 31;
     *lo = (blk[64 * h + 32 * (c & 1) + l] >> (4 * (c >> 1))) & 15u;
@@ -83,87 +17,8 @@ __device__ __forceinline__ uint32_t q6_raw_value(const uint8_t *blk, uint32_t e,
     return *lo | (*hi2 << 4);
 }
 
-// units per tile: 512 low-plane words, 256 high-plane words, 16 scale rows, 1 d row
-__global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
-    const uint64_t units_per_tile = 512 + 256 + 16 + 1;
-    uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
-    uint64_t total = (uint64_t)gm.row_tiles * gm.nsb * units_per_tile;
-    if (idx >= total) return;
-    uint64_t tile = idx / units_per_tile;
-    uint32_t u = (uint32_t)(idx % units_per_tile);
-    uint32_t rt = (uint32_t)(tile / gm.nsb), sb = (uint32_t)(tile % gm.nsb);
-    uint8_t *tile_ptr = image + tile * kQ6TileBytes;
-    uint64_t sb_global = gm.k0 / 256 + sb;
-    int64_t k_base = (int64_t)sb_global * 256;
-    auto in_shard = [&](uint32_t e) {
-        int64_t k = k_base + e;
-        return k >= (int64_t)gm.k0 && k < (int64_t)(gm.k0 + gm.n_in);
-    };
-    if (u < 512) { // low nibble plane: uint4 index q*32+lane, q = rowsel*2 + half
-        uint32_t q = u >> 7, lane = (u >> 2) & 31, wi = u & 3;
-        uint32_t g = lane >> 2, t = lane & 3;
-        uint32_t row = rt * 16 + g + 8 * (q >> 1);
-        uint32_t j = t + 4 * (2 * (q & 1) + (wi >> 1)), h = wi & 1;
-        uint32_t word = 0;
-        if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
-            for (uint32_t b = 0; b < 4; ++b) {
-                uint32_t lo, hi2, ea = 16 * j + 8 * h + b, eb = ea + 4;
-                if (in_shard(ea)) {
-                    q6_raw_value(blk, ea, &lo, &hi2);
-                    word |= lo << (8 * b);
-                }
-                if (in_shard(eb)) {
-                    q6_raw_value(blk, eb, &lo, &hi2);
-                    word |= lo << (8 * b + 4);
-                }
-            }
-        }
-        reinterpret_cast<uint32_t *>(tile_ptr)[(q * 32 + lane) * 4 + wi] = word;
-    } else if (u < 768) { // high 2-bit plane: uint4 index rowsel*32+lane; word wi holds sub-block t + 4wi
-        uint32_t v = u - 512;
-        uint32_t rowsel = v >> 7, lane = (v >> 2) & 31, wi = v & 3;
-        uint32_t g = lane >> 2, t = lane & 3;
-        uint32_t row = rt * 16 + g + 8 * rowsel;
-        uint32_t word = 0;
-        if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
-            for (uint32_t x = 0; x < 4; ++x)
-                for (uint32_t b = 0; b < 4; ++b) {
-                    uint32_t lo, hi2, e = 16 * (t + 4 * wi) + 4 * x + b;
-                    if (!in_shard(e)) continue;
-                    q6_raw_value(blk, e, &lo, &hi2);
-                    word |= hi2 << (8 * b + 2 * x);
-                }
-        }
-        reinterpret_cast<uint32_t *>(tile_ptr + kQ6OffHi)[(rowsel * 32 + lane) * 4 + wi] = word;
-    } else if (u < 784) { // 16 int8 scales of one row
-        uint32_t r = u - 768, row = rt * 16 + r;
-        uint8_t sc[16];
-        for (int i = 0; i < 16; ++i) sc[i] = 0;
-        if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
-            for (uint32_t s = 0; s < 16; ++s) sc[s] = in_shard(16 * s) ? blk[192 + s] : 0;
-        }
-        uint4 v;
-        memcpy(&v, sc, 16);
-        reinterpret_cast<uint4 *>(tile_ptr + kQ6OffSc)[r] = v;
-    } else { // the 16 super-scales
-        for (uint32_t r = 0; r < 16; ++r) {
-            uint32_t row = rt * 16 + r;
-            uint16_t d = 0;
-            if (row < gm.n_out) {
-                const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 210;
-                d = (uint16_t)(blk[208] | (blk[209] << 8));
-            }
-            reinterpret_cast<uint16_t *>(tile_ptr + kQ6OffD)[r] = d;
-        }
-    }
-}
-
-// ------------------------------------------------------------------------------ column layout (layout 1)
-// The same tensors in the layout of the decode kernel: a lane owns a quarter of every sub-block (kquant_layout.cuh).
-__global__ void repack_q4k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
+// Tile layout: kquant_layout.cuh (a lane owns a quarter of every sub-block of its two rows).
+__global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
     const uint64_t units_per_tile = 512 + 16;
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= (uint64_t)gm.row_tiles * gm.nsb * units_per_tile) return;
@@ -223,7 +78,7 @@ __global__ void repack_q4k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *
     }
 }
 
-__global__ void repack_q6k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
+__global__ void repack_q6k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
     const uint64_t units_per_tile = 512 + 256 + 16 + 1;
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= (uint64_t)gm.row_tiles * gm.nsb * units_per_tile) return;
@@ -295,21 +150,10 @@ __global__ void repack_q6k_col_kernel(const uint8_t *__restrict__ raw, uint8_t *
 muser_cuda_status launch_repack_kquant(Ctx *ctx, Weight *w, const uint8_t *dev_blocks, cudaStream_t stream) {
     KqGeom gm = kq_geom(*w);
     uint64_t tiles = (uint64_t)gm.row_tiles * gm.nsb;
-    if (w->layout == 1) {
-        if (w->dtype == MUSER_DTYPE_Q4_K)
-            repack_q4k_col_kernel<<<(unsigned)((tiles * 528 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
-        else
-            repack_q6k_col_kernel<<<(unsigned)((tiles * 785 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
-        MUSER_CUDA_TRY(ctx, cudaGetLastError());
-        return MUSER_CUDA_OK;
-    }
-    if (w->dtype == MUSER_DTYPE_Q4_K) {
-        uint64_t total = tiles * 528;
-        repack_q4k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
-    } else {
-        uint64_t total = tiles * 785;
-        repack_q6k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
-    }
+    if (w->dtype == MUSER_DTYPE_Q4_K)
+        repack_q4k_kernel<<<(unsigned)((tiles * 528 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
+    else
+        repack_q6k_kernel<<<(unsigned)((tiles * 785 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
@@ -359,16 +203,13 @@ muser_cuda_status launch_repack_nvfp4(Ctx *ctx, Weight *w, const uint8_t *dev_pa
 
 // ------------------------------------------------------------------------------ image -> f32
 // One weight out of the repacked image: row `row`, position `kk` in the tile grid (input index + k_off).
-template <int LAYOUT>
 __device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ4TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t j = e >> 5, wi = (e >> 3) & 3, i = e & 7;
     uint32_t q = rowsel * 2 + (j >> 2);
-    // layout 0: lane (g, j % 4) holds the sub-block, word = 8-element group; layout 1: lane (g, group), word = j % 4
-    uint32_t word = LAYOUT == 0 ? reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + (j & 3)) * 4 + wi]
-                                : reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + wi) * 4 + (j & 3)];
+    uint32_t word = reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + wi) * 4 + (j & 3)]; // lane (g, 8-element group), word = sub-block % 4
     uint32_t nib = (word >> (4 * q4_nibble_pos(i))) & 15u;
     const uint8_t *hdr = tile + 2048 + r * 16;
     float d = __half2float(*reinterpret_cast<const __half *>(hdr));
@@ -386,53 +227,40 @@ __device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, u
     return __fsub_rn(__fmul_rn(d1, (float)nib), m1); // k_block.rs:40-41
 }
 
-template <int LAYOUT>
 __device__ __forceinline__ float q6k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
     const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ6TileBytes;
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t s = e >> 4, el = e & 15;
-    int qv;
-    if constexpr (LAYOUT == 0) {
-        uint32_t o = s >> 2, lane = g * 4 + (s & 3);
-        uint32_t lo_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (o >> 1)) * 32 + lane) * 4 + (o & 1) * 2 + (el >> 3)];
-        uint32_t lo = (lo_word >> (8 * (el & 3) + 4 * ((el >> 2) & 1))) & 15u;
-        uint32_t hi_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + o];
-        uint32_t hi2 = (hi_word >> (8 * (el & 3) + 2 * (el >> 2))) & 3u;
-        qv = (int)(lo | (hi2 << 4)) - 32;
-    } else {
-        uint32_t lane = g * 4 + (el >> 2), b = el & 3;
-        uint32_t t_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (s >> 3)) * 32 + lane) * 4 + ((s & 7) >> 1)];
-        uint32_t top = (t_word >> (8 * b + 4 * (s & 1))) & 15u;
-        uint32_t l_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + (s >> 2)];
-        uint32_t low = (l_word >> (8 * b + 2 * (s & 3))) & 3u;
-        qv = (int)(((top << 2) | low) ^ 32u) - 32; // the image holds (q - 32) & 63
-    }
+    uint32_t lane = g * 4 + (el >> 2), b = el & 3;
+    uint32_t t_word = reinterpret_cast<const uint32_t *>(tile)[((rowsel * 2 + (s >> 3)) * 32 + lane) * 4 + ((s & 7) >> 1)];
+    uint32_t top = (t_word >> (8 * b + 4 * (s & 1))) & 15u;
+    uint32_t l_word = reinterpret_cast<const uint32_t *>(tile + kQ6OffHi)[(rowsel * 32 + lane) * 4 + (s >> 2)];
+    uint32_t low = (l_word >> (8 * b + 2 * (s & 3))) & 3u;
+    int qv = (int)(((top << 2) | low) ^ 32u) - 32; // the image holds (q - 32) & 63
     float d = __half2float(reinterpret_cast<const __half *>(tile + kQ6OffD)[r]);
     int sc = reinterpret_cast<const int8_t *>(tile + kQ6OffSc)[r * 16 + s];
     return __fmul_rn(__fmul_rn(d, (float)sc), (float)qv); // q6.rs:305-313
 }
 
 // One thread per output element; reads the repacked image only.
-template <int LAYOUT>
 __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= gm.n_out * gm.n_in) return;
-    out[idx] = q4k_weight<LAYOUT>(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+    out[idx] = q4k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
 }
 
-template <int LAYOUT>
 __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= gm.n_out * gm.n_in) return;
-    out[idx] = q6k_weight<LAYOUT>(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+    out[idx] = q6k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
 }
 
 // ------------------------------------------------------------------------------ selected rows
 // weights::matmul_rows (src/weights.rs:425-449): out[t][i] = dot(W_rows[i], x_t) for a list of output rows, the way
 // the reference scores a handful of LM-head rows.  One warp per listed row; lanes stride over the inputs, decode
 // each weight from the image and keep up to eight token sums; a butterfly adds the lanes (fixed order).
-template <bool Q4, bool XF32, int LAYOUT>
+template <bool Q4, bool XF32>
 __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restrict__ image, KqGeom gm, const uint32_t *__restrict__ rows,
                                                           uint32_t n_rows, const void *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ out) {
@@ -444,7 +272,7 @@ __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restr
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (row < gm.n_out) {
             for (uint64_t k = lane; k < gm.n_in; k += 32) {
-                const float w = Q4 ? q4k_weight<LAYOUT>(image, gm.nsb, row, k + gm.k_off) : q6k_weight<LAYOUT>(image, gm.nsb, row, k + gm.k_off);
+                const float w = Q4 ? q4k_weight(image, gm.nsb, row, k + gm.k_off) : q6k_weight(image, gm.nsb, row, k + gm.k_off);
 #pragma unroll
                 for (uint32_t t = 0; t < 8; ++t)
                     if (t < nt) {
@@ -469,16 +297,10 @@ muser_cuda_status launch_kquant_rows(Ctx *ctx, const Weight *w, const uint32_t *
     const unsigned blocks = (n_rows + 7) / 8;
     const KqGeom gm = kq_geom(*w);
     const bool q4 = w->dtype == MUSER_DTYPE_Q4_K, xf32 = x_dtype == MUSER_DTYPE_F32;
-#define MUSER_ROWS_LAUNCH(Q4_, XF32_)                                                                                        \
-    do {                                                                                                                      \
-        if (w->layout == 1) kquant_rows_kernel<Q4_, XF32_, 1><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out); \
-        else kquant_rows_kernel<Q4_, XF32_, 0><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);       \
-    } while (0)
-    if (q4 && xf32) MUSER_ROWS_LAUNCH(true, true);
-    else if (q4) MUSER_ROWS_LAUNCH(true, false);
-    else if (xf32) MUSER_ROWS_LAUNCH(false, true);
-    else MUSER_ROWS_LAUNCH(false, false);
-#undef MUSER_ROWS_LAUNCH
+    if (q4 && xf32) kquant_rows_kernel<true, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else if (q4) kquant_rows_kernel<true, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else if (xf32) kquant_rows_kernel<false, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    else kquant_rows_kernel<false, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
@@ -511,11 +333,9 @@ muser_cuda_status launch_dequant(Ctx *ctx, const Weight *w, float *out, cudaStre
         dequant_nvfp4_kernel<<<blocks, 256, 0, stream>>>(w->packed, w->scales, out, w->n_out, w->n_in,
                                                          (uint32_t)((w->n_in + 63) / 64), w->scale2);
     } else if (w->dtype == MUSER_DTYPE_Q4_K) {
-        if (w->layout == 1) dequant_q4k_kernel<1><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
-        else dequant_q4k_kernel<0><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        dequant_q4k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     } else {
-        if (w->layout == 1) dequant_q6k_kernel<1><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
-        else dequant_q6k_kernel<0><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        dequant_q6k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     }
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;

@@ -22,9 +22,8 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, TUNE_GEMV_MAX_TOKENS_Q4_K,
-                   TUNE_GEMV_MAX_TOKENS_Q6_K, TUNE_MATMUL_WARPS, TUNE_TC_MIN_ROWS, TUNE_TC_MIN_TOKENS_Q4_K,
-                   TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
+from ._lib import (BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING,
+                   TUNE_DECODE_WARPS, TUNE_TC_MIN_ROWS, TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
 
 _L = _lib.lib
 _TORCH_DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -195,6 +194,22 @@ class CudaKernels:
             _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
+    def encode_quantized_matmul_group(self, weights, input: torch.Tensor, outputs, tokens: int, epilogues=None) -> None:
+        """Up to four K-quant projections of the same `input` in one launch (q | k | v, or gate | up), the counterpart
+        of the reference's one-barrier-interval dispatch (decode.rs:5569-5598).  `epilogues`: per projection a dict of
+        encode_quantized_matmul's keyword arguments, or None."""
+        n = len(weights)
+        items = (_lib.GroupItem * n)()
+        keep = []
+        for i, (w, y) in enumerate(zip(weights, outputs)):
+            ep = _epilogue(**(epilogues[i] or {})) if epilogues else None
+            keep.append(ep)
+            items[i].w, items[i].y, items[i].y_dtype, items[i].reserved = w._h.value, y.data_ptr(), _TORCH_DTYPE[y.dtype], 0
+            items[i].epilogue = C.pointer(ep) if ep is not None else None
+        self.ctx.check(_L.muser_cuda_quantized_matmul_group(
+            self.ctx._h, items, n, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
     def encode_quantized_matmul_rows(self, weights: Weight, rows: torch.Tensor, input: torch.Tensor, output: torch.Tensor,
                                      tokens: int) -> None:
         """weights::matmul_rows: output[t][i] = dot(W_rows[i], x_t); rows int32/uint32 on the device, output f32."""
@@ -307,6 +322,12 @@ def matmul(ctx: Context, w: Weight, x: np.ndarray, n_tokens: int, out: np.ndarra
         out = np.empty((n_tokens, w.n_out), dtype=np.float32)
     ctx.check(_L.muser_cuda_matmul_host(ctx._h, w._h, x.ctypes.data, n_tokens, out.ctypes.data))
     return out
+
+
+def matmul_enqueue(ctx: Context, w: Weight, x_ptr: int, n_tokens: int, out_ptr: int, stream: int) -> None:
+    """muser_cuda_matmul_host_enqueue: weights::matmul on host f32 buffers (given as addresses, ideally of pinned memory)
+    without the wait; ctx.sync_status() on the same stream completes the step."""
+    ctx.check(_L.muser_cuda_matmul_host_enqueue(ctx._h, w._h, x_ptr, n_tokens, out_ptr, stream))
 
 
 def unswizzle_scales(swizzled: torch.Tensor, rows: int, n_in: int) -> torch.Tensor:

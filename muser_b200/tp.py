@@ -66,6 +66,40 @@ class ShardPlan:
         return self.world > 1 and LAYER_AXES[name] == SHARD_K
 
 
+class Collective:
+    """The library's own all-reduce for one context (muser_cuda_ctx_comm_init + muser_cuda_all_reduce): rank 0 makes
+    the id, torch.distributed only carries its 128 bytes to the other ranks, and every later sum runs inside the
+    library on the caller's stream: a one-shot exchange over peer memory for decode-sized payloads, NCCL above."""
+
+    def __init__(self, ctx, rank: int, world: int, group=None):
+        import ctypes as C
+
+        from . import _lib
+        self.ctx, self.rank, self.world, self._L = ctx, rank, world, _lib.lib
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            st = self._L.muser_cuda_comm_unique_id(buf, 128)
+            if st != 0:
+                raise _lib.MuserCudaError(st, (self._L.muser_cuda_last_error(None) or b"").decode())
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        dev = torch.device("cuda", ctx.device)
+        carrier = ident.to(dev) if dist.get_backend(group) == "nccl" else ident
+        dist.broadcast(carrier, src=0, group=group)
+        self._id = bytes(carrier.cpu().tolist())
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ctx.check(self._L.muser_cuda_ctx_comm_init(ctx._h, self._id, rank, world, stream))
+        self.oneshot = bool(self._L.muser_cuda_ctx_comm_has_oneshot(ctx._h))
+        self.kind = ("library: one-shot peer exchange up to 256 KiB of f32, ncclAllReduce above" if self.oneshot
+                     else "library: ncclAllReduce (peer buffers could not be mapped)")
+
+    def all_reduce_sum(self, partial: torch.Tensor) -> torch.Tensor:
+        from .operator import _TORCH_DTYPE
+        stream = torch.cuda.current_stream(partial.device).cuda_stream
+        self.ctx.check(self._L.muser_cuda_all_reduce(self.ctx._h, partial.data_ptr(), partial.numel(), _TORCH_DTYPE[partial.dtype], stream))
+        return partial
+
+
 def all_reduce_sum(partial: torch.Tensor, group=None) -> torch.Tensor:
     """Sum the row-parallel partial outputs in place across ranks (NCCL over NVLink on the box)."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
