@@ -128,7 +128,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
  * force one kernel in a test.  A TC_MIN_TOKENS value above 64 switches the tensor-core skinny kernel off. */
 #define MUSER_TUNE_TC_MIN_TOKENS_Q4_K 1u /* Q4_K calls with at least this many tokens take the tcgen05 kernel (default 17) */
 #define MUSER_TUNE_TC_MIN_TOKENS_Q6_K 2u /* likewise for Q6_K (default 17) */
-#define MUSER_TUNE_TC_MIN_ROWS 3u        /* ... if the weight has at least this many output rows (default 2048) */
+#define MUSER_TUNE_TC_MIN_ROWS 3u        /* ... if the weight has at least this many output rows (default 1024) */
 #define MUSER_TUNE_DECODE_WARPS 8u       /* decode kernel: warps per CTA, even (0: from its cost model) */
 #define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: from its cost model) */
 #define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: from its cost model) */

@@ -234,6 +234,8 @@ muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muse
     if (e == cudaSuccess) e = cudaMalloc(&ctx->tc_scratch, ctx->tc_scratch_bytes);
     ctx->norm_scratch_bytes = (size_t)64 * 32768 * sizeof(float); // 64 tokens x the widest row
     if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_scratch, ctx->norm_scratch_bytes);
+    ctx->inv_rms_rows = 1u << 20; // token rows per call of a fused input norm
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->inv_rms, (size_t)ctx->inv_rms_rows * sizeof(float));
     if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
@@ -255,6 +257,7 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->gemv_partial);
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->norm_scratch);
+    cudaFree(ctx->inv_rms);
     cudaFree(ctx->tc_scratch);
     cudaFree(ctx->dev_stage);
     cudaFree(ctx->arena);

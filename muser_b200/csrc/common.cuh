@@ -36,10 +36,12 @@ struct Ctx {
     void *tc_scratch = nullptr;            // f16 activations + sub-block sums of the tensor-core K-quant kernel
     size_t tc_scratch_bytes = 0;
     uint32_t tc_min_tokens[2] = {17, 17};  // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
-    uint32_t tc_min_rows = 2048;           // and from how many output rows); fewer tokens take the decode kernel
+    uint32_t tc_min_rows = 1024;           // and from how many output rows); fewer tokens take the decode kernel
     uint32_t dec_warps = 0, dec_ksplit = 0, dec_ring = 0; // decode kernel plan overrides (0: from its cost model)
     float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
     size_t norm_scratch_bytes = 0;
+    float *inv_rms = nullptr;              // one 1/rms per token row of a fused input norm (NVFP4 quantizer, skinny kernel)
+    uint32_t inv_rms_rows = 0;
     cudaStream_t copy_stream = nullptr;
     void *host_stage = nullptr; // pinned staging for matmul_host
     size_t host_stage_bytes = 0;

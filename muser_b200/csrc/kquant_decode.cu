@@ -119,8 +119,8 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
     constexpr int TOK = 4 * NG;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     uint32_t *fw = reinterpret_cast<uint32_t *>(frag), *mw = reinterpret_cast<uint32_t *>(meta);
-    // one task = one (tile, token); a warp takes tasks warp, warp + warps, ... and fetches the next task's inputs
-    // before it works on the current one (the loads come from L2 and would otherwise be paid once per task in turn)
+    // one task = one (tile, token); a warp takes its tasks a few at a time and has all their inputs in flight before
+    // it works on the first (the loads come from L2 and would otherwise be paid once per task in turn)
     auto fetch = [&](uint32_t task, float (&v)[8]) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
@@ -150,11 +150,17 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
             if ((i / kMetaU4) % TOK >= a.tokens) meta[i] = make_uint4(0, 0, 0, 0);
     }
     const uint32_t n_tasks = n_tiles * a.tokens; // task -> (tile, token < tokens)
-    float v[8], nxt[8];
-    fetch(warp, v);
-    for (uint32_t task = warp; task < n_tasks; task += warps) {
+    constexpr int kBatch = NG >= 3 ? 4 : 2;      // tasks whose inputs are in flight together (they come from L2)
+    for (uint32_t task0 = warp * kBatch; task0 < n_tasks; task0 += warps * kBatch) {
+      float vb[kBatch][8];
+#pragma unroll
+      for (int bi = 0; bi < kBatch; ++bi) fetch(task0 + bi, vb[bi]);
+#pragma unroll
+      for (int bi = 0; bi < kBatch; ++bi) {
+        const uint32_t task = task0 + bi;
+        if (task >= n_tasks) break;
         const uint32_t tile = task / a.tokens, tok = task % a.tokens, gp = tok >> 2, t4 = tok & 3;
-        fetch(task + warps, nxt);
+        float (&v)[8] = vb[bi];
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -209,8 +215,7 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
             e[16] = l0, e[20] = l1; // and of the low-plane column
             if (lane == 0) mrow[0] = __float_as_uint(sx * 0.25f); // the fragment bytes are 4 * (q - 32)
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = nxt[i];
+      }
     }
 }
 

@@ -182,7 +182,7 @@ def test_tensor_core_skinny_kernel(gpu, dtype, x_dtype):
     finally:
         ctx.tuning_set(op.TUNE_TC_MIN_TOKENS_Q4_K, 17)
         ctx.tuning_set(op.TUNE_TC_MIN_TOKENS_Q6_K, 17)
-        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1024)
     ctx.sync_status()
 
 
@@ -234,7 +234,7 @@ def test_tensor_parallel_shards(gpu, dtype):
             ctx.sync_status()
             assert H.rel_l2(acc.cpu().numpy(), want) <= REL_L2_TOL, x_dtype
     finally:
-        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1024)
         ctx.tuning_set(key, 17)
 
 
@@ -429,7 +429,7 @@ def test_lm_head_tail_and_selected_rows(gpu, dtype):
             k.encode_quantized_matmul(w, x.cuda(), y, tokens, out_scale=scale)
             assert H.rel_l2(y.cpu().numpy(), O.logit_tail(plain, scale, 0.0)) <= REL_L2_TOL
     finally:
-        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 2048)
+        ctx.tuning_set(op.TUNE_TC_MIN_ROWS, 1024)
     rows = np.array([299, 0, 17, 17, 128, 255, 16], dtype=np.int32)
     for x_dtype in (torch.bfloat16, torch.float32):
         x = torch.from_numpy(H.lcg_activations(11 * n_in, seed=9).reshape(11, n_in)).to(x_dtype)
