@@ -293,9 +293,11 @@ MUSER_CUDA_API int muser_cuda_ctx_comm_has_oneshot(const muser_cuda_ctx *ctx);
 /* The all-reduce(sum) after a row-parallel projection (o_proj, down_proj), in place on `buf` (count elements of F32,
  * F16 or BF16), enqueued on `stream`; every rank must make the same calls in the same order.  f32 payloads up to
  * 256 KiB (a decode step's [tokens][hidden] partial sums) take a one-shot exchange over peer memory: each rank stores
- * its values into every rank's buffer over NVLink, raises a flag there, waits (bounded: a give-up is reported by
- * muser_cuda_sync_status as MUSER_CUDA_TIMEOUT and leaves `buf` as it was) and adds the copies in rank order, so all
- * ranks end with identical bits.  Larger payloads and 16-bit types go to ncclAllReduce on the same stream. */
+ * its values into every rank's buffer over NVLink, each paired with the call's sequence number, polls its own buffer
+ * until every rank's values are there (bounded: a give-up is reported by muser_cuda_sync_status as
+ * MUSER_CUDA_TIMEOUT, and the elements that were still waiting keep this rank's partial sums) and adds them in rank
+ * order, so all ranks end with identical bits.  Larger payloads and 16-bit types go to ncclAllReduce on the same
+ * stream. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_all_reduce(muser_cuda_ctx *ctx, void *buf, uint64_t count, uint32_t dtype, void *stream);
 
 /* weights::matmul itself (src/weights.rs:398): HOST slices in, HOST slices out, f32 both ways.

@@ -4,10 +4,10 @@
 // so nothing here has a counterpart there.  A context can be given a communicator of `world` ranks, one process per
 // GPU of one box; muser_cuda_all_reduce then sums a buffer in place across the ranks on the caller's stream:
 //   - payloads up to 256 KiB of f32 (a decode step's [tokens][hidden] partial sums: 20 KB per token) take a one-shot
-//     exchange over peer memory: every rank PUSHES its chunk into a slot of every rank's buffer with plain stores
-//     over NVLink, publishes a flag in the receiver's memory, waits (bounded) for the other ranks' flags in its own
-//     memory and adds the world's copies in rank order, so all ranks get the same bits.  One small kernel, no
-//     library call, a few microseconds;
+//     exchange over peer memory: every rank PUSHES each value, paired with the call's sequence number in one 8-byte
+//     store, into a cell of every rank's buffer over NVLink, then polls (bounded) its own cells until every rank's
+//     value of the call is there and adds them in rank order, so all ranks get the same bits.  No flag, no fence:
+//     latency is one one-way trip.  One small kernel, no library call;
 //   - everything else goes to ncclAllReduce, found at run time in the NCCL that the process already carries
 //     (dlopen of libnccl.so.2), so the library itself has no link-time dependency on it.
 // The peer buffers are cudaMalloc'd once per context at comm set-up and mapped into the other processes through
@@ -24,17 +24,17 @@
 namespace muser {
 
 constexpr uint32_t kMaxRanks = 8;
-constexpr uint32_t kOneShotMaxBytes = 256u << 10; // per rank and call
-constexpr uint32_t kOneShotMaxCtas = 64;
-constexpr uint32_t kOneShotChunkFloats = 2048;    // 8 KiB per CTA
-constexpr uint32_t kOneShotWaitLimit = 1u << 22;  // polls of a flag (with a short sleep between) before the wait gives up: about a second
+constexpr uint32_t kOneShotMaxBytes = 256u << 10;            // f32 payload per rank and call
+constexpr uint32_t kOneShotMaxElems = kOneShotMaxBytes / 4;
+constexpr uint32_t kOneShotChunkElems = 2048;                // values per CTA
+constexpr uint32_t kOneShotMaxCtas = kOneShotMaxElems / kOneShotChunkElems;
+constexpr uint32_t kOneShotWaitLimit = 1u << 21;             // polls of one value (with a short sleep between) before the wait gives up: about a second
 
-// Layout of one rank's buffer: data[2 slots][kMaxRanks senders][kOneShotMaxBytes], then flags[2][kMaxRanks][kOneShotMaxCtas]
-// (uint32: the sender CTA's sequence number), then seq[kOneShotMaxCtas] (this rank's own per-CTA sequence numbers).
-constexpr size_t kDataBytes = (size_t)2 * kMaxRanks * kOneShotMaxBytes;
-constexpr size_t kFlagBytes = (size_t)2 * kMaxRanks * kOneShotMaxCtas * sizeof(uint32_t);
+// Layout of one rank's buffer: cell[2 slots][kMaxRanks senders][kOneShotMaxElems] of 8 bytes (value bits, sequence
+// number), then seq[kOneShotMaxCtas] (this rank's own per-CTA sequence numbers).
+constexpr size_t kCellBytes = (size_t)2 * kMaxRanks * kOneShotMaxElems * 8;
 constexpr size_t kSeqBytes = kOneShotMaxCtas * sizeof(uint32_t);
-constexpr size_t kPeerBufBytes = kDataBytes + kFlagBytes + kSeqBytes;
+constexpr size_t kPeerBufBytes = kCellBytes + kSeqBytes;
 
 struct NcclApi {
     void *lib = nullptr;
@@ -90,87 +90,59 @@ struct OneShotArgs {
     int *status;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// A value travels together with its sequence number in one 8-byte store, which arrives whole or not at all: the
+// receiver needs no fence and no separate flag, it polls the cell until the number is the one it expects.
+__device__ __forceinline__ void st_cell(uint2 *p, uint32_t bits, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(seq) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_cell(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 
-// One CTA per 8 KiB chunk.  CTA c keeps its own sequence number (in this rank's buffer, bumped once per launch), so
+// One CTA per 2048 values.  CTA c keeps its own sequence number (in this rank's buffer, bumped once per launch), so
 // the kernel can sit in a CUDA graph: nothing that changes from call to call is a launch argument.  The slot
-// alternates with the sequence number; a rank can only be two calls ahead of a peer that still reads a slot after
-// that peer has published the call in between, so two slots suffice.
+// alternates with the sequence number, so a cell still holds the number of two calls ago when a new value is due;
+// a rank can be at most one call ahead of the slowest reader of a slot (it needs that reader's values of the call in
+// between to get there), so two slots suffice.
 __global__ void __launch_bounds__(256) oneshot_all_reduce_kernel(const OneShotArgs a) {
     __shared__ uint32_t seq_s;
-    __shared__ int failed;
     pdl_wait(); // `buf` comes from the kernel before this one; the sequence counter from the all-reduce before it
     const uint32_t c = blockIdx.x, tid = threadIdx.x;
     uint8_t *mine = a.peer[a.rank];
     if (tid == 0) {
-        uint32_t *seq = reinterpret_cast<uint32_t *>(mine + kDataBytes + kFlagBytes) + c;
+        uint32_t *seq = reinterpret_cast<uint32_t *>(mine + kCellBytes) + c;
         seq_s = *seq + 1;
         *seq = seq_s;
-        failed = 0;
     }
     __syncthreads();
     const uint32_t seq = seq_s, slot = seq & 1u;
-    const uint32_t begin = c * kOneShotChunkFloats, end = min(begin + kOneShotChunkFloats, a.count);
-    const size_t my_data = ((size_t)slot * kMaxRanks + a.rank) * kOneShotMaxBytes;
-    // 1. push this rank's chunk into every rank's copy of (slot, this rank)
-    for (uint32_t i = begin + 4 * tid; i < end; i += 4 * 256) {
-        if (i + 4 <= end) {
-            const float4 v = *reinterpret_cast<const float4 *>(a.buf + i);
-            for (uint32_t p = 0; p < a.world; ++p) *reinterpret_cast<float4 *>(a.peer[p] + my_data + (size_t)i * 4) = v;
-        } else {
-            for (uint32_t j = i; j < end; ++j)
-                for (uint32_t p = 0; p < a.world; ++p) *reinterpret_cast<float *>(a.peer[p] + my_data + (size_t)j * 4) = a.buf[j];
-        }
+    const uint32_t begin = c * kOneShotChunkElems, end = min(begin + kOneShotChunkElems, a.count);
+    // 1. push this rank's values into every rank's cells of (slot, this rank)
+    const size_t my_cells = ((size_t)slot * kMaxRanks + a.rank) * kOneShotMaxElems;
+    for (uint32_t i = begin + tid; i < end; i += 256) {
+        const uint32_t bits = __float_as_uint(a.buf[i]);
+        for (uint32_t p = 0; p < a.world; ++p) st_cell(reinterpret_cast<uint2 *>(a.peer[p]) + my_cells + i, bits, seq);
     }
-    __syncthreads();
-    // 2. publish: thread p tells rank p (the barrier above and the fence order the CTA's stores before the flag)
-    if (tid < a.world) {
-        __threadfence_system();
-        uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer[tid] + kDataBytes) + ((size_t)slot * kMaxRanks + a.rank) * kOneShotMaxCtas + c;
-        st_release_sys(flag, seq);
-    }
-    // 3. wait, bounded, for every rank's chunk to have landed here
-    if (tid < a.world) {
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(mine + kDataBytes) + ((size_t)slot * kMaxRanks + tid) * kOneShotMaxCtas + c;
-        bool ok = false;
-        for (uint32_t n = 0; n < kOneShotWaitLimit; ++n) {
-            if (ld_acquire_sys(flag) == seq) {
-                ok = true;
-                break;
+    // 2. take every rank's value of each element as it lands (bounded) and add them in rank order
+    const uint2 *cells = reinterpret_cast<const uint2 *>(mine) + (size_t)slot * kMaxRanks * kOneShotMaxElems;
+    for (uint32_t i = begin + tid; i < end; i += 256) {
+        float sum = 0.0f;
+        for (uint32_t p = 0; p < a.world; ++p) {
+            const uint2 *cell = cells + (size_t)p * kOneShotMaxElems + i;
+            uint2 v = ld_cell(cell);
+            for (uint32_t n = 0; v.y != seq && n < kOneShotWaitLimit; ++n) {
+                if (n > 32) __nanosleep(100);
+                v = ld_cell(cell);
             }
-            if (n > 64) __nanosleep(64);
-        }
-        if (!ok) {
-            failed = 1;
-            atomicExch(a.status + 1, 401);
-        }
-    }
-    __syncthreads();
-    if (failed) return; // the output keeps this rank's partial sum; muser_cuda_sync_status reports the give-up
-    // 4. add the world's copies in rank order
-    const uint8_t *slot_base = mine + (size_t)slot * kMaxRanks * kOneShotMaxBytes;
-    for (uint32_t i = begin + 4 * tid; i < end; i += 4 * 256) {
-        if (i + 4 <= end) {
-            float4 s = __ldcv(reinterpret_cast<const float4 *>(slot_base + (size_t)i * 4));
-            for (uint32_t p = 1; p < a.world; ++p) {
-                const float4 v = __ldcv(reinterpret_cast<const float4 *>(slot_base + (size_t)p * kOneShotMaxBytes + (size_t)i * 4));
-                s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+            if (v.y != seq) { // this thread stops here: its remaining outputs keep the rank's own partial sums
+                atomicExch(a.status + 1, 401);
+                return;
             }
-            *reinterpret_cast<float4 *>(a.buf + i) = s;
-        } else {
-            for (uint32_t j = i; j < end; ++j) {
-                float s = __ldcv(reinterpret_cast<const float *>(slot_base + (size_t)j * 4));
-                for (uint32_t p = 1; p < a.world; ++p) s += __ldcv(reinterpret_cast<const float *>(slot_base + (size_t)p * kOneShotMaxBytes + (size_t)j * 4));
-                a.buf[j] = s;
-            }
+            sum += __uint_as_float(v.x);
         }
+        a.buf[i] = sum;
     }
 }
 
@@ -190,7 +162,7 @@ static void setup_oneshot(Ctx *ctx, Comm *cm, cudaStream_t stream) {
         cudaFree(dev_handles);
     };
     cudaError_t e = cudaMalloc(&cm->local, kPeerBufBytes);
-    if (e == cudaSuccess) e = cudaMemsetAsync(cm->local, 0, kPeerBufBytes, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(cm->local, 0, kPeerBufBytes, stream); // sequence number 0 is never expected
     if (e == cudaSuccess) e = cudaMalloc(&dev_handles, sizeof(handles));
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&handles[cm->rank], cm->local);
     if (e == cudaSuccess) e = cudaMemcpyAsync(dev_handles + cm->rank, &handles[cm->rank], sizeof(cudaIpcMemHandle_t), cudaMemcpyHostToDevice, stream);
@@ -322,7 +294,7 @@ muser_cuda_status muser_cuda_all_reduce(muser_cuda_ctx *c, void *buf, uint64_t c
         a.rank = cm->rank;
         a.world = cm->world;
         a.status = ctx->dev_status;
-        const uint32_t ctas = ((uint32_t)count + kOneShotChunkFloats - 1) / kOneShotChunkFloats;
+        const uint32_t ctas = ((uint32_t)count + kOneShotChunkElems - 1) / kOneShotChunkElems;
         MUSER_CUDA_TRY(ctx, launch_pdl(oneshot_all_reduce_kernel, dim3(ctas), dim3(256), 0, stream, a));
         return MUSER_CUDA_OK;
     }
