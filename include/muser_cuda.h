@@ -132,6 +132,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_DECODE_WARPS 8u       /* decode kernel: warps per CTA, even (0: from its cost model) */
 #define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: from its cost model) */
 #define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: from its cost model) */
+#define MUSER_TUNE_DECODE_WSPLIT 12u      /* decode kernel: warps of a CTA that share one row tile and split K between them (0: from its cost model) */
 #define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 262144; 0: always NCCL) */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
@@ -186,6 +187,22 @@ typedef struct muser_cuda_group_item {
 MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul_group(muser_cuda_ctx *ctx, const muser_cuda_group_item *items,
                                                     uint32_t n_items, const void *x, uint32_t x_dtype, uint32_t tokens,
                                                     void *stream);
+
+/* No counterpart in the reference (its Metal pipelines have fixed threadgroup shapes).  The decode kernel's launch
+ * plan (warps per CTA, how K is split between CTAs and between the warps of a CTA) comes from a cost model; this
+ * call measures the model's best candidates for one projection or one group (`weights`, as they will be passed to
+ * muser_cuda_quantized_matmul / _group; `w_up` non-NULL for the fused gate/up form of weights[0]) at 1 .. max_tokens
+ * tokens and remembers the fastest for this device, for every later call on the same geometry in this process.
+ * Every candidate is timed as a CUDA graph of back-to-back launches over temporary copies of the weight images (so
+ * that they stream from HBM).  Optional load-time work: it allocates scratch (up to ~350 MB), synchronizes
+ * `stream`, runs on a stream of its own, and frees the scratch. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_decode_autotune(muser_cuda_ctx *ctx, const muser_cuda_weight *const *weights,
+                                             uint32_t n_weights, const muser_cuda_weight *w_up, uint32_t max_tokens,
+                                             void *stream);
+
+/* Diagnostics: the launch plan of the decode kernel's latest launch on this context, as (warps per CTA, K slices
+ * between CTAs, K parts between the warps of a CTA, weight tiles in flight per warp). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_decode_last_plan(const muser_cuda_ctx *ctx, uint32_t out[4]);
 
 /* weights::matmul_rows (src/weights.rs:425-449): the projection restricted to a list of output rows, as the
  * reference scores selected LM-head rows.  rows: n_rows row indices on the device (an index >= n_out yields NaN);

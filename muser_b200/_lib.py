@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmuser_cuda.so"
 F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
 SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
 TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
-TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES = 8, 9, 10, 11
+TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES, TUNE_DECODE_WSPLIT = 8, 9, 10, 11, 12
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 
@@ -28,7 +28,7 @@ EXPORTS = [
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
     "muser_cuda_static_sync_status", "muser_cuda_wait_probe", "muser_cuda_quantized_matmul_group",
     "muser_cuda_matmul_host_enqueue", "muser_cuda_comm_unique_id", "muser_cuda_ctx_comm_init", "muser_cuda_ctx_comm_attach",
-    "muser_cuda_ctx_comm_has_oneshot", "muser_cuda_all_reduce",
+    "muser_cuda_ctx_comm_has_oneshot", "muser_cuda_all_reduce", "muser_cuda_decode_autotune", "muser_cuda_decode_last_plan",
 ]
 
 
@@ -95,6 +95,8 @@ def _load() -> C.CDLL:
         "muser_cuda_ctx_comm_attach": (i32, [vp, vp, u32, u32, vp]),
         "muser_cuda_ctx_comm_has_oneshot": (i32, [vp]),
         "muser_cuda_all_reduce": (i32, [vp, vp, u64, u32, vp]),
+        "muser_cuda_decode_autotune": (i32, [vp, C.POINTER(vp), u32, vp, u32, vp]),
+        "muser_cuda_decode_last_plan": (i32, [vp, C.POINTER(u32 * 4)]),
         "muser_cuda_nvfp4_matmul_static": (i32, [vp, vp, u32, vp, u32, u32, vp]),
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),

@@ -296,6 +296,7 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
     case MUSER_TUNE_DECODE_WARPS: ctx->dec_warps = value & ~1u; return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_KSPLIT: ctx->dec_ksplit = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_RING: ctx->dec_ring = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_DECODE_WSPLIT: ctx->dec_wsplit = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
@@ -422,6 +423,22 @@ muser_cuda_status muser_cuda_quantized_matmul_group(muser_cuda_ctx *c, const mus
         if (st != MUSER_CUDA_OK) return st;
     }
     return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_decode_last_plan(const muser_cuda_ctx *c, uint32_t out[4]) {
+    const Ctx *ctx = reinterpret_cast<const Ctx *>(c);
+    if (!ctx || !out) return MUSER_CUDA_BAD_ARG;
+    for (int i = 0; i < 4; ++i) out[i] = ctx->dec_last_plan[i];
+    return MUSER_CUDA_OK;
+}
+
+muser_cuda_status muser_cuda_decode_autotune(muser_cuda_ctx *c, const muser_cuda_weight *const *weights, uint32_t n_weights,
+                                             const muser_cuda_weight *w_up, uint32_t max_tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !weights) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return decode_autotune(ctx, reinterpret_cast<const Weight *const *>(weights), reinterpret_cast<const Weight *>(w_up), n_weights, max_tokens,
+                           (cudaStream_t)stream);
 }
 
 muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx *c, const muser_cuda_weight *wp, const uint32_t *rows,

@@ -37,7 +37,8 @@ struct Ctx {
     size_t tc_scratch_bytes = 0;
     uint32_t tc_min_tokens[2] = {17, 17};  // from how many tokens Q4_K / Q6_K calls take that kernel (tuning knobs,
     uint32_t tc_min_rows = 1024;           // and from how many output rows); fewer tokens take the decode kernel
-    uint32_t dec_warps = 0, dec_ksplit = 0, dec_ring = 0; // decode kernel plan overrides (0: from its cost model)
+    uint32_t dec_warps = 0, dec_ksplit = 0, dec_ring = 0, dec_wsplit = 0;
+    uint32_t dec_last_plan[4] = {0, 0, 0, 0}; // (warps, ksplit, wsplit, ring) of the decode kernel's latest launch on this context // decode kernel plan overrides (0: from its cost model)
     float *norm_scratch = nullptr;         // normalized rows for the skinny K-quant kernel (fused input norm)
     size_t norm_scratch_bytes = 0;
     float *inv_rms = nullptr;              // one 1/rms per token row of a fused input norm (NVFP4 quantizer, skinny kernel)
@@ -162,6 +163,7 @@ muser_cuda_status launch_kquant_matmul(Ctx *, const Weight *w, const Weight *w_u
                                        cudaStream_t);
 cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype,
                              uint32_t tokens, const Epilogue &, cudaStream_t);
+muser_cuda_status decode_autotune(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, uint32_t max_tokens, cudaStream_t);
 cudaError_t launch_kquant_decode(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
                                  const Epilogue *ep, cudaStream_t);

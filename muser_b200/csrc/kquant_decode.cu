@@ -25,6 +25,9 @@
 // (deterministic).  Every wait on a copy barrier is bounded.
 #include <algorithm>
 #include <cmath>
+#include <cstring>
+#include <map>
+#include <vector>
 
 #include "common.cuh"
 #include "kquant_layout.cuh"
@@ -59,6 +62,8 @@ struct DecArgs {
     unsigned int *counters; // zero between launches
     int *status;            // context status words; [1] records a wait that gave up
     uint32_t n_in, nsb, k_off, tokens, x_f32, ksplit, max_tiles, ring /* tiles in flight per warp: 2 or 4 */;
+    uint32_t slot_bytes; // bytes of one ring slot: the largest tile among the launch's jobs
+    uint32_t wsplit;     // warps of a CTA that share one row tile, each with a part of the CTA's K slice (1: none)
 };
 
 namespace dec {
@@ -377,8 +382,11 @@ template <> struct RegsOf<MUSER_DTYPE_Q4_K> { using type = Q4Regs; };
 template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
 
 // ------------------------------------------------------------------------------------ one CTA's work
-// Warp w of CTA group G takes row tiles G * warps + w, + groups * warps, ... and streams the K slice's tiles of each
-// through its own ring.
+// The CTA's warps form warps / wsplit row slots of wsplit warps each.  Slot r of CTA group G takes row tiles
+// G * slots + r, + groups * slots, ...; its warps cut the CTA's K slice into wsplit parts, each streams its part's
+// tiles through its own ring, and the parts meet in shared memory (named barrier per slot, first warp adds them in
+// part order), which costs a few hundred cycles where the exchange between CTAs through global memory costs
+// microseconds.  Small weights, which need every warp of the GPU to hide HBM latency, are split this way.
 template <int DT, int NG, bool DUAL>
 __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
     using Regs = typename RegsOf<DT>::type;
@@ -391,32 +399,36 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     uint4 *frag = dyn;                                                  // max_tiles x NG x 2 KiB
     uint4 *meta = frag + (size_t)a.max_tiles * NG * kFragU4;            // max_tiles x TOK x 48 bytes
     uint8_t *ring_base = reinterpret_cast<uint8_t *>(meta + (size_t)a.max_tiles * TOK * kMetaU4);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_base + (size_t)warps * ring_n * kQ6TileBytes); // sized for the larger tile
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_base + (size_t)warps * ring_n * a.slot_bytes); // sized for the launch's largest tile
+    constexpr int kOutWords = kImages * NG * 2;                         // partial sums per lane
+    float *red = reinterpret_cast<float *>(bars + warps * ring_n);      // [2][warps][kOutWords][32], used when wsplit > 1
     if (threadIdx.x < (unsigned)(warps * ring_n))
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bars + threadIdx.x)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 
     // this warp's tiles, over all its row tiles, form one stream: n -> (row tile, image, tile); start it before staging
-    const uint32_t first_row = group * warps + warp, row_step = jb.groups * warps;
+    const uint32_t wsplit = a.wsplit, slots = warps / wsplit, wslot = warp / wsplit, wpart = warp % wsplit;
+    const uint32_t t_first = n_tiles * wpart / wsplit, my_tiles = n_tiles * (wpart + 1) / wsplit - t_first; // this warp's part of the slice
+    const uint32_t first_row = group * slots + wslot, row_step = jb.groups * slots;
     const uint32_t my_rows = jb.row_tiles > first_row ? (jb.row_tiles - first_row + row_step - 1) / row_step : 0;
-    const uint32_t per_row = n_tiles * kImages, total = per_row * my_rows;
+    const uint32_t per_row = my_tiles * kImages, total = per_row * my_rows;
     uint8_t *ring = ring_base + (size_t)warp * ring_n * kBytes;
     const uint32_t bar0 = smem_addr(bars + warp * ring_n);
-    uint32_t f_tile = first_row * a.nsb + sb_first, f_tl = 0, f_im = 0;
+    uint32_t f_tile = first_row * a.nsb + sb_first + t_first, f_tl = 0, f_im = 0;
     auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, lane 0 issues the copy
         const uint8_t *base = jb.image;
         if constexpr (DUAL) base = f_im ? jb.image_up : jb.image;
         if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot);
         ++f_tile;
-        if (++f_tl == n_tiles) {
+        if (++f_tl == my_tiles) {
             f_tl = 0;
             if (DUAL && f_im == 0) {
                 f_im = 1;
-                f_tile -= n_tiles;
+                f_tile -= my_tiles;
             } else {
                 f_im = 0;
-                f_tile += row_step * a.nsb - n_tiles;
+                f_tile += row_step * a.nsb - my_tiles;
             }
         }
     };
@@ -438,15 +450,15 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     stage<DT, NG>(a, sb_first, n_tiles, frag, meta, inv_rms);
     __syncthreads();
 
-    uint32_t n = 0;
+    uint32_t n = 0, iter = 0;
     bool healthy = true;
-    for (uint32_t rt = first_row; rt < jb.row_tiles; rt += row_step) {
+    for (uint32_t rt = first_row; rt < jb.row_tiles; rt += row_step, ++iter) {
         float out[kImages][NG][2];
 #pragma unroll
         for (int im = 0; im < kImages; ++im) {
 #pragma unroll
             for (int gp = 0; gp < NG; ++gp) out[im][gp][0] = out[im][gp][1] = 0.f;
-            for (uint32_t tl = 0; tl < n_tiles; ++tl, ++n) {
+            for (uint32_t tl = t_first; tl < t_first + my_tiles; ++tl, ++n) {
                 const uint32_t slot = n & ring_mask;
                 if (healthy && !tile_wait(bar0 + 8 * slot, (n >> ring_shift) & 1)) {
                     healthy = false;
@@ -461,6 +473,31 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
             }
         }
         // this lane now holds, per group gp: [0] -> row g, [1] -> row g + 8, token 4 * gp + t
+        if (wsplit > 1) {
+            // the slot's warps meet: every warp leaves its sums, the first one adds them in part order.  Two buffers
+            // taken in turn: a warp can be at most one row tile ahead of the slot's first warp (the next barrier needs
+            // that warp too), so what it writes is never what is still being read.
+            float *mine = red + ((size_t)(iter & 1) * warps + warp) * (kOutWords * 32) + lane;
+#pragma unroll
+            for (int im = 0; im < kImages; ++im)
+#pragma unroll
+                for (int gp = 0; gp < NG; ++gp) {
+                    mine[((im * NG + gp) * 2 + 0) * 32] = out[im][gp][0];
+                    mine[((im * NG + gp) * 2 + 1) * 32] = out[im][gp][1];
+                }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + wslot), "r"(wsplit * 32) : "memory");
+            if (wpart != 0) continue;
+#pragma unroll
+            for (int im = 0; im < kImages; ++im)
+#pragma unroll
+                for (int gp = 0; gp < NG; ++gp)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        float sum = out[im][gp][c];
+                        for (uint32_t p = 1; p < wsplit; ++p) sum += mine[(size_t)p * (kOutWords * 32) + ((im * NG + gp) * 2 + c) * 32];
+                        out[im][gp][c] = sum;
+                    }
+        }
         bool finish = true;
         if (a.ksplit > 1) {
 #pragma unroll
@@ -521,10 +558,10 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     }
 }
 
-// Threads and CTAs per SM by token groups: one group runs two CTAs of 14 warps an SM (72 registers a thread), two
-// groups two CTAs of 12 warps (80 registers), more groups one CTA of 16 warps.
-constexpr int max_warps(int ng) { return ng == 1 ? 14 : ng == 2 ? 12 : 16; }
-constexpr int ctas_per_sm(int ng) { return ng <= 2 ? 2 : 1; }
+// One CTA per SM, so that the activations are staged once per SM: up to 28 warps for one token group (72 registers a
+// thread), 24 for two (80 registers), 16 beyond.
+constexpr int max_warps(int ng) { return ng == 1 ? 28 : ng == 2 ? 24 : 16; }
+constexpr int ctas_per_sm(int ng) { return 1; }
 
 } // namespace dec
 
@@ -547,45 +584,91 @@ __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG))
 namespace {
 
 struct DecPlan {
-    int warps, ksplit, ring;
+    int warps, ksplit, ring, wsplit;
 };
 
-size_t dec_smem_bytes(uint32_t nsb, int ksplit, int warps, int ring, int ng) {
+size_t dec_smem_bytes(uint32_t nsb, int ksplit, int warps, int ring, int ng, bool q6, int out_words) {
     const uint32_t max_tiles = (nsb + ksplit - 1) / ksplit + 1;
-    return (size_t)max_tiles * ng * (dec::kFragU4 * 16 + 4 * dec::kMetaU4 * 16) + (size_t)warps * ring * (kQ6TileBytes + 8) + 16;
+    return (size_t)max_tiles * ng * (dec::kFragU4 * 16 + 4 * dec::kMetaU4 * 16) + (size_t)warps * ring * ((q6 ? kQ6TileBytes : kQ4TileBytes) + 8) +
+           (size_t)2 * warps * out_words * 32 * sizeof(float) + 16;
 }
 
-// K slices, warps per CTA and ring depth from a small cost model: a tile costs `per_tile` issue slots of its warp,
-// a scheduler retires about 0.12 instructions per clock per resident warp up to ~0.9, and an SM cannot take tiles
-// faster than HBM delivers them.  As many busy warps per SM as fit, spread evenly over the SMs, and slices only as
-// far as that needs, because every slice costs a trip through the scratch buffer and a staging pass per CTA.
-DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6) {
-    DecPlan best{2, 1, 2};
-    double best_cost = 1e300;
-    const double instr = (q6 ? 330.0 : 260.0) + (ng - 1) * (q6 ? 130.0 : 110.0); // issue slots per tile
-    const double hbm_cycles = q6 ? 150.0 : 105.0;                                 // per tile and SM at full HBM rate
-    for (int ring = 2; ring <= 4; ring += 2)
-        for (int ks = 1; ks <= 16 && (uint32_t)ks <= nsb; ++ks)
-            for (int w = 2; w <= dec::max_warps(ng); w += 2) {
-                const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng);
+// Warps per CTA, K slices between CTAs (`ksplit`, met through global scratch), K parts between the warps of a CTA
+// (`wsplit`, met through shared memory) from a cost model in SM cycles, fitted to timings of ~1800 (shape, tokens,
+// plan) combinations on a B200: a warp needs about 1300 (Q4_K) / 1750 (Q6_K) cycles per tile, 1450 / 1600 more per
+// further token group, whatever the number of warps beside it up to 16 an SM and ~7 % more per warp beyond; the
+// tensor cannot arrive faster than HBM delivers it; staging costs every CTA ~930 warp cycles per (tile, token) spread
+// over its warps; a meeting in shared memory costs ~330 cycles, one through global memory ~5800; a launch ~5900.
+// The landscape is rugged (whether the row tiles fill one wave of CTAs exactly matters more than anything smooth), so
+// the model ranks the candidates and muser_cuda_decode_autotune can measure the best of them.
+struct DecCandidate {
+    DecPlan plan;
+    double cost;
+};
+
+void dec_candidates(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6, uint32_t tokens, int out_words, std::vector<DecCandidate> &out) {
+    out.clear();
+    const double t_warp = (q6 ? 1750.0 : 1300.0) + (ng - 1) * (q6 ? 1600.0 : 1450.0);
+    const double bytes = (double)nsb * row_tiles * (q6 ? kQ6TileBytes : kQ4TileBytes), hbm_bytes_per_cycle = 2800.0;
+    const int max_w = dec::max_warps(ng), batch = ng >= 3 ? 4 : 2, ring = 2;
+    static const int kParts[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12};
+    for (int ks = 1; ks <= 16 && (uint32_t)ks <= nsb; ++ks)
+        for (int ws : kParts)
+            for (int w = 4; w <= max_w; w += 2) {
+                if (w % ws) continue;
+                const int slots = w / ws;
+                if (ws > 1 && slots > 15) continue; // one named barrier per slot
+                if ((uint32_t)ws > nsb / ks) continue;
+                const double tiles_cta = std::ceil((double)nsb / ks), tiles_warp = std::ceil(tiles_cta / ws);
+                const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng, q6, out_words);
                 if (smem > 220u * 1024) continue;
                 int ctas = (int)((227u * 1024) / (smem + 1024));
-                ctas = std::min(ctas, std::max(1, dec::max_warps(ng) * dec::ctas_per_sm(ng) / w)); // the register file
-                const double tiles = std::ceil((double)nsb / ks);
-                const double wanted = std::ceil((double)row_tiles / w);                   // CTAs per slice if every warp took one row tile
+                ctas = std::min(ctas, std::max(1, max_w / w)); // the register file
+                const double wanted = std::ceil((double)row_tiles / slots); // CTAs per slice if every slot took one row tile
                 const double groups = std::min(wanted, std::floor((double)ctas * sm_count / ks));
                 if (groups < 1.0) continue;
-                const double rows_per_warp = std::ceil(wanted / groups);
-                const double ctas_on_sm = std::ceil(groups * ks / sm_count);              // the busiest SM
-                const double busy = ctas_on_sm * w;                                       // warps at work there
-                const double ipc = std::min(3.0, 0.11 * busy * (ring == 4 ? 1.1 : 1.0));  // SM-wide
-                const double per_tile = std::max(hbm_cycles, instr / ipc);                // SM cycles per tile
-                const double staging = ctas_on_sm * tiles * ng * 45.0 + 1500.0;           // per SM, before the first tile
-                const double per_item = 400.0 + (ks > 1 ? 1500.0 : 0.0);                  // epilogue latency, scratch round trip
-                const double cost = busy * rows_per_warp * tiles * per_tile + rows_per_warp * per_item + staging;
-                if (cost < best_cost * (1.0 - 1e-9)) best_cost = cost, best = DecPlan{w, ks, ring};
+                const double rows_per_slot = std::ceil(wanted / groups);
+                const double ctas_on_sm = std::ceil(groups * ks / sm_count); // the busiest SM
+                const double busy = ctas_on_sm * w;                          // warps at work there
+                const double tasks = tiles_cta * tokens;
+                const double staging = ctas_on_sm * (std::ceil(tasks / (w * batch)) * 100.0 + tasks * 930.0 / w);
+                const double warp_time = rows_per_slot * tiles_warp * t_warp * (1.0 + 0.066 * std::max(0.0, busy - 16.0));
+                const double tail = rows_per_slot * ((ws > 1 ? 330.0 : 0.0) + (ks > 1 ? 5800.0 : 0.0));
+                out.push_back({DecPlan{w, ks, ring, ws}, 5900.0 + staging + std::max(warp_time, bytes / hbm_bytes_per_cycle) + tail});
             }
-    return best;
+    std::sort(out.begin(), out.end(), [](const DecCandidate &x, const DecCandidate &y) { return x.cost < y.cost; });
+}
+
+DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6, uint32_t tokens, int out_words) {
+    std::vector<DecCandidate> c;
+    dec_candidates(nsb, row_tiles, sm_count, ng, q6, tokens, out_words, c);
+    return c.empty() ? DecPlan{2, 1, 2, 1} : c[0].plan;
+}
+
+// Plans that muser_cuda_decode_autotune measured, per device: (jobs' row tiles, dtype mix, nsb, token groups, fused
+// gate/up) -> plan per token count.  Looked up before the cost model.
+struct TunedKey {
+    uint32_t nsb, n_jobs, rows[kDecMaxJobs], q6, dual, tokens;
+    bool operator<(const TunedKey &o) const { return memcmp(this, &o, sizeof(*this)) < 0; }
+};
+struct TunedTable {
+    std::mutex mu;
+    std::map<TunedKey, DecPlan> plans[kMaxDevices];
+    uint32_t generation[kMaxDevices] = {}; // bumped (under mu) when a device's plans change, so cached launch plans are looked up again
+};
+TunedTable &tuned_table() {
+    static TunedTable t;
+    return t;
+}
+TunedKey tuned_key(const DecArgs &a, bool dual) {
+    TunedKey k;
+    memset(&k, 0, sizeof(k));
+    k.nsb = a.nsb, k.n_jobs = a.n_jobs, k.dual = dual, k.tokens = a.tokens;
+    for (uint32_t i = 0; i < a.n_jobs; ++i) {
+        k.rows[i] = a.job[i].row_tiles;
+        k.q6 |= (a.job[i].dtype == MUSER_DTYPE_Q6_K ? 1u : 0u) << i;
+    }
+    return k;
 }
 
 template <int NG, bool DUAL>
@@ -593,10 +676,10 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
     struct Cached {
         uint32_t nsb = 0, rows[kDecMaxJobs] = {0, 0, 0, 0}, n_jobs = 0;
         bool q6 = false;
-        DecPlan plan{1, 1, 2};
+        DecPlan plan{1, 1, 2, 1};
         size_t smem = 0;
         uint32_t groups[kDecMaxJobs] = {0, 0, 0, 0};
-        uint32_t forced_w = 0, forced_k = 0, forced_r = 0;
+        uint32_t forced_w = 0, forced_k = 0, forced_r = 0, forced_s = 0, tokens = 0, generation = 0;
     };
     static PerDevice<Cached> cached; // last geometry of this instantiation, per device
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return cudaErrorInvalidDevice;
@@ -604,8 +687,16 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
     {
         std::lock_guard<std::mutex> lock(cached.mu);
         Cached &slot = cached.slot[ctx->device];
-        bool same = slot.nsb == a.nsb && slot.n_jobs == a.n_jobs && slot.forced_w == (uint32_t)forced.warps &&
-                    slot.forced_k == (uint32_t)forced.ksplit && slot.forced_r == (uint32_t)forced.ring;
+        constexpr int kOutWords = (DUAL ? 2 : 1) * NG * 2;
+        bool same = slot.nsb == a.nsb && slot.n_jobs == a.n_jobs && slot.tokens == a.tokens && slot.forced_w == (uint32_t)forced.warps &&
+                    slot.forced_k == (uint32_t)forced.ksplit && slot.forced_r == (uint32_t)forced.ring && slot.forced_s == (uint32_t)forced.wsplit;
+        uint32_t generation;
+        {
+            TunedTable &tt = tuned_table();
+            std::lock_guard<std::mutex> tl(tt.mu);
+            generation = tt.generation[ctx->device];
+        }
+        same = same && slot.generation == generation;
         bool q6 = false;
         uint32_t total_tiles = 0;
         size_t out_floats = 0;
@@ -617,18 +708,29 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
         }
         same = same && slot.q6 == q6;
         if (!same) {
-            DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, q6);
+            DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, q6, a.tokens, kOutWords);
+            {
+                TunedTable &tt = tuned_table();
+                std::lock_guard<std::mutex> tl(tt.mu);
+                auto it = tt.plans[ctx->device].find(tuned_key(a, DUAL));
+                if (it != tt.plans[ctx->device].end()) p = it->second;
+            }
             if (forced.warps) p.warps = std::min(forced.warps, dec::max_warps(NG));
             if (forced.ksplit) p.ksplit = (int)std::min<uint32_t>((uint32_t)forced.ksplit, a.nsb);
             if (forced.ring) p.ring = forced.ring >= 4 ? 4 : 2;
+            if (forced.wsplit) p.wsplit = forced.wsplit;
+            if (forced.warps || forced.ksplit || forced.wsplit) { // a forced plan is made consistent rather than refused
+                const uint32_t tiles_cta = a.nsb / p.ksplit; // the shortest slice
+                while (p.wsplit > 1 && (p.warps % p.wsplit || (uint32_t)p.wsplit > std::max(1u, tiles_cta) || p.warps / p.wsplit > 15)) --p.wsplit;
+            }
             while (p.ksplit > 1 && (size_t)p.ksplit * out_floats * sizeof(float) > ctx->gemv_partial_bytes) --p.ksplit;
             if (total_tiles > ctx->gemv_counter_slots) p.ksplit = 1;
-            size_t smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
-            while (smem > 226u * 1024 && p.ring > 2) p.ring = 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+            size_t smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
+            while (smem > 226u * 1024 && p.ring > 2) p.ring = 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
             while (smem > 226u * 1024 && (uint32_t)p.ksplit < a.nsb &&
                    (size_t)(p.ksplit + 1) * out_floats * sizeof(float) <= ctx->gemv_partial_bytes && total_tiles <= ctx->gemv_counter_slots)
-                ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
-            while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG);
+                ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
+            while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, p.wsplit = 1, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
             if (smem > 226u * 1024) return cudaErrorNotSupported;
             cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL>), ctx->device, smem);
             if (e != cudaSuccess) return e;
@@ -637,24 +739,31 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
             if (e != cudaSuccess) return e;
             if (per_sm < 1) return cudaErrorInvalidConfiguration;
             // CTAs per slice over all jobs: all that fit at once, but no more than there are row tiles for their warps
+            const uint32_t slots = (uint32_t)(p.warps / p.wsplit);
             uint32_t wanted = 0;
-            for (uint32_t i = 0; i < a.n_jobs; ++i) wanted += (a.job[i].row_tiles + p.warps - 1) / p.warps;
+            for (uint32_t i = 0; i < a.n_jobs; ++i) wanted += (a.job[i].row_tiles + slots - 1) / slots;
             const uint32_t resident = std::max(1u, (uint32_t)per_sm * ctx->sm_count / p.ksplit);
             const uint32_t rounds = (wanted + resident - 1) / resident;
             slot = Cached{};
             for (uint32_t i = 0; i < a.n_jobs; ++i) {
-                const uint32_t w_i = (a.job[i].row_tiles + p.warps - 1) / p.warps;
+                const uint32_t w_i = (a.job[i].row_tiles + slots - 1) / slots;
                 slot.groups[i] = std::max(1u, (w_i + rounds - 1) / rounds);
                 slot.rows[i] = a.job[i].row_tiles;
             }
             slot.nsb = a.nsb, slot.n_jobs = a.n_jobs, slot.q6 = q6;
             slot.plan = p, slot.smem = smem;
-            slot.forced_w = forced.warps, slot.forced_k = forced.ksplit, slot.forced_r = forced.ring;
+            slot.forced_w = forced.warps, slot.forced_k = forced.ksplit, slot.forced_r = forced.ring, slot.forced_s = forced.wsplit;
+            slot.tokens = a.tokens;
+            slot.generation = generation;
         }
         cache = slot;
     }
+    a.slot_bytes = cache.q6 ? kQ6TileBytes : kQ4TileBytes;
     a.ksplit = cache.plan.ksplit;
     a.ring = cache.plan.ring;
+    a.wsplit = (uint32_t)cache.plan.wsplit;
+    ctx->dec_last_plan[0] = (uint32_t)cache.plan.warps, ctx->dec_last_plan[1] = (uint32_t)cache.plan.ksplit;
+    ctx->dec_last_plan[2] = (uint32_t)cache.plan.wsplit, ctx->dec_last_plan[3] = (uint32_t)cache.plan.ring;
     a.max_tiles = (a.nsb + a.ksplit - 1) / a.ksplit + 1;
     uint32_t cta = 0, counter = 0;
     size_t partial = 0;
@@ -708,8 +817,8 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     a.nsb = w[0]->nsb;
     a.k_off = w[0]->k_off;
     a.tokens = tokens;
-    a.ksplit = 1, a.max_tiles = 0, a.ring = 2;
-    const DecPlan forced{(int)ctx->dec_warps, (int)ctx->dec_ksplit, (int)ctx->dec_ring};
+    a.ksplit = 1, a.max_tiles = 0, a.ring = 2, a.slot_bytes = kQ6TileBytes, a.wsplit = 1;
+    const DecPlan forced{(int)ctx->dec_warps, (int)ctx->dec_ksplit, (int)ctx->dec_ring, (int)ctx->dec_wsplit};
     const uint32_t ng = (tokens + 3) / 4;
     if (w_up) {
         if (n_jobs != 1) return cudaErrorNotSupported;
@@ -726,6 +835,145 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     case 3: return dec_launch<3, false>(a, ctx, forced, stream);
     default: return dec_launch<4, false>(a, ctx, forced, stream);
     }
+}
+
+// ------------------------------------------------------------------------------------ measured plans
+// Times the cost model's best candidates for this group of weights at 1, 2, 4, 8, 12 and 16 tokens and remembers the
+// fastest per token count for this device.  Every candidate runs the way a decode step runs it: a CUDA graph of
+// back-to-back launches (so each overlaps its predecessor's tail as in the step) that rotate over temporary copies of
+// the weight images, together larger than L2, so that every launch streams its weights from HBM.  A measured plan
+// replaces the model's choice only if it is at least 2 % faster.  Load-time work: allocates its scratch (the image
+// copies, up to ~350 MB), synchronizes, frees it.
+muser_cuda_status decode_autotune(Ctx *ctx, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, uint32_t max_tokens, cudaStream_t stream) {
+    constexpr int kCandidates = 24, kLaunches = 12, kReplays = 3;
+    if (n_jobs == 0 || n_jobs > (uint32_t)kDecMaxJobs || (w_up && n_jobs != 1)) return fail(ctx, MUSER_CUDA_BAD_ARG, "a group holds 1..4 projections");
+    max_tokens = std::min(std::max(max_tokens, 1u), 16u);
+    size_t y_floats = 0, image_bytes = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        if (!w[i] || w[i]->device != ctx->device || (w[i]->dtype != MUSER_DTYPE_Q4_K && w[i]->dtype != MUSER_DTYPE_Q6_K))
+            return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "autotune takes K-quant weights of this context's device");
+        if (w[i]->n_in != w[0]->n_in || w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the projections of a group must share n_in and the K shard geometry");
+        y_floats += (size_t)16 * w[i]->n_out;
+        image_bytes += w[i]->image_bytes;
+    }
+    if (w_up) {
+        if (w_up->dtype != w[0]->dtype || w_up->n_in != w[0]->n_in || w_up->n_out != w[0]->n_out || w_up->nsb != w[0]->nsb)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "gate and up geometry differ");
+        image_bytes += w_up->image_bytes;
+    }
+    const int copies = (int)std::min<size_t>(12, std::max<size_t>(2, ((size_t)256 << 20) / image_bytes + 1));
+    uint8_t *x = nullptr;
+    float *y = nullptr;
+    std::vector<uint8_t *> images;                 // copies x (jobs + up)
+    std::vector<Weight> shadow((size_t)copies * (n_jobs + 1));
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    cudaStream_t side = nullptr;
+    auto cleanup = [&]() {
+        cudaFree(x), cudaFree(y);
+        for (uint8_t *p : images) cudaFree(p);
+        if (ev[0]) cudaEventDestroy(ev[0]);
+        if (ev[1]) cudaEventDestroy(ev[1]);
+        if (side) cudaStreamDestroy(side);
+        ctx->dec_warps = ctx->dec_ksplit = ctx->dec_ring = ctx->dec_wsplit = 0;
+    };
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&x, (size_t)16 * w[0]->n_in * 2);
+    if (e == cudaSuccess) e = cudaMemsetAsync(x, 0x3c, (size_t)16 * w[0]->n_in * 2, side); // bf16 0x3c3c: small positive values
+    if (e == cudaSuccess) e = cudaMalloc(&y, y_floats * sizeof(float));
+    if (e == cudaSuccess) e = cudaEventCreate(&ev[0]);
+    if (e == cudaSuccess) e = cudaEventCreate(&ev[1]);
+    for (int c = 0; c < copies && e == cudaSuccess; ++c)
+        for (uint32_t i = 0; i <= n_jobs && e == cudaSuccess; ++i) {
+            const Weight *src = i < n_jobs ? w[i] : w_up;
+            if (!src) continue;
+            uint8_t *p = nullptr;
+            e = cudaMalloc(&p, src->image_bytes);
+            if (e != cudaSuccess) break;
+            images.push_back(p);
+            e = cudaMemcpyAsync(p, src->image, src->image_bytes, cudaMemcpyDeviceToDevice, side);
+            shadow[(size_t)c * (n_jobs + 1) + i] = *src;
+            shadow[(size_t)c * (n_jobs + 1) + i].image = p;
+        }
+    if (e != cudaSuccess) {
+        cleanup();
+        return fail(ctx, MUSER_CUDA_ERROR, std::string("autotune scratch: ") + cudaGetErrorString(e));
+    }
+    void *ys[kDecMaxJobs];
+    uint32_t yd[kDecMaxJobs];
+    Epilogue eps[kDecMaxJobs];
+    uint32_t total_tiles = 0;
+    bool q6 = false;
+    {
+        float *yp = y;
+        for (uint32_t i = 0; i < n_jobs; ++i) {
+            ys[i] = yp, yd[i] = MUSER_DTYPE_F32;
+            yp += (size_t)16 * w[i]->n_out;
+            total_tiles += w[i]->row_tiles;
+            q6 = q6 || w[i]->dtype == MUSER_DTYPE_Q6_K;
+        }
+    }
+    auto launch_copy = [&](int c, uint32_t tokens) {
+        const Weight *wc[kDecMaxJobs];
+        for (uint32_t i = 0; i < n_jobs; ++i) wc[i] = &shadow[(size_t)c * (n_jobs + 1) + i];
+        return launch_kquant_decode(ctx, wc, w_up ? &shadow[(size_t)c * (n_jobs + 1) + n_jobs] : nullptr, n_jobs, x, MUSER_DTYPE_BF16, ys, yd, tokens, eps, side);
+    };
+    static const uint32_t kTokenSteps[] = {1, 2, 4, 8, 12, 16};
+    std::vector<DecCandidate> cands;
+    muser_cuda_status st = MUSER_CUDA_OK;
+    for (uint32_t tokens : kTokenSteps) {
+        if (tokens > max_tokens && tokens != 1 && (tokens + 3) / 4 != (max_tokens + 3) / 4) continue;
+        const int ng = (int)(tokens + 3) / 4;
+        dec_candidates(w[0]->nsb, total_tiles, ctx->sm_count, ng, q6, tokens, (w_up ? 2 : 1) * ng * 2, cands);
+        const int n_c = std::min<int>(kCandidates, (int)cands.size());
+        int best = 0;
+        float best_ms = 1e30f, model_ms = 1e30f;
+        for (int c = 0; c < n_c && st == MUSER_CUDA_OK; ++c) {
+            ctx->dec_warps = cands[c].plan.warps, ctx->dec_ksplit = cands[c].plan.ksplit, ctx->dec_ring = cands[c].plan.ring, ctx->dec_wsplit = cands[c].plan.wsplit;
+            cudaError_t le = launch_copy(0, tokens); // outside the capture: sets the kernel's attributes for this plan
+            cudaGraph_t graph = nullptr;
+            cudaGraphExec_t exec = nullptr;
+            if (le == cudaSuccess) le = cudaStreamBeginCapture(side, cudaStreamCaptureModeThreadLocal);
+            if (le == cudaSuccess) {
+                for (int l = 0; l < kLaunches && le == cudaSuccess; ++l) le = launch_copy(l % copies, tokens);
+                const cudaError_t ce = cudaStreamEndCapture(side, &graph);
+                if (le == cudaSuccess) le = ce;
+            }
+            if (le == cudaSuccess) le = cudaGraphInstantiate(&exec, graph, 0);
+            if (le == cudaSuccess) le = cudaGraphLaunch(exec, side); // warm
+            if (le == cudaSuccess) le = cudaEventRecord(ev[0], side);
+            for (int r = 0; r < kReplays && le == cudaSuccess; ++r) le = cudaGraphLaunch(exec, side);
+            if (le == cudaSuccess) le = cudaEventRecord(ev[1], side);
+            if (le == cudaSuccess) le = cudaStreamSynchronize(side);
+            float ms = 1e30f;
+            if (le == cudaSuccess) le = cudaEventElapsedTime(&ms, ev[0], ev[1]);
+            if (exec) cudaGraphExecDestroy(exec);
+            if (graph) cudaGraphDestroy(graph);
+            if (le != cudaSuccess) {
+                st = fail(ctx, MUSER_CUDA_ERROR, std::string("autotune measurement: ") + cudaGetErrorString(le));
+                break;
+            }
+            if (c == 0) model_ms = ms;
+            if (ms < best_ms) best_ms = ms, best = c;
+        }
+        if (st != MUSER_CUDA_OK) break;
+        if (best_ms > 0.98f * model_ms) best = 0; // not clearly better than the model's own choice: keep that
+        // remember it for this token count and for the counts below it that run the same token groups
+        DecArgs key_args;
+        key_args.nsb = w[0]->nsb, key_args.n_jobs = n_jobs;
+        for (uint32_t i = 0; i < n_jobs; ++i) key_args.job[i].row_tiles = w[i]->row_tiles, key_args.job[i].dtype = w[i]->dtype;
+        TunedTable &tt = tuned_table();
+        std::lock_guard<std::mutex> tl(tt.mu);
+        for (uint32_t t = tokens; t >= 1 && (t + 3) / 4 == (tokens + 3) / 4; --t) {
+            if (t < tokens && (t == 1 || t == 2 || t == 4 || t == 8 || t == 12)) break; // tuned on its own
+            key_args.tokens = t;
+            tt.plans[ctx->device][tuned_key(key_args, w_up != nullptr)] = cands[best].plan;
+        }
+        ++tt.generation[ctx->device];
+    }
+    cleanup();
+    return st;
 }
 
 // ------------------------------------------------------------------------------------ dispatch

@@ -23,7 +23,7 @@ import torch
 
 from . import _lib
 from ._lib import (BF16, F16, F32, NVFP4, Q4_K, Q6_K, SHARD_K, SHARD_NONE, SHARD_ROWS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING,
-                   TUNE_DECODE_WARPS, TUNE_TC_MIN_ROWS, TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
+                   TUNE_DECODE_WARPS, TUNE_DECODE_WSPLIT, TUNE_TC_MIN_ROWS, TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, MuserCudaError)
 
 _L = _lib.lib
 _TORCH_DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -209,6 +209,19 @@ class CudaKernels:
         self.ctx.check(_L.muser_cuda_quantized_matmul_group(
             self.ctx._h, items, n, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, _stream_ptr(self.ctx.device)))
         self.launches += 1
+
+    def last_decode_plan(self) -> tuple:
+        """(warps per CTA, K slices between CTAs, K parts between a CTA's warps, ring depth) of the latest decode launch."""
+        out = (C.c_uint32 * 4)()
+        _L.muser_cuda_decode_last_plan(self.ctx._h, C.byref(out))
+        return tuple(out)
+
+    def autotune(self, weights, up: Weight | None = None, max_tokens: int = 16) -> None:
+        """muser_cuda_decode_autotune: measure the decode kernel's launch plans for one projection or one group of
+        projections (and `up` for the fused gate/up form) and keep the fastest per token count.  Load-time work."""
+        arr = (C.c_void_p * len(weights))(*[w._h.value for w in weights])
+        self.ctx.check(_L.muser_cuda_decode_autotune(self.ctx._h, arr, len(weights), up._h if up is not None else None, max_tokens,
+                                                     _stream_ptr(self.ctx.device)))
 
     def encode_quantized_matmul_rows(self, weights: Weight, rows: torch.Tensor, input: torch.Tensor, output: torch.Tensor,
                                      tokens: int) -> None:

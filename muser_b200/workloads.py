@@ -79,7 +79,7 @@ class DecodeLayer:
 
     GROUPS = (("attn_q", "attn_k", "attn_v"), ("attn_o",), ("ffn_gate", "ffn_up"), ("ffn_down",))
 
-    def __init__(self, ctx, kern, plan: tp.ShardPlan, token_counts, device, all_reduce=None, seed: int = 0):
+    def __init__(self, ctx, kern, plan: tp.ShardPlan, token_counts, device, all_reduce=None, seed: int = 0, autotune: bool = True):
         self.ctx, self.kern, self.plan, self.dev = ctx, kern, plan, device
         self.projs = synth.LAYER_PROJECTIONS
         self.all_reduce = all_reduce
@@ -97,6 +97,9 @@ class DecodeLayer:
                 for name in group:
                     self.y[(name, m)] = torch.empty((m, self.weights[name].n_out), dtype=torch.float32, device=device)
         self.launches_per_pass = len(self.GROUPS)
+        if autotune:  # load-time: measured launch plans for the four launches of a pass
+            for group in self.GROUPS:
+                kern.autotune([self.weights[n] for n in group], max_tokens=min(16, max(token_counts)))
 
     def full_input(self, gi: int, m: int, seed: int = 0) -> torch.Tensor:
         """The unsharded activations that group gi reads at m tokens (what x[(gi, m)] is a column slice of)."""

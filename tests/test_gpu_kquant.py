@@ -240,33 +240,35 @@ def test_tensor_parallel_shards(gpu, dtype):
 
 @pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
 def test_every_launch_plan_of_the_decode_kernel(gpu, dtype):
-    """The decode kernel's plan forced through its tuning keys: few and many warps per CTA, one to ten K slices (one
-    slice: no scratch exchange; ten: one tile per slice), both ring depths, every token-group variant, bf16 and f32
-    activations, against the CPU lane; a fixed plan must also give identical bits on a repeated call."""
+    """The decode kernel's plan forced through its tuning keys: few and many warps per CTA, one to ten K slices between
+    CTAs (one slice: no scratch exchange; ten: one tile per slice), one to five K parts between the warps of a CTA
+    (shared-memory meeting), both ring depths, every token-group variant, bf16 and f32 activations, against the CPU
+    lane; a fixed plan must also give identical bits on a repeated call."""
     op, ctx, k = gpu
     n_in, n_out = 2560, 5000          # 10 K tiles, a short last row tile
     raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=123 + dtype)
     ow = O.TensorView(raw, dtype, n_in, n_out)
     w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
-    plans = [(0, 0, 0), (2, 1, 2), (6, 3, 4), (12, 2, 2), (14, 10, 2), (16, 7, 4)]
+    plans = [(0, 0, 0, 0), (2, 1, 2, 1), (6, 3, 4, 3), (12, 2, 2, 2), (14, 10, 2, 1), (16, 7, 4, 1), (20, 1, 2, 5), (16, 2, 2, 4), (10, 1, 2, 10)]
     try:
         for x_dtype in (torch.bfloat16, torch.float32):
             for tokens in (1, 2, 3, 4, 5, 8, 9, 12, 13, 16):
                 x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=40 + tokens).reshape(tokens, n_in)).to(x_dtype).cuda()
                 want = O.matmul(ow, x.float().cpu().numpy())
-                for warps, ksplit, ring in plans if tokens in (1, 4, 8, 13) else plans[:2]:
+                for warps, ksplit, ring, wsplit in plans if tokens in (1, 4, 8, 13) else plans[:2]:
                     ctx.tuning_set(op.TUNE_DECODE_WARPS, warps)
                     ctx.tuning_set(op.TUNE_DECODE_KSPLIT, ksplit)
                     ctx.tuning_set(op.TUNE_DECODE_RING, ring)
+                    ctx.tuning_set(op.TUNE_DECODE_WSPLIT, wsplit)
                     y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
                     k.encode_quantized_matmul(w, x, y, tokens)
                     again = torch.empty_like(y)
                     k.encode_quantized_matmul(w, x, again, tokens)
                     ctx.sync_status()
-                    assert torch.equal(y, again), (x_dtype, tokens, warps, ksplit, ring)
-                    assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, (x_dtype, tokens, warps, ksplit, ring)
+                    assert torch.equal(y, again), (x_dtype, tokens, warps, ksplit, ring, wsplit)
+                    assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, (x_dtype, tokens, warps, ksplit, ring, wsplit)
     finally:
-        for key in (op.TUNE_DECODE_WARPS, op.TUNE_DECODE_KSPLIT, op.TUNE_DECODE_RING):
+        for key in (op.TUNE_DECODE_WARPS, op.TUNE_DECODE_KSPLIT, op.TUNE_DECODE_RING, op.TUNE_DECODE_WSPLIT):
             ctx.tuning_set(key, 0)
         w.free()
 
@@ -326,6 +328,39 @@ def test_grouped_projections_in_one_launch(gpu):
         k.encode_quantized_matmul_group(ws[:1], x17, [torch.zeros((17, 300), device="cuda")], 17)
     assert e.value.status_name == "BAD_SHAPE"
     for w in ws + [other]:
+        w.free()
+
+
+def test_measured_launch_plans_keep_the_results(gpu):
+    """muser_cuda_decode_autotune replaces the cost model's launch plans with measured ones for a group, a single
+    projection and a fused gate/up pair: results stay within tolerance of the CPU lane and repeat bit for bit."""
+    op, ctx, k = gpu
+    n_in = 2048
+    shapes = [(O.Q4_K, 1100), (O.Q6_K, 260)]
+    raws = [H.lcg_weights(dt, n, n_in // 256, seed=90 + i) for i, (dt, n) in enumerate(shapes)]
+    ws = [op.Weight(ctx, op.TensorView(r, dt, n_in, n)) for r, (dt, n) in zip(raws, shapes)]
+    ows = [O.TensorView(r, dt, n_in, n) for r, (dt, n) in zip(raws, shapes)]
+    up = op.Weight(ctx, op.TensorView(H.lcg_weights(O.Q4_K, 1100, n_in // 256, seed=95), O.Q4_K, n_in, 1100))
+    k.autotune(ws, max_tokens=16)
+    k.autotune(ws[:1], max_tokens=6)
+    k.autotune(ws[:1], up=up, max_tokens=4)
+    ctx.sync_status()
+    for tokens in (1, 3, 6, 11, 16):
+        x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=tokens).reshape(tokens, n_in)).to(torch.bfloat16).cuda()
+        ys = [torch.full((tokens, n), float("nan"), dtype=torch.float32, device="cuda") for _, n in shapes]
+        again = [torch.empty_like(y) for y in ys]
+        k.encode_quantized_matmul_group(ws, x, ys, tokens)
+        k.encode_quantized_matmul_group(ws, x, again, tokens)
+        alone = torch.empty_like(ys[0])
+        k.encode_quantized_matmul(ws[0], x, alone, tokens)
+        ctx.sync_status()
+        for i in range(2):
+            assert torch.equal(ys[i], again[i])
+            assert H.rel_l2(ys[i].cpu().numpy(), O.matmul(ows[i], x.float().cpu().numpy(), threads=4)) <= REL_L2_TOL, (tokens, i)
+        assert H.rel_l2(alone.cpu().numpy(), ys[0].cpu().numpy()) <= 1e-5
+    with pytest.raises(op.MuserCudaError):
+        k.autotune(ws, up=up)   # the fused pair form takes one gate weight
+    for w in ws + [up]:
         w.free()
 
 
