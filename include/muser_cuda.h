@@ -242,7 +242,12 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_rmsnorm_quantize_nvfp4_activation(mu
 /* MetalKernels::encode_nvfp4_matmul with input_scale_inv = Some(..) (src/metal/encode/qkv.rs:128-227),
  * i.e. weights::matmul's W4A4 lane (src/weights.rs:111-121, quant/nvfp4.rs:304-338): quantizes x
  * into the context workspace, then runs the block-scaled tensor-core GEMM.  y_dtype F32, F16 or BF16
- * (F16 is the reference's output boundary, nvfp4.rs:337). */
+ * (F16 is the reference's output boundary, nvfp4.rs:337).
+ * A weight repacked WITHOUT input_scale_inv takes the reference's weight-only lane instead (input_scale_inv = None,
+ * src/weights.rs:117-121, quant::dot_nvfp4_a16_q8_f32 src/quant/nvfp4.rs:348-379): activations go to int8 per 256
+ * inputs, the contraction is exact integer arithmetic, and the f16-rounded result equals the reference's bit for bit
+ * (an F32 output holds that f16 value).  That lane takes no epilogue, needs n_in % 256 == 0 and tokens * (n_in + 16)
+ * bytes of context workspace. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
                                           uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                           const muser_cuda_epilogue *epilogue, void *stream);

@@ -558,10 +558,10 @@ muser_cuda_status muser_cuda_rmsnorm_quantize_nvfp4_activation(muser_cuda_ctx *c
     return launch_nvfp4_quantize(ctx, x, x_dtype, tokens, n_in, isi, packed, scales, (cudaStream_t)stream, norm_weight, norm_eps);
 }
 
-static muser_cuda_status nvfp4_checks(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e) {
+static muser_cuda_status nvfp4_checks(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e, bool a16_ok = false) {
     if (w->dtype != MUSER_DTYPE_NVFP4_E2M1) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "nvfp4_matmul takes NVFP4 weights");
-    if (!w->has_input_scale_inv)
-        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "weight-only NVFP4 (no input_scale_inv) has no CUDA kernel yet");
+    if (!w->has_input_scale_inv && !a16_ok)
+        return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "this entry point is the W4A4 lane: the weight has no input_scale_inv (muser_cuda_nvfp4_matmul serves the weight-only lane)");
     return take_epilogue(ctx, w, ep, e);
 }
 
@@ -590,9 +590,16 @@ muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_we
     muser_cuda_status st = check_io(ctx, w, x, x_dtype, y, y_dtype, tokens, true);
     if (st != MUSER_CUDA_OK) return st;
     Epilogue e;
-    st = nvfp4_checks(ctx, w, ep, &e);
+    st = nvfp4_checks(ctx, w, ep, &e, true);
     if (st != MUSER_CUDA_OK) return st;
     if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "gate and up are two weights: use muser_cuda_ffn_gate_up_silu for the fused SwiGLU form");
+    if (!w->has_input_scale_inv) {
+        // the weight-only lane (weights.rs:117-121): its result is the reference's f16-rounded dot, nothing is fused around it
+        if (ep && (ep->row_scale || ep->residual || ep->norm_weight || e.out_scale != 1.0f || e.softcap > 0.0f))
+            return fail(ctx, MUSER_CUDA_BAD_ARG, "the weight-only NVFP4 lane takes no epilogue");
+        MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        return launch_nvfp4_a16(ctx, w, x, x_dtype, y, y_dtype, tokens, ctx->workspace, ctx->workspace_bytes, (cudaStream_t)stream);
+    }
     const size_t tok_pad = ((size_t)tokens + 127) / 128 * 128;
     const size_t packed_bytes = tok_pad * (w->n_in / 2);
     const size_t scale_bytes = muser_cuda_nvfp4_swizzled_scale_bytes(tokens, w->n_in);

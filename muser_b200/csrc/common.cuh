@@ -175,6 +175,8 @@ muser_cuda_status launch_rmsnorm_rows(Ctx *, const void *x, uint32_t x_dtype, ui
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
                                     void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t,
                                     const Weight *w_up = nullptr);
+muser_cuda_status launch_nvfp4_a16(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
+                                   void *workspace, size_t workspace_bytes, cudaStream_t);
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);
 muser_cuda_status launch_f16_mma_probe(Ctx *, uint32_t n_cols, uint32_t iters, double *cycles_per_mma);
 muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);

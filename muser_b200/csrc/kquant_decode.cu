@@ -387,7 +387,7 @@ template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
 // tiles through its own ring, and the parts meet in shared memory (named barrier per slot, first warp adds them in
 // part order), which costs a few hundred cycles where the exchange between CTAs through global memory costs
 // microseconds.  Small weights, which need every warp of the GPU to hide HBM latency, are split this way.
-template <int DT, int NG, bool DUAL>
+template <int DT, int NG, bool DUAL, bool WSPLIT>
 __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
     using Regs = typename RegsOf<DT>::type;
     constexpr int kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = 4 * NG;
@@ -408,7 +408,7 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 
     // this warp's tiles, over all its row tiles, form one stream: n -> (row tile, image, tile); start it before staging
-    const uint32_t wsplit = a.wsplit, slots = warps / wsplit, wslot = warp / wsplit, wpart = warp % wsplit;
+    const uint32_t wsplit = WSPLIT ? a.wsplit : 1u, slots = warps / wsplit, wslot = warp / wsplit, wpart = warp % wsplit;
     const uint32_t t_first = n_tiles * wpart / wsplit, my_tiles = n_tiles * (wpart + 1) / wsplit - t_first; // this warp's part of the slice
     const uint32_t first_row = group * slots + wslot, row_step = jb.groups * slots;
     const uint32_t my_rows = jb.row_tiles > first_row ? (jb.row_tiles - first_row + row_step - 1) / row_step : 0;
@@ -473,7 +473,7 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
             }
         }
         // this lane now holds, per group gp: [0] -> row g, [1] -> row g + 8, token 4 * gp + t
-        if (wsplit > 1) {
+        if constexpr (WSPLIT) {
             // the slot's warps meet: every warp leaves its sums, the first one adds them in part order.  Two buffers
             // taken in turn: a warp can be at most one row tile ahead of the slot's first warp (the next barrier needs
             // that warp too), so what it writes is never what is still being read.
@@ -566,7 +566,7 @@ constexpr int ctas_per_sm(int ng) { return 1; }
 } // namespace dec
 
 // blockIdx.x -> (job, CTA group, K slice): a job's CTAs are contiguous, group-major.
-template <int NG, bool DUAL>
+template <int NG, bool DUAL, bool WSPLIT>
 __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG)) kquant_decode_kernel(const __grid_constant__ DecArgs a) {
     extern __shared__ uint4 dec_dyn[];
     __shared__ float inv_rms[4 * NG];
@@ -576,8 +576,8 @@ __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG))
         if (i < a.n_jobs && blockIdx.x >= a.job[i].cta0) ji = i;
     const DecJob &jb = a.job[ji];
     const uint32_t local = blockIdx.x - jb.cta0, slice = local % a.ksplit, group = local / a.ksplit;
-    if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
-    else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+    if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL, WSPLIT>(a, jb, group, slice, dec_dyn, inv_rms);
+    else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL, WSPLIT>(a, jb, group, slice, dec_dyn, inv_rms);
 }
 
 // ------------------------------------------------------------------------------------ host side
@@ -732,10 +732,13 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
                 ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
             while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, p.wsplit = 1, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
             if (smem > 226u * 1024) return cudaErrorNotSupported;
-            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL>), ctx->device, smem);
+            const bool shared = p.wsplit > 1;
+            cudaError_t e = ensure_dynamic_smem(shared ? reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL, true>)
+                                                       : reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL, false>), ctx->device, smem);
             if (e != cudaSuccess) return e;
             int per_sm = 0;
-            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL>, p.warps * 32, smem);
+            e = shared ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL, true>, p.warps * 32, smem)
+                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL, false>, p.warps * 32, smem);
             if (e != cudaSuccess) return e;
             if (per_sm < 1) return cudaErrorInvalidConfiguration;
             // CTAs per slice over all jobs: all that fit at once, but no more than there are row tiles for their warps
@@ -776,7 +779,8 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
         counter += a.job[i].row_tiles;
         partial += (size_t)a.ksplit * (DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
     }
-    return launch_pdl(kquant_decode_kernel<NG, DUAL>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
+    if (cache.plan.wsplit > 1) return launch_pdl(kquant_decode_kernel<NG, DUAL, true>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
+    return launch_pdl(kquant_decode_kernel<NG, DUAL, false>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
 }
 
 } // namespace

@@ -253,15 +253,47 @@ def test_prefill_shape_sampled_rows(gpu):
     assert H.rel_l2(y[rows.cuda()].cpu().numpy(), ref) <= REL_L2_TOL
 
 
+def test_weight_only_lane_is_bit_identical(gpu, golden):
+    """A weight without input_scale_inv takes the reference's weight-only lane (int8 activations per 256, exact
+    integer contraction, f16 result).  First the reference's own fixture (7 tokens x 11 rows x 256 inputs: its Q8
+    codes, scales and expected f16 bits were produced by the reference's Python), then larger shapes with several
+    blocks, negative block scales, bf16 and f32 activations, against the CPU lane: equal bits everywhere."""
+    op, ctx, k = gpu
+    wp, ws, s2 = golden["a16_w_packed"], golden["a16_w_scales"], float(golden["a16_scale2"])
+    x16 = torch.from_numpy(golden["a16_activation_f16_bits"].view(np.float16).astype(np.float32))
+    w = op.Weight(ctx, op.TensorView(wp, O.NVFP4, 256, 11, ws, s2, None))
+    y = torch.zeros((7, 11), dtype=torch.float16, device="cuda")
+    k.encode_nvfp4_matmul(w, x16.cuda(), y, 7)
+    ctx.sync_status()
+    assert np.array_equal(y.cpu().numpy().view(np.uint16), golden["a16_expected_f16_bits"])
+    w.free()
+    for n_out, n_in, tokens, x_dtype in ((300, 1024, 19, torch.bfloat16), (37, 2560, 8, torch.float32), (130, 256, 1, torch.float32)):
+        packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=n_out, negative_scales=True)
+        w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, None))
+        x = (torch.from_numpy(H.lcg_activations(tokens * n_in, seed=tokens).reshape(tokens, n_in)) * 3.0).to(x_dtype)
+        x[0, :256] = 0.0   # a block of zeros is skipped
+        want = O.matmul(O.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, None), x.float().numpy(), threads=4)
+        y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+        k.encode_nvfp4_matmul(w, x.cuda(), y, tokens)
+        ctx.sync_status()
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.astype(np.float32).view(np.uint32)), (n_out, n_in, tokens)
+        w.free()
+
+
 def test_workspace_and_dtype_misuse(gpu):
     op, ctx, k = gpu
     packed, scales, scale2 = make_weight(op, ctx, 64, 256, seed=1)
     w_only = op.Weight(ctx, op.TensorView(packed, O.NVFP4, 256, 64, scales, scale2, None))
     x = torch.zeros((4, 256), dtype=torch.bfloat16, device="cuda")
     y = torch.zeros((4, 64), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_matmul(w_only, x, y, 4)   # no input_scale_inv: the weight-only lane serves it
+    xp, xs = k.quantize_nvfp4_activation(x, 10.0)
     with pytest.raises(op.MuserCudaError) as e:
-        k.encode_nvfp4_matmul(w_only, x, y, 4)
+        k.encode_nvfp4_prequant(w_only, xp, xs, y, 4)   # pre-quantized activations are the W4A4 lane's
     assert e.value.status_name == "UNSUPPORTED_DTYPE"
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_nvfp4_matmul(w_only, x, y, 4, residual=y)   # the weight-only lane fuses nothing
+    assert e.value.status_name == "BAD_ARG"
     small = op.Context(0, workspace_bytes=1024)
     w = op.Weight(small, op.TensorView(packed, O.NVFP4, 256, 64, scales, scale2, 10.0))
     with pytest.raises(op.MuserCudaError) as e:
