@@ -34,7 +34,7 @@ __global__ void wait_probe_kernel(uint32_t polls, int *status) {
     if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, polls)) atomicExch(status + 1, 901);
 }
 
-static bool is_kquant(uint32_t t) { return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q6_K; }
+static bool is_kquant(uint32_t t) { return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q5_K || t == MUSER_DTYPE_Q6_K; }
 
 // 64-bit digest of a device buffer, independent of thread scheduling: sum over 8-byte words of a
 // position-keyed multiplicative mix.
@@ -64,7 +64,7 @@ static muser_cuda_status validate_shard(Ctx *ctx, uint32_t dtype, uint64_t n_in,
         if (n_out % shard->world) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "n_out is not divisible by the shard count");
         w->n_out = n_out / shard->world;
     } else {
-        const uint64_t gran = dtype == MUSER_DTYPE_Q4_K ? 32 : dtype == MUSER_DTYPE_Q6_K ? 16 : 64;
+        const uint64_t gran = (dtype == MUSER_DTYPE_Q4_K || dtype == MUSER_DTYPE_Q5_K) ? 32 : dtype == MUSER_DTYPE_Q6_K ? 16 : 64;
         if (n_in % shard->world || (n_in / shard->world) % gran)
             return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the K shard is not a whole number of sub-blocks");
         w->n_in = n_in / shard->world;
@@ -95,12 +95,12 @@ static muser_cuda_status repack_common(Ctx *ctx, uint32_t dtype, const uint8_t *
     size_t raw_bytes = 0, raw_scale_bytes = 0;
     if (is_kquant(dtype)) {
         if (n_in % 256) return bail(fail(ctx, MUSER_CUDA_BAD_SHAPE, "K-quant rows need n_in % 256 == 0"));
-        raw_bytes = n_out * (n_in / 256) * (dtype == MUSER_DTYPE_Q4_K ? 144 : 210);
+        raw_bytes = n_out * (n_in / 256) * (dtype == MUSER_DTYPE_Q4_K ? 144 : dtype == MUSER_DTYPE_Q5_K ? 176 : 210);
         const uint64_t k0 = w->shard.axis == MUSER_SHARD_K ? w->shard.rank * w->n_in : 0;
         w->k_off = (uint32_t)(k0 % 256);
         w->nsb = (uint32_t)((w->k_off + w->n_in + 255) / 256);
         w->row_tiles = (uint32_t)((w->n_out + 15) / 16);
-        w->image_bytes = (uint64_t)w->row_tiles * w->nsb * (dtype == MUSER_DTYPE_Q4_K ? kQ4TileBytes : kQ6TileBytes);
+        w->image_bytes = (uint64_t)w->row_tiles * w->nsb * kquant_tile_bytes(dtype);
         cudaError_t e = cudaMalloc(&w->image, w->image_bytes);
         if (e != cudaSuccess) return bail(fail(ctx, MUSER_CUDA_ERROR, std::string("cudaMalloc(image): ") + cudaGetErrorString(e)));
     } else {
@@ -194,7 +194,7 @@ extern "C" {
 uint32_t muser_cuda_abi_version(void) { return MUSER_CUDA_ABI_VERSION; }
 
 int muser_cuda_supports_projection(uint32_t t) {
-    return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q6_K || t == MUSER_DTYPE_NVFP4_E2M1;
+    return t == MUSER_DTYPE_Q4_K || t == MUSER_DTYPE_Q5_K || t == MUSER_DTYPE_Q6_K || t == MUSER_DTYPE_NVFP4_E2M1;
 }
 
 muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muser_cuda_ctx **out) {

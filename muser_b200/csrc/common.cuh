@@ -21,6 +21,8 @@ namespace muser {
 constexpr int kTileRows = 16;
 constexpr int kQ4TileBytes = 2048 + 256;             // nibbles | 16 x (d, dmin, scales[12])
 constexpr int kQ6TileBytes = 2048 + 1024 + 256 + 32; // low nibbles | high 2-bit | 16 x sc[16] | 16 x d
+constexpr int kQ5TileBytes = 2048 + 512 + 256;       // nibbles | fifth bits | 16 x (d, dmin, scales[12])
+constexpr int kQ5OffHi = 2048, kQ5OffHdr = 2560;
 constexpr int kQ6OffHi = 2048, kQ6OffSc = 3072, kQ6OffD = 3328;
 
 struct Ctx {
@@ -119,6 +121,10 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 #endif
+
+inline int kquant_tile_bytes(uint32_t dtype) {
+    return dtype == MUSER_DTYPE_Q4_K ? kQ4TileBytes : dtype == MUSER_DTYPE_Q5_K ? kQ5TileBytes : kQ6TileBytes;
+}
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

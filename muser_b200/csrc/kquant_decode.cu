@@ -1,4 +1,4 @@
-// Decode / small-batch projection for Q4_K and Q6_K weights, 1 to 16 tokens: y[t][r] = dot(W_r, x_t), for up to
+// Decode / small-batch projection for Q4_K, Q5_K and Q6_K weights, 1 to 16 tokens: y[t][r] = dot(W_r, x_t), for up to
 // four projections of the same input in one launch.
 //
 // Stands in for MetalKernels::encode_quantized_matmul at decode (crates/muser-engine/src/metal/encode/qkv.rs:425-449),
@@ -13,7 +13,7 @@
 //     |error| <= amax(tile) * 2^-15), once per CTA, parked in shared memory in tensor-core fragment order;
 //   - the 4-bit (6-bit) quants go straight from the tile into int8 mma.sync fragments: the image is laid out so that
 //     a lane already owns its fragment's bytes (kquant_layout.cuh);
-//   - one MMA multiplies a whole sub-block (32 weights of 16 rows for Q4_K, 16 for Q6_K) with a group of four
+//   - one MMA multiplies a whole sub-block (32 weights of 16 rows for Q4_K / Q5_K, 16 for Q6_K) with a group of four
 //     tokens: the eight fragment columns are (token, plane) pairs, so a lane ends up with the high- and low-plane
 //     sums of ITS token for rows g and g + 8 and no value ever crosses lanes;
 //   - the sub-block scale (6-bit, or int8 for Q6_K) is applied to the integer sums with integer multiply-adds, the
@@ -69,10 +69,18 @@ struct DecArgs {
 namespace dec {
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void tile_fetch(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+// Weight tiles are read once per launch: they travel with an evict-first L2 policy, so that a launch's 15 to 230 MB
+// of weights do not push the kernels' own code, the activations and the split-K scratch out of the 126 MB L2 (a
+// launch whose code had been evicted by its predecessor's stream started about 3 us later).
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tile_fetch(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
 __device__ __forceinline__ bool tile_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kDecWaitLimit; ++i) {
@@ -107,6 +115,7 @@ __device__ __forceinline__ int sbyte(uint32_t w, int i) { // sign-extended byte 
 template <int DT> struct Fmt;
 template <> struct Fmt<MUSER_DTYPE_Q4_K> { static constexpr int kTileBytes = kQ4TileBytes; };
 template <> struct Fmt<MUSER_DTYPE_Q6_K> { static constexpr int kTileBytes = kQ6TileBytes; };
+template <> struct Fmt<MUSER_DTYPE_Q5_K> { static constexpr int kTileBytes = kQ5TileBytes; };
 
 constexpr int kFragU4 = 128; // uint4 of B fragments per (tile, token group): 4 fragment quads x 32 lanes
 constexpr int kMetaU4 = 2;   // uint4 per (tile, token): sx, then (Q4_K) the eight sub-block sums as three byte planes
@@ -191,7 +200,7 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
         const float sx = usable ? __fdiv_rn(amax, 16383.0f) : 0.f;
         uint32_t *mrow = mw + (size_t)(tile * TOK + tok) * (kMetaU4 * 4);
         uint32_t *fbase = fw + (size_t)(tile * NG + gp) * (kFragU4 * 4);
-        if constexpr (DT == MUSER_DTYPE_Q4_K) {
+        if constexpr (DT != MUSER_DTYPE_Q6_K) { // Q4_K and Q5_K: 32-element sub-blocks with a min term
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             const uint32_t j = lane >> 2, tq = lane & 3;
@@ -229,6 +238,24 @@ struct Q4Regs {
     uint4 q[4]; // [2*rowsel + half]: row g + 8*rowsel, word jj = sub-block 4*half + jj, this lane's eight elements
     uint4 ha, hb;
 };
+struct Q5Regs {
+    uint4 q[4];
+    uint4 hbits; // [2*rowsel + half]: byte jj = the fifth bits of the lane's eight elements of sub-block 4*half + jj
+    uint4 ha, hb;
+};
+__device__ __forceinline__ Q5Regs load_regs(const uint8_t *tile, int lane, Q5Regs *) { // tile: shared memory
+    Q5Regs r;
+    const uint4 *q = reinterpret_cast<const uint4 *>(tile);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = q[32 * i + lane];
+    r.hbits = reinterpret_cast<const uint4 *>(tile + kQ5OffHi)[lane];
+    const uint4 *h = reinterpret_cast<const uint4 *>(tile + kQ5OffHdr);
+    r.ha = h[lane >> 2];
+    r.hb = h[(lane >> 2) + 8];
+    return r;
+}
+// four fifth bits (x < 16) onto bit 4 of four bytes
+__device__ __forceinline__ uint32_t spread_bit4(uint32_t x) { return (x * 0x02040810u) & 0x10101010u; }
 __device__ __forceinline__ Q4Regs load_regs(const uint8_t *tile, int lane, Q4Regs *) { // tile: shared memory
     Q4Regs r;
     const uint4 *q = reinterpret_cast<const uint4 *>(tile);
@@ -256,8 +283,10 @@ __device__ __forceinline__ Q4Hdr q4_hdr(uint4 h) {
 }
 
 // out[gp][0 / 1]: row g / g + 8, token 4 * gp + t.  fb: this lane's fragment entries of the tile; mt: the tile's meta.
-template <int NG>
-__device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+// Regs is Q4Regs or Q5Regs: the same arithmetic on 4-bit or 5-bit quants.
+template <int NG, typename Regs>
+__device__ __forceinline__ void q45_compute(const Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+    constexpr bool Q5 = sizeof(Regs) == sizeof(Q5Regs);
     const Q4Hdr ha = q4_hdr(r.ha), hb = q4_hdr(r.hb);
     int acc[NG][4];
 #pragma unroll
@@ -271,8 +300,13 @@ __device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, c
         for (int e = 0; e < 2; ++e) {
             const int j = 2 * jp + e;
             const uint32_t wa = gw(r.q[j >> 2], j & 3), wb = gw(r.q[2 + (j >> 2)], j & 3);
-            const uint32_t a0 = wa & 0x0F0F0F0Fu, a2 = (wa >> 4) & 0x0F0F0F0Fu;
-            const uint32_t a1 = wb & 0x0F0F0F0Fu, a3 = (wb >> 4) & 0x0F0F0F0Fu;
+            uint32_t a0 = wa & 0x0F0F0F0Fu, a2 = (wa >> 4) & 0x0F0F0F0Fu;
+            uint32_t a1 = wb & 0x0F0F0F0Fu, a3 = (wb >> 4) & 0x0F0F0F0Fu;
+            if constexpr (Q5) {
+                const uint32_t ba = (uint32_t)ubyte(gw(r.hbits, j >> 2), j & 3), bb = (uint32_t)ubyte(gw(r.hbits, 2 + (j >> 2)), j & 3);
+                a0 |= spread_bit4(ba & 15u), a2 |= spread_bit4(ba >> 4);
+                a1 |= spread_bit4(bb & 15u), a3 |= spread_bit4(bb >> 4);
+            }
             const int sa = ubyte(ha.sc[j >> 2], j & 3), sb = ubyte(hb.sc[j >> 2], j & 3);
 #pragma unroll
             for (int gp = 0; gp < NG; ++gp) {
@@ -299,6 +333,15 @@ __device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, c
         out[gp][0] = fmaf(sx, fmaf(-ha.dmin, (float)mina, ha.d * pa), out[gp][0]);
         out[gp][1] = fmaf(sx, fmaf(-hb.dmin, (float)minb, hb.d * pb), out[gp][1]);
     }
+}
+
+template <int NG>
+__device__ __forceinline__ void tile_compute(const Q4Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+    q45_compute<NG>(r, fb, mt, t, out);
+}
+template <int NG>
+__device__ __forceinline__ void tile_compute(const Q5Regs &r, const uint4 *fb, const uint4 *mt, int t, float (&out)[NG][2]) {
+    q45_compute<NG>(r, fb, mt, t, out);
 }
 
 // ------------------------------------------------------------------------------------ Q6_K tile
@@ -380,6 +423,7 @@ __device__ __forceinline__ void tile_compute(const Q6Regs &r, const uint4 *fb, c
 template <int DT> struct RegsOf;
 template <> struct RegsOf<MUSER_DTYPE_Q4_K> { using type = Q4Regs; };
 template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
+template <> struct RegsOf<MUSER_DTYPE_Q5_K> { using type = Q5Regs; };
 
 // ------------------------------------------------------------------------------------ one CTA's work
 // The CTA's warps form warps / wsplit row slots of wsplit warps each.  Slot r of CTA group G takes row tiles
@@ -387,7 +431,7 @@ template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
 // tiles through its own ring, and the parts meet in shared memory (named barrier per slot, first warp adds them in
 // part order), which costs a few hundred cycles where the exchange between CTAs through global memory costs
 // microseconds.  Small weights, which need every warp of the GPU to hide HBM latency, are split this way.
-template <int DT, int NG, bool DUAL, bool WSPLIT>
+template <int DT, int NG, bool DUAL>
 __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
     using Regs = typename RegsOf<DT>::type;
     constexpr int kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = 4 * NG;
@@ -408,7 +452,7 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 
     // this warp's tiles, over all its row tiles, form one stream: n -> (row tile, image, tile); start it before staging
-    const uint32_t wsplit = WSPLIT ? a.wsplit : 1u, slots = warps / wsplit, wslot = warp / wsplit, wpart = warp % wsplit;
+    const uint32_t wsplit = a.wsplit, slots = warps / wsplit, wslot = warp / wsplit, wpart = warp % wsplit;
     const uint32_t t_first = n_tiles * wpart / wsplit, my_tiles = n_tiles * (wpart + 1) / wsplit - t_first; // this warp's part of the slice
     const uint32_t first_row = group * slots + wslot, row_step = jb.groups * slots;
     const uint32_t my_rows = jb.row_tiles > first_row ? (jb.row_tiles - first_row + row_step - 1) / row_step : 0;
@@ -416,10 +460,11 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     uint8_t *ring = ring_base + (size_t)warp * ring_n * kBytes;
     const uint32_t bar0 = smem_addr(bars + warp * ring_n);
     uint32_t f_tile = first_row * a.nsb + sb_first + t_first, f_tl = 0, f_im = 0;
+    const uint64_t policy = evict_first_policy();
     auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, lane 0 issues the copy
         const uint8_t *base = jb.image;
         if constexpr (DUAL) base = f_im ? jb.image_up : jb.image;
-        if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot);
+        if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot, policy);
         ++f_tile;
         if (++f_tl == my_tiles) {
             f_tl = 0;
@@ -473,7 +518,7 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
             }
         }
         // this lane now holds, per group gp: [0] -> row g, [1] -> row g + 8, token 4 * gp + t
-        if constexpr (WSPLIT) {
+        if (wsplit > 1) {
             // the slot's warps meet: every warp leaves its sums, the first one adds them in part order.  Two buffers
             // taken in turn: a warp can be at most one row tile ahead of the slot's first warp (the next barrier needs
             // that warp too), so what it writes is never what is still being read.
@@ -566,7 +611,13 @@ constexpr int ctas_per_sm(int ng) { return 1; }
 } // namespace dec
 
 // blockIdx.x -> (job, CTA group, K slice): a job's CTAs are contiguous, group-major.
-template <int NG, bool DUAL, bool WSPLIT>
+// FAM 0: jobs of Q4_K and Q6_K in any mix (the layer's projections); FAM 1: Q5_K jobs only (the LM head), compiled
+// apart so that the common kernels do not carry its code.  Everything else that varies between the launches of a
+// decode step (warps, K slices, warp parts, jobs) is a run-time argument of ONE function per token-group count:
+// measured on a B200, a launch whose function differs from its predecessor's starts ~3 us later when the predecessor
+// streamed enough weights to push the code out of L2 (instruction fetches then miss all the way to HBM), which is
+// more than any specialised variant saved.
+template <int NG, bool DUAL, int FAM>
 __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG)) kquant_decode_kernel(const __grid_constant__ DecArgs a) {
     extern __shared__ uint4 dec_dyn[];
     __shared__ float inv_rms[4 * NG];
@@ -576,8 +627,12 @@ __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG))
         if (i < a.n_jobs && blockIdx.x >= a.job[i].cta0) ji = i;
     const DecJob &jb = a.job[ji];
     const uint32_t local = blockIdx.x - jb.cta0, slice = local % a.ksplit, group = local / a.ksplit;
-    if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL, WSPLIT>(a, jb, group, slice, dec_dyn, inv_rms);
-    else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL, WSPLIT>(a, jb, group, slice, dec_dyn, inv_rms);
+    if constexpr (FAM == 1) {
+        dec::run<MUSER_DTYPE_Q5_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+    } else {
+        if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+        else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+    }
 }
 
 // ------------------------------------------------------------------------------------ host side
@@ -587,9 +642,12 @@ struct DecPlan {
     int warps, ksplit, ring, wsplit;
 };
 
-size_t dec_smem_bytes(uint32_t nsb, int ksplit, int warps, int ring, int ng, bool q6, int out_words) {
+// fmt: 0 = Q4_K jobs only, 1 = Q6_K among them (the largest tile), 2 = Q5_K
+constexpr int fmt_tile_bytes(int fmt) { return fmt == 0 ? kQ4TileBytes : fmt == 1 ? kQ6TileBytes : kQ5TileBytes; }
+
+size_t dec_smem_bytes(uint32_t nsb, int ksplit, int warps, int ring, int ng, int fmt, int out_words) {
     const uint32_t max_tiles = (nsb + ksplit - 1) / ksplit + 1;
-    return (size_t)max_tiles * ng * (dec::kFragU4 * 16 + 4 * dec::kMetaU4 * 16) + (size_t)warps * ring * ((q6 ? kQ6TileBytes : kQ4TileBytes) + 8) +
+    return (size_t)max_tiles * ng * (dec::kFragU4 * 16 + 4 * dec::kMetaU4 * 16) + (size_t)warps * ring * (fmt_tile_bytes(fmt) + 8) +
            (size_t)2 * warps * out_words * 32 * sizeof(float) + 16;
 }
 
@@ -606,10 +664,10 @@ struct DecCandidate {
     double cost;
 };
 
-void dec_candidates(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6, uint32_t tokens, int out_words, std::vector<DecCandidate> &out) {
+void dec_candidates(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, int fmt, uint32_t tokens, int out_words, std::vector<DecCandidate> &out) {
     out.clear();
-    const double t_warp = (q6 ? 1750.0 : 1300.0) + (ng - 1) * (q6 ? 1600.0 : 1450.0);
-    const double bytes = (double)nsb * row_tiles * (q6 ? kQ6TileBytes : kQ4TileBytes), hbm_bytes_per_cycle = 2800.0;
+    const double t_warp = (fmt == 1 ? 1750.0 : fmt == 2 ? 1800.0 : 1300.0) + (ng - 1) * (fmt == 1 ? 1600.0 : 1450.0);
+    const double bytes = (double)nsb * row_tiles * fmt_tile_bytes(fmt), hbm_bytes_per_cycle = 2800.0;
     const int max_w = dec::max_warps(ng), batch = ng >= 3 ? 4 : 2, ring = 2;
     static const int kParts[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12};
     for (int ks = 1; ks <= 16 && (uint32_t)ks <= nsb; ++ks)
@@ -620,7 +678,7 @@ void dec_candidates(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool
                 if (ws > 1 && slots > 15) continue; // one named barrier per slot
                 if ((uint32_t)ws > nsb / ks) continue;
                 const double tiles_cta = std::ceil((double)nsb / ks), tiles_warp = std::ceil(tiles_cta / ws);
-                const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng, q6, out_words);
+                const size_t smem = dec_smem_bytes(nsb, ks, w, ring, ng, fmt, out_words);
                 if (smem > 220u * 1024) continue;
                 int ctas = (int)((227u * 1024) / (smem + 1024));
                 ctas = std::min(ctas, std::max(1, max_w / w)); // the register file
@@ -639,9 +697,9 @@ void dec_candidates(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool
     std::sort(out.begin(), out.end(), [](const DecCandidate &x, const DecCandidate &y) { return x.cost < y.cost; });
 }
 
-DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, bool q6, uint32_t tokens, int out_words) {
+DecPlan dec_plan(uint32_t nsb, uint32_t row_tiles, int sm_count, int ng, int fmt, uint32_t tokens, int out_words) {
     std::vector<DecCandidate> c;
-    dec_candidates(nsb, row_tiles, sm_count, ng, q6, tokens, out_words, c);
+    dec_candidates(nsb, row_tiles, sm_count, ng, fmt, tokens, out_words, c);
     return c.empty() ? DecPlan{2, 1, 2, 1} : c[0].plan;
 }
 
@@ -666,16 +724,16 @@ TunedKey tuned_key(const DecArgs &a, bool dual) {
     k.nsb = a.nsb, k.n_jobs = a.n_jobs, k.dual = dual, k.tokens = a.tokens;
     for (uint32_t i = 0; i < a.n_jobs; ++i) {
         k.rows[i] = a.job[i].row_tiles;
-        k.q6 |= (a.job[i].dtype == MUSER_DTYPE_Q6_K ? 1u : 0u) << i;
+        k.q6 |= (a.job[i].dtype == MUSER_DTYPE_Q6_K ? 1u : a.job[i].dtype == MUSER_DTYPE_Q5_K ? 2u : 0u) << (2 * i);
     }
     return k;
 }
 
-template <int NG, bool DUAL>
+template <int NG, bool DUAL, int FAM>
 cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t stream) {
     struct Cached {
         uint32_t nsb = 0, rows[kDecMaxJobs] = {0, 0, 0, 0}, n_jobs = 0;
-        bool q6 = false;
+        int fmt = 0;
         DecPlan plan{1, 1, 2, 1};
         size_t smem = 0;
         uint32_t groups[kDecMaxJobs] = {0, 0, 0, 0};
@@ -697,18 +755,18 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
             generation = tt.generation[ctx->device];
         }
         same = same && slot.generation == generation;
-        bool q6 = false;
+        int fmt = FAM == 1 ? 2 : 0;
         uint32_t total_tiles = 0;
         size_t out_floats = 0;
         for (uint32_t i = 0; i < a.n_jobs; ++i) {
             same = same && slot.rows[i] == a.job[i].row_tiles;
-            q6 = q6 || a.job[i].dtype == MUSER_DTYPE_Q6_K;
+            if (a.job[i].dtype == MUSER_DTYPE_Q6_K) fmt = 1;
             total_tiles += a.job[i].row_tiles;
             out_floats += (size_t)(DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
         }
-        same = same && slot.q6 == q6;
+        same = same && slot.fmt == fmt;
         if (!same) {
-            DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, q6, a.tokens, kOutWords);
+            DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, fmt, a.tokens, kOutWords);
             {
                 TunedTable &tt = tuned_table();
                 std::lock_guard<std::mutex> tl(tt.mu);
@@ -725,20 +783,17 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
             }
             while (p.ksplit > 1 && (size_t)p.ksplit * out_floats * sizeof(float) > ctx->gemv_partial_bytes) --p.ksplit;
             if (total_tiles > ctx->gemv_counter_slots) p.ksplit = 1;
-            size_t smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
-            while (smem > 226u * 1024 && p.ring > 2) p.ring = 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
+            size_t smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, fmt, kOutWords);
+            while (smem > 226u * 1024 && p.ring > 2) p.ring = 2, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, fmt, kOutWords);
             while (smem > 226u * 1024 && (uint32_t)p.ksplit < a.nsb &&
                    (size_t)(p.ksplit + 1) * out_floats * sizeof(float) <= ctx->gemv_partial_bytes && total_tiles <= ctx->gemv_counter_slots)
-                ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
-            while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, p.wsplit = 1, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, q6, kOutWords);
+                ++p.ksplit, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, fmt, kOutWords);
+            while (smem > 226u * 1024 && p.warps > 2) p.warps -= 2, p.wsplit = 1, smem = dec_smem_bytes(a.nsb, p.ksplit, p.warps, p.ring, NG, fmt, kOutWords);
             if (smem > 226u * 1024) return cudaErrorNotSupported;
-            const bool shared = p.wsplit > 1;
-            cudaError_t e = ensure_dynamic_smem(shared ? reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL, true>)
-                                                       : reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL, false>), ctx->device, smem);
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_decode_kernel<NG, DUAL, FAM>), ctx->device, smem);
             if (e != cudaSuccess) return e;
             int per_sm = 0;
-            e = shared ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL, true>, p.warps * 32, smem)
-                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL, false>, p.warps * 32, smem);
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kquant_decode_kernel<NG, DUAL, FAM>, p.warps * 32, smem);
             if (e != cudaSuccess) return e;
             if (per_sm < 1) return cudaErrorInvalidConfiguration;
             // CTAs per slice over all jobs: all that fit at once, but no more than there are row tiles for their warps
@@ -753,7 +808,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
                 slot.groups[i] = std::max(1u, (w_i + rounds - 1) / rounds);
                 slot.rows[i] = a.job[i].row_tiles;
             }
-            slot.nsb = a.nsb, slot.n_jobs = a.n_jobs, slot.q6 = q6;
+            slot.nsb = a.nsb, slot.n_jobs = a.n_jobs, slot.fmt = fmt;
             slot.plan = p, slot.smem = smem;
             slot.forced_w = forced.warps, slot.forced_k = forced.ksplit, slot.forced_r = forced.ring, slot.forced_s = forced.wsplit;
             slot.tokens = a.tokens;
@@ -761,7 +816,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
         }
         cache = slot;
     }
-    a.slot_bytes = cache.q6 ? kQ6TileBytes : kQ4TileBytes;
+    a.slot_bytes = (uint32_t)fmt_tile_bytes(cache.fmt);
     a.ksplit = cache.plan.ksplit;
     a.ring = cache.plan.ring;
     a.wsplit = (uint32_t)cache.plan.wsplit;
@@ -779,8 +834,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
         counter += a.job[i].row_tiles;
         partial += (size_t)a.ksplit * (DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
     }
-    if (cache.plan.wsplit > 1) return launch_pdl(kquant_decode_kernel<NG, DUAL, true>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
-    return launch_pdl(kquant_decode_kernel<NG, DUAL, false>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
+    return launch_pdl(kquant_decode_kernel<NG, DUAL, FAM>, dim3(cta), dim3(cache.plan.warps * 32), cache.smem, stream, a);
 }
 
 } // namespace
@@ -824,20 +878,31 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     a.ksplit = 1, a.max_tiles = 0, a.ring = 2, a.slot_bytes = kQ6TileBytes, a.wsplit = 1;
     const DecPlan forced{(int)ctx->dec_warps, (int)ctx->dec_ksplit, (int)ctx->dec_ring, (int)ctx->dec_wsplit};
     const uint32_t ng = (tokens + 3) / 4;
+    uint32_t n_q5 = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) n_q5 += w[i]->dtype == MUSER_DTYPE_Q5_K;
+    if (n_q5 != 0 && (n_q5 != n_jobs || w_up)) return cudaErrorNotSupported; // Q5_K jobs run in launches of their own, unfused
+    if (n_q5) {
+        switch (ng) {
+        case 1: return dec_launch<1, false, 1>(a, ctx, forced, stream);
+        case 2: return dec_launch<2, false, 1>(a, ctx, forced, stream);
+        case 3: return dec_launch<3, false, 1>(a, ctx, forced, stream);
+        default: return dec_launch<4, false, 1>(a, ctx, forced, stream);
+        }
+    }
     if (w_up) {
         if (n_jobs != 1) return cudaErrorNotSupported;
         switch (ng) {
-        case 1: return dec_launch<1, true>(a, ctx, forced, stream);
-        case 2: return dec_launch<2, true>(a, ctx, forced, stream);
-        case 3: return dec_launch<3, true>(a, ctx, forced, stream);
-        default: return dec_launch<4, true>(a, ctx, forced, stream);
+        case 1: return dec_launch<1, true, 0>(a, ctx, forced, stream);
+        case 2: return dec_launch<2, true, 0>(a, ctx, forced, stream);
+        case 3: return dec_launch<3, true, 0>(a, ctx, forced, stream);
+        default: return dec_launch<4, true, 0>(a, ctx, forced, stream);
         }
     }
     switch (ng) {
-    case 1: return dec_launch<1, false>(a, ctx, forced, stream);
-    case 2: return dec_launch<2, false>(a, ctx, forced, stream);
-    case 3: return dec_launch<3, false>(a, ctx, forced, stream);
-    default: return dec_launch<4, false>(a, ctx, forced, stream);
+    case 1: return dec_launch<1, false, 0>(a, ctx, forced, stream);
+    case 2: return dec_launch<2, false, 0>(a, ctx, forced, stream);
+    case 3: return dec_launch<3, false, 0>(a, ctx, forced, stream);
+    default: return dec_launch<4, false, 0>(a, ctx, forced, stream);
     }
 }
 
@@ -854,7 +919,7 @@ muser_cuda_status decode_autotune(Ctx *ctx, const Weight *const *w, const Weight
     max_tokens = std::min(std::max(max_tokens, 1u), 16u);
     size_t y_floats = 0, image_bytes = 0;
     for (uint32_t i = 0; i < n_jobs; ++i) {
-        if (!w[i] || w[i]->device != ctx->device || (w[i]->dtype != MUSER_DTYPE_Q4_K && w[i]->dtype != MUSER_DTYPE_Q6_K))
+        if (!w[i] || w[i]->device != ctx->device || (w[i]->dtype != MUSER_DTYPE_Q4_K && w[i]->dtype != MUSER_DTYPE_Q5_K && w[i]->dtype != MUSER_DTYPE_Q6_K))
             return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "autotune takes K-quant weights of this context's device");
         if (w[i]->n_in != w[0]->n_in || w[i]->nsb != w[0]->nsb || w[i]->k_off != w[0]->k_off)
             return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the projections of a group must share n_in and the K shard geometry");
@@ -908,14 +973,15 @@ muser_cuda_status decode_autotune(Ctx *ctx, const Weight *const *w, const Weight
     uint32_t yd[kDecMaxJobs];
     Epilogue eps[kDecMaxJobs];
     uint32_t total_tiles = 0;
-    bool q6 = false;
+    int fmt = 0;
     {
         float *yp = y;
         for (uint32_t i = 0; i < n_jobs; ++i) {
             ys[i] = yp, yd[i] = MUSER_DTYPE_F32;
             yp += (size_t)16 * w[i]->n_out;
             total_tiles += w[i]->row_tiles;
-            q6 = q6 || w[i]->dtype == MUSER_DTYPE_Q6_K;
+            if (w[i]->dtype == MUSER_DTYPE_Q6_K) fmt = 1;
+            else if (w[i]->dtype == MUSER_DTYPE_Q5_K && fmt == 0) fmt = 2;
         }
     }
     auto launch_copy = [&](int c, uint32_t tokens) {
@@ -929,7 +995,7 @@ muser_cuda_status decode_autotune(Ctx *ctx, const Weight *const *w, const Weight
     for (uint32_t tokens : kTokenSteps) {
         if (tokens > max_tokens && tokens != 1 && (tokens + 3) / 4 != (max_tokens + 3) / 4) continue;
         const int ng = (int)(tokens + 3) / 4;
-        dec_candidates(w[0]->nsb, total_tiles, ctx->sm_count, ng, q6, tokens, (w_up ? 2 : 1) * ng * 2, cands);
+        dec_candidates(w[0]->nsb, total_tiles, ctx->sm_count, ng, fmt, tokens, (w_up ? 2 : 1) * ng * 2, cands);
         const int n_c = std::min<int>(kCandidates, (int)cands.size());
         int best = 0;
         float best_ms = 1e30f, model_ms = 1e30f;
@@ -990,7 +1056,7 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
                                        cudaStream_t stream) {
     const bool q6 = w->dtype == MUSER_DTYPE_Q6_K, xf32 = x_dtype == MUSER_DTYPE_F32;
     const uint32_t tc_from = ctx->tc_min_tokens[q6 ? 1 : 0]; // above 64: switched off
-    const bool tc_fits = !w_up && tokens >= tc_from && tokens <= (xf32 ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
+    const bool tc_fits = !w_up && w->dtype != MUSER_DTYPE_Q5_K && tokens >= tc_from && tokens <= (xf32 ? 32u : 64u) && w->n_out >= ctx->tc_min_rows;
     if (tc_fits) {
         const void *xin = x;
         uint32_t xin_dtype = x_dtype;

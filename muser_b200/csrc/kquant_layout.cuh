@@ -12,6 +12,13 @@
 //               nibbles of bytes 0..3 are elements 8t + (0, 4, 1, 5), the high nibbles 8t + (2, 6, 3, 7), and
 //               (word >> 4p) & 0x000F000F yields the pair (2p, 2p + 1) in one operation.
 //   [2048,2304) 16 x the block's 16-byte header (d f16, dmin f16, 12 bytes of packed 6-bit scale/min, GGUF packing).
+// Q5_K tile (2816 bytes): the Q4_K tile with a plane of fifth bits between the nibbles and the headers.
+//   [0, 2048)   the low four bits of every weight, exactly as in a Q4_K tile.
+//   [2048,2560) uint4 (lane): word 0 = row g, sub-blocks 0-3; word 1 = row g, sub-blocks 4-7; words 2, 3 = row g + 8.
+//               Byte jj of a word holds the fifth bits of the lane's eight elements of that sub-block in the order the
+//               nibble word yields them: bit b (0..3) belongs to the element in the LOW nibble of byte b, bit 4 + b to
+//               the one in the HIGH nibble, so (x * 0x02040810) & 0x10101010 drops four of them onto bit 4 of four bytes.
+//   [2560,2816) 16 x the block's 16-byte header (d, dmin, 6-bit scales and mins), as in Q4_K.
 // Q6_K tile (3360 bytes).  A weight is stored as v = (q - 32) & 63 (six-bit two's complement), split into its top
 // four bits T = v >> 2 and low two bits L = v & 3, so that (T << 4) | (L << 2) is the signed byte 4 * (q - 32).
 //   [0, 2048)   T plane: uint4 (u, lane), u = 2*rowsel + half: row g + 8*rowsel, sub-blocks 8*half .. 8*half + 7.

@@ -18,40 +18,67 @@ __device__ __forceinline__ uint32_t q6_raw_value(const uint8_t *blk, uint32_t e,
 }
 
 // Tile layout: kquant_layout.cuh (a lane owns a quarter of every sub-block of its two rows).
+// Q4_K and Q5_K share everything but the fifth-bit plane (Q5 blocks: d, dmin, scales[12], qh[32], qs[128];
+// element e's fifth bit is bit e / 32 of qh[e % 32], quant/k_block.rs:61-105).
+template <bool Q5>
 __global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ image, KqGeom gm) {
-    const uint64_t units_per_tile = 512 + 16;
+    constexpr uint32_t kBlock = Q5 ? 176 : 144, kQsOff = Q5 ? 48 : 16, kTile = Q5 ? kQ5TileBytes : kQ4TileBytes, kHdrOff = Q5 ? kQ5OffHdr : 2048;
+    const uint64_t units_per_tile = 512 + 16 + (Q5 ? 128 : 0);
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= (uint64_t)gm.row_tiles * gm.nsb * units_per_tile) return;
     uint64_t tile = idx / units_per_tile;
     uint32_t unit = (uint32_t)(idx % units_per_tile);
     uint32_t rt = (uint32_t)(tile / gm.nsb), sb = (uint32_t)(tile % gm.nsb);
-    uint8_t *tile_ptr = image + tile * kQ4TileBytes;
+    uint8_t *tile_ptr = image + tile * kTile;
     uint64_t sb_global = gm.k0 / 256 + sb;
     int64_t k_base = (int64_t)sb_global * 256;
+    auto in_shard = [&](uint32_t e) {
+        int64_t k = k_base + e;
+        return k >= (int64_t)gm.k0 && k < (int64_t)(gm.k0 + gm.n_in);
+    };
     if (unit < 512) {
         uint32_t u = unit >> 7, lane = (unit >> 2) & 31, jj = unit & 3;
         uint32_t g = lane >> 2, t = lane & 3;
         uint32_t row = rt * 16 + g + 8 * (u >> 1), j = 4 * (u & 1) + jj;
         uint32_t word = 0;
         if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * kBlock;
             for (int i = 0; i < 8; ++i) {
                 uint32_t e = 32 * j + 8 * t + i;
-                int64_t k = k_base + e;
-                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) continue;
+                if (!in_shard(e)) continue;
                 uint32_t grp = e >> 6, l = e & 63;
-                uint8_t byte = blk[16 + 32 * grp + (l & 31)];
+                uint8_t byte = blk[kQsOff + 32 * grp + (l & 31)];
                 uint32_t nib = l < 32 ? (byte & 15u) : (byte >> 4);
                 word |= nib << (4 * q4_nibble_pos(i));
             }
         }
         reinterpret_cast<uint32_t *>(tile_ptr)[(u * 32 + lane) * 4 + jj] = word;
+    } else if (Q5 && unit < 512 + 128) { // one word of the fifth-bit plane: (lane, rowsel, half) -> four sub-blocks' bytes
+        uint32_t v = unit - 512, lane = v >> 2, wi = v & 3;
+        uint32_t g = lane >> 2, t = lane & 3;
+        uint32_t row = rt * 16 + g + 8 * (wi >> 1), half = wi & 1;
+        uint32_t word = 0;
+        if (row < gm.n_out) {
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * kBlock;
+            for (uint32_t jj = 0; jj < 4; ++jj) {
+                uint32_t j = 4 * half + jj;
+                for (uint32_t i = 0; i < 8; ++i) {
+                    uint32_t e = 32 * j + 8 * t + i;
+                    if (!in_shard(e)) continue;
+                    uint32_t bit = (blk[16 + (e & 31)] >> j) & 1u;
+                    // element i sits in nibble q4_nibble_pos(i) of the nibble word: byte pos / 2, low or high nibble
+                    uint32_t pos = q4_nibble_pos(i), b = pos >> 1, hi = pos & 1;
+                    word |= bit << (8 * jj + 4 * hi + b);
+                }
+            }
+        }
+        reinterpret_cast<uint32_t *>(tile_ptr + kQ5OffHi)[lane * 4 + wi] = word;
     } else {
-        uint32_t r = unit - 512, row = rt * 16 + r;
+        uint32_t r = unit - 512 - (Q5 ? 128 : 0), row = rt * 16 + r;
         uint8_t hdr[16];
         for (int i = 0; i < 16; ++i) hdr[i] = 0;
         if (row < gm.n_out) {
-            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * 144;
+            const uint8_t *blk = raw + ((uint64_t)(gm.row0 + row) * gm.blocks_per_row + sb_global) * kBlock;
             const uint8_t *sp = blk + 4;
             uint8_t sc[8], mn[8];
             for (int j = 0; j < 8; ++j) {
@@ -62,8 +89,7 @@ __global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
                     sc[j] = (uint8_t)((sp[j + 4] & 15) | ((sp[j - 4] >> 6) << 4));
                     mn[j] = (uint8_t)((sp[j + 4] >> 4) | ((sp[j] >> 6) << 4));
                 }
-                int64_t k = k_base + 32 * j; // a sub-block outside the shard contributes nothing
-                if (k < (int64_t)gm.k0 || k >= (int64_t)(gm.k0 + gm.n_in)) sc[j] = mn[j] = 0;
+                if (!in_shard(32 * j)) sc[j] = mn[j] = 0; // a sub-block outside the shard contributes nothing
             }
             hdr[0] = blk[0], hdr[1] = blk[1], hdr[2] = blk[2], hdr[3] = blk[3];
             for (int j = 0; j < 4; ++j) {
@@ -74,7 +100,7 @@ __global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
         }
         uint4 v;
         memcpy(&v, hdr, 16);
-        reinterpret_cast<uint4 *>(tile_ptr + 2048)[r] = v;
+        reinterpret_cast<uint4 *>(tile_ptr + kHdrOff)[r] = v;
     }
 }
 
@@ -151,7 +177,9 @@ muser_cuda_status launch_repack_kquant(Ctx *ctx, Weight *w, const uint8_t *dev_b
     KqGeom gm = kq_geom(*w);
     uint64_t tiles = (uint64_t)gm.row_tiles * gm.nsb;
     if (w->dtype == MUSER_DTYPE_Q4_K)
-        repack_q4k_kernel<<<(unsigned)((tiles * 528 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
+        repack_q4k_kernel<false><<<(unsigned)((tiles * 528 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
+    else if (w->dtype == MUSER_DTYPE_Q5_K)
+        repack_q4k_kernel<true><<<(unsigned)((tiles * 656 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
     else
         repack_q6k_kernel<<<(unsigned)((tiles * 785 + 255) / 256), 256, 0, stream>>>(dev_blocks, w->image, gm);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
@@ -203,15 +231,21 @@ muser_cuda_status launch_repack_nvfp4(Ctx *ctx, Weight *w, const uint8_t *dev_pa
 
 // ------------------------------------------------------------------------------ image -> f32
 // One weight out of the repacked image: row `row`, position `kk` in the tile grid (input index + k_off).
+template <bool Q5>
 __device__ __forceinline__ float q4k_weight(const uint8_t *__restrict__ image, uint32_t nsb, uint32_t row, uint64_t kk) {
     uint32_t sb = (uint32_t)(kk / 256), e = (uint32_t)(kk % 256);
-    const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * kQ4TileBytes;
+    const uint8_t *tile = image + ((uint64_t)(row / 16) * nsb + sb) * (Q5 ? kQ5TileBytes : kQ4TileBytes);
     uint32_t r = row % 16, g = r & 7, rowsel = r >> 3;
     uint32_t j = e >> 5, wi = (e >> 3) & 3, i = e & 7;
     uint32_t q = rowsel * 2 + (j >> 2);
     uint32_t word = reinterpret_cast<const uint32_t *>(tile)[(q * 32 + g * 4 + wi) * 4 + (j & 3)]; // lane (g, 8-element group), word = sub-block % 4
     uint32_t nib = (word >> (4 * q4_nibble_pos(i))) & 15u;
-    const uint8_t *hdr = tile + 2048 + r * 16;
+    if constexpr (Q5) { // the fifth bit: byte (j % 4) of word (2 * rowsel + j / 4) of the lane's uint4, see kquant_layout.cuh
+        uint32_t hw = reinterpret_cast<const uint32_t *>(tile + kQ5OffHi)[(g * 4 + wi) * 4 + rowsel * 2 + (j >> 2)];
+        uint32_t pos = q4_nibble_pos(i);
+        nib |= ((hw >> (8 * (j & 3) + 4 * (pos & 1) + (pos >> 1))) & 1u) << 4;
+    }
+    const uint8_t *hdr = tile + (Q5 ? kQ5OffHdr : 2048) + r * 16;
     float d = __half2float(*reinterpret_cast<const __half *>(hdr));
     float dmin = __half2float(*reinterpret_cast<const __half *>(hdr + 2));
     const uint8_t *s = hdr + 4;
@@ -244,10 +278,11 @@ __device__ __forceinline__ float q6k_weight(const uint8_t *__restrict__ image, u
 }
 
 // One thread per output element; reads the repacked image only.
+template <bool Q5>
 __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
     uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
     if (idx >= gm.n_out * gm.n_in) return;
-    out[idx] = q4k_weight(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
+    out[idx] = q4k_weight<Q5>(image, gm.nsb, (uint32_t)(idx / gm.n_in), idx % gm.n_in + gm.k_off);
 }
 
 __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__restrict__ out, KqGeom gm) {
@@ -260,7 +295,7 @@ __global__ void dequant_q6k_kernel(const uint8_t *__restrict__ image, float *__r
 // weights::matmul_rows (src/weights.rs:425-449): out[t][i] = dot(W_rows[i], x_t) for a list of output rows, the way
 // the reference scores a handful of LM-head rows.  One warp per listed row; lanes stride over the inputs, decode
 // each weight from the image and keep up to eight token sums; a butterfly adds the lanes (fixed order).
-template <bool Q4, bool XF32>
+template <int DT, bool XF32>
 __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restrict__ image, KqGeom gm, const uint32_t *__restrict__ rows,
                                                           uint32_t n_rows, const void *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ out) {
@@ -272,7 +307,9 @@ __global__ void __launch_bounds__(256) kquant_rows_kernel(const uint8_t *__restr
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (row < gm.n_out) {
             for (uint64_t k = lane; k < gm.n_in; k += 32) {
-                const float w = Q4 ? q4k_weight(image, gm.nsb, row, k + gm.k_off) : q6k_weight(image, gm.nsb, row, k + gm.k_off);
+                const float w = DT == MUSER_DTYPE_Q4_K ? q4k_weight<false>(image, gm.nsb, row, k + gm.k_off)
+                              : DT == MUSER_DTYPE_Q5_K ? q4k_weight<true>(image, gm.nsb, row, k + gm.k_off)
+                                                       : q6k_weight(image, gm.nsb, row, k + gm.k_off);
 #pragma unroll
                 for (uint32_t t = 0; t < 8; ++t)
                     if (t < nt) {
@@ -296,11 +333,16 @@ muser_cuda_status launch_kquant_rows(Ctx *ctx, const Weight *w, const uint32_t *
                                      uint32_t x_dtype, float *out, uint32_t tokens, cudaStream_t stream) {
     const unsigned blocks = (n_rows + 7) / 8;
     const KqGeom gm = kq_geom(*w);
-    const bool q4 = w->dtype == MUSER_DTYPE_Q4_K, xf32 = x_dtype == MUSER_DTYPE_F32;
-    if (q4 && xf32) kquant_rows_kernel<true, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else if (q4) kquant_rows_kernel<true, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else if (xf32) kquant_rows_kernel<false, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
-    else kquant_rows_kernel<false, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);
+    const bool xf32 = x_dtype == MUSER_DTYPE_F32;
+#define MUSER_ROWS(DT_)                                                                                                   \
+    do {                                                                                                                   \
+        if (xf32) kquant_rows_kernel<DT_, true><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);   \
+        else kquant_rows_kernel<DT_, false><<<blocks, 256, 0, stream>>>(w->image, gm, rows, n_rows, x, tokens, out);       \
+    } while (0)
+    if (w->dtype == MUSER_DTYPE_Q4_K) MUSER_ROWS(MUSER_DTYPE_Q4_K);
+    else if (w->dtype == MUSER_DTYPE_Q5_K) MUSER_ROWS(MUSER_DTYPE_Q5_K);
+    else MUSER_ROWS(MUSER_DTYPE_Q6_K);
+#undef MUSER_ROWS
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }
@@ -333,7 +375,9 @@ muser_cuda_status launch_dequant(Ctx *ctx, const Weight *w, float *out, cudaStre
         dequant_nvfp4_kernel<<<blocks, 256, 0, stream>>>(w->packed, w->scales, out, w->n_out, w->n_in,
                                                          (uint32_t)((w->n_in + 63) / 64), w->scale2);
     } else if (w->dtype == MUSER_DTYPE_Q4_K) {
-        dequant_q4k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+        dequant_q4k_kernel<false><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
+    } else if (w->dtype == MUSER_DTYPE_Q5_K) {
+        dequant_q4k_kernel<true><<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     } else {
         dequant_q6k_kernel<<<blocks, 256, 0, stream>>>(w->image, out, kq_geom(*w));
     }

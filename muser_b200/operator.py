@@ -148,6 +148,8 @@ class Weight:
 def _row_bytes(dtype: int, n_in: int) -> int:
     if dtype == Q4_K:
         return n_in // 256 * 144
+    if dtype == _lib.Q5_K:
+        return n_in // 256 * 176
     if dtype == Q6_K:
         return n_in // 256 * 210
     if dtype == NVFP4:

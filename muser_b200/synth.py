@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 Q4_K, Q5_K, Q6_K, NVFP4 = 12, 13, 14, 1000
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
 
 # One synthetic decoder layer (hidden 5120, 40 q / 8 kv heads x 128, SwiGLU FFN 27648) in the
 # "Q4_K_M" mix: Q6_K for attn_v and ffn_down, Q4_K elsewhere.  name -> (n_in, n_out, k-quant dtype)

@@ -23,16 +23,20 @@ def gpu():
 def fixtures(dtype):
     from muser_b200 import synth
     bs = O.BLOCK_BYTES[dtype]
-    closed = H.quant_rows(144, 64) if dtype == O.Q4_K else H.q6_rows(64)
-    yield "closed-form", closed, 256, 64
+    if dtype != O.Q5_K:   # the reference's closed-form rows exist for Q4_K and Q6_K
+        closed = H.quant_rows(144, 64) if dtype == O.Q4_K else H.q6_rows(64)
+        assert closed.shape[1] == bs
+        yield "closed-form", closed, 256, 64
     yield "lcg-13x512", H.lcg_weights(dtype, 13, 2, seed=41 + dtype), 512, 13
     yield "lcg-37x1024", H.lcg_weights(dtype, 37, 4, seed=97 + dtype), 1024, 37
-    w = synth.normal_weights(48, 2048, seed=0, stream=dtype)
-    yield "synthetic-48x2048", synth.quantize_kquant(w, dtype).numpy(), 2048, 48
-    assert closed.shape[1] == bs
+    if dtype != O.Q5_K:
+        w = synth.normal_weights(48, 2048, seed=0, stream=dtype)
+        yield "synthetic-48x2048", synth.quantize_kquant(w, dtype).numpy(), 2048, 48
+    else:
+        yield "lcg-300x2048", H.lcg_weights(dtype, 300, 8, seed=5), 2048, 300
 
 
-@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q5_K, O.Q6_K])
 def test_dequantised_weights_are_bit_exact(gpu, dtype):
     op, ctx, k = gpu
     for name, raw, n_in, n_out in fixtures(dtype):
@@ -65,7 +69,7 @@ def check_close(got, want, name, magnitude=None):
     assert np.all(np.abs(got - want) <= bound), (name, float(np.max(np.abs(got - want) / bound)))
 
 
-@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q5_K, O.Q6_K])
 @pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float32])
 def test_matmul_matches_cpu_lane(gpu, dtype, x_dtype):
     op, ctx, k = gpu
@@ -186,7 +190,7 @@ def test_tensor_core_skinny_kernel(gpu, dtype, x_dtype):
     ctx.sync_status()
 
 
-@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q5_K, O.Q6_K])
 def test_tensor_parallel_shards(gpu, dtype):
     """Row shards concatenate to the unsharded result exactly; K shards sum to it within tolerance."""
     op, ctx, k = gpu
@@ -238,7 +242,7 @@ def test_tensor_parallel_shards(gpu, dtype):
         ctx.tuning_set(key, 17)
 
 
-@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q5_K, O.Q6_K])
 def test_every_launch_plan_of_the_decode_kernel(gpu, dtype):
     """The decode kernel's plan forced through its tuning keys: few and many warps per CTA, one to ten K slices between
     CTAs (one slice: no scratch exchange; ten: one tile per slice), one to five K parts between the warps of a CTA
@@ -441,7 +445,7 @@ def test_host_slice_entry_point_repeated_calls(gpu, dtype):
     w.free()
 
 
-@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q5_K, O.Q6_K])
 def test_lm_head_tail_and_selected_rows(gpu, dtype):
     """The LM-head end of the path (reference.rs:559-570, weights.rs:425-449): logit scale and tanh soft cap fused
     behind the projection in every K-quant kernel, and the projection restricted to a list of rows."""
@@ -484,7 +488,7 @@ def test_misuse_returns_statuses(gpu):
     op, ctx, k = gpu
     raw = H.lcg_weights(O.Q4_K, 16, 1, seed=1)
     with pytest.raises(op.MuserCudaError) as e:
-        op.Weight(ctx, op.TensorView(raw, 13, 256, 16))      # Q5_K: no projection kernel
+        op.Weight(ctx, op.TensorView(raw, 8, 256, 16))       # Q8_0: no projection kernel
     assert e.value.status_name == "UNSUPPORTED_DTYPE"
     with pytest.raises(op.MuserCudaError) as e:
         op.Weight(ctx, op.TensorView(raw[:, :100], O.Q4_K, 256, 16))
