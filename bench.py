@@ -223,12 +223,20 @@ def run_gpu(args):
     # The launches of a step are microseconds each: replay them as one CUDA graph so that the device, not the
     # host's launch rate, is what gets timed.  (Capture falls back to plain launches if a collective refuses it.)
     run_step, graphed = step, False
+    per_graph = 1  # steps per graph replay: the largest divisor of --steps up to 10, so that exactly --steps steps are timed
     if not args.no_graph:
+        per_graph = max(d for d in range(1, 11) if args.steps % d == 0)
+
+        def steps_chunk():
+            for _ in range(per_graph):
+                step()
+
         try:
-            run_step, graphed = workloads.capture(step), True
+            run_step, graphed = workloads.capture(steps_chunk), True
         except Exception as exc:  # pragma: no cover - depends on the collective in use
             print(f"graph capture unavailable ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
             torch.cuda.synchronize()
+            per_graph = 1
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         # The timed region can be a few milliseconds, less than one nvidia-smi query: the sampler therefore also
@@ -240,7 +248,7 @@ def run_gpu(args):
             torch.cuda.synchronize()
         barrier()
         start.record()
-        for _ in range(args.steps):
+        for _ in range(args.steps // per_graph):
             run_step()
         stop.record()
         barrier()
@@ -411,7 +419,7 @@ def run_gpu(args):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),
-            "run": {"launch": "one CUDA graph replay per step" if graphed else "plain launches",
+            "run": {"launch": f"CUDA graph replays of {per_graph} step(s) each" if graphed else "plain launches",
                     "schedule": "per token count: q|k|v grouped, o, gate|up grouped, down; one stream",
                     "collective": collective.kind if collective else None},
             "roofline": {"bound": "hbm", "achieved": value, "peak": peak * world, "unit": "GB/s", "frac": value / (peak * world),

@@ -108,7 +108,8 @@ typedef struct muser_cuda_weight_info {
 
 MUSER_CUDA_API uint32_t muser_cuda_abi_version(void);
 
-/* MetalKernels::supports_projection, src/metal/encode.rs:370-385 */
+/* MetalKernels::supports_projection, src/metal/encode.rs:370-385.  True for Q4_K, Q5_K, Q6_K (the K-quant calls
+ * below) and NVFP4_E2M1 (the muser_cuda_nvfp4_* calls). */
 MUSER_CUDA_API int muser_cuda_supports_projection(uint32_t ggml_type);
 
 /* MetalContext::new + MetalKernels::new (src/metal/context.rs, src/metal/encode.rs:278-280).
@@ -162,10 +163,11 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_weight_info_get(const muser_cuda_wei
 MUSER_CUDA_API muser_cuda_status muser_cuda_dequant(muser_cuda_ctx *ctx, const muser_cuda_weight *w, float *out, void *stream);
 
 /* MetalKernels::encode_quantized_matmul (src/metal/encode/qkv.rs:414-424) and its CPU twin
- * weights::matmul (src/weights.rs:398-421) for K-quant weights: y[t][r] = dot(W_r, x_t).
+ * weights::matmul (src/weights.rs:398-421) for K-quant weights (Q4_K, Q5_K, Q6_K): y[t][r] = dot(W_r, x_t).
  * x_dtype is F32 or BF16, y_dtype F32 or BF16; 1 <= tokens <= 64 (decode, decode groups as in
  * encode_quantized_decode_group qkv.rs:234-244, and speculative-verify batches).  Activations are taken as 15-bit
- * fixed point per 256 inputs up to 16 tokens (error <= amax * 2^-15 per input) and as f16 beyond. */
+ * fixed point per 256 inputs up to 16 tokens (error <= amax * 2^-15 per input) and as f16 beyond (Q5_K, the LM
+ * head's type, always takes the fixed-point kernel, 16 tokens at a time). */
 MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
                                               uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                               const muser_cuda_epilogue *epilogue, void *stream);
@@ -173,7 +175,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *ctx
 /* The projections that read the same activations, in ONE launch: the reference dispatches q, k, v (and gate) of a
  * decode step inside one barrier interval (src/decode.rs:5569-5598) and groups up to four sequences per dispatch
  * (MetalKernels::encode_quantized_decode_group, src/metal/encode/qkv.rs:234-281).  1 <= n_items <= 4 K-quant weights of
- * one n_in (and, when K-sharded, one shard geometry), Q4_K and Q6_K may mix; 1 <= tokens <= 16; each item has its own
+ * one n_in (and, when K-sharded, one shard geometry), Q4_K and Q6_K may mix, Q5_K only with Q5_K; 1 <= tokens <= 16; each item has its own
  * output and epilogue, but the fused input norm (norm_weight / norm_eps) must be the same in all of them (or absent
  * in all), since x is staged once.  Results equal n_items calls of muser_cuda_quantized_matmul up to the order in
  * which the f32 partial sums of the K slices are added (the launch plan depends on the group's total size). */
@@ -215,7 +217,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx
  * silu_fast(gate) * up (src/reference.rs:511-513, quant/helpers.rs:72):
  * y[t][j] = silu(Wgate_j . x_t) * (Wup_j . x_t), x read once, the two projections never written out.
  * `epilogue` may be NULL; only its norm_weight / norm_eps are honoured (rms_norm_mul of the FFN input,
- * reference.rs:489).  K-quant weights: 1 <= tokens <= 16.  NVFP4 weights (both with the same input_scale_inv): any token count; x is
+ * reference.rs:489).  K-quant weights (Q4_K or Q6_K): 1 <= tokens <= 16.  NVFP4 weights (both with the same input_scale_inv): any token count; x is
  * quantized into the context workspace once and one tensor-core GEMM computes both projections, each rounded
  * to f16 as the W4A4 lane returns it (quant/nvfp4.rs:337) before the SwiGLU. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_ffn_gate_up_silu(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,
