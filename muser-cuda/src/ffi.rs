@@ -28,6 +28,7 @@ pub const MUSER_TUNE_DECODE_KSPLIT: u32 = 9;
 pub const MUSER_TUNE_DECODE_RING: u32 = 10;
 pub const MUSER_TUNE_ONESHOT_MAX_BYTES: u32 = 11;
 pub const MUSER_TUNE_DECODE_WSPLIT: u32 = 12;
+pub const MUSER_TUNE_NVFP4_PAIR: u32 = 13;
 
 pub const MUSER_CUDA_COMM_ID_BYTES: usize = 128;
 

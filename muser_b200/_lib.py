@@ -14,6 +14,7 @@ F32, F16, Q4_K, Q5_K, Q6_K, BF16, NVFP4 = 0, 1, 12, 13, 14, 30, 1000
 SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
 TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
 TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES, TUNE_DECODE_WSPLIT = 8, 9, 10, 11, 12
+TUNE_NVFP4_PAIR = 13
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 

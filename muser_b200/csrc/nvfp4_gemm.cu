@@ -365,6 +365,322 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------------------------------ paired CTAs
+// The same GEMM on pairs of SMs (tcgen05 cta_group::2): a cluster of two CTAs owns a 256-token x 256-row output tile,
+// each CTA holding 128 of the tokens (its own accumulator, 128 lanes x 256 columns) and HALF of the weight rows of
+// every K slab; the tensor cores of the pair read both halves.  Per slab a CTA therefore fetches 16 KiB of
+// activations + 16 KiB of weights (+ 6 KiB of scale factors) for the same 128 x 256 x 256 of work that costs the
+// single-CTA kernel 48 + 6 KiB: the L2-to-SM traffic, which bounds that kernel, drops by 30 %.
+//
+// Roles as above, with the pair's hand-offs made of plain cluster instructions (no multicast of any kind):
+//   - every CTA loads its own operands (TMA, own mbarrier);
+//   - the follower (cluster rank 1) has one thread that waits for each of its stages to land and then arrives on the
+//     leader's barrier of that stage (mbarrier.arrive on the mapped address), so one wait in the leader covers the pair;
+//   - the leader (rank 0) issues the scale copies and the MMAs for both CTAs; "stage consumed" and "accumulator
+//     complete" are committed twice, once to its own barrier and once to the follower's;
+//   - the follower's epilogue warps hand the accumulator back by arriving on the leader's barrier.
+// All waits are bounded as in the single-CTA kernel; both CTAs meet at a cluster barrier before they free tensor
+// memory and leave, so no arrival can reach a CTA that is gone.
+constexpr int kPStages = 5;
+constexpr int kPBBytes = (BN / 2) * BK / 2; // 16 KiB: this CTA's half of the pair's 256 weight rows
+constexpr int kPStageBytes = kABytes + kPBBytes + kSfaBytes + kSfbBytes;
+constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024 + 256;
+static_assert(kPSmemBytes <= 227 * 1024, "stage ring exceeds the shared memory of one CTA");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t cta_addr, uint32_t rank) { // shared::cta address -> that CTA's window
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// mbar_wait for barriers that the other CTA of the pair arrives on.
+__device__ __forceinline__ bool mbar_wait_pair(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void pair_commit(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void pair_cp_scales(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void pair_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+template <bool DUAL, bool TAIL>
+__global__ void __launch_bounds__(352, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kPStages * kPStageBytes);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kPStages);
+    const uint32_t bar_acc_full = smem_u32(bars + 2 * kPStages), bar_acc_empty = smem_u32(bars + 2 * kPStages + 1);
+    const uint32_t bar_sf_full = smem_u32(bars + 2 * kPStages + 2), bar_sf_empty = smem_u32(bars + 2 * kPStages + 2 + kSfBufs);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kPStages + 2 + 2 * kSfBufs);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank(), leader = rank == 0;
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t m_blocks = (g.tokens + BM - 1) / BM;            // 128-token blocks (the rows of the scale image)
+    const uint32_t m_tiles = (m_blocks + 1) / 2, n_tiles_total = g.n_tiles * m_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(bar_full + 8 * s, leader ? 2 : 1); // leader: its own copies and the follower's "landed"
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        mbar_init(bar_acc_empty, 16); // one arrival per epilogue warp of the pair (used in the leader)
+        for (int b = 0; b < (int)kSfBufs; ++b) {
+            mbar_init(bar_sf_full + 8 * b, 1);
+            mbar_init(bar_sf_empty + 8 * b, 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    cluster_barrier(); // both CTAs' barriers exist before anything arrives on them
+    if (warp == 1) {   // one warp of EACH CTA of the pair takes part in the paired allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer (both CTAs)
+        if (lane == 0) {
+            uint32_t it = 0, issued = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
+                const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+                const uint32_t m_block = 2 * tile_m + rank;
+                // a follower whose 128 tokens do not exist reads zero-filled activation boxes; its scale chunks
+                // come from block 0 so that the copy stays inside the scale image (the products are zero anyway)
+                const uint8_t *sfa = g.a_scales + (size_t)(m_block < m_blocks ? m_block : 0) * g.kt64 * 512;
+                const uint8_t *sfb0 = g.b_scales + (size_t)(DUAL ? tile_n : 2 * tile_n) * g.kt64 * 512;
+                const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
+                // this CTA's half of the weight rows: the leader takes rows 0..127 of the tile (the gate rows of the
+                // fused form), the follower rows 128..255 (the up rows)
+                const CUtensorMap *mb = (DUAL && rank) ? &map_b2 : &map_b;
+                const int b_row = DUAL ? (int)(tile_n * (BN / 2)) : (int)(tile_n * BN + rank * (BN / 2));
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kPStages, round = it / kPStages;
+                    if (round > 0) ok = mbar_wait_pair(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    const uint32_t st = base + s * kPStageBytes;
+                    const uint32_t full = bar_full + 8 * s;
+                    const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
+                    mbar_expect_tx(full, kABytes + kPBBytes + 3 * sf_bytes);
+                    tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(m_block * BM), full);
+                    tma_load_2d(st + kABytes, mb, (int)(kt * (BK / 2)), b_row, full);
+                    bulk_load(st + kABytes + kPBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
+                    bulk_load(st + kABytes + kPBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
+                    bulk_load(st + kABytes + kPBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
+                    issued = it + 1;
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(g.status + 1, 0, 111);
+                // let the copies already in flight land before the CTA's shared memory goes away (bounded: the
+                // leader's phases also need the follower's arrival)
+                const uint32_t first = issued > (uint32_t)kPStages ? issued - kPStages : 0;
+                for (uint32_t k = first; k < issued; ++k) mbar_wait_alone(bar_full + 8 * (k % kPStages), (k / kPStages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---------------------------------------------------------------- MMA issuer (leader, for the pair)
+            // M = 256 (128 rows in each CTA), N = 256: N >> 3 at bit 17, M >> 4 at bit 24
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t peer_empty = map_to_rank(bar_empty, 1), peer_acc_full = map_to_rank(bar_acc_full, 1);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs, ++local) {
+                if (local > 0) {
+                    ok = mbar_wait_pair(bar_acc_empty, (local - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kPStages, round = it / kPStages;
+                    ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag);
+                    if (!ok) break;
+                    const uint32_t st = base + s * kPStageBytes;
+                    const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
+                    const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
+                    const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
+                    ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (uint32_t kb = 0; kb < nkb; ++kb)
+                        pair_mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
+                    pair_commit(bar_sf_empty + 8 * buf);
+                    pair_commit(bar_empty + 8 * s);   // both CTAs may overwrite the stage once these MMAs have read it
+                    pair_commit(peer_empty + 8 * s);
+                }
+                if (ok) {
+                    pair_commit(bar_acc_full);
+                    pair_commit(peer_acc_full);
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(g.status + 1, 0, 112);
+            }
+        } else if (lane == 0) {
+            // ---------------------------------------------------------------- follower: "my stage has landed"
+            const uint32_t leader_full = map_to_rank(bar_full, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kPStages, round = it / kPStages;
+                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_cluster(leader_full + 8 * s);
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(g.status + 1, 0, 116);
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------------------------------------------------------- scale copier (leader, for the pair)
+        if (lane == 0 && leader) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
+                for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kPStages, round = it / kPStages, buf = it % kSfBufs;
+                    ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag);
+                    if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = base + s * kPStageBytes, sfa = st + kABytes + kPBBytes, sfb = sfa + kSfaBytes;
+                    const uint32_t sf = tmem + kSfCol + buf * kSfBufCols, nkb = min(4u, g.kt64 - 4 * kt);
+                    for (uint32_t kb = 0; kb < nkb; ++kb) { // each CTA copies from its own shared memory into its own tensor memory
+                        pair_cp_scales(sf + 4 * kb, scale_desc(sfa + 512 * kb));
+                        pair_cp_scales(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
+                        pair_cp_scales(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                    }
+                    pair_commit(bar_sf_full + 8 * buf);
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicCAS(g.status + 1, 0, 115);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9 of both CTAs)
+        const uint32_t quad = warp & 3;
+        const uint32_t part = (uint32_t)(warp - 2) >> 2;
+        constexpr uint32_t kOutCols = DUAL ? BN / 2 : BN, kPartCols = kOutCols / 2;
+        const uint32_t leader_acc_empty = map_to_rank(bar_acc_empty, 0);
+        uint32_t local = 0;
+        for (uint32_t tile = pair; tile < n_tiles_total; tile += pairs, ++local) {
+            const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_pair(bar_acc_full, local & 1, abort_flag));
+            if (!ok) {
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicCAS(g.status + 1, 0, 113);
+                }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tok = (2 * tile_m + rank) * BM + quad * 32 + lane;
+            const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
+            const bool vec_ok = (g.n_out & 7) == 0;
+            const uint32_t lane_base = tmem + ((quad * 32) << 16), col0 = part * kPartCols;
+            uint32_t r[2][32], r_up[DUAL ? 32 : 1];
+            tmem_ld32(lane_base + col0, r[0]);
+#pragma unroll
+            for (uint32_t s = 0; s < kPartCols / 32; ++s) {
+                const uint32_t c0 = col0 + 32 * s;
+                uint32_t(&cur)[32] = r[s & 1];
+                if constexpr (DUAL) tmem_ld32(lane_base + kOutCols + c0, r_up);
+                tmem_ld_wait();
+                if (s + 1 < kPartCols / 32) {
+                    tmem_ld32(lane_base + c0 + 32, r[(s + 1) & 1]);
+                } else {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+                }
+                const uint32_t n0 = tile_n * kOutCols + c0;
+                if (tok < g.tokens && n0 < g.n_out) {
+                    const size_t o = (size_t)tok * g.n_out + n0;
+                    const uint32_t valid = min(32u, g.n_out - n0);
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(cur[i]), g.scale2), g.inv_input_scale);
+                        if constexpr (DUAL) {
+                            const float gate = __half2float(__float2half_rn(v[i]));
+                            const float up = __half2float(__float2half_rn(
+                                __fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
+                            v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up;
+                        }
+                        v[i] *= rs;
+                        if constexpr (TAIL) v[i] = logit_tail(v[i], g.out_scale, g.softcap);
+                    }
+                    if (g.y_dtype == MUSER_DTYPE_F32)
+                        store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
+                                           g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
+                    else if (g.y_dtype == MUSER_DTYPE_BF16)
+                        store_strip<__nv_bfloat16>(v, reinterpret_cast<__nv_bfloat16 *>(g.y) + o,
+                                                   g.residual ? reinterpret_cast<const __nv_bfloat16 *>(g.residual) + o : nullptr, valid, vec_ok);
+                    else
+                        store_strip<__half>(v, reinterpret_cast<__half *>(g.y) + o,
+                                            g.residual ? reinterpret_cast<const __half *>(g.residual) + o : nullptr, valid, vec_ok);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_barrier(); // nothing of the pair is in flight towards this CTA any more
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
 // Tensor-pipe ceiling for this instruction: every SM issues `iters` x 4 block-scaled FP4 MMAs (128 x 256 x 64 each)
 // on whatever its shared and tensor memory hold, with no loads, no scale copies and no epilogue.  The time of this
 // kernel is the denominator for the GEMM's roofline fraction.
@@ -505,11 +821,53 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.scale2_up = w_up ? w_up->scale2 : 0.0f;
     g.inv_input_scale = 1.0f / w->input_scale_inv;
     g.n_tiles = w_up ? (uint32_t)((w->n_out + BN / 2 - 1) / (BN / 2)) : (uint32_t)(w->n_out_pad / BN);
-    const uint32_t tiles = g.n_tiles * ((tokens + BM - 1) / BM);
-    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(w_up ? w->tmap_half : w->tmap_cache);
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
     const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
+    const uint32_t m_blocks = (tokens + BM - 1) / BM;
+    // Pairs of SMs on 256-token tiles when the token count fills them (an odd last block wastes half a tile)
+    const bool pair = ctx->nvfp4_pair == 2 || (ctx->nvfp4_pair == 0 && m_blocks >= 2 && (m_blocks % 2 == 0 || m_blocks >= 9));
+    if (pair) {
+        struct PairLimit { int n[3] = {0, 0, 0}; };
+        static PerDevice<PairLimit> max_pairs; // co-resident clusters of two, asked once per device and kernel
+        const void *kfn = w_up ? reinterpret_cast<const void *>(nvfp4_gemm_pair_kernel<true, false>)
+                          : tail ? reinterpret_cast<const void *>(nvfp4_gemm_pair_kernel<false, true>)
+                                 : reinterpret_cast<const void *>(nvfp4_gemm_pair_kernel<false, false>);
+        MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(kfn, ctx->device, kPSmemBytes));
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(352), cfg.dynamicSmemBytes = kPSmemBytes, cfg.stream = stream, cfg.attrs = attr, cfg.numAttrs = 1;
+        int cached;
+        {
+            std::lock_guard<std::mutex> lock(max_pairs.mu);
+            int &slot = max_pairs.slot[ctx->device].n[w_up ? 1 : tail ? 2 : 0];
+            if (slot == 0) {
+                cfg.gridDim = dim3(2 * (ctx->sm_count / 2));
+                int n = 0;
+                MUSER_CUDA_TRY(ctx, cudaOccupancyMaxActiveClusters(&n, kfn, &cfg));
+                if (n < 1) return fail(ctx, MUSER_CUDA_ERROR, "no cluster of two CTAs of the paired NVFP4 GEMM fits on this device");
+                slot = n;
+            }
+            cached = slot;
+        }
+        const uint32_t pair_tiles = g.n_tiles * ((m_blocks + 1) / 2);
+        const uint32_t pairs = std::min<uint32_t>(pair_tiles, std::min<uint32_t>((uint32_t)cached, (uint32_t)ctx->sm_count / 2));
+        cfg.gridDim = dim3(2 * pairs);
+        // every CTA of a pair fetches 128 weight rows per slab: the maps with 128-row boxes, in both forms
+        const CUtensorMap &half = *reinterpret_cast<const CUtensorMap *>(w->tmap_half);
+        const CUtensorMap &half_up = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : half;
+        if (w_up)
+            MUSER_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<true, false>, map_a, half, half_up, g));
+        else if (tail)
+            MUSER_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<false, true>, map_a, half, half_up, g));
+        else
+            MUSER_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<false, false>, map_a, half, half_up, g));
+        return MUSER_CUDA_OK;
+    }
+    const uint32_t tiles = g.n_tiles * m_blocks;
+    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     // (the attribute is per device: set where the launch happens, with the launching context's device current)
     const void *kfn = w_up ? reinterpret_cast<const void *>(nvfp4_gemm_kernel<true, false>)
                       : tail ? reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, true>)

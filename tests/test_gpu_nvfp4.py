@@ -171,6 +171,49 @@ def test_fused_gate_up_silu_matches_cpu_lane(gpu, n_out, n_in, tokens):
     assert e.value.status_name == "BAD_ARG"
 
 
+@pytest.mark.parametrize("n_out,n_in,tokens", [(256, 256, 256), (256, 256, 128), (300, 1024, 130), (512, 2048, 300),
+                                               (768, 1088, 1024), (1000, 512, 640)])
+def test_paired_sm_gemm_equals_the_single_sm_gemm(gpu, n_out, n_in, tokens):
+    """The cta_group::2 form (pairs of SMs on 256-token tiles) adds the same products in the same order as the
+    single-CTA form, so every output must carry the same bits; both are checked against the CPU lane as well.
+    Covers a follower CTA without tokens (128, 130), an odd block count (300, 640), ragged K (1088 = 4.25 slabs),
+    rows that do not fill a tile (300, 1000), the fused gate/up form, the LM-head tail, and residual + row scale."""
+    from muser_b200 import synth
+    from muser_b200._lib import TUNE_NVFP4_PAIR
+    op, ctx, k = gpu
+    packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 3, negative_scales=True)
+    up, us, u2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 4)
+    x = synth.normal_activations(tokens, n_in, seed=12)
+    isi = synth.activation_input_scale_inv(x)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi))
+    wu = op.Weight(ctx, op.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi))
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    rs = torch.linspace(0.5, 1.5, tokens, device="cuda")
+    res = torch.randn((tokens, n_out), device="cuda")
+    out = {}
+    try:
+        for mode in (1, 2):
+            ctx.tuning_set(TUNE_NVFP4_PAIR, mode)
+            ys = [torch.full((tokens, n_out), float("nan"), dtype=dt, device="cuda")
+                  for dt in (torch.float32, torch.float16, torch.bfloat16, torch.float32, torch.float32, torch.float32)]
+            k.encode_nvfp4_prequant(w, xp, xs, ys[0], tokens)
+            k.encode_nvfp4_prequant(w, xp, xs, ys[1], tokens)
+            k.encode_nvfp4_prequant(w, xp, xs, ys[2], tokens, row_scale=rs)
+            k.encode_nvfp4_prequant(w, xp, xs, ys[3], tokens, row_scale=rs, residual=res)
+            k.encode_nvfp4_matmul(w, x.cuda(), ys[4], tokens, out_scale=3.0, softcap=30.0)
+            k.encode_nvfp4_ffn_gate_up_silu_prequant(w, wu, xp, xs, ys[5], tokens)
+            ctx.sync_status()
+            out[mode] = [y.cpu() for y in ys]
+    finally:
+        ctx.tuning_set(TUNE_NVFP4_PAIR, 0)
+    for i, (a, b) in enumerate(zip(out[1], out[2])):
+        assert torch.equal(a.view(torch.int32 if a.dtype == torch.float32 else torch.int16),
+                           b.view(torch.int32 if b.dtype == torch.float32 else torch.int16)), f"output {i} differs between the two kernels"
+    ow = O.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi)
+    _, ref_f32 = O.matmul(ow, x.float().numpy(), threads=O.host_threads(), return_pre_round=True)
+    assert H.rel_l2(out[2][0].numpy(), ref_f32) <= REL_L2_TOL
+
+
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 def test_fused_input_rmsnorm(gpu, x_dtype):
     """rms_norm_mul (reference.rs:59-80) fused into the activation quantizer.  The block adds the squares as a tree
