@@ -135,7 +135,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: from its cost model) */
 #define MUSER_TUNE_DECODE_WSPLIT 12u      /* decode kernel: warps of a CTA that share one row tile and split K between them (0: from its cost model) */
 #define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 262144; 0: always NCCL) */
-#define MUSER_TUNE_NVFP4_PAIR 13u         /* NVFP4 GEMM on pairs of SMs (256-token tiles): 0 by token count (default), 1 never, 2 always */
+#define MUSER_TUNE_NVFP4_PAIR 13u         /* NVFP4 GEMM: 0 one CTA per 128-token tile (default), 1 pairs of SMs on 256-token tiles (tcgen05 cta_group::2) */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file

@@ -37,7 +37,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         obj = objdir / (src.stem + ".o")
         if not force and obj.exists() and obj.stat().st_mtime >= _newest([src] + deps):
             return obj
-        cmd = [nvcc(), *NVCC_FLAGS, "-Xptxas", "-v", "-c", str(src), "-o", str(obj)]
+        extra = os.environ.get("MUSER_CUDA_NVCC_EXTRA", "").split()  # e.g. -DMUSER_GEMM_WAIT_PROFILE for a development build
+        cmd = [nvcc(), *NVCC_FLAGS, *extra, "-Xptxas", "-v", "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         (objdir / (src.stem + ".ptxas.log")).write_text(r.stderr)
         if r.returncode != 0:

@@ -298,7 +298,7 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
     case MUSER_TUNE_DECODE_RING: ctx->dec_ring = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_DECODE_WSPLIT: ctx->dec_wsplit = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_NVFP4_PAIR:
-        if (value > 2) return fail(ctx, MUSER_CUDA_BAD_ARG, "MUSER_TUNE_NVFP4_PAIR takes 0 (by token count), 1 (never) or 2 (always)");
+        if (value > 1) return fail(ctx, MUSER_CUDA_BAD_ARG, "MUSER_TUNE_NVFP4_PAIR takes 0 (one CTA per tile) or 1 (pairs of SMs)");
         ctx->nvfp4_pair = value;
         return MUSER_CUDA_OK;
     case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;

@@ -53,7 +53,7 @@ struct Ctx {
     void *arena = nullptr; // device staging of matmul_host_enqueue: bumped per call, rewound by sync_status
     size_t arena_bytes = 0, arena_used = 0;
     void *comm = nullptr;                      // tensor-parallel communicator (collective.cu), or null
-    uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs: 0 by token count, 1 never, 2 always
+    uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs (cta_group::2): 0 off, 1 on
     uint32_t oneshot_max_bytes = 256u << 10;   // all-reduce payloads up to this size take the one-shot peer exchange
     std::string last_error;
 };

@@ -21,6 +21,25 @@
 
 namespace muser {
 
+// Development aid, compiled in only with -DMUSER_GEMM_WAIT_PROFILE: the single-thread roles of the first CTAs add
+// up the SM cycles they spend in each kind of wait, and a debug entry point copies the sums out.
+#ifdef MUSER_GEMM_WAIT_PROFILE
+__device__ unsigned long long g_wait_prof[4 * 8 * 4]; // [cta < 4][role < 8][slot < 4]
+#define PROF_DECL long long prof_t0 = 0, prof_start = clock64(); unsigned long long prof_acc[3] = {0, 0, 0};
+#define PROF_BEGIN prof_t0 = clock64();
+#define PROF_END(i) prof_acc[i] += (unsigned long long)(clock64() - prof_t0);
+#define PROF_FLUSH(role)                                                                              \
+    if (blockIdx.x < 4) {                                                                             \
+        for (int i_ = 0; i_ < 3; ++i_) g_wait_prof[(blockIdx.x * 8 + (role)) * 4 + i_] = prof_acc[i_]; \
+        g_wait_prof[(blockIdx.x * 8 + (role)) * 4 + 3] = (unsigned long long)(clock64() - prof_start); \
+    }
+#else
+#define PROF_DECL
+#define PROF_BEGIN
+#define PROF_END(i)
+#define PROF_FLUSH(role)
+#endif
+
 constexpr int BM = 128, BN = 256, BK = 256;      // tile: tokens x weight rows x values
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK / 2;             // 16 KiB
@@ -178,7 +197,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             uint32_t it = 0, issued = 0; // k slabs issued so far, over all tiles
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
                 const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
@@ -186,7 +205,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
-                    if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
+                    PROF_BEGIN if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     const uint32_t st = base + s * kStageBytes;
                     const uint32_t full = bar_full + 8 * s;
@@ -207,6 +226,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     issued = it + 1;
                 }
             }
+            PROF_FLUSH(0)
             if (!ok) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 101);
@@ -226,17 +246,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             // kind::mxf4nvf4: A and B E2M1 (format 1), K-major, UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, local = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++local) {
                 // the accumulator is free again once the epilogue warps have read the previous tile out of it
                 if (local > 0) {
-                    ok = mbar_wait(bar_acc_empty, (local - 1) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
-                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes;
@@ -244,7 +264,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
                     // the scale factors of this slab were copied into tensor memory by the copier warp
                     const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
-                    ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb) // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
@@ -254,6 +274,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 if (ok) mma_commit(bar_acc_full);
             }
+            PROF_FLUSH(1)
             if (!ok) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 102);
@@ -265,12 +286,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // own: in the MMA thread's instruction stream the twelve copies of a slab took as long as its four MMAs.
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages, buf = it % kSfBufs;
-                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
-                    if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes, sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
@@ -283,6 +304,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     mma_commit(bar_sf_full + 8 * buf);
                 }
             }
+            PROF_FLUSH(2)
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 105);
@@ -291,9 +313,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         // Eight warps: two per 32-lane quarter of the accumulator, one for each half of the tile's output columns.
-        // The MMA warp cannot start the next tile before the last tcgen05.ld of this one (there is room for one
-        // accumulator only), so the read-out is kept short: half the columns per warp, and the next strip's load is
-        // in flight while the current one is scaled and stored.
+        // There is room for one accumulator only, so the MMA warp cannot start the next tile before the last
+        // tcgen05.ld of this one.
         const uint32_t quad = warp & 3;                 // the 32 accumulator lanes this warp may read
         const uint32_t part = (uint32_t)(warp - 2) >> 2; // which half of the output columns
         constexpr uint32_t kOutCols = DUAL ? BN / 2 : BN, kPartCols = kOutCols / 2;
@@ -313,21 +334,22 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
             const bool vec_ok = (g.n_out & 7) == 0;
             const uint32_t lane_base = tmem + ((quad * 32) << 16), col0 = part * kPartCols;
-            uint32_t r[2][32], r_up[DUAL ? 32 : 1];
-            tmem_ld32(lane_base + col0, r[0]);
+            // All of this warp's part of the accumulator goes to registers first (128 values a thread) and the
+            // accumulator is handed back at once: the MMA warp cannot start the next tile before that, so nothing
+            // that touches global memory may sit in between.
+            uint32_t r[4][32];
+#pragma unroll
+            for (uint32_t s = 0; s < 4; ++s) // fused form: strips 0, 1 are gate columns, 2, 3 the same columns of up
+                tmem_ld32(lane_base + col0 + (DUAL ? (s & 1) * 32 + (s >> 1) * kOutCols : 32 * s), r[s]);
+            tmem_ld_wait();
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
 #pragma unroll
             for (uint32_t s = 0; s < kPartCols / 32; ++s) {
                 const uint32_t c0 = col0 + 32 * s;
-                uint32_t(&cur)[32] = r[s & 1];
-                if constexpr (DUAL) tmem_ld32(lane_base + kOutCols + c0, r_up);
-                tmem_ld_wait();
-                if (s + 1 < kPartCols / 32) {
-                    tmem_ld32(lane_base + c0 + 32, r[(s + 1) & 1]); // in flight under this strip's arithmetic and stores
-                } else { // everything this warp needs is in registers: hand the accumulator back
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
-                }
+                uint32_t(&cur)[32] = r[s];
+                uint32_t(&r_up)[32] = r[DUAL ? 2 + s : s];
                 const uint32_t n0 = tile_n * kOutCols + c0;
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
@@ -483,7 +505,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // ---------------------------------------------------------------- producer (both CTAs)
         if (lane == 0) {
             uint32_t it = 0, issued = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
                 const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
                 const uint32_t m_block = 2 * tile_m + rank;
@@ -498,7 +520,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const int b_row = DUAL ? (int)(tile_n * (BN / 2)) : (int)(tile_n * BN + rank * (BN / 2));
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    if (round > 0) ok = mbar_wait_pair(bar_empty + 8 * s, (round - 1) & 1, abort_flag);
+                    PROF_BEGIN if (round > 0) ok = mbar_wait_pair(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     const uint32_t st = base + s * kPStageBytes;
                     const uint32_t full = bar_full + 8 * s;
@@ -512,6 +534,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     issued = it + 1;
                 }
             }
+            PROF_FLUSH(0)
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 111);
@@ -528,22 +551,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
             const uint32_t peer_empty = map_to_rank(bar_empty, 1), peer_acc_full = map_to_rank(bar_acc_full, 1);
             uint32_t it = 0, local = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs, ++local) {
                 if (local > 0) {
-                    ok = mbar_wait_pair(bar_acc_empty, (local - 1) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait_pair(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     const uint32_t st = base + s * kPStageBytes;
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
                     const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
-                    ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb)
@@ -557,6 +580,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     pair_commit(peer_acc_full);
                 }
             }
+            PROF_FLUSH(1)
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 112);
@@ -565,15 +589,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // ---------------------------------------------------------------- follower: "my stage has landed"
             const uint32_t leader_full = map_to_rank(bar_full, 0);
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     mbar_arrive_cluster(leader_full + 8 * s);
                 }
             }
+            PROF_FLUSH(3)
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 116);
@@ -583,12 +608,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // ---------------------------------------------------------------- scale copier (leader, for the pair)
         if (lane == 0 && leader) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages, buf = it % kSfBufs;
-                    ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag);
-                    if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag);
+                    PROF_BEGIN ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kPStageBytes, sfa = st + kABytes + kPBBytes, sfb = sfa + kSfaBytes;
@@ -601,6 +626,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     pair_commit(bar_sf_full + 8 * buf);
                 }
             }
+            PROF_FLUSH(2)
             if (!ok) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 115);
@@ -628,21 +654,19 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
             const bool vec_ok = (g.n_out & 7) == 0;
             const uint32_t lane_base = tmem + ((quad * 32) << 16), col0 = part * kPartCols;
-            uint32_t r[2][32], r_up[DUAL ? 32 : 1];
-            tmem_ld32(lane_base + col0, r[0]);
+            uint32_t r[4][32]; // as in the single-CTA kernel: everything to registers, then the accumulator goes back
+#pragma unroll
+            for (uint32_t s = 0; s < 4; ++s)
+                tmem_ld32(lane_base + col0 + (DUAL ? (s & 1) * 32 + (s >> 1) * kOutCols : 32 * s), r[s]);
+            tmem_ld_wait();
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
 #pragma unroll
             for (uint32_t s = 0; s < kPartCols / 32; ++s) {
                 const uint32_t c0 = col0 + 32 * s;
-                uint32_t(&cur)[32] = r[s & 1];
-                if constexpr (DUAL) tmem_ld32(lane_base + kOutCols + c0, r_up);
-                tmem_ld_wait();
-                if (s + 1 < kPartCols / 32) {
-                    tmem_ld32(lane_base + c0 + 32, r[(s + 1) & 1]);
-                } else {
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
-                }
+                uint32_t(&cur)[32] = r[s];
+                uint32_t(&r_up)[32] = r[DUAL ? 2 + s : s];
                 const uint32_t n0 = tile_n * kOutCols + c0;
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
@@ -738,6 +762,11 @@ muser_cuda_status launch_nvfp4_peak(Ctx *ctx, uint32_t iters, double *flops, cud
 }
 
 // ------------------------------------------------------------------------------------------ host side
+#ifdef MUSER_GEMM_WAIT_PROFILE
+extern "C" __attribute__((visibility("default"))) int muser_cuda_debug_wait_profile(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_wait_prof, sizeof(g_wait_prof));
+}
+#endif
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -825,8 +854,10 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
     const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
     const uint32_t m_blocks = (tokens + BM - 1) / BM;
-    // Pairs of SMs on 256-token tiles when the token count fills them (an odd last block wastes half a tile)
-    const bool pair = ctx->nvfp4_pair == 2 || (ctx->nvfp4_pair == 0 && m_blocks >= 2 && (m_blocks % 2 == 0 || m_blocks >= 9));
+    // Pairs of SMs on 256-token tiles are opt-in: the pair halves the operand traffic per SM, but this GEMM is bound
+    // by the scale-factor copies into tensor memory, which a pair does not reduce, and the pair's hand-offs cost more
+    // than its traffic saves (ffn_gate at 2048 tokens: 2.4 against 2.8 PFLOP/s).
+    const bool pair = ctx->nvfp4_pair == 1;
     if (pair) {
         struct PairLimit { int n[3] = {0, 0, 0}; };
         static PerDevice<PairLimit> max_pairs; // co-resident clusters of two, asked once per device and kernel
