@@ -292,6 +292,16 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_static_sync_status(int device, void 
  * done.  Timing it gives the tensor-pipe ceiling that the prefill GEMM's roofline fraction is quoted against. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *ctx, uint32_t iters, double *flops, void *stream);
 
+/* Measurement aid, no counterpart in the reference.  The instruction mix of one 256-value slab of the NVFP4 GEMM's
+ * 128 x 256 tile, issued `iters` times by one thread per SM on resident operands, so that the cost of each part can
+ * be timed alone: mode 0 the slab's four MMAs; 1 its twelve scale-factor copies into tensor memory (tcgen05.cp
+ * 32x128b.warpx4), then the MMAs; 2 (three copies, one MMA) four times; 3 the copies alone; 4 six 128x256b copies
+ * alone; 5 those, then the MMAs; 6 nothing.  load_kib (a multiple of 18, or 0): KiB per iteration that a second
+ * thread streams from the context workspace (L2-resident) into shared memory beside it, as the GEMM's producer does.
+ * random_data: operands and scales are pseudo-random non-zero values instead of zeros.  Enqueues one kernel. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_fp4_pipe_probe(muser_cuda_ctx *ctx, uint32_t mode, uint32_t iters, uint32_t load_kib,
+                                            uint32_t random_data, void *stream);
+
 /* Measurement aid, no counterpart in the reference.  Issue interval of the instruction the K-quant skinny kernel is
  * built on: every SM issues iters x 4 tcgen05.mma kind::f16 (128 rows x n_cols x 16, n_cols in {16,32,64,128,256})
  * back to back on resident operands; returns SM clock cycles per instruction.  Synchronizes the device. */

@@ -175,8 +175,24 @@ def main(argv=None) -> None:
         args.tokens = args.tokens or [32768]
         run_layers(args)
     else:
-        ctx = op.Context(0)
+        ctx = op.Context(0, workspace_bytes=32 << 20)
         print(f"dense block-scaled FP4 tensor peak: {op.fp4_peak_tflops(ctx):.1f} TFLOP/s")
+        # the GEMM's per-slab instruction mix in isolation (one 128 x 256 x 256 slab per iteration and SM)
+        mhz = int(getattr(torch.cuda.get_device_properties(0), "clock_rate", 1965000)) // 1000  # the device's maximum SM clock
+        iters = 20000
+        flops = 2.0 * 128 * 256 * 256 * iters * torch.cuda.get_device_properties(0).multi_processor_count
+        print(f"{'per slab':<58} {'us/kernel':>10} {'ns/slab':>8} {'cycles@' + str(mhz):>11} {'TFLOP/s':>8}")
+        rows = [(0, 0, False, "4 MMAs, zero operands"), (0, 0, True, "4 MMAs, random non-zero codes and scales"),
+                (3, 0, True, "12 scale copies (32x128b.warpx4) alone"), (1, 0, True, "12 scale copies, then 4 MMAs"),
+                (2, 0, True, "(3 scale copies, 1 MMA) x 4"), (4, 0, True, "6 scale copies of 128x256b alone"),
+                (5, 0, True, "6 scale copies of 128x256b, then 4 MMAs"),
+                (6, 54, True, "54 KiB of bulk loads from L2 alone"), (6, 36, True, "36 KiB of bulk loads from L2 alone"),
+                (0, 54, True, "4 MMAs beside 54 KiB of loads"), (0, 36, True, "4 MMAs beside 36 KiB of loads"),
+                (2, 54, True, "(3 copies, 1 MMA) x 4 beside 54 KiB of loads"), (1, 54, True, "12 copies, then 4 MMAs beside 54 KiB of loads")]
+        for mode, kib, rnd, label in rows:
+            us = op.fp4_pipe_probe_us(ctx, mode, iters, kib, rnd)
+            tf = f"{flops / us / 1e6:8.0f}" if mode in (0, 1, 2, 5) else f"{'':>8}"
+            print(f"{label:<58} {us:>10.1f} {us * 1e3 / iters:>8.1f} {us * mhz / iters:>11.0f} {tf}")
         for n in (16, 32, 64, 128, 256):
             print(f"tcgen05.mma kind::f16, 128 x {n:3d} x 16, back to back: {op.f16_mma_cycles(ctx, n):.1f} cycles per instruction")
 

@@ -264,6 +264,7 @@ extern "C" {
     ) -> muser_cuda_status;
     pub fn muser_cuda_static_sync_status(device: c_int, stream: *mut c_void) -> muser_cuda_status;
     pub fn muser_cuda_fp4_peak_probe(ctx: *mut muser_cuda_ctx, iters: u32, flops: *mut f64, stream: *mut c_void) -> muser_cuda_status;
+    pub fn muser_cuda_fp4_pipe_probe(ctx: *mut muser_cuda_ctx, mode: u32, iters: u32, load_kib: u32, random_data: u32, stream: *mut c_void) -> muser_cuda_status;
     pub fn muser_cuda_f16_mma_probe(ctx: *mut muser_cuda_ctx, n_cols: u32, iters: u32, cycles_per_mma: *mut f64) -> muser_cuda_status;
     pub fn muser_cuda_wait_probe(ctx: *mut muser_cuda_ctx, polls: u32, stream: *mut c_void) -> muser_cuda_status;
     pub fn muser_cuda_comm_unique_id(out: *mut u8, out_bytes: usize) -> muser_cuda_status;

@@ -626,6 +626,13 @@ muser_cuda_status muser_cuda_fp4_peak_probe(muser_cuda_ctx *c, uint32_t iters, d
     return launch_nvfp4_peak(ctx, iters, flops, (cudaStream_t)stream);
 }
 
+muser_cuda_status muser_cuda_fp4_pipe_probe(muser_cuda_ctx *c, uint32_t mode, uint32_t iters, uint32_t load_kib, uint32_t random_data, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || iters == 0 || iters > (1u << 20)) return fail(ctx, MUSER_CUDA_BAD_ARG, "bad probe arguments");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_pipe_probe(ctx, mode, iters, load_kib, random_data, (cudaStream_t)stream);
+}
+
 muser_cuda_status muser_cuda_wait_probe(muser_cuda_ctx *c, uint32_t polls, void *stream) {
     Ctx *ctx = reinterpret_cast<Ctx *>(c);
     if (!ctx || polls == 0 || polls > (1u << 16)) return fail(ctx, MUSER_CUDA_BAD_ARG, "polls must be 1..65536");

@@ -187,6 +187,7 @@ muser_cuda_status launch_nvfp4_a16(Ctx *, const Weight *w, const void *x, uint32
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);
 muser_cuda_status launch_f16_mma_probe(Ctx *, uint32_t n_cols, uint32_t iters, double *cycles_per_mma);
 muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);
+muser_cuda_status launch_nvfp4_pipe_probe(Ctx *, uint32_t mode, uint32_t iters, uint32_t load_kib, uint32_t random, cudaStream_t);
 void nvfp4_free_tensor_map(Weight *);
 
 } // namespace muser

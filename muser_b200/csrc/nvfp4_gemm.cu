@@ -753,6 +753,108 @@ __global__ void __launch_bounds__(192, 1) nvfp4_peak_kernel(uint32_t iters, int 
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
 }
 
+// What the tensor pipe and the shared-memory ports do with the GEMM's instruction mix, measured in isolation: one
+// thread per SM issues, per iteration (= one 256-value slab of a 128 x 256 tile), the slab's four MMAs and / or its
+// scale-factor copies in a chosen order, on resident operands; another thread may stream bulk copies from an
+// L2-resident buffer into shared memory beside it, as the GEMM's producer does.
+//   mode 0: 4 MMAs                       mode 1: 12 copies (32x128b.warpx4), then 4 MMAs
+//   mode 2: (3 copies, 1 MMA) x 4         mode 3: 12 copies only
+//   mode 4: 6 copies of 128x256b only     mode 5: 6 copies of 128x256b, then 4 MMAs        mode 6: nothing (loads only)
+constexpr int kProbeLoadRing = 6, kProbeLoadChunk = 18 * 1024;
+constexpr int kProbeSmemBytes = kStageBytes + 16384 + kProbeLoadRing * kProbeLoadChunk + 2048;
+__global__ void __launch_bounds__(192, 1) nvfp4_pipe_probe_kernel(uint32_t mode, uint32_t iters, uint32_t load_chunks, uint32_t random,
+                                                                  const uint8_t *src, uint32_t src_chunks, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t scales = base + kABytes + kBBytes, load_base = base + kStageBytes + 16384;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + kStageBytes + 16384 + kProbeLoadRing * kProbeLoadChunk);
+    const uint32_t bar_done = smem_u32(bars), bar_load = smem_u32(bars + 1);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 1 + kProbeLoadRing);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < (kStageBytes + 16384) / 16; i += blockDim.x) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (random) { // non-zero E2M1 codes; scale bytes 0x30..0x3f (E4M3 0.5 .. 1.9) so that the sums stay finite
+            uint32_t h = (i + 1u) * 2654435761u + blockIdx.x * 40503u;
+            auto next = [&]() { h ^= h << 13; h ^= h >> 17; h ^= h << 5; return h; };
+            v = make_uint4(next(), next(), next(), next());
+            if (16 * i >= (uint32_t)(kABytes + kBBytes)) v.x = (v.x & 0x0f0f0f0fu) | 0x30303030u, v.y = (v.y & 0x0f0f0f0fu) | 0x30303030u, v.z = (v.z & 0x0f0f0f0fu) | 0x30303030u, v.w = (v.w & 0x0f0f0f0fu) | 0x30303030u;
+        }
+        reinterpret_cast<uint4 *>(aligned)[i] = v;
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(bar_done, 1);
+        for (int i = 0; i < kProbeLoadRing; ++i) mbar_init(bar_load + 8 * i, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot, sf = tmem + kSfCol, sf2 = sf + kSfBufCols;
+    if (warp == 1 && lane == 0 && mode != 6) {
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        const uint64_t da = operand_desc(base), db = operand_desc(base + kABytes);
+        auto wide_desc = [&](uint32_t a) { // 128 rows x 32 bytes, the two halves of a row 8 KiB apart
+            return (uint64_t)((a >> 4) & 0x3FFF) | (uint64_t)(8192 >> 4) << 16 | (uint64_t)(128 >> 4) << 32 | (uint64_t)1 << 46;
+        };
+        for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales(sf + 4 * c, scale_desc(scales + 512 * c)); // what the MMAs read
+        for (uint32_t i = 0; i < iters; ++i) {
+            if (mode == 1 || mode == 3)
+                for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales(sf2 + 4 * c, scale_desc(scales + 512 * c));
+            if (mode == 4 || mode == 5)
+                for (uint32_t c = 0; c < 6; ++c) asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(sf2 + 8 * c), "l"(wide_desc(scales + 2048 * (c % 3))) : "memory");
+            if (mode == 2) {
+#pragma unroll
+                for (uint32_t kb = 0; kb < 4; ++kb) {
+                    for (uint32_t c = 0; c < 3; ++c) tmem_cp_scales(sf2 + 4 * (3 * kb + c), scale_desc(scales + 512 * (3 * kb + c)));
+                    mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
+                }
+            } else if (mode == 0 || mode == 1 || mode == 5) {
+#pragma unroll
+                for (uint32_t kb = 0; kb < 4; ++kb) mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
+            }
+        }
+        mma_commit(bar_done);
+        if (!mbar_wait(bar_done, 0, abort_flag)) atomicExch(status + 1, 107);
+    }
+    if (warp == 0 && lane == 0 && load_chunks) {
+        uint32_t at = (blockIdx.x * 977u) % src_chunks;
+        for (uint32_t it = 0; it < load_chunks + kProbeLoadRing; ++it) {
+            const uint32_t slot = it % kProbeLoadRing, bar = bar_load + 8 * slot;
+            if (it >= (uint32_t)kProbeLoadRing && !mbar_wait(bar, ((it / kProbeLoadRing) - 1) & 1, abort_flag)) {
+                atomicExch(status + 1, 108);
+                break;
+            }
+            if (it < load_chunks) {
+                mbar_expect_tx(bar, kProbeLoadChunk);
+                bulk_load(load_base + slot * kProbeLoadChunk, src + (size_t)at * kProbeLoadChunk, kProbeLoadChunk, bar);
+                at = (at + 149u) % src_chunks;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
+muser_cuda_status launch_nvfp4_pipe_probe(Ctx *ctx, uint32_t mode, uint32_t iters, uint32_t load_kib, uint32_t random, cudaStream_t stream) {
+    const uint32_t chunks_per_iter = load_kib / 18, src_chunks = (uint32_t)std::min<size_t>(1024, ctx->workspace_bytes / kProbeLoadChunk);
+    if (mode > 6 || load_kib % 18 || (chunks_per_iter && src_chunks < 2))
+        return fail(ctx, MUSER_CUDA_BAD_ARG, "pipe probe: mode 0..6, loads in multiples of 18 KiB, and a context workspace of at least 36 KiB to read them from");
+    MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_pipe_probe_kernel), ctx->device, kProbeSmemBytes));
+    nvfp4_pipe_probe_kernel<<<ctx->sm_count, 192, kProbeSmemBytes, stream>>>(mode, iters, chunks_per_iter * iters, random,
+                                                                            reinterpret_cast<const uint8_t *>(ctx->workspace), src_chunks, ctx->dev_status);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
+}
+
 muser_cuda_status launch_nvfp4_peak(Ctx *ctx, uint32_t iters, double *flops, cudaStream_t stream) {
     MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_peak_kernel), ctx->device, kStageBytes + 2048));
     nvfp4_peak_kernel<<<ctx->sm_count, 192, kStageBytes + 2048, stream>>>(iters, ctx->dev_status);

@@ -305,6 +305,18 @@ def fp4_peak_tflops(ctx: Context, iters: int = 20000, reps: int = 3) -> float:
     return best
 
 
+def fp4_pipe_probe_us(ctx: Context, mode: int, iters: int = 20000, load_kib: int = 0, random_data: bool = False) -> float:
+    """Microseconds of one muser_cuda_fp4_pipe_probe kernel (second of two runs); divide by `iters` for one slab."""
+    for _ in range(2):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.check(_L.muser_cuda_fp4_pipe_probe(ctx._h, mode, iters, load_kib, int(random_data), _stream_ptr(ctx.device)))
+        e1.record()
+        torch.cuda.synchronize()
+    ctx.sync_status()
+    return e0.elapsed_time(e1) * 1e3
+
+
 def f16_mma_cycles(ctx: Context, n_cols: int, iters: int = 2000) -> float:
     """SM cycles per tcgen05.mma kind::f16 (128 x n_cols x 16) issued back to back (muser_cuda_f16_mma_probe)."""
     out = C.c_double()
