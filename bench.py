@@ -38,9 +38,11 @@ TOKEN_COUNTS = (1, 2, 4, 8)
 SKINNY_TOKENS = (8, 16, 32, 64)
 KQ_BYTES_PER_256 = {12: 144, 14: 210}
 
-# DRAM bytes of one step's 16 launches on one GPU (dram__bytes_read.sum + dram__bytes_write.sum over the launches
-# of one step, one ncu pass per launch); None until a capture of the current kernels exists.
-MEASURED_STEP_TRAFFIC_BYTES = None
+# DRAM bytes of one step's 16 launches on one GPU: dram__bytes_read.sum + dram__bytes_write.sum summed over the 160
+# kernel nodes of a ten-step graph replay, divided by ten (ncu, one capture of `bench.py --steps 10 --no-autotune`
+# with the kernels of the commit "Evict-first L2 policy on the weight stream"; the launch plans came from the cost
+# model).  1.005 x the algorithmic bytes: every weight byte crosses the DRAM interface once.
+MEASURED_STEP_TRAFFIC_BYTES = 1260822810
 
 
 def layer_projections():
@@ -185,7 +187,7 @@ def run_gpu(args):
     # weights: seeded N(0, 0.02), quantized on the device, repacked into this rank's shard
     projs = layer_projections()
     tokens_all = sorted(set(TOKEN_COUNTS) | set(SKINNY_TOKENS))
-    layer = workloads.DecodeLayer(ctx, kern, plan, tokens_all, dev, all_reduce=all_reduce)
+    layer = workloads.DecodeLayer(ctx, kern, plan, tokens_all, dev, all_reduce=all_reduce, autotune=not args.no_autotune)
     launches_per_step = layer.launches_per_pass * len(TOKEN_COUNTS)
 
     def step():
@@ -242,7 +244,7 @@ def run_gpu(args):
         # The timed region can be a few milliseconds, less than one nvidia-smi query: the sampler therefore also
         # covers ~0.5 s of the same replays immediately before it (same kernels, same load), all untimed.
         lead = time.time()
-        while time.time() - lead < 0.5:
+        while time.time() - lead < args.lead_seconds:
             for _ in range(10):
                 run_step()
             torch.cuda.synchronize()
@@ -315,7 +317,7 @@ def run_gpu(args):
     # end to end through the host-buffer entry point (weights::matmul's signature, the wait once per step): pinned
     # f32 host x in, f32 host y out, host<->device copies inside the timed region
     e2e = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_e2e:
         hx = {(name, m): synth.normal_activations(m, layer.weights[name].n_in, seed=0, stream=2000).float().pin_memory()
               for name in projs for m in TOKEN_COUNTS}
         hy = {(name, m): torch.empty((m, layer.weights[name].n_out), dtype=torch.float32).pin_memory() for name in projs for m in TOKEN_COUNTS}
@@ -344,7 +346,7 @@ def run_gpu(args):
                "ms_per_step": dt_e2e / e2e_steps * 1e3, "rel_l2_vs_device_call": e2e_check,
                "note": "28 x muser_cuda_matmul_host_enqueue (pinned f32 host x up, projection, f32 y down) + one "
                        "muser_cuda_sync_status per step; wall clock around the steps"}
-    elif rank == 0:
+    elif rank == 0 and world > 1:
         e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
                "note": "not measured at N > 1: the host-buffer entry point runs one rank's shard without the all-reduce"}
 
@@ -531,6 +533,9 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=32768)
     ap.add_argument("--chunks", type=int, default=4, help="token chunks per row-parallel projection in prefill_layers (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels one by one instead of as a CUDA graph")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg through host buffers")
+    ap.add_argument("--no-autotune", action="store_true", help="launch plans from the cost model alone (no measuring at load time)")
+    ap.add_argument("--lead-seconds", type=float, default=0.5, help="untimed replays under the clock sampler right before the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -20,21 +20,17 @@
 #include <new>
 
 #include "common.cuh"
+#include "oneshot_exchange.h"
 
 namespace muser {
 
-constexpr uint32_t kMaxRanks = 8;
-constexpr uint32_t kOneShotMaxBytes = 256u << 10;            // f32 payload per rank and call
-constexpr uint32_t kOneShotMaxElems = kOneShotMaxBytes / 4;
-constexpr uint32_t kOneShotChunkElems = 2048;                // values per CTA
-constexpr uint32_t kOneShotMaxCtas = kOneShotMaxElems / kOneShotChunkElems;
-constexpr uint32_t kOneShotWaitLimit = 1u << 21;             // polls of one value (with a short sleep between) before the wait gives up: about a second
-
-// Layout of one rank's buffer: cell[2 slots][kMaxRanks senders][kOneShotMaxElems] of 8 bytes (value bits, sequence
-// number), then seq[kOneShotMaxCtas] (this rank's own per-CTA sequence numbers).
-constexpr size_t kCellBytes = (size_t)2 * kMaxRanks * kOneShotMaxElems * 8;
-constexpr size_t kSeqBytes = kOneShotMaxCtas * sizeof(uint32_t);
-constexpr size_t kPeerBufBytes = kCellBytes + kSeqBytes;
+// Layout and protocol of the peer buffers: oneshot_exchange.h (shared with the host harness that tests the protocol).
+constexpr uint32_t kMaxRanks = xchg::kMaxRanks;
+constexpr uint32_t kOneShotMaxBytes = xchg::kMaxBytes;
+constexpr uint32_t kOneShotChunkElems = xchg::kChunkElems;
+constexpr uint32_t kOneShotWaitLimit = 1u << 21; // polls of one value (with a short sleep between) before the wait gives up: about a second
+constexpr size_t kCellBytes = xchg::kCellBytes;
+constexpr size_t kPeerBufBytes = xchg::kBufBytes;
 
 struct NcclApi {
     void *lib = nullptr;
@@ -92,58 +88,40 @@ struct OneShotArgs {
 
 // A value travels together with its sequence number in one 8-byte store, which arrives whole or not at all: the
 // receiver needs no fence and no separate flag, it polls the cell until the number is the one it expects.
-__device__ __forceinline__ void st_cell(uint2 *p, uint32_t bits, uint32_t seq) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(seq) : "memory");
-}
-__device__ __forceinline__ uint2 ld_cell(const uint2 *p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
+struct DeviceCells {
+    __device__ __forceinline__ void store(xchg::Cell *p, uint32_t bits, uint32_t seq) {
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(seq) : "memory");
+    }
+    __device__ __forceinline__ xchg::Cell load(const xchg::Cell *p) {
+        xchg::Cell v;
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.bits), "=r"(v.seq) : "l"(p) : "memory");
+        return v;
+    }
+    __device__ __forceinline__ void pause(uint32_t n) {
+        if (n > 32) __nanosleep(100);
+    }
+    __device__ __forceinline__ float get(const float *p) { return *p; }
+    __device__ __forceinline__ void put(float *p, float v) { *p = v; }
+};
 
 // One CTA per 2048 values.  CTA c keeps its own sequence number (in this rank's buffer, bumped once per launch), so
-// the kernel can sit in a CUDA graph: nothing that changes from call to call is a launch argument.  The slot
-// alternates with the sequence number, so a cell still holds the number of two calls ago when a new value is due;
-// a rank can be at most one call ahead of the slowest reader of a slot (it needs that reader's values of the call in
-// between to get there), so two slots suffice.
+// the kernel can sit in a CUDA graph: nothing that changes from call to call is a launch argument.
 __global__ void __launch_bounds__(256) oneshot_all_reduce_kernel(const OneShotArgs a) {
     __shared__ uint32_t seq_s;
     pdl_wait(); // `buf` comes from the kernel before this one; the sequence counter from the all-reduce before it
     const uint32_t c = blockIdx.x, tid = threadIdx.x;
-    uint8_t *mine = a.peer[a.rank];
     if (tid == 0) {
-        uint32_t *seq = reinterpret_cast<uint32_t *>(mine + kCellBytes) + c;
+        uint32_t *seq = reinterpret_cast<uint32_t *>(a.peer[a.rank] + kCellBytes) + c;
         seq_s = *seq + 1;
         *seq = seq_s;
     }
     __syncthreads();
-    const uint32_t seq = seq_s, slot = seq & 1u;
     const uint32_t begin = c * kOneShotChunkElems, end = min(begin + kOneShotChunkElems, a.count);
-    // 1. push this rank's values into every rank's cells of (slot, this rank)
-    const size_t my_cells = ((size_t)slot * kMaxRanks + a.rank) * kOneShotMaxElems;
-    for (uint32_t i = begin + tid; i < end; i += 256) {
-        const uint32_t bits = __float_as_uint(a.buf[i]);
-        for (uint32_t p = 0; p < a.world; ++p) st_cell(reinterpret_cast<uint2 *>(a.peer[p]) + my_cells + i, bits, seq);
-    }
-    // 2. take every rank's value of each element as it lands (bounded) and add them in rank order
-    const uint2 *cells = reinterpret_cast<const uint2 *>(mine) + (size_t)slot * kMaxRanks * kOneShotMaxElems;
-    for (uint32_t i = begin + tid; i < end; i += 256) {
-        float sum = 0.0f;
-        for (uint32_t p = 0; p < a.world; ++p) {
-            const uint2 *cell = cells + (size_t)p * kOneShotMaxElems + i;
-            uint2 v = ld_cell(cell);
-            for (uint32_t n = 0; v.y != seq && n < kOneShotWaitLimit; ++n) {
-                if (n > 32) __nanosleep(100);
-                v = ld_cell(cell);
-            }
-            if (v.y != seq) { // this thread stops here: its remaining outputs keep the rank's own partial sums
-                atomicExch(a.status + 1, 401);
-                return;
-            }
-            sum += __uint_as_float(v.x);
-        }
-        a.buf[i] = sum;
-    }
+    DeviceCells mem;
+    // a thread that gives up stops there: its remaining outputs keep the rank's own partial sums
+    if (xchg::exchange_elements(mem, reinterpret_cast<xchg::Cell *const *>(a.peer), a.rank, a.world, seq_s, a.buf, begin, end, tid, 256,
+                                kOneShotWaitLimit) != 0)
+        atomicExch(a.status + 1, xchg::kGaveUp);
 }
 
 static muser_cuda_status nccl_fail(Ctx *ctx, Comm *cm, const char *what, ncclResult_t r) {

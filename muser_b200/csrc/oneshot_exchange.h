@@ -1,0 +1,78 @@
+// The one-shot all-reduce's exchange protocol, written once for the GPU kernel (collective.cu) and for a host
+// harness in which the ranks are CPU threads (tests/exchange_harness.cpp), so that the protocol's logic (slots,
+// sequence numbers, rank-order sums, what a rank does when a peer never shows up) is tested without a GPU.
+//
+// Every rank owns a buffer of cells[2 slots][kMaxRanks senders][kMaxElems]; a cell is 8 bytes, the value's bits and
+// the sequence number of the call that sent it, written by ONE store and therefore seen whole or not at all.  A call:
+//   1. push: this rank stores (value, seq) into cell (seq & 1, this rank, i) of EVERY rank's buffer;
+//   2. gather: for each element it polls its own buffer's cells of all senders until they carry `seq` (bounded),
+//      adds the values in rank order (identical bits on every rank), and writes the sum back.
+// The slot alternates with the sequence number: a cell still holds the number of two calls ago when a new value is
+// due.  A rank can run at most one call ahead of the slowest reader of a slot (to get further it needs that reader's
+// values of the call in between), so two slots are enough.  When a wait gives up, the element and all later
+// elements of that caller keep this rank's own partial sums and the call returns kGaveUp: no stale or half-summed
+// value is ever written.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define MUSER_XCHG __device__ __forceinline__
+#else
+#define MUSER_XCHG static inline
+#endif
+
+namespace muser {
+namespace xchg {
+
+constexpr uint32_t kMaxRanks = 8;
+constexpr uint32_t kMaxBytes = 256u << 10;        // f32 payload per rank and call
+constexpr uint32_t kMaxElems = kMaxBytes / 4;
+constexpr uint32_t kChunkElems = 2048;            // values per CTA; each chunk has its own sequence counter
+constexpr uint32_t kMaxChunks = kMaxElems / kChunkElems;
+constexpr int kGaveUp = 401;
+
+struct Cell {
+    uint32_t bits, seq;
+};
+
+constexpr size_t kCellBytes = (size_t)2 * kMaxRanks * kMaxElems * sizeof(Cell);
+constexpr size_t kSeqBytes = kMaxChunks * sizeof(uint32_t); // this rank's own per-chunk sequence numbers, behind the cells
+constexpr size_t kBufBytes = kCellBytes + kSeqBytes;
+
+MUSER_XCHG size_t cell_index(uint32_t slot, uint32_t sender, uint32_t i) { return ((size_t)slot * kMaxRanks + sender) * kMaxElems + i; }
+
+// Mem supplies: void store(Cell *, uint32_t bits, uint32_t seq); Cell load(const Cell *); void pause(uint32_t polls_so_far);
+// float get(const float *); void put(float *, float)  (how the payload itself is read and written).
+// Elements first, first + stride, ... of [begin, end) are this caller's.
+template <class Mem>
+MUSER_XCHG int exchange_elements(Mem &mem, Cell *const *peer, uint32_t rank, uint32_t world, uint32_t seq, float *buf, uint32_t begin,
+                                 uint32_t end, uint32_t first, uint32_t stride, uint32_t wait_limit) {
+    const uint32_t slot = seq & 1u;
+    for (uint32_t i = begin + first; i < end; i += stride) {
+        union { float f; uint32_t u; } v;
+        v.f = mem.get(buf + i);
+        for (uint32_t p = 0; p < world; ++p) mem.store(peer[p] + cell_index(slot, rank, i), v.u, seq);
+    }
+    const Cell *mine = peer[rank];
+    for (uint32_t i = begin + first; i < end; i += stride) {
+        float sum = 0.0f;
+        for (uint32_t p = 0; p < world; ++p) {
+            const Cell *cell = mine + cell_index(slot, p, i);
+            Cell c = mem.load(cell);
+            for (uint32_t n = 0; c.seq != seq && n < wait_limit; ++n) {
+                mem.pause(n);
+                c = mem.load(cell);
+            }
+            if (c.seq != seq) return kGaveUp;
+            union { float f; uint32_t u; } v;
+            v.u = c.bits;
+            sum += v.f;
+        }
+        mem.put(buf + i, sum);
+    }
+    return 0;
+}
+
+} // namespace xchg
+} // namespace muser

@@ -137,3 +137,32 @@ def test_misuse_on_k_shards_is_refused():
     k.encode_quantized_matmul(w, x, y, 1, out_scale=0.5)  # a plain scale is linear and stays allowed
     w.free()
     ctx.close()
+
+
+def test_image_hash_is_deterministic_and_tells_shards_apart():
+    """Repacking is deterministic: two repacks of one tensor (host and device source, two contexts) carry the same
+    64-bit image digest; another tensor, another dtype and each tensor-parallel shard carry different ones."""
+    from muser_b200 import operator as op
+    from muser_b200 import synth
+    from muser_b200._lib import NVFP4, SHARD_K, SHARD_ROWS
+    ctx_a, ctx_b = op.Context(0, workspace_bytes=1 << 20), op.Context(0, workspace_bytes=1 << 20)
+    try:
+        raw, ow = _kquant_case(O.Q4_K, 512, 8, 21)
+        view = op.TensorView(raw, O.Q4_K, ow.n_in, ow.n_out)
+        h = [op.Weight(ctx_a, view).info().image_hash, op.Weight(ctx_b, view).info().image_hash,
+             op.Weight(ctx_a, op.TensorView(torch.from_numpy(raw).cuda(), O.Q4_K, ow.n_in, ow.n_out)).info().image_hash]
+        assert h[0] == h[1] == h[2] and h[0] != 0
+        other, _ = _kquant_case(O.Q4_K, 512, 8, 22)
+        assert op.Weight(ctx_a, op.TensorView(other, O.Q4_K, ow.n_in, ow.n_out)).info().image_hash != h[0]
+        shards = {op.Weight(ctx_a, view, shard=(r, 2, axis)).info().image_hash for r in (0, 1) for axis in (SHARD_ROWS, SHARD_K)}
+        assert len(shards) == 4 and h[0] not in shards
+        raw6, ow6 = _kquant_case(O.Q6_K, 512, 8, 21)
+        assert op.Weight(ctx_a, op.TensorView(raw6, O.Q6_K, ow6.n_in, ow6.n_out)).info().image_hash != h[0]
+        wp, ws, s2 = synth.nvfp4_weight(synth.normal_weights(256, 512, seed=0, stream=1))
+        n1 = op.Weight(ctx_a, op.TensorView(wp, NVFP4, 512, 256, ws, s2, 4.0)).info().image_hash
+        n2 = op.Weight(ctx_b, op.TensorView(wp, NVFP4, 512, 256, ws, s2, 4.0)).info().image_hash
+        n3 = op.Weight(ctx_a, op.TensorView(wp, NVFP4, 512, 256, ws, s2, 4.0), shard=(1, 2, SHARD_ROWS)).info().image_hash
+        assert n1 == n2 and n1 != n3
+    finally:
+        ctx_a.close()
+        ctx_b.close()
