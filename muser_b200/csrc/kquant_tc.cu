@@ -597,8 +597,9 @@ template <bool XF32>
 __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__restrict__ x, uint32_t tokens, uint32_t n_in, uint32_t k_off,
                                                                 uint32_t nsb, __half *__restrict__ xh, __half *__restrict__ xs) {
     // Output row = token.  bf16 activations inside f16's range (2^-14 <= |x| <= 65504, which covers normalized
-    // hidden states) are exact in f16; larger magnitudes are clamped to 65504 and smaller ones lose bits, so for such
-    // inputs this kernel's result differs from the exact kernels that serve lower token counts.  f32 activations
+    // hidden states) are exact in f16; larger magnitudes are clamped to 65504 and smaller ones lose bits: the range
+    // limit of this kernel (the decode kernel, which serves up to 16 tokens, scales every tile by its own maximum
+    // and has none).  f32 activations
     // are carried (to 22 bits, same range) as an f16 head in row 2t and the remainder in row 2t + 1; the kernel
     // adds the two columns at the end.
     const uint32_t tile = blockIdx.x, r = blockIdx.y, i = threadIdx.x;

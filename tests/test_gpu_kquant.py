@@ -86,6 +86,43 @@ def test_matmul_matches_cpu_lane(gpu, dtype, x_dtype):
         w.free()
 
 
+@pytest.mark.parametrize("dtype", [O.Q4_K, O.Q6_K])
+def test_activations_beyond_the_f16_range(gpu, dtype):
+    """bf16 and f32 activations can exceed f16's range (|x| > 65504).  The decode kernel (up to 16 tokens, and longer
+    batches on weights below the tcgen05 kernel's row threshold) scales every 256-input tile by its own maximum, so
+    such inputs cost nothing; the tcgen05 kernel (17-64 tokens) takes activations as f16 and clamps them: the stated
+    range limit of that kernel, checked here so that it stays a clamp and never becomes inf or NaN."""
+    from muser_b200._lib import TUNE_TC_MIN_ROWS
+    op, ctx, k = gpu
+    n_in, n_out = 1024, 1100
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=71 + dtype)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    ow = O.TensorView(raw, dtype, n_in, n_out)
+    for x_dtype in (torch.bfloat16, torch.float32):
+        for tokens in (1, 4, 16, 24):
+            x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=9 + tokens).reshape(tokens, n_in)).clone()
+            x[0, 5], x[tokens - 1, 700], x[0, 300] = 3.0e5, -1.0e6, 7.0e4
+            x = x.to(x_dtype)
+            want = O.matmul(ow, x.float().numpy(), threads=4)
+            y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+            try:
+                ctx.tuning_set(TUNE_TC_MIN_ROWS, 1 << 30)  # every token count through the decode kernel
+                k.encode_quantized_matmul(w, x.cuda(), y, tokens)
+                ctx.sync_status()
+            finally:
+                ctx.tuning_set(TUNE_TC_MIN_ROWS, 1024)
+            assert H.rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL, (x_dtype, tokens, H.rel_l2(y.cpu().numpy(), want))
+        # the tcgen05 kernel on the same 24 tokens: finite, and equal to the CPU lane on the clamped activations
+        tokens = 24
+        y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+        k.encode_quantized_matmul(w, x.cuda(), y, tokens)
+        ctx.sync_status()
+        assert torch.isfinite(y).all()
+        want_clamped = O.matmul(ow, x.float().clamp(-65504.0, 65504.0).numpy(), threads=4)
+        assert H.rel_l2(y.cpu().numpy(), want_clamped) <= REL_L2_TOL, (x_dtype, H.rel_l2(y.cpu().numpy(), want_clamped))
+    w.free()
+
+
 def test_epilogue_row_scale_residual_and_bf16_output(gpu):
     op, ctx, k = gpu
     raw = H.lcg_weights(O.Q4_K, 37, 2, seed=3)
