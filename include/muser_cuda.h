@@ -214,6 +214,21 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx
                                                    const uint32_t *rows, uint32_t n_rows, const void *x, uint32_t x_dtype,
                                                    float *y, uint32_t tokens, void *stream);
 
+/* The LM head with the greedy pick fused in: logits = matmul(output.weight, x), times out_scale, tanh softcap
+ * (src/reference.rs:559-570, through `epilogue`, which may also carry the final norm and a row scale), then per token the
+ * index of the FIRST maximum (src/api.rs:1842-1850; on the GPU the two-phase reduction of
+ * shaders/ferrite/argmax_f32.metal, which keeps the lower index among equal values).  The pick happens in the
+ * projection kernel's epilogue: every finishing warp raises a per-token 64-bit key (ordered value bits, inverted row)
+ * with an atomic max, so the 202048-row logits never have to be written or read again.  logits: [tokens][n_out] in
+ * logits_dtype (F32 or BF16), or NULL when only the pick is wanted.  out_index: [tokens] u32 on the device; out_value
+ * (the winning logit, f32) and out_nonfinite (1 where some logit of the token was NaN or infinite, the condition the
+ * reference refuses with NonfiniteLogits, src/api.rs:1856-1861) may be NULL.  A NaN never wins; a token whose logits are
+ * all NaN yields index 0.  K-quant weights (the real model's LM head is Q5_K), unsharded, 1 <= tokens <= 16. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_lm_head_argmax(muser_cuda_ctx *ctx, const muser_cuda_weight *w, const void *x,
+                                            uint32_t x_dtype, uint32_t tokens, const muser_cuda_epilogue *epilogue,
+                                            void *logits, uint32_t logits_dtype, uint32_t *out_index, float *out_value,
+                                            uint32_t *out_nonfinite, void *stream);
+
 /* MetalKernels::encode_ffn_q4k_gate_up_silu_4r2s (src/metal/encode/ffn.rs:10-19) and the CPU lane's
  * silu_fast(gate) * up (src/reference.rs:511-513, quant/helpers.rs:72):
  * y[t][j] = silu(Wgate_j . x_t) * (Wup_j . x_t), x read once, the two projections never written out.

@@ -4,6 +4,7 @@ algorithmic bytes, TMAC/s, and (with --check) the differential against the CPU l
 
     python microbench.py kquant --proj ffn_gate,ffn_down --tokens 1,2,4,8 [--check] [--no-graph]
     python microbench.py groups --tokens 1,2,4,8          (the decode step's four launches: q|k|v, o, gate|up, down)
+    python microbench.py lmhead --tokens 1,4,16           (202048-row Q5_K LM head with the fused greedy pick)
     python microbench.py nvfp4  --proj ffn_gate --tokens 2048 [--reps 5]
     python microbench.py peak
     python microbench.py layers --tokens 32768 --layers 52 [--chunks 4]      (torchrun for TP > 1)
@@ -74,6 +75,29 @@ def run_kquant(args) -> None:
                   f"{nbytes / sec / 1e9 / HBM_PEAK_GBS * 100:>6.1f} {2 * m * n * k / sec / 1e12:>8.2f} {rel:>10.2e}", flush=True)
         for w in ws:
             w.free()
+
+
+def run_lmhead(args) -> None:
+    """The LM head of the real model's geometry (202048 rows x 5120, Q5_K: crates/muser-bench/src/m16.rs:195-201) with
+    the greedy pick fused in, against the plain projection that writes the logits."""
+    ctx = op.Context(0)
+    kern = op.CudaKernels(ctx)
+    n, k, dt = 202048, 5120, 13  # GgmlType::Q5_K
+    raw = torch.cat([synth.quantize_kquant(synth.normal_weights(n // 8, k, seed=0, stream=90 + i, device="cuda"), dt) for i in range(8)])
+    w = op.Weight(ctx, op.TensorView(raw, dt, k, n))
+    nbytes_w = raw.numel()
+    del raw
+    print(f"{'LM head 5120->202048 Q5_K':<28} {'tokens':>6} {'pick us':>9} {'GB/s':>9} {'%HBM':>6} {'logits us':>10} {'same pick':>10}")
+    for m in args.tokens:
+        x = synth.normal_activations(m, k, device="cuda")
+        y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        res = {}
+        t_pick = _time(lambda: res.__setitem__("r", kern.encode_lm_head_argmax(w, x, m, out_scale=0.5, softcap=30.0)), args.reps)
+        t_full = _time(lambda: kern.encode_quantized_matmul(w, x, y, m, out_scale=0.5, softcap=30.0), args.reps)
+        same = bool(torch.equal(res["r"][0].long(), torch.argmax(y, dim=1)))
+        nbytes = nbytes_w + m * k * 2
+        print(f"{'':<28} {m:>6} {t_pick * 1e6:>9.1f} {nbytes / t_pick / 1e9:>9.1f} {nbytes / t_pick / 1e9 / HBM_PEAK_GBS * 100:>6.1f} {t_full * 1e6:>10.1f} {str(same):>10}", flush=True)
+    ctx.sync_status()
 
 
 def run_nvfp4(args) -> None:
@@ -153,7 +177,7 @@ def run_layers(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["kquant", "groups", "nvfp4", "peak", "layers"])
+    ap.add_argument("what", choices=["kquant", "groups", "lmhead", "nvfp4", "peak", "layers"])
     ap.add_argument("--layers", type=int, default=52)
     ap.add_argument("--chunks", type=int, default=4, help="token chunks per row-parallel projection (TP > 1)")
     ap.add_argument("--proj", type=lambda s: s.split(","), default=list(synth.LAYER_PROJECTIONS))
@@ -168,6 +192,9 @@ def main(argv=None) -> None:
     elif args.what == "groups":
         args.tokens = args.tokens or [1, 2, 4, 8]
         run_groups(args)
+    elif args.what == "lmhead":
+        args.tokens = args.tokens or [1, 2, 4, 8, 16]
+        run_lmhead(args)
     elif args.what == "nvfp4":
         args.tokens = args.tokens or [2048]
         run_nvfp4(args)

@@ -183,6 +183,20 @@ extern "C" {
         tokens: u32,
         stream: *mut c_void,
     ) -> muser_cuda_status;
+    pub fn muser_cuda_lm_head_argmax(
+        ctx: *mut muser_cuda_ctx,
+        w: *const muser_cuda_weight,
+        x: *const c_void,
+        x_dtype: u32,
+        tokens: u32,
+        epilogue: *const muser_cuda_epilogue,
+        logits: *mut c_void,
+        logits_dtype: u32,
+        out_index: *mut u32,
+        out_value: *mut f32,
+        out_nonfinite: *mut u32,
+        stream: *mut c_void,
+    ) -> muser_cuda_status;
     pub fn muser_cuda_ffn_gate_up_silu(
         ctx: *mut muser_cuda_ctx,
         w_gate: *const muser_cuda_weight,

@@ -234,6 +234,10 @@ muser_cuda_status muser_cuda_ctx_create(int device, size_t workspace_bytes, muse
     if (e == cudaSuccess) e = cudaMalloc(&ctx->tc_scratch, ctx->tc_scratch_bytes);
     ctx->norm_scratch_bytes = (size_t)64 * 32768 * sizeof(float); // 64 tokens x the widest row
     if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_scratch, ctx->norm_scratch_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->amax_keys, 16 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(ctx->amax_keys, 0, 16 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->amax_flags, 16 * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->amax_flags, 0, 16 * sizeof(unsigned int));
     ctx->inv_rms_rows = 1u << 20; // token rows per call of a fused input norm
     if (e == cudaSuccess) e = cudaMalloc(&ctx->inv_rms, (size_t)ctx->inv_rms_rows * sizeof(float));
     if (e == cudaSuccess && workspace_bytes) e = cudaMalloc(&ctx->workspace, workspace_bytes);
@@ -258,6 +262,8 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->norm_scratch);
     cudaFree(ctx->inv_rms);
+    cudaFree(ctx->amax_keys);
+    cudaFree(ctx->amax_flags);
     cudaFree(ctx->tc_scratch);
     cudaFree(ctx->dev_stage);
     cudaFree(ctx->arena);
@@ -456,6 +462,28 @@ muser_cuda_status muser_cuda_quantized_matmul_rows(muser_cuda_ctx *c, const muse
     if (!is_kquant(w->dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "matmul_rows takes K-quant weights");
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_kquant_rows(ctx, w, rows, n_rows, x, x_dtype, y, tokens, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_lm_head_argmax(muser_cuda_ctx *c, const muser_cuda_weight *wp, const void *x, uint32_t x_dtype,
+                                            uint32_t tokens, const muser_cuda_epilogue *ep, void *logits, uint32_t logits_dtype,
+                                            uint32_t *out_index, float *out_value, uint32_t *out_nonfinite, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *w = reinterpret_cast<const Weight *>(wp);
+    if (!out_index) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    muser_cuda_status st = check_io(ctx, w, x, x_dtype, logits ? logits : x, logits ? logits_dtype : MUSER_DTYPE_F32, tokens, false);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!is_kquant(w->dtype)) return fail(ctx, MUSER_CUDA_UNSUPPORTED_DTYPE, "lm_head_argmax takes K-quant weights");
+    if (tokens > 16) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "lm_head_argmax serves 1..16 tokens per call");
+    if (w->shard.world > 1) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the greedy pick needs the whole vocabulary: unsharded weights only");
+    if (ep && (ep->swiglu || ep->residual)) return fail(ctx, MUSER_CUDA_BAD_ARG, "lm_head_argmax takes the input norm, row scale, logit scale and softcap only");
+    Epilogue e;
+    st = take_epilogue(ctx, w, ep, &e);
+    if (st != MUSER_CUDA_OK) return st;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const cudaError_t de = launch_lm_head_argmax(ctx, w, x, x_dtype, logits, logits_dtype, tokens, e, out_index, out_value, out_nonfinite, (cudaStream_t)stream);
+    if (de == cudaErrorNotSupported) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "this weight's geometry does not fit the decode kernel");
+    MUSER_CUDA_TRY(ctx, de);
+    return MUSER_CUDA_OK;
 }
 
 // The NVFP4 side of the fused gate/up call: both weights must quantize their input alike, because one set of

@@ -53,6 +53,8 @@ struct Ctx {
     void *arena = nullptr; // device staging of matmul_host_enqueue: bumped per call, rewound by sync_status
     size_t arena_bytes = 0, arena_used = 0;
     void *comm = nullptr;                      // tensor-parallel communicator (collective.cu), or null
+    unsigned long long *amax_keys = nullptr;   // fused greedy pick: one key and one flag word per token (16 each), zero between calls
+    unsigned int *amax_flags = nullptr;
     uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs (cta_group::2): 0 off, 1 on
     uint32_t oneshot_max_bytes = 256u << 10;   // all-reduce payloads up to this size take the one-shot peer exchange
     std::string last_error;
@@ -173,7 +175,10 @@ cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_d
 muser_cuda_status decode_autotune(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, uint32_t max_tokens, cudaStream_t);
 cudaError_t launch_kquant_decode(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
-                                 const Epilogue *ep, cudaStream_t);
+                                 const Epilogue *ep, cudaStream_t, unsigned long long *amax_keys = nullptr, unsigned int *amax_flags = nullptr);
+cudaError_t launch_lm_head_argmax(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *logits, uint32_t logits_dtype,
+                                  uint32_t tokens, const Epilogue &ep, uint32_t *out_index, float *out_value, uint32_t *out_nonfinite,
+                                  cudaStream_t);
 muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
                                         float input_scale_inv, uint8_t *packed, uint8_t *scales, cudaStream_t,
                                         const float *norm_weight = nullptr, float norm_eps = 0.0f);

@@ -50,6 +50,10 @@ struct DecJob {
     uint32_t groups;   // CTAs per K slice
     uint32_t counter0; // first arrival counter of this job (one per row tile)
     uint32_t partial0; // first float of this job's partial sums in the scratch
+    // fused greedy pick (AMAX kernels only): per token one 64-bit key (ordered value bits, ~row) that every finishing
+    // warp raises with an atomic max, and one flag word that records a non-finite output; y may then be null
+    unsigned long long *amax_keys;
+    unsigned int *amax_flags;
 };
 
 struct DecArgs {
@@ -180,7 +184,13 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const bool usable = amax > 0.f && amax < 3.0e38f; // an all-zero or non-finite tile contributes nothing
+        bool nan = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) nan = nan || v[i] != v[i];
+        // an all-zero tile contributes nothing; a tile with a NaN or an infinity makes every output of its token NaN
+        // (its integers are zero and its scale is NaN), as such inputs do on the CPU lane
+        const bool poisoned = __any_sync(0xffffffffu, nan) || !(amax < 3.0e38f);
+        const bool usable = amax > 0.f && !poisoned;
         const float inv = usable ? __fdiv_rn(16383.0f, amax) : 0.f;
         int xi[8], sum = 0;
 #pragma unroll
@@ -197,7 +207,7 @@ __device__ __forceinline__ void stage(const DecArgs &a, uint32_t sb_first, uint3
                 lo |= (uint32_t)(xi[e[b]] & 127) << (8 * b);
             }
         };
-        const float sx = usable ? __fdiv_rn(amax, 16383.0f) : 0.f;
+        const float sx = usable ? __fdiv_rn(amax, 16383.0f) : poisoned ? __uint_as_float(0x7FC00000u) : 0.f;
         uint32_t *mrow = mw + (size_t)(tile * TOK + tok) * (kMetaU4 * 4);
         uint32_t *fbase = fw + (size_t)(tile * NG + gp) * (kFragU4 * 4);
         if constexpr (DT != MUSER_DTYPE_Q6_K) { // Q4_K and Q5_K: 32-element sub-blocks with a min term
@@ -431,7 +441,17 @@ template <> struct RegsOf<MUSER_DTYPE_Q5_K> { using type = Q5Regs; };
 // tiles through its own ring, and the parts meet in shared memory (named barrier per slot, first warp adds them in
 // part order), which costs a few hundred cycles where the exchange between CTAs through global memory costs
 // microseconds.  Small weights, which need every warp of the GPU to hide HBM latency, are split this way.
-template <int DT, int NG, bool DUAL>
+// Largest first, and among equal values the lowest row first: the scalar first-maximum convention of the reference's
+// greedy pick (crates/muser-engine/src/api.rs:1842-1850, shaders/ferrite/argmax_f32.metal).  A NaN yields key 0 and
+// never wins.
+__device__ __forceinline__ unsigned long long amax_key(float v, uint32_t row) {
+    if (v != v) return 0ull;
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return (unsigned long long)u << 32 | (0xFFFFFFFFu - row);
+}
+
+template <int DT, int NG, bool DUAL, bool AMAX = false>
 __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
     using Regs = typename RegsOf<DT>::type;
     constexpr int kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = 4 * NG;
@@ -581,7 +601,9 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
         }
         if (finish) {
 #pragma unroll
-            for (int gp = 0; gp < NG; ++gp)
+            for (int gp = 0; gp < NG; ++gp) {
+                unsigned long long best = 0ull; // AMAX: this lane's rows g, g + 8 of token 4 * gp + t
+                bool bad = false;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const uint32_t row = rt * 16 + g + 8 * c, tok = 4 * gp + t;
@@ -593,12 +615,33 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
                     r = logit_tail(r, jb.out_scale, jb.softcap);
                     if (jb.y_bf16) {
                         if (jb.residual) r += __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(jb.residual)[o]);
-                        reinterpret_cast<__nv_bfloat16 *>(jb.y)[o] = __float2bfloat16_rn(r);
+                        if (!AMAX || jb.y) reinterpret_cast<__nv_bfloat16 *>(jb.y)[o] = __float2bfloat16_rn(r);
                     } else {
                         if (jb.residual) r += reinterpret_cast<const float *>(jb.residual)[o];
-                        reinterpret_cast<float *>(jb.y)[o] = r;
+                        if (!AMAX || jb.y) reinterpret_cast<float *>(jb.y)[o] = r;
+                    }
+                    if constexpr (AMAX) {
+                        const unsigned long long key = amax_key(r, row);
+                        best = key > best ? key : best;
+                        bad = bad || !(fabsf(r) <= 3.402823466e38f);
                     }
                 }
+                if constexpr (AMAX) {
+                    // the eight lanes that share a token column hold the tile's 16 rows of it: one candidate per token
+                    // and row tile, and an atomic only if it would beat what is there already
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) {
+                        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                        best = other > best ? other : best;
+                    }
+                    const uint32_t bad_lanes = __ballot_sync(0xffffffffu, bad);
+                    const uint32_t tok = 4 * gp + t;
+                    if (g == 0 && tok < a.tokens) {
+                        if (best != 0ull && best > *reinterpret_cast<volatile unsigned long long *>(jb.amax_keys + tok)) atomicMax(jb.amax_keys + tok, best);
+                        if (bad_lanes & (0x11111111u << t)) atomicOr(jb.amax_flags + tok, 1u);
+                    }
+                }
+            }
         }
     }
 }
@@ -627,11 +670,12 @@ __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG))
         if (i < a.n_jobs && blockIdx.x >= a.job[i].cta0) ji = i;
     const DecJob &jb = a.job[ji];
     const uint32_t local = blockIdx.x - jb.cta0, slice = local % a.ksplit, group = local / a.ksplit;
-    if constexpr (FAM == 1) {
-        dec::run<MUSER_DTYPE_Q5_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+    constexpr bool AMAX = FAM >= 2; // FAM 2, 3: FAM 0, 1 with the fused greedy pick over the output rows (the LM head)
+    if constexpr ((FAM & 1) == 1) {
+        dec::run<MUSER_DTYPE_Q5_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
     } else {
-        if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
-        else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL>(a, jb, group, slice, dec_dyn, inv_rms);
+        if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
+        else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
     }
 }
 
@@ -755,7 +799,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
             generation = tt.generation[ctx->device];
         }
         same = same && slot.generation == generation;
-        int fmt = FAM == 1 ? 2 : 0;
+        int fmt = (FAM & 1) == 1 ? 2 : 0;
         uint32_t total_tiles = 0;
         size_t out_floats = 0;
         for (uint32_t i = 0; i < a.n_jobs; ++i) {
@@ -843,7 +887,7 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
 // w_up: the fused gate/up form (one job).  Returns cudaErrorNotSupported when the shape does not fit this kernel.
 cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
-                                 const Epilogue *ep, cudaStream_t stream) {
+                                 const Epilogue *ep, cudaStream_t stream, unsigned long long *amax_keys, unsigned int *amax_flags) {
     if (n_jobs == 0 || n_jobs > (uint32_t)kDecMaxJobs || tokens == 0 || tokens > 16 || w[0]->nsb > 4096) return cudaErrorNotSupported;
     DecArgs a;
     a.n_jobs = n_jobs;
@@ -862,6 +906,7 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
         j.row_tiles = w[i]->row_tiles;
         j.y_bf16 = y_dtype[i] == MUSER_DTYPE_BF16;
         j.cta0 = j.groups = j.counter0 = j.partial0 = 0;
+        j.amax_keys = amax_keys, j.amax_flags = amax_flags;
     }
     for (uint32_t i = n_jobs; i < (uint32_t)kDecMaxJobs; ++i) a.job[i] = a.job[0];
     a.x = x;
@@ -881,6 +926,23 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     uint32_t n_q5 = 0;
     for (uint32_t i = 0; i < n_jobs; ++i) n_q5 += w[i]->dtype == MUSER_DTYPE_Q5_K;
     if (n_q5 != 0 && (n_q5 != n_jobs || w_up)) return cudaErrorNotSupported; // Q5_K jobs run in launches of their own, unfused
+    if (amax_keys) { // the LM head with the fused greedy pick: one projection
+        if (n_jobs != 1 || w_up || !amax_flags) return cudaErrorNotSupported;
+        if (n_q5) {
+            switch (ng) {
+            case 1: return dec_launch<1, false, 3>(a, ctx, forced, stream);
+            case 2: return dec_launch<2, false, 3>(a, ctx, forced, stream);
+            case 3: return dec_launch<3, false, 3>(a, ctx, forced, stream);
+            default: return dec_launch<4, false, 3>(a, ctx, forced, stream);
+            }
+        }
+        switch (ng) {
+        case 1: return dec_launch<1, false, 2>(a, ctx, forced, stream);
+        case 2: return dec_launch<2, false, 2>(a, ctx, forced, stream);
+        case 3: return dec_launch<3, false, 2>(a, ctx, forced, stream);
+        default: return dec_launch<4, false, 2>(a, ctx, forced, stream);
+        }
+    }
     if (n_q5) {
         switch (ng) {
         case 1: return dec_launch<1, false, 1>(a, ctx, forced, stream);
@@ -904,6 +966,33 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     case 3: return dec_launch<3, false, 0>(a, ctx, forced, stream);
     default: return dec_launch<4, false, 0>(a, ctx, forced, stream);
     }
+}
+
+// Keys -> (row index, value, non-finite flag) per token, and the keys go back to zero for the next call.
+__global__ void lm_head_argmax_finalize_kernel(unsigned long long *keys, unsigned int *flags, uint32_t tokens, uint32_t *out_index,
+                                               float *out_value, uint32_t *out_nonfinite) {
+    pdl_wait();
+    const uint32_t t = threadIdx.x;
+    if (t >= tokens) return;
+    const unsigned long long key = keys[t];
+    const unsigned int flag = flags[t];
+    keys[t] = 0ull, flags[t] = 0u;
+    uint32_t u = (uint32_t)(key >> 32);
+    u = (u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u;
+    // no candidate at all (every output NaN): the scalar scan never leaves index 0 (api.rs:1842-1850)
+    out_index[t] = key ? 0xFFFFFFFFu - (uint32_t)key : 0u;
+    if (out_value) out_value[t] = key ? __uint_as_float(u) : __uint_as_float(0x7FC00000u);
+    if (out_nonfinite) out_nonfinite[t] = flag | (key ? 0u : 1u);
+}
+
+cudaError_t launch_lm_head_argmax(Ctx *ctx, const Weight *w, const void *x, uint32_t x_dtype, void *logits, uint32_t logits_dtype,
+                                  uint32_t tokens, const Epilogue &ep, uint32_t *out_index, float *out_value, uint32_t *out_nonfinite,
+                                  cudaStream_t stream) {
+    void *ys[1] = {logits};
+    uint32_t yd[1] = {logits_dtype};
+    const cudaError_t e = launch_kquant_decode(ctx, &w, nullptr, 1, x, x_dtype, ys, yd, tokens, &ep, stream, ctx->amax_keys, ctx->amax_flags);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(lm_head_argmax_finalize_kernel, dim3(1), dim3(32), 0, stream, ctx->amax_keys, ctx->amax_flags, tokens, out_index, out_value, out_nonfinite);
 }
 
 // ------------------------------------------------------------------------------------ measured plans

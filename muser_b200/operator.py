@@ -233,6 +233,23 @@ class CudaKernels:
             output.data_ptr(), tokens, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
+    def encode_lm_head_argmax(self, weights: Weight, input: torch.Tensor, tokens: int, logits: torch.Tensor | None = None,
+                              norm_weight=None, norm_eps=0.0, out_scale=1.0, softcap=0.0):
+        """muser_cuda_lm_head_argmax: the LM head (logit scale and softcap of reference.rs:559-570) with the greedy pick
+        fused into the projection kernel.  Returns (index u32 [tokens], value f32 [tokens], nonfinite u32 [tokens]) on
+        the device; `logits` ([tokens][n_out], f32 or bf16) also receives the full logits when given."""
+        dev = input.device
+        index = torch.empty(tokens, dtype=torch.int32, device=dev)
+        value = torch.empty(tokens, dtype=torch.float32, device=dev)
+        nonfinite = torch.empty(tokens, dtype=torch.int32, device=dev)
+        ep = _epilogue(None, None, norm_weight, norm_eps, out_scale, softcap)
+        self.ctx.check(_L.muser_cuda_lm_head_argmax(
+            self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], tokens, C.byref(ep) if ep else None,
+            logits.data_ptr() if logits is not None else None, _TORCH_DTYPE[logits.dtype] if logits is not None else F32,
+            index.data_ptr(), value.data_ptr(), nonfinite.data_ptr(), _stream_ptr(self.ctx.device)))
+        self.launches += 2
+        return index, value, nonfinite
+
     def encode_ffn_gate_up_silu(self, gate_w: Weight, up_w: Weight, input: torch.Tensor, output: torch.Tensor,
                                 tokens: int, norm_weight=None, norm_eps=0.0) -> None:
         """output[t][j] = silu(gate_j . x_t) * (up_j . x_t); K-quant (tokens <= 16) or NVFP4 weights."""

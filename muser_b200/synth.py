@@ -56,20 +56,17 @@ def _f16_bytes(v: torch.Tensor) -> torch.Tensor:
         torch.tensor([0, 8], device=v.device, dtype=torch.int32)).bitwise_and(0xFF).to(torch.uint8)
 
 
-def quantize_q4_k(w: torch.Tensor) -> torch.Tensor:
-    """[n_out][n_in] f32 -> [n_out][n_in/256*144] u8 of Q4_K super-blocks.
-
-    Block layout as decoded by quant/k_block.rs:16-48: d f16, dmin f16,
-    12 bytes of packed 6-bit (scale, min) pairs, 128 bytes of nibbles where
-    byte 32g+l holds element 64g+l (low) and 64g+32+l (high).
-    """
+def _quantize_q45_k(w: torch.Tensor, bits: int) -> torch.Tensor:
+    """Min/max encoder shared by Q4_K (bits = 4) and Q5_K (bits = 5): per 32-element sub-block a 6-bit scale and a
+    6-bit min against the super-block's f16 d and dmin, `bits`-bit quants."""
     n_out, n_in = w.shape
     assert n_in % 256 == 0
     nb = n_in // 256
+    qmax = float((1 << bits) - 1)
     v = w.reshape(n_out, nb, 8, 32)
     lo = v.amin(-1).clamp_max(0.0)
     hi = v.amax(-1).clamp_min(0.0)
-    scale = (hi - lo) / 15.0
+    scale = (hi - lo) / qmax
     mn = -lo
     d = (scale.amax(-1) / 63.0).to(torch.float16)
     dmin = (mn.amax(-1) / 63.0).to(torch.float16)
@@ -78,17 +75,41 @@ def quantize_q4_k(w: torch.Tensor) -> torch.Tensor:
     m = torch.where(dminf > 0, (mn / dminf.clamp_min(1e-30)).round(), torch.zeros_like(mn)).clamp(0, 63)
     step = (df * sc).unsqueeze(-1)
     q = torch.where(step > 0, ((v + (dminf * m).unsqueeze(-1)) / step.clamp_min(1e-30)).round(), torch.zeros_like(v))
-    q = q.clamp(0, 15).to(torch.uint8)
+    q = q.clamp(0, qmax).to(torch.uint8)
     sc, m = sc.to(torch.uint8), m.to(torch.uint8)
     scales = torch.empty((n_out, nb, 12), dtype=torch.uint8, device=w.device)
     scales[..., 0:4] = sc[..., 0:4] | ((sc[..., 4:8] >> 4) << 6)
     scales[..., 4:8] = m[..., 0:4] | ((m[..., 4:8] >> 4) << 6)
     scales[..., 8:12] = (sc[..., 4:8] & 0x0F) | ((m[..., 4:8] & 0x0F) << 4)
     qg = q.reshape(n_out, nb, 4, 2, 32)
-    qs = (qg[:, :, :, 0, :] | (qg[:, :, :, 1, :] << 4)).reshape(n_out, nb, 128)
-    blocks = torch.cat([_f16_bytes(d.float()), _f16_bytes(dmin.float()), scales, qs], dim=-1)
-    assert blocks.shape[-1] == 144
-    return blocks.reshape(n_out, nb * 144).contiguous()
+    qs = ((qg[:, :, :, 0, :] & 15) | ((qg[:, :, :, 1, :] & 15) << 4)).reshape(n_out, nb, 128)
+    parts = [_f16_bytes(d.float()), _f16_bytes(dmin.float()), scales]
+    if bits == 5:  # qh[l]: bit 2g is the fifth bit of element 64g + l, bit 2g + 1 of element 64g + 32 + l
+        qh = torch.zeros((n_out, nb, 32), dtype=torch.uint8, device=w.device)
+        for g in range(4):
+            qh |= ((qg[:, :, g, 0, :] >> 4) & 1) << (2 * g)
+            qh |= ((qg[:, :, g, 1, :] >> 4) & 1) << (2 * g + 1)
+        parts.append(qh)
+    parts.append(qs)
+    blocks = torch.cat(parts, dim=-1)
+    assert blocks.shape[-1] == (144 if bits == 4 else 176)
+    return blocks.reshape(n_out, nb * blocks.shape[-1]).contiguous()
+
+
+def quantize_q4_k(w: torch.Tensor) -> torch.Tensor:
+    """[n_out][n_in] f32 -> [n_out][n_in/256*144] u8 of Q4_K super-blocks.
+
+    Block layout as decoded by quant/k_block.rs:16-48: d f16, dmin f16,
+    12 bytes of packed 6-bit (scale, min) pairs, 128 bytes of nibbles where
+    byte 32g+l holds element 64g+l (low) and 64g+32+l (high).
+    """
+    return _quantize_q45_k(w, 4)
+
+
+def quantize_q5_k(w: torch.Tensor) -> torch.Tensor:
+    """[n_out][n_in] f32 -> [n_out][n_in/256*176] u8 of Q5_K super-blocks (quant/k_block.rs:61-105): the Q4_K block
+    with a 32-byte plane of fifth bits between the scales and the nibbles."""
+    return _quantize_q45_k(w, 5)
 
 
 def quantize_q6_k(w: torch.Tensor) -> torch.Tensor:
@@ -166,4 +187,4 @@ def activation_input_scale_inv(x: torch.Tensor) -> float:
 
 
 def quantize_kquant(w: torch.Tensor, dtype: int) -> torch.Tensor:
-    return {Q4_K: quantize_q4_k, Q6_K: quantize_q6_k}[dtype](w)
+    return {Q4_K: quantize_q4_k, Q5_K: quantize_q5_k, Q6_K: quantize_q6_k}[dtype](w)

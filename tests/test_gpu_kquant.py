@@ -521,6 +521,71 @@ def test_lm_head_tail_and_selected_rows(gpu, dtype):
     ctx.sync_status()
 
 
+@pytest.mark.parametrize("dtype", [O.Q5_K, O.Q4_K, O.Q6_K])
+def test_lm_head_with_the_greedy_pick_fused_in(gpu, dtype):
+    """muser_cuda_lm_head_argmax: logits through the LM-head tail (reference.rs:559-570), then the index of the first
+    maximum per token (api.rs:1842-1850).  The pick must equal a first-maximum scan of the logits the same call
+    wrote, bit for bit; equal maxima must resolve to the lowest row wherever the rows sit in the grid; the CPU lane's
+    logit at the picked row must be its maximum up to the kernel's error; NaN inputs raise the flag and never win."""
+    op, ctx, k = gpu
+    n_in, n_out = 1024, 20011
+    raw = H.lcg_weights(dtype, n_out, n_in // 256, seed=81 + dtype).copy()
+    scale, cap = 0.37, 30.0
+    ow = O.TensorView(raw, dtype, n_in, n_out)
+    for tokens in (1, 3, 8, 16):
+        x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=31 + tokens).reshape(tokens, n_in)).to(torch.bfloat16)
+        w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+        logits = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+        idx, val, bad = k.encode_lm_head_argmax(w, x.cuda(), tokens, logits=logits, out_scale=scale, softcap=cap)
+        idx2, val2, _ = k.encode_lm_head_argmax(w, x.cuda(), tokens, out_scale=scale, softcap=cap)  # pick only; keys were reset
+        ctx.sync_status()
+        got = logits.cpu().numpy()
+        first_max = np.array([int(np.flatnonzero(row == row.max())[0]) for row in got])
+        assert np.array_equal(idx.cpu().numpy(), first_max), tokens
+        assert np.array_equal(idx2.cpu().numpy(), first_max) and torch.equal(val, val2)
+        assert np.array_equal(val.cpu().numpy().view(np.uint32), got[np.arange(tokens), first_max].view(np.uint32))
+        assert not bad.cpu().numpy().any()
+        want = O.logit_tail(O.matmul(ow, x.float().numpy(), threads=O.host_threads()), scale, cap)
+        assert H.rel_l2(got, want) <= REL_L2_TOL
+        picked = want[np.arange(tokens), first_max]
+        assert np.all(want.max(axis=1) - picked <= 2e-3 * np.abs(want).max()), tokens
+        w.free()
+    # ties: the winning row of token 0 copied to an earlier and to a much later row -> the earliest of the three wins
+    tokens = 4
+    x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=77).reshape(tokens, n_in)).to(torch.bfloat16)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    idx, _, _ = k.encode_lm_head_argmax(w, x.cuda(), tokens)
+    r0 = int(idx.cpu()[0])
+    w.free()
+    row_bytes = raw.size // n_out
+    rows = raw.reshape(n_out, row_bytes)
+    early, late = (5 if r0 != 5 else 6), (n_out - 3 if r0 != n_out - 3 else n_out - 4)
+    tied = rows.copy()
+    tied[early], tied[late] = rows[r0], rows[r0]
+    w = op.Weight(ctx, op.TensorView(tied.reshape(-1), dtype, n_in, n_out))
+    idx, _, bad = k.encode_lm_head_argmax(w, x.cuda(), tokens)
+    assert int(idx.cpu()[0]) == min(early, r0) and not bad.cpu().numpy().any()
+    # a NaN activation poisons token 1 only: flagged there, index 0 by the scalar scan's convention; the others keep their pick
+    xn = x.clone()
+    xn[1, 100] = float("nan")
+    idx_n, _, bad_n = k.encode_lm_head_argmax(w, xn.cuda(), tokens)
+    ctx.sync_status()
+    assert bad_n.cpu().numpy().tolist() == [0, 1, 0, 0]
+    assert idx_n.cpu().numpy()[[0, 2, 3]].tolist() == idx.cpu().numpy()[[0, 2, 3]].tolist()
+    # misuse
+    y = torch.empty((17, n_out), dtype=torch.float32, device="cuda")
+    x17 = torch.zeros((17, n_in), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_lm_head_argmax(w, x17, 17)
+    assert e.value.status_name == "BAD_SHAPE"
+    w.free()
+    ws = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out), shard=(0, 2, 2))  # a K shard: partial sums have no maximum
+    with pytest.raises(op.MuserCudaError) as e:
+        k.encode_lm_head_argmax(ws, x[:, :n_in // 2].contiguous().cuda(), tokens)
+    assert e.value.status_name == "BAD_SHAPE"
+    ws.free()
+
+
 def test_misuse_returns_statuses(gpu):
     op, ctx, k = gpu
     raw = H.lcg_weights(O.Q4_K, 16, 1, seed=1)
