@@ -285,6 +285,19 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muse
                                                              const uint8_t *x_scales_swizzled, void *y, uint32_t y_dtype,
                                                              uint32_t tokens, void *stream);
 
+/* The FFN front half feeding the down projection without a detour through numbers: silu(gate) * up as above, then
+ * quant::quantize_nvfp4_activation of that f32 product (src/quant/nvfp4.rs:173-238) with the DOWN projection's static
+ * input_scale_inv, inside the GEMM's epilogue.  out_packed [tokens][n_out / 2] and out_scales_swizzled
+ * (muser_cuda_nvfp4_swizzled_scale_bytes(tokens, n_out) bytes) are what muser_cuda_quantize_nvfp4_activation would
+ * have produced from the fused call's f32 output, byte for byte; pass them to muser_cuda_nvfp4_matmul_prequant with
+ * the down weight.  n_out % 64 == 0.  The reference quantizes the intermediate in a pass of its own
+ * (src/weights.rs:111-121 on the CPU lane; scripts/gx10/vllm/muser_vllm/exact_fp4_quant.py on the GB10 producer). */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_requant(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,
+                                                            const muser_cuda_weight *w_up, const uint8_t *x_packed,
+                                                            const uint8_t *x_scales_swizzled, uint32_t tokens,
+                                                            float out_input_scale_inv, uint8_t *out_packed,
+                                                            uint8_t *out_scales_swizzled, void *stream);
+
 /* No counterpart in the reference.  The same W4A4 projection as muser_cuda_nvfp4_matmul for callers that cannot
  * allocate device memory: a driver that works out of arenas it sized once has no allocator to lend and, on the
  * step path, may not stall on the device-wide lock that cudaMalloc / cudaFree take.  This call needs no context

@@ -267,6 +267,18 @@ extern "C" {
         tokens: u32,
         stream: *mut c_void,
     ) -> muser_cuda_status;
+    pub fn muser_cuda_nvfp4_ffn_gate_up_silu_requant(
+        ctx: *mut muser_cuda_ctx,
+        w_gate: *const muser_cuda_weight,
+        w_up: *const muser_cuda_weight,
+        x_packed: *const u8,
+        x_scales_swizzled: *const u8,
+        tokens: u32,
+        out_input_scale_inv: f32,
+        out_packed: *mut u8,
+        out_scales_swizzled: *mut u8,
+        stream: *mut c_void,
+    ) -> muser_cuda_status;
     pub fn muser_cuda_nvfp4_matmul_static(
         w: *const muser_cuda_weight,
         x: *const c_void,

@@ -557,6 +557,23 @@ muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muser_cuda_ctx *c, 
     return launch_nvfp4_gemm(ctx, g, xp, xs, y, y_dtype, tokens, Epilogue{}, (cudaStream_t)stream, u);
 }
 
+muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_requant(muser_cuda_ctx *c, const muser_cuda_weight *gp,
+                                                            const muser_cuda_weight *up, const uint8_t *xp, const uint8_t *xs,
+                                                            uint32_t tokens, float out_input_scale_inv, uint8_t *out_packed,
+                                                            uint8_t *out_scales, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    const Weight *g = reinterpret_cast<const Weight *>(gp), *u = reinterpret_cast<const Weight *>(up);
+    muser_cuda_status st = check_io(ctx, g, xp, MUSER_DTYPE_BF16, out_packed, MUSER_DTYPE_BF16, tokens, false);
+    if (st != MUSER_CUDA_OK) return st;
+    if (!xs || !aligned16(xs) || !out_scales || !aligned16(out_scales)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "scale planes must be 16-byte aligned");
+    if (!(std::isfinite(out_input_scale_inv) && out_input_scale_inv > 0.0f)) return fail(ctx, MUSER_CUDA_NAN_SCALE, "input_scale_inv must be finite and positive");
+    st = nvfp4_pair_checks(ctx, g, u);
+    if (st != MUSER_CUDA_OK) return st;
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const NvFp4Out q{out_packed, out_scales, out_input_scale_inv};
+    return launch_nvfp4_gemm(ctx, g, xp, xs, nullptr, MUSER_DTYPE_BF16, tokens, Epilogue{}, (cudaStream_t)stream, u, &q);
+}
+
 size_t muser_cuda_nvfp4_swizzled_scale_bytes(uint64_t rows, uint64_t n_in) {
     return (size_t)((rows + 127) / 128 * ((n_in + 63) / 64) * 512);
 }

@@ -184,9 +184,13 @@ muser_cuda_status launch_nvfp4_quantize(Ctx *, const void *x, uint32_t x_dtype, 
                                         const float *norm_weight = nullptr, float norm_eps = 0.0f);
 muser_cuda_status launch_rmsnorm_rows(Ctx *, const void *x, uint32_t x_dtype, uint32_t tokens, uint64_t n_in,
                                       const float *norm_weight, float norm_eps, float *out, cudaStream_t);
+struct NvFp4Out { // where a GEMM leaves its output as NVFP4 activations for the next projection
+    uint8_t *packed, *scales;
+    float input_scale_inv;
+};
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
                                     void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t,
-                                    const Weight *w_up = nullptr);
+                                    const Weight *w_up = nullptr, const NvFp4Out *qout = nullptr);
 muser_cuda_status launch_nvfp4_a16(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                    void *workspace, size_t workspace_bytes, cudaStream_t);
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);

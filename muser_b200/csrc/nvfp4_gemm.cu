@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "nvfp4_codec.cuh"
 #include "tcgen05.cuh"
 
 namespace muser {
@@ -65,6 +66,11 @@ struct GemmArgs {
     uint32_t n_tiles;                      // 256-row tiles of the weight
     uint32_t y_dtype;
     float scale2, scale2_up, inv_input_scale;
+    // QOUT form: the output leaves as NVFP4 activations for the next projection instead of as numbers
+    uint8_t *q_packed;  // [tokens][n_out / 2]
+    uint8_t *q_scales;  // swizzled, ceil(tokens / 128) x (n_out / 64) chunks
+    float q_isi;        // the next projection's input_scale_inv
+    uint32_t q_kt;      // n_out / 64
 };
 
 // Scale-factor chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
@@ -151,7 +157,11 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 // the same 128 rows of the up weight (map_b, map_b2: 128-row boxes), and the epilogue writes silu_fast(gate) * up,
 // each factor first rounded to f16 as the unfused W4A4 lane returns it (quant/nvfp4.rs:337).
 // TAIL compiles the LM-head tail (logit scale, tanh soft cap) into the epilogue; the common instantiation has none of it.
-template <bool DUAL, bool TAIL>
+// QOUT (with DUAL): silu(gate) * up is not stored but quantized on the spot for the down projection, exactly as
+// quant::quantize_nvfp4_activation would quantize the f32 product (quant/nvfp4.rs:173-238): a thread holds 64
+// consecutive outputs of its token, i.e. four 16-value groups = one chunk of the swizzled scale plane, and writes
+// 32 bytes of codes and one word of scales.  The 27648-wide intermediate is never written or read as numbers.
+template <bool DUAL, bool TAIL, bool QOUT = false>
 __global__ void __launch_bounds__(352, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
@@ -345,12 +355,36 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty) : "memory");
+            uint32_t q_word = 0; // QOUT: the four scale bytes of this thread's 64 outputs
 #pragma unroll
             for (uint32_t s = 0; s < kPartCols / 32; ++s) {
                 const uint32_t c0 = col0 + 32 * s;
                 uint32_t(&cur)[32] = r[s];
                 uint32_t(&r_up)[32] = r[DUAL ? 2 + s : s];
                 const uint32_t n0 = tile_n * kOutCols + c0;
+                if constexpr (QOUT) {
+                    // rows of the last 128-token block that hold no token get zero scale bytes: the next GEMM reads the
+                    // block's whole scale chunk (their codes come from TMA's zero fill)
+                    if (n0 < g.n_out) {
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float gate = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(__uint_as_float(cur[i]), g.scale2), g.inv_input_scale)));
+                            const float up = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
+                            v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up;
+                        }
+                        if (tok < g.tokens) {
+                            uint8_t *codes = g.q_packed + (size_t)tok * (g.n_out / 2) + n0 / 2;
+                            float(&lo)[16] = *reinterpret_cast<float(*)[16]>(&v[0]);
+                            float(&hi)[16] = *reinterpret_cast<float(*)[16]>(&v[16]);
+                            q_word |= quantize_group(lo, g.q_isi, codes) << (16 * s);
+                            q_word |= quantize_group(hi, g.q_isi, codes + 8) << (16 * s + 8);
+                        }
+                    }
+                    if (s + 1 == kPartCols / 32 && tile_n * kOutCols + col0 < g.n_out)
+                        *reinterpret_cast<uint32_t *>(g.q_scales + swizzled_scale_offset(tok, (tile_n * kOutCols + col0) / 16, g.q_kt)) = q_word;
+                    continue;
+                }
                 if (tok < g.tokens && n0 < g.n_out) {
                     const size_t o = (size_t)tok * g.n_out + n0;
                     const uint32_t valid = min(32u, g.n_out - n0);
@@ -929,7 +963,7 @@ void nvfp4_free_tensor_map(Weight *w) {
 
 muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales, void *y,
                                     uint32_t y_dtype, uint32_t tokens, const Epilogue &ep, cudaStream_t stream,
-                                    const Weight *w_up) {
+                                    const Weight *w_up, const NvFp4Out *qout) {
     CUtensorMap map_a;
     if (!make_map(&map_a, x_packed, tokens, w->n_in / 2, BM))
         return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the activations");
@@ -952,6 +986,11 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.scale2_up = w_up ? w_up->scale2 : 0.0f;
     g.inv_input_scale = 1.0f / w->input_scale_inv;
     g.n_tiles = w_up ? (uint32_t)((w->n_out + BN / 2 - 1) / (BN / 2)) : (uint32_t)(w->n_out_pad / BN);
+    g.q_packed = qout ? qout->packed : nullptr;
+    g.q_scales = qout ? qout->scales : nullptr;
+    g.q_isi = qout ? qout->input_scale_inv : 0.0f;
+    g.q_kt = (uint32_t)(w->n_out / 64);
+    if (qout && (!w_up || w->n_out % 64)) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "quantized outputs come from the fused gate/up form, with n_out % 64 == 0");
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(w_up ? w->tmap_half : w->tmap_cache);
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;
     const bool tail = ep.out_scale != 1.0f || ep.softcap > 0.0f;
@@ -959,7 +998,7 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     // Pairs of SMs on 256-token tiles are opt-in: the pair halves the operand traffic per SM, but this GEMM is bound
     // by the scale-factor copies into tensor memory, which a pair does not reduce, and the pair's hand-offs cost more
     // than its traffic saves (ffn_gate at 2048 tokens: 2.4 against 2.8 PFLOP/s).
-    const bool pair = ctx->nvfp4_pair == 1;
+    const bool pair = ctx->nvfp4_pair == 1 && !qout;
     if (pair) {
         struct PairLimit { int n[3] = {0, 0, 0}; };
         static PerDevice<PairLimit> max_pairs; // co-resident clusters of two, asked once per device and kernel
@@ -1006,7 +1045,11 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
                       : tail ? reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, true>)
                              : reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, false>);
     MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(kfn, ctx->device, kSmemBytes));
-    if (w_up)
+    if (qout) {
+        const void *qfn = reinterpret_cast<const void *>(nvfp4_gemm_kernel<true, false, true>);
+        MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(qfn, ctx->device, kSmemBytes));
+        nvfp4_gemm_kernel<true, false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+    } else if (w_up)
         nvfp4_gemm_kernel<true, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
     else if (tail)
         nvfp4_gemm_kernel<false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);

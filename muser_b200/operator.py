@@ -259,6 +259,22 @@ class CudaKernels:
             _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
         self.launches += 2 if gate_w.dtype == NVFP4 else 1
 
+    def encode_nvfp4_ffn_gate_up_silu_requant(self, gate_w: Weight, up_w: Weight, packed: torch.Tensor, scales: torch.Tensor,
+                                              tokens: int, out_input_scale_inv: float, out_packed: torch.Tensor | None = None,
+                                              out_scales: torch.Tensor | None = None):
+        """muser_cuda_nvfp4_ffn_gate_up_silu_requant: silu(gate) * up leaves the GEMM as NVFP4 activations for the down
+        projection (codes [tokens][n_out / 2] + swizzled scales), never as numbers."""
+        n_out = gate_w.n_out
+        if out_packed is None:
+            out_packed = torch.empty((tokens, n_out // 2), dtype=torch.uint8, device=packed.device)
+        if out_scales is None:
+            out_scales = torch.empty(_L.muser_cuda_nvfp4_swizzled_scale_bytes(tokens, n_out), dtype=torch.uint8, device=packed.device)
+        self.ctx.check(_L.muser_cuda_nvfp4_ffn_gate_up_silu_requant(
+            self.ctx._h, gate_w._h, up_w._h, packed.data_ptr(), scales.data_ptr(), tokens, C.c_float(out_input_scale_inv),
+            out_packed.data_ptr(), out_scales.data_ptr(), _stream_ptr(self.ctx.device)))
+        self.launches += 1
+        return out_packed, out_scales
+
     def encode_nvfp4_ffn_gate_up_silu_prequant(self, gate_w: Weight, up_w: Weight, packed: torch.Tensor,
                                                scales: torch.Tensor, output: torch.Tensor, columns: int) -> None:
         self.ctx.check(_L.muser_cuda_nvfp4_ffn_gate_up_silu_prequant(

@@ -137,8 +137,9 @@ class PrefillLayer:
     that the CPU lane's composition can be followed without modelling bf16 roundings)."""
 
     def __init__(self, ctx, kern, plan: tp.ShardPlan, tokens: int, device, all_reduce=None, chunks: int = 1,
-                 act_dtype=torch.bfloat16, eps: float = 1e-6):
+                 act_dtype=torch.bfloat16, eps: float = 1e-6, requant: bool = True):
         self.ctx, self.kern, self.plan, self.M, self.eps, self.dev = ctx, kern, plan, tokens, eps, device
+        self.requant = requant  # silu(gate) * up leaves its GEMM as NVFP4 codes for down_proj (never as numbers)
         self.all_reduce = all_reduce
         P = self.P = synth.LAYER_PROJECTIONS
         H, F, world, M = P["attn_q"][0], P["ffn_gate"][1], plan.world, tokens
@@ -172,6 +173,9 @@ class PrefillLayer:
         self.ffn_act, self.h1, self.h2 = torch.empty((M, Fl), **kw), torch.empty((M, H), **kw), torch.empty((M, H), **kw)
         self.xq = (torch.empty((M, H // 2), dtype=torch.uint8, device=device),
                    torch.empty((op._L.muser_cuda_nvfp4_swizzled_scale_bytes(M, H),), dtype=torch.uint8, device=device))
+        self.fq = (torch.empty((M, Fl // 2), dtype=torch.uint8, device=device),
+                   torch.empty((op._L.muser_cuda_nvfp4_swizzled_scale_bytes(M, Fl),), dtype=torch.uint8, device=device))
+        self.Fl = Fl
         chunks = max(1, chunks if world > 1 else 1)
         step = (M + chunks - 1) // chunks // 128 * 128 or M
         self.bounds = [(a, min(M, a + step)) for a in range(0, M, step)]
@@ -183,9 +187,15 @@ class PrefillLayer:
         return (tokens + 128) * (F // world // 2 + F // world // 16 + 64) + (1 << 20)
 
     def _row_parallel(self, name, x, res, out):
-        """out = all_reduce(x @ W_shard^T) + res, in token chunks; the residual is added on rank 0's partial sum."""
+        """out = all_reduce(x @ W_shard^T) + res, in token chunks; the residual is added on rank 0's partial sum.
+        x: activations, or (codes, swizzled scales) of activations quantized earlier."""
         for a, b in self.bounds:
-            self.kern.encode_nvfp4_matmul(self.weights[name], x[a:b], out[a:b], b - a, residual=res[a:b] if self.plan.rank == 0 else None)
+            residual = res[a:b] if self.plan.rank == 0 else None
+            if isinstance(x, tuple):
+                chunk_bytes = (x[0].shape[1] * 2 + 63) // 64 * 512  # scale bytes per 128-row block
+                self.kern.encode_nvfp4_prequant(self.weights[name], x[0][a:b], x[1][(a // 128) * chunk_bytes:], out[a:b], b - a, residual=residual)
+            else:
+                self.kern.encode_nvfp4_matmul(self.weights[name], x[a:b], out[a:b], b - a, residual=residual)
             if self.all_reduce is not None and self.plan.world > 1:
                 self.all_reduce(out[a:b])
 
@@ -196,8 +206,14 @@ class PrefillLayer:
         k.encode_nvfp4_prequant(W["attn_k"], self.xq[0], self.xq[1], self.k, M)
         k.encode_nvfp4_prequant(W["attn_v"], self.xq[0], self.xq[1], self.v, M)
         self._row_parallel("attn_o", self.q, x, self.h1)
-        k.encode_ffn_gate_up_silu(W["ffn_gate"], W["ffn_up"], self.h1, self.ffn_act, M, norm_weight=self.norm_w[1], norm_eps=self.eps)
-        self._row_parallel("ffn_down", self.ffn_act, self.h1, self.h2)
+        if self.requant:
+            k.quantize_nvfp4_activation(self.h1, self.isi["ffn_gate"], norm_weight=self.norm_w[1], norm_eps=self.eps, out=self.xq)
+            k.encode_nvfp4_ffn_gate_up_silu_requant(W["ffn_gate"], W["ffn_up"], self.xq[0], self.xq[1], M, self.isi["ffn_down"],
+                                                    out_packed=self.fq[0], out_scales=self.fq[1])
+            self._row_parallel("ffn_down", self.fq, self.h1, self.h2)
+        else:
+            k.encode_ffn_gate_up_silu(W["ffn_gate"], W["ffn_up"], self.h1, self.ffn_act, M, norm_weight=self.norm_w[1], norm_eps=self.eps)
+            self._row_parallel("ffn_down", self.ffn_act, self.h1, self.h2)
         return self.h2
 
     def run(self, layers: int):

@@ -82,9 +82,17 @@ def test_one_prefill_layer_at_32768_tokens():
     M = 32768
     ctx = op.Context(0, workspace_bytes=workloads.PrefillLayer.workspace_bytes(M, 1))
     k = op.CudaKernels(ctx)
-    pl = workloads.PrefillLayer(ctx, k, tp.ShardPlan(0, 1), M, "cuda", act_dtype=torch.float32)
+    pl = workloads.PrefillLayer(ctx, k, tp.ShardPlan(0, 1), M, "cuda", act_dtype=torch.float32, requant=False)
+    # first the form the benchmark runs: silu(gate) * up leaves its GEMM as NVFP4 codes.  With f32 activations in
+    # between, the separate path quantizes exactly the numbers the fused epilogue holds, so the layer outputs must
+    # carry the same bits.
+    pl.requant = True
+    h2_fused = pl.layer(pl.h).clone()
+    pl.requant = False
     pl.layer(pl.h)
     ctx.sync_status()
+    assert torch.equal(h2_fused.view(torch.int32), pl.h2.view(torch.int32))
+    del h2_fused
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(3))[:16].cuda()
     thr = O.host_threads()
 

@@ -214,6 +214,47 @@ def test_paired_sm_gemm_equals_the_single_sm_gemm(gpu, n_out, n_in, tokens):
     assert H.rel_l2(out[1][0].numpy(), ref_f32) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("n_out,n_in,tokens", [(128, 256, 128), (192, 320, 9), (704, 1024, 260), (2048, 512, 1000)])
+def test_fused_gate_up_silu_leaves_as_nvfp4_activations(gpu, n_out, n_in, tokens):
+    """muser_cuda_nvfp4_ffn_gate_up_silu_requant: codes and scale bytes must equal, byte for byte, what
+    muser_cuda_quantize_nvfp4_activation makes of the fused call's f32 output (quant/nvfp4.rs:173-238 on
+    silu_fast(f16(gate)) * f16(up)); the slots of rows past the last token in the last 128-row block are zero."""
+    from muser_b200 import synth
+    op, ctx, k = gpu
+    gp, gs, g2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 11, negative_scales=True)
+    up, us, u2 = make_weight(op, ctx, n_out, n_in, seed=n_out + 12)
+    x = synth.normal_activations(tokens, n_in, seed=19)
+    isi = synth.activation_input_scale_inv(x)
+    wg = op.Weight(ctx, op.TensorView(gp, O.NVFP4, n_in, n_out, gs, g2, isi))
+    wu = op.Weight(ctx, op.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi))
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    y = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_nvfp4_ffn_gate_up_silu_prequant(wg, wu, xp, xs, y, tokens)
+    isi_next = synth.activation_input_scale_inv(y)
+    want_p, want_s = k.quantize_nvfp4_activation(y, isi_next)
+    got_s = torch.full_like(want_s, 0xAB)
+    got_p, got_s = k.encode_nvfp4_ffn_gate_up_silu_requant(wg, wu, xp, xs, tokens, isi_next, out_scales=got_s)
+    ctx.sync_status()
+    assert torch.equal(got_p, want_p)
+    assert np.array_equal(op.unswizzle_scales(got_s, tokens, n_out).cpu().numpy(), op.unswizzle_scales(want_s, tokens, n_out).cpu().numpy())
+    pad = (tokens + 127) // 128 * 128
+    if pad > tokens:
+        assert not op.unswizzle_scales(got_s, pad, n_out)[tokens:].any()
+    # and it feeds the down projection like any quantized activation
+    dp, ds, d2 = make_weight(op, ctx, 96, n_out, seed=5)
+    wd = op.Weight(ctx, op.TensorView(dp, O.NVFP4, n_out, 96, ds, d2, isi_next))
+    a = torch.empty((tokens, 96), dtype=torch.float32, device="cuda")
+    b = torch.empty_like(a)
+    k.encode_nvfp4_prequant(wd, got_p, got_s, a, tokens)
+    k.encode_nvfp4_matmul(wd, y, b, tokens)
+    ctx.sync_status()
+    assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+    with pytest.raises(op.MuserCudaError) as e:  # whole 64-value chunks only
+        w40 = op.Weight(ctx, op.TensorView(gp[:40], O.NVFP4, n_in, 40, gs[:40], g2, isi))
+        k.encode_nvfp4_ffn_gate_up_silu_requant(w40, w40, xp, xs, tokens, isi_next)
+    assert e.value.status_name == "BAD_SHAPE"
+
+
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 def test_fused_input_rmsnorm(gpu, x_dtype):
     """rms_norm_mul (reference.rs:59-80) fused into the activation quantizer.  The block adds the squares as a tree
