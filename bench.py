@@ -318,15 +318,17 @@ def run_gpu(args):
     # f32 host x in, f32 host y out, host<->device copies inside the timed region
     e2e = None
     if rank == 0 and world == 1 and not args.no_e2e:
-        hx = {(name, m): synth.normal_activations(m, layer.weights[name].n_in, seed=0, stream=2000).float().pin_memory()
-              for name in projs for m in TOKEN_COUNTS}
+        hx = {(gi, m): synth.normal_activations(m, layer.weights[group[0]].n_in, seed=0, stream=2000 + gi).float().pin_memory()
+              for gi, group in enumerate(layer.GROUPS) for m in TOKEN_COUNTS}
         hy = {(name, m): torch.empty((m, layer.weights[name].n_out), dtype=torch.float32).pin_memory() for name in projs for m in TOKEN_COUNTS}
-        calls = [(layer.weights[name], hx[(name, m)].data_ptr(), m, hy[(name, m)].data_ptr()) for m in TOKEN_COUNTS for name in projs]
+        # the step's call list, built once as a driver would: per token count the four launches of the decode step, each
+        # group's projections reading one host x and writing their own host y
+        calls = op.host_groups([([layer.weights[n] for n in group], hx[(gi, m)].data_ptr(), m, [hy[(n, m)].data_ptr() for n in group])
+                                for m in TOKEN_COUNTS for gi, group in enumerate(layer.GROUPS)])
         stream = torch.cuda.current_stream().cuda_stream
 
         def e2e_step():
-            for w, xp, m, yp in calls:
-                op.matmul_enqueue(ctx, w, xp, m, yp, stream)
+            op.matmul_groups_enqueue(ctx, calls, stream)
             ctx.sync_status()  # the step's one wait; also folds device-side give-ups into an exception
 
         for _ in range(3):
@@ -338,14 +340,15 @@ def run_gpu(args):
         dt_e2e = time.perf_counter() - t0
         name, m = "ffn_down", 8
         ref_dev = torch.empty((m, layer.weights[name].n_out), dtype=torch.float32, device=dev)
-        kern.encode_quantized_matmul(layer.weights[name], hx[(name, m)].to(dev), ref_dev, m)
+        kern.encode_quantized_matmul(layer.weights[name], hx[(3, m)].to(dev), ref_dev, m)
         e2e_check = float((hy[(name, m)] - ref_dev.cpu()).norm() / ref_dev.cpu().norm())
         e2e = {"value": step_bytes(4) * e2e_steps / dt_e2e / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": sum(m * layer.weights[name].n_in * 4 for name in projs for m in TOKEN_COUNTS),
+               "h2d_bytes_per_step": sum(m * layer.weights[group[0]].n_in * 4 for group in layer.GROUPS for m in TOKEN_COUNTS),
                "d2h_bytes_per_step": sum(m * layer.weights[name].n_out * 4 for name in projs for m in TOKEN_COUNTS),
                "ms_per_step": dt_e2e / e2e_steps * 1e3, "rel_l2_vs_device_call": e2e_check,
-               "note": "28 x muser_cuda_matmul_host_enqueue (pinned f32 host x up, projection, f32 y down) + one "
-                       "muser_cuda_sync_status per step; wall clock around the steps"}
+               "note": "one muser_cuda_matmul_host_groups_enqueue per step (16 groups: pinned f32 host x copied up once per "
+                       "group on a copy stream, one launch per group, f32 y stored into the pinned host buffers in batches "
+                       "beside the next launches) + one muser_cuda_sync_status; wall clock around the steps"}
     elif rank == 0 and world > 1:
         e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
                "note": "not measured at N > 1: the host-buffer entry point runs one rank's shard without the all-reduce"}

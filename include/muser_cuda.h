@@ -136,6 +136,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_DECODE_WSPLIT 12u      /* decode kernel: warps of a CTA that share one row tile and split K between them (0: from its cost model) */
 #define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 262144; 0: always NCCL) */
 #define MUSER_TUNE_NVFP4_PAIR 13u         /* NVFP4 GEMM: 0 one CTA per 128-token tile (default), 1 pairs of SMs on 256-token tiles (tcgen05 cta_group::2) */
+#define MUSER_TUNE_HOST_DIRECT_OUTPUT 14u /* muser_cuda_matmul_host_groups_enqueue: 1 (default) a kernel stores the outputs into pinned host buffers, 0 one cudaMemcpyAsync per output */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 
 /* The weight-loader step that MuseWeights / bind_nvfp4 views perform on the mmap'd file
@@ -376,6 +377,24 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, con
  * only allocation; a step that outgrows it makes the call wait for the stream once and start the arena over. */
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *ctx, const muser_cuda_weight *w,
                                                  const float *x_host, uint32_t tokens, float *y_host, void *stream);
+
+/* A whole decode step's projections through host buffers in ONE call: the drivers of the reference encode a step into
+ * one command buffer (src/decode.rs:5448-5460) and group the projections that read the same hidden state
+ * (src/decode.rs:5569-5598, src/metal/encode/qkv.rs:234-281).  Every group is 1..4 K-quant projections of one x_host
+ * ([tokens][n_in] f32, 1 <= tokens <= 16): x is copied up once, the group runs as one launch
+ * (muser_cuda_quantized_matmul_group), and the outputs y_host[i] ([tokens][n_out_i] f32) leave in batches beside the
+ * following groups' launches: stored by a small kernel where the device can address the buffer (pinned, mapped host
+ * memory), copied otherwise.  At most 30 groups per call.  Nothing is synchronized: wait with muser_cuda_sync_status,
+ * after which the outputs are complete.  Buffers must stay valid until then. */
+typedef struct muser_cuda_host_group {
+    const muser_cuda_weight *w[4];
+    float *y_host[4];
+    const float *x_host;
+    uint32_t n_items;
+    uint32_t tokens;
+} muser_cuda_host_group;
+MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *ctx, const muser_cuda_host_group *groups,
+                                                        uint32_t n_groups, void *stream);
 
 #ifdef __cplusplus
 }

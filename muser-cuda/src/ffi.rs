@@ -29,6 +29,7 @@ pub const MUSER_TUNE_DECODE_RING: u32 = 10;
 pub const MUSER_TUNE_ONESHOT_MAX_BYTES: u32 = 11;
 pub const MUSER_TUNE_DECODE_WSPLIT: u32 = 12;
 pub const MUSER_TUNE_NVFP4_PAIR: u32 = 13;
+pub const MUSER_TUNE_HOST_DIRECT_OUTPUT: u32 = 14;
 
 pub const MUSER_CUDA_COMM_ID_BYTES: usize = 128;
 
@@ -103,6 +104,16 @@ pub struct muser_cuda_group_item {
     pub y_dtype: u32,
     pub reserved: u32,
     pub epilogue: *const muser_cuda_epilogue,
+}
+
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct muser_cuda_host_group {
+    pub w: [*const muser_cuda_weight; 4],
+    pub y_host: [*mut f32; 4],
+    pub x_host: *const f32,
+    pub n_items: u32,
+    pub tokens: u32,
 }
 
 extern "C" {
@@ -307,4 +318,5 @@ extern "C" {
         y_host: *mut f32,
         stream: *mut c_void,
     ) -> muser_cuda_status;
+    pub fn muser_cuda_matmul_host_groups_enqueue(ctx: *mut muser_cuda_ctx, groups: *const muser_cuda_host_group, n_groups: u32, stream: *mut c_void) -> muser_cuda_status;
 }

@@ -15,6 +15,7 @@ SHARD_NONE, SHARD_ROWS, SHARD_K = 0, 1, 2
 TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
 TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES, TUNE_DECODE_WSPLIT = 8, 9, 10, 11, 12
 TUNE_NVFP4_PAIR = 13
+TUNE_HOST_DIRECT_OUTPUT = 14
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 
@@ -25,7 +26,7 @@ EXPORTS = [
     "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
-    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_fp4_pipe_probe", "muser_cuda_lm_head_argmax", "muser_cuda_nvfp4_ffn_gate_up_silu_requant", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
+    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_fp4_pipe_probe", "muser_cuda_lm_head_argmax", "muser_cuda_matmul_host_groups_enqueue", "muser_cuda_nvfp4_ffn_gate_up_silu_requant", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
     "muser_cuda_static_sync_status", "muser_cuda_wait_probe", "muser_cuda_quantized_matmul_group",
     "muser_cuda_matmul_host_enqueue", "muser_cuda_comm_unique_id", "muser_cuda_ctx_comm_init", "muser_cuda_ctx_comm_attach",
@@ -45,6 +46,10 @@ class Epilogue(C.Structure):
 class GroupItem(C.Structure):
     _fields_ = [("w", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_uint32), ("reserved", C.c_uint32),
                 ("epilogue", C.POINTER(Epilogue))]
+
+
+class HostGroup(C.Structure):
+    _fields_ = [("w", C.c_void_p * 4), ("y_host", C.c_void_p * 4), ("x_host", C.c_void_p), ("n_items", C.c_uint32), ("tokens", C.c_uint32)]
 
 
 class WeightInfo(C.Structure):
@@ -102,6 +107,7 @@ def _load() -> C.CDLL:
         "muser_cuda_fp4_peak_probe": (i32, [vp, u32, C.POINTER(C.c_double), vp]),
         "muser_cuda_fp4_pipe_probe": (i32, [vp, u32, u32, u32, u32, vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_requant": (i32, [vp, vp, vp, vp, vp, u32, C.c_float, vp, vp, vp]),
+        "muser_cuda_matmul_host_groups_enqueue": (i32, [vp, vp, u32, vp]),
         "muser_cuda_lm_head_argmax": (i32, [vp, vp, vp, u32, u32, vp, vp, u32, vp, vp, vp, vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
         "muser_cuda_tuning_set": (i32, [vp, u32, u32]),

@@ -268,6 +268,8 @@ void muser_cuda_ctx_destroy(muser_cuda_ctx *c) {
     cudaFree(ctx->dev_stage);
     cudaFree(ctx->arena);
     if (ctx->host_stage) cudaFreeHost(ctx->host_stage);
+    for (cudaEvent_t ev : ctx->copy_events)
+        if (ev) cudaEventDestroy(ev);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     delete ctx;
 }
@@ -308,6 +310,7 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
         ctx->nvfp4_pair = value;
         return MUSER_CUDA_OK;
     case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;
+    case MUSER_TUNE_HOST_DIRECT_OUTPUT: ctx->host_direct_output = value != 0; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
 }
@@ -732,6 +735,120 @@ muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *c, const muser_
     }
     if (st != MUSER_CUDA_OK) return st;
     MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(y_host, dy, yb, cudaMemcpyDeviceToHost, s));
+    return MUSER_CUDA_OK;
+}
+
+// Staged outputs -> the caller's pinned host buffers, 16 bytes a lane, every warp a contiguous 512 bytes.
+struct HostScatter {
+    static constexpr uint32_t kMax = 12;
+    const uint4 *src[kMax];
+    uint4 *dst[kMax];
+    uint32_t n16[kMax];
+    uint32_t n;
+};
+static __global__ void __launch_bounds__(256) host_scatter_kernel(const HostScatter t) {
+    for (uint32_t e = 0; e < t.n; ++e)
+        for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < t.n16[e]; i += gridDim.x * 256) t.dst[e][i] = t.src[e][i];
+}
+
+muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const muser_cuda_host_group *groups, uint32_t n_groups,
+                                                        void *stream_) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    cudaStream_t s = (cudaStream_t)stream_;
+    if (!ctx || !groups || n_groups == 0) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    size_t need = 0;
+    for (uint32_t gi = 0; gi < n_groups; ++gi) {
+        const muser_cuda_host_group &g = groups[gi];
+        if (g.n_items == 0 || g.n_items > 4 || !g.x_host || g.tokens == 0 || g.tokens > 16)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "a host group holds 1..4 projections of 1..16 tokens");
+        for (uint32_t i = 0; i < g.n_items; ++i)
+            if (!g.w[i] || !g.y_host[i]) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+        need += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[0])->n_in * 4 + 255) / 256 * 256;
+        for (uint32_t i = 0; i < g.n_items; ++i) need += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4 + 255) / 256 * 256;
+    }
+    if (ctx->arena_used + need > ctx->arena_bytes) {
+        MUSER_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+        ctx->arena_used = 0;
+        if (need > ctx->arena_bytes) {
+            cudaFree(ctx->arena);
+            ctx->arena = nullptr;
+            ctx->arena_bytes = 0;
+            const size_t want = need > ((size_t)64 << 20) ? need : ((size_t)64 << 20);
+            MUSER_CUDA_TRY(ctx, cudaMalloc(&ctx->arena, want));
+            ctx->arena_bytes = want;
+        }
+    }
+    uint8_t *const first = reinterpret_cast<uint8_t *>(ctx->arena) + ctx->arena_used;
+    ctx->arena_used += need;
+    // The inputs travel on the context's copy stream, each followed by an event that its launch waits for: a small
+    // host-to-device copy takes several microseconds to land, and on the launches' own stream every kernel would
+    // wait for all the copies issued before it.
+    constexpr uint32_t kEvents = 32;
+    if (n_groups > kEvents - 2) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "at most 30 groups per call");
+    if (!ctx->copy_events[0])
+        for (uint32_t i = 0; i < kEvents; ++i) MUSER_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->copy_events[i], cudaEventDisableTiming));
+    uint8_t *at = first;
+    for (uint32_t gi = 0; gi < n_groups; ++gi) { // pass 1: inputs
+        const muser_cuda_host_group &g = groups[gi];
+        const size_t xb = (size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[0])->n_in * 4;
+        MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(at, g.x_host, xb, cudaMemcpyHostToDevice, ctx->copy_stream));
+        MUSER_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[gi], ctx->copy_stream));
+        at += (xb + 255) / 256 * 256;
+        for (uint32_t i = 0; i < g.n_items; ++i) at += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4 + 255) / 256 * 256;
+    }
+    // Pass 2: the launches, back to back.  Outputs are written to the arena and leave in batches: after every four
+    // groups one small kernel on the copy stream stores them into the caller's pinned buffers with full-width,
+    // contiguous stores (the bus takes those at several times the rate of the projection kernel's own 32-byte
+    // pieces), beside the next groups' projections.  Buffers the device cannot address get a plain copy instead.
+    HostScatter batch;
+    batch.n = 0;
+    bool copies_pending = false;
+    auto flush = [&]() -> cudaError_t {
+        if (batch.n == 0) return cudaSuccess;
+        cudaError_t e = cudaEventRecord(ctx->copy_events[kEvents - 1], s);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[kEvents - 1], 0);
+        if (e != cudaSuccess) return e;
+        host_scatter_kernel<<<32, 256, 0, ctx->copy_stream>>>(batch);
+        batch.n = 0;
+        copies_pending = true;
+        return cudaGetLastError();
+    };
+    at = first;
+    for (uint32_t gi = 0; gi < n_groups; ++gi) {
+        const muser_cuda_host_group &g = groups[gi];
+        MUSER_CUDA_TRY(ctx, cudaStreamWaitEvent(s, ctx->copy_events[gi], 0));
+        uint8_t *dx = at;
+        at += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[0])->n_in * 4 + 255) / 256 * 256;
+        muser_cuda_group_item items[4];
+        uint8_t *staged[4];
+        for (uint32_t i = 0; i < g.n_items; ++i) {
+            staged[i] = at;
+            items[i].w = g.w[i], items[i].y = at, items[i].y_dtype = MUSER_DTYPE_F32, items[i].reserved = 0, items[i].epilogue = nullptr;
+            at += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4 + 255) / 256 * 256;
+        }
+        const muser_cuda_status st = muser_cuda_quantized_matmul_group(c, items, g.n_items, dx, MUSER_DTYPE_F32, g.tokens, s);
+        if (st != MUSER_CUDA_OK) return st;
+        for (uint32_t i = 0; i < g.n_items; ++i) {
+            const size_t yb = (size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4;
+            void *mapped = nullptr;
+            if (ctx->host_direct_output && cudaHostGetDevicePointer(&mapped, g.y_host[i], 0) == cudaSuccess && ((uintptr_t)mapped & 15u) == 0 && yb % 16 == 0) {
+                batch.src[batch.n] = reinterpret_cast<const uint4 *>(staged[i]);
+                batch.dst[batch.n] = reinterpret_cast<uint4 *>(mapped);
+                batch.n16[batch.n] = (uint32_t)(yb / 16);
+                if (++batch.n == HostScatter::kMax) MUSER_CUDA_TRY(ctx, flush());
+            } else {
+                (void)cudaGetLastError();
+                MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(g.y_host[i], staged[i], yb, cudaMemcpyDeviceToHost, s));
+            }
+        }
+        if ((gi & 3) == 3) MUSER_CUDA_TRY(ctx, flush());
+    }
+    MUSER_CUDA_TRY(ctx, flush());
+    if (copies_pending) { // the caller's wait on `stream` covers the copy stream's stores
+        MUSER_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[kEvents - 2], ctx->copy_stream));
+        MUSER_CUDA_TRY(ctx, cudaStreamWaitEvent(s, ctx->copy_events[kEvents - 2], 0));
+    }
     return MUSER_CUDA_OK;
 }
 

@@ -46,6 +46,7 @@ struct Ctx {
     float *inv_rms = nullptr;              // one 1/rms per token row of a fused input norm (NVFP4 quantizer, skinny kernel)
     uint32_t inv_rms_rows = 0;
     cudaStream_t copy_stream = nullptr;
+    cudaEvent_t copy_events[32] = {};          // "this group's input has landed", made on first use of the host-group entry
     void *host_stage = nullptr; // pinned staging for matmul_host
     size_t host_stage_bytes = 0;
     void *dev_stage = nullptr;
@@ -55,6 +56,7 @@ struct Ctx {
     void *comm = nullptr;                      // tensor-parallel communicator (collective.cu), or null
     unsigned long long *amax_keys = nullptr;   // fused greedy pick: one key and one flag word per token (16 each), zero between calls
     unsigned int *amax_flags = nullptr;
+    bool host_direct_output = true;            // host-group entry: a kernel stores the outputs into mapped host buffers (else memcpy)
     uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs (cta_group::2): 0 off, 1 on
     uint32_t oneshot_max_bytes = 256u << 10;   // all-reduce payloads up to this size take the one-shot peer exchange
     std::string last_error;

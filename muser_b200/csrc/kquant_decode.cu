@@ -783,33 +783,49 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
         uint32_t groups[kDecMaxJobs] = {0, 0, 0, 0};
         uint32_t forced_w = 0, forced_k = 0, forced_r = 0, forced_s = 0, tokens = 0, generation = 0;
     };
-    static PerDevice<Cached> cached; // last geometry of this instantiation, per device
+    // The geometries this instantiation was launched with lately, per device: a decode step alternates between a
+    // handful (q|k|v, o, gate|up, down, each at a few token counts), and working a plan out again (cost model,
+    // occupancy query) costs tens of microseconds of host time, more than the launch itself.
+    struct CacheSet {
+        Cached entry[16];
+        uint32_t next = 0;
+    };
+    static PerDevice<CacheSet> cached;
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return cudaErrorInvalidDevice;
     Cached cache;
     {
         std::lock_guard<std::mutex> lock(cached.mu);
-        Cached &slot = cached.slot[ctx->device];
+        CacheSet &set = cached.slot[ctx->device];
         constexpr int kOutWords = (DUAL ? 2 : 1) * NG * 2;
-        bool same = slot.nsb == a.nsb && slot.n_jobs == a.n_jobs && slot.tokens == a.tokens && slot.forced_w == (uint32_t)forced.warps &&
-                    slot.forced_k == (uint32_t)forced.ksplit && slot.forced_r == (uint32_t)forced.ring && slot.forced_s == (uint32_t)forced.wsplit;
         uint32_t generation;
         {
             TunedTable &tt = tuned_table();
             std::lock_guard<std::mutex> tl(tt.mu);
             generation = tt.generation[ctx->device];
         }
-        same = same && slot.generation == generation;
         int fmt = (FAM & 1) == 1 ? 2 : 0;
         uint32_t total_tiles = 0;
         size_t out_floats = 0;
         for (uint32_t i = 0; i < a.n_jobs; ++i) {
-            same = same && slot.rows[i] == a.job[i].row_tiles;
             if (a.job[i].dtype == MUSER_DTYPE_Q6_K) fmt = 1;
             total_tiles += a.job[i].row_tiles;
             out_floats += (size_t)(DUAL ? 2 : 1) * 4 * NG * a.job[i].n_out;
         }
-        same = same && slot.fmt == fmt;
+        Cached *hit = nullptr;
+        for (Cached &c : set.entry) {
+            bool same = c.nsb == a.nsb && c.n_jobs == a.n_jobs && c.tokens == a.tokens && c.forced_w == (uint32_t)forced.warps &&
+                        c.forced_k == (uint32_t)forced.ksplit && c.forced_r == (uint32_t)forced.ring && c.forced_s == (uint32_t)forced.wsplit &&
+                        c.generation == generation && c.fmt == fmt;
+            for (uint32_t i = 0; same && i < a.n_jobs; ++i) same = c.rows[i] == a.job[i].row_tiles;
+            if (same) {
+                hit = &c;
+                break;
+            }
+        }
+        const bool same = hit != nullptr;
+        Cached &slot = same ? *hit : set.entry[set.next];
         if (!same) {
+            set.next = (set.next + 1) % 16;
             DecPlan p = dec_plan(a.nsb, total_tiles, ctx->sm_count, NG, fmt, a.tokens, kOutWords);
             {
                 TunedTable &tt = tuned_table();

@@ -390,6 +390,23 @@ def matmul_enqueue(ctx: Context, w: Weight, x_ptr: int, n_tokens: int, out_ptr: 
     ctx.check(_L.muser_cuda_matmul_host_enqueue(ctx._h, w._h, x_ptr, n_tokens, out_ptr, stream))
 
 
+def host_groups(groups):
+    """A decode step's call list for matmul_groups_enqueue, built once: `groups` is a sequence of
+    (weights, x_host_address, tokens, [y_host_addresses]) with 1..4 weights that read the same x."""
+    arr = (_lib.HostGroup * len(groups))()
+    for g, (weights, x_ptr, tokens, y_ptrs) in zip(arr, groups):
+        for i, (w, y) in enumerate(zip(weights, y_ptrs)):
+            g.w[i], g.y_host[i] = w._h.value, y
+        g.x_host, g.n_items, g.tokens = x_ptr, len(weights), tokens
+    return arr
+
+
+def matmul_groups_enqueue(ctx: Context, groups, stream: int) -> None:
+    """muser_cuda_matmul_host_groups_enqueue: a whole step's grouped projections through host f32 buffers in one call;
+    `groups` from host_groups().  ctx.sync_status() on the same stream completes the step."""
+    ctx.check(_L.muser_cuda_matmul_host_groups_enqueue(ctx._h, groups, len(groups), stream))
+
+
 def unswizzle_scales(swizzled: torch.Tensor, rows: int, n_in: int) -> torch.Tensor:
     """Logical [rows][n_in/16] view of the [rows/128][n_in/64][32][4][4] scale plane (test helper)."""
     groups = n_in // 16

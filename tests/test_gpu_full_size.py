@@ -177,3 +177,42 @@ def test_host_enqueue_entry_point_matches_the_blocking_one(gpu):
     assert H.rel_l2(ys[0].numpy(), want) <= REL_L2_TOL and torch.equal(ys[0], ys[-1])
     for w in ws:
         w.free()
+
+
+def test_a_step_of_grouped_projections_through_host_buffers(gpu):
+    """muser_cuda_matmul_host_groups_enqueue: a step's groups (q | k | v of mixed Q4_K / Q6_K, a single projection, a
+    pair) in one call, outputs written by the kernels into pinned host buffers, or copied back where the caller's
+    buffer is ordinary pageable memory; compared with the CPU lane and with the per-projection host entry."""
+    op, ctx, k = gpu
+    n_in = 1024
+    shapes = [(O.Q4_K, 700), (O.Q4_K, 130), (O.Q6_K, 130), (O.Q4_K, 1024), (O.Q5_K, 333)]
+    raws = [H.lcg_weights(dt, n, n_in // 256, seed=60 + i) for i, (dt, n) in enumerate(shapes)]
+    ws = [op.Weight(ctx, op.TensorView(r, dt, n_in, n)) for r, (dt, n) in zip(raws, shapes)]
+    stream = torch.cuda.current_stream().cuda_stream
+    groups, expect = [], []
+    for tokens in (1, 4, 8, 16):
+        for members, pinned in (((0, 1, 2), True), ((3,), False), ((4,), True), ((0, 3), True)):
+            x = torch.from_numpy(H.lcg_activations(tokens * n_in, seed=7 * tokens + len(members)).reshape(tokens, n_in)).pin_memory()
+            ys = [torch.full((tokens, shapes[i][1]), float("nan")) for i in members]
+            ys = [y.pin_memory() if pinned else y for y in ys]
+            groups.append(([ws[i] for i in members], x.data_ptr(), tokens, [y.data_ptr() for y in ys]))
+            expect.append((members, x, ys, tokens))
+    calls = op.host_groups(groups)
+    for _ in range(2):  # the list is reusable step after step
+        op.matmul_groups_enqueue(ctx, calls, stream)
+        ctx.sync_status()
+    for members, x, ys, tokens in expect:
+        for i, y in zip(members, ys):
+            dt, n = shapes[i]
+            want = O.matmul(O.TensorView(raws[i], dt, n_in, n), x.numpy(), threads=4)
+            assert H.rel_l2(y.numpy(), want) <= REL_L2_TOL, (members, tokens)
+            single = torch.empty_like(y).pin_memory()
+            op.matmul_enqueue(ctx, ws[i], x.data_ptr(), tokens, single.data_ptr(), stream)
+            ctx.sync_status()
+            assert H.rel_l2(y.numpy(), single.numpy()) <= 1e-5
+    bad = op.host_groups([([ws[0]], 0, 4, [0])])
+    with pytest.raises(op.MuserCudaError) as e:
+        op.matmul_groups_enqueue(ctx, bad, stream)
+    assert e.value.status_name in ("BAD_ARG", "BAD_SHAPE")
+    for w in ws:
+        w.free()
