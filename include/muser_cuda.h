@@ -384,8 +384,10 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *
  * ([tokens][n_in] f32, 1 <= tokens <= 16): x is copied up once, the group runs as one launch
  * (muser_cuda_quantized_matmul_group), and the outputs y_host[i] ([tokens][n_out_i] f32) leave in batches beside the
  * following groups' launches: stored by a small kernel where the device can address the buffer (pinned, mapped host
- * memory), copied otherwise.  At most 30 groups per call.  Nothing is synchronized: wait with muser_cuda_sync_status,
- * after which the outputs are complete.  Buffers must stay valid until then. */
+ * memory), copied otherwise.  At most 28 groups per call.  Nothing is synchronized: wait with muser_cuda_sync_status,
+ * after which the outputs are complete.  Buffers must stay valid until then.  The call can be captured into a CUDA
+ * graph on `stream` (after one plain call, which makes the arena and the events) and replayed step after step: the
+ * graph then reads and writes the same host buffers and the same part of the arena. */
 typedef struct muser_cuda_host_group {
     const muser_cuda_weight *w[4];
     float *y_host[4];

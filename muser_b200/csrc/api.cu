@@ -768,6 +768,10 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
         for (uint32_t i = 0; i < g.n_items; ++i) need += ((size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4 + 255) / 256 * 256;
     }
     if (ctx->arena_used + need > ctx->arena_bytes) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        MUSER_CUDA_TRY(ctx, cudaStreamIsCapturing(s, &capturing));
+        if (capturing != cudaStreamCaptureStatusNone)
+            return fail(ctx, MUSER_CUDA_WORKSPACE_TOO_SMALL, "the staging arena is full and cannot be rewound during a stream capture: call muser_cuda_sync_status first");
         MUSER_CUDA_TRY(ctx, cudaStreamSynchronize(s));
         ctx->arena_used = 0;
         if (need > ctx->arena_bytes) {
@@ -785,9 +789,12 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
     // host-to-device copy takes several microseconds to land, and on the launches' own stream every kernel would
     // wait for all the copies issued before it.
     constexpr uint32_t kEvents = 32;
-    if (n_groups > kEvents - 2) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "at most 30 groups per call");
+    if (n_groups > kEvents - 4) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "at most 28 groups per call");
     if (!ctx->copy_events[0])
         for (uint32_t i = 0; i < kEvents; ++i) MUSER_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->copy_events[i], cudaEventDisableTiming));
+    // the copy stream's work hangs off `stream` at both ends, so the call can be captured into a CUDA graph from there
+    MUSER_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[kEvents - 3], s));
+    MUSER_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[kEvents - 3], 0));
     uint8_t *at = first;
     for (uint32_t gi = 0; gi < n_groups; ++gi) { // pass 1: inputs
         const muser_cuda_host_group &g = groups[gi];
@@ -842,13 +849,12 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
                 MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(g.y_host[i], staged[i], yb, cudaMemcpyDeviceToHost, s));
             }
         }
-        if ((gi & 3) == 3) MUSER_CUDA_TRY(ctx, flush());
+        if ((gi & 3) == 3) MUSER_CUDA_TRY(ctx, flush()); // (a store kernel per group measured slower than one per four)
     }
     MUSER_CUDA_TRY(ctx, flush());
-    if (copies_pending) { // the caller's wait on `stream` covers the copy stream's stores
-        MUSER_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[kEvents - 2], ctx->copy_stream));
-        MUSER_CUDA_TRY(ctx, cudaStreamWaitEvent(s, ctx->copy_events[kEvents - 2], 0));
-    }
+    (void)copies_pending; // the caller's wait on `stream` covers the copy stream's stores
+    MUSER_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[kEvents - 2], ctx->copy_stream));
+    MUSER_CUDA_TRY(ctx, cudaStreamWaitEvent(s, ctx->copy_events[kEvents - 2], 0));
     return MUSER_CUDA_OK;
 }
 

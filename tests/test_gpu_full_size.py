@@ -216,3 +216,30 @@ def test_a_step_of_grouped_projections_through_host_buffers(gpu):
     assert e.value.status_name in ("BAD_ARG", "BAD_SHAPE")
     for w in ws:
         w.free()
+
+
+def test_host_groups_call_replayed_from_a_cuda_graph(gpu):
+    """The host-buffer step captured once and replayed: every replay reads the pinned inputs as they are then and
+    rewrites the pinned outputs."""
+    op, ctx, k = gpu
+    from muser_b200 import workloads
+    n_in = 1024
+    raws = [H.lcg_weights(O.Q4_K, 300, 4, seed=90), H.lcg_weights(O.Q6_K, 200, 4, seed=91)]
+    ws = [op.Weight(ctx, op.TensorView(raws[0], O.Q4_K, n_in, 300)), op.Weight(ctx, op.TensorView(raws[1], O.Q6_K, n_in, 200))]
+    x = torch.from_numpy(H.lcg_activations(4 * n_in, seed=1).reshape(4, n_in)).pin_memory()
+    ys = [torch.full((4, 300), float("nan")).pin_memory(), torch.full((4, 200), float("nan")).pin_memory()]
+    calls = op.host_groups([(ws, x.data_ptr(), 4, [y.data_ptr() for y in ys]), ([ws[1]], x.data_ptr(), 4, [ys[1].data_ptr()])])
+    op.matmul_groups_enqueue(ctx, calls, torch.cuda.current_stream().cuda_stream)
+    ctx.sync_status()
+    replay = workloads.capture(lambda: op.matmul_groups_enqueue(ctx, calls, torch.cuda.current_stream().cuda_stream))
+    for seed in (2, 3):
+        x.copy_(torch.from_numpy(H.lcg_activations(4 * n_in, seed=seed).reshape(4, n_in)))
+        for y in ys:
+            y.fill_(float("nan"))
+        replay()
+        ctx.sync_status()
+        for raw, dt, n, y in ((raws[0], O.Q4_K, 300, ys[0]), (raws[1], O.Q6_K, 200, ys[1])):
+            want = O.matmul(O.TensorView(raw, dt, n_in, n), x.numpy(), threads=4)
+            assert H.rel_l2(y.numpy(), want) <= REL_L2_TOL, seed
+    for w in ws:
+        w.free()
