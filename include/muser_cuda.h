@@ -378,6 +378,24 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host(muser_cuda_ctx *ctx, con
 MUSER_CUDA_API muser_cuda_status muser_cuda_matmul_host_enqueue(muser_cuda_ctx *ctx, const muser_cuda_weight *w,
                                                  const float *x_host, uint32_t tokens, float *y_host, void *stream);
 
+/* The step either side of the projections, so that a layer's non-attention work can stay on the device between two
+ * projection calls.  All f32, device pointers, rows 16-byte aligned.
+ *
+ * muser_fused_norm_residual_rms_norm_32sg (src/shaders/ferrite/rmsnorm_batch_tail.metal:147-200), the sandwich-norm
+ * tail of src/reference.rs:466-490: hidden[t] += rms_norm(src[t], eps1) * weight1 (the post-norm of a projection's
+ * output with its own epsilon, onto the residual stream, in place) and, when `output` is given,
+ * output[t] = rms_norm(hidden[t], eps2) * weight2 (the next pre-norm).  tokens rows of n values, n % 4 == 0. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_fused_norm_residual_rms_norm(muser_cuda_ctx *ctx, float *hidden, const float *src, float *output,
+                                                          const float *weight1, const float *weight2, uint32_t tokens,
+                                                          uint32_t n, float eps1, float eps2, void *stream);
+/* The attention output gate in front of o_proj (src/reference.rs:447-455; shaders/ferrite sigmoid_gate):
+ * x[i] *= 1 / (1 + exp(-gate[i])), in place; count % 4 == 0. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_sigmoid_gate(muser_cuda_ctx *ctx, float *x, const float *gate, uint64_t count, void *stream);
+/* The per-head QK norm (src/reference.rs:384-393): every head_dim-long piece of x ([tokens][heads * head_dim], in place)
+ * becomes rms_norm(piece, eps) * weight, weight [head_dim]; head_dim % 4 == 0. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_head_rms_norm(muser_cuda_ctx *ctx, float *x, const float *weight, float eps, uint32_t tokens,
+                                           uint32_t heads, uint32_t head_dim, void *stream);
+
 /* A whole decode step's projections through host buffers in ONE call: the drivers of the reference encode a step into
  * one command buffer (src/decode.rs:5448-5460) and group the projections that read the same hidden state
  * (src/decode.rs:5569-5598, src/metal/encode/qkv.rs:234-281).  Every group is 1..4 K-quant projections of one x_host

@@ -318,5 +318,20 @@ extern "C" {
         y_host: *mut f32,
         stream: *mut c_void,
     ) -> muser_cuda_status;
+    pub fn muser_cuda_fused_norm_residual_rms_norm(
+        ctx: *mut muser_cuda_ctx,
+        hidden: *mut f32,
+        src: *const f32,
+        output: *mut f32,
+        weight1: *const f32,
+        weight2: *const f32,
+        tokens: u32,
+        n: u32,
+        eps1: f32,
+        eps2: f32,
+        stream: *mut c_void,
+    ) -> muser_cuda_status;
+    pub fn muser_cuda_sigmoid_gate(ctx: *mut muser_cuda_ctx, x: *mut f32, gate: *const f32, count: u64, stream: *mut c_void) -> muser_cuda_status;
+    pub fn muser_cuda_head_rms_norm(ctx: *mut muser_cuda_ctx, x: *mut f32, weight: *const f32, eps: f32, tokens: u32, heads: u32, head_dim: u32, stream: *mut c_void) -> muser_cuda_status;
     pub fn muser_cuda_matmul_host_groups_enqueue(ctx: *mut muser_cuda_ctx, groups: *const muser_cuda_host_group, n_groups: u32, stream: *mut c_void) -> muser_cuda_status;
 }

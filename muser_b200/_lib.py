@@ -26,7 +26,8 @@ EXPORTS = [
     "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
     "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
-    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_fp4_pipe_probe", "muser_cuda_lm_head_argmax", "muser_cuda_matmul_host_groups_enqueue", "muser_cuda_nvfp4_ffn_gate_up_silu_requant", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
+    "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_fp4_pipe_probe", "muser_cuda_lm_head_argmax", "muser_cuda_matmul_host_groups_enqueue", "muser_cuda_fused_norm_residual_rms_norm",
+    "muser_cuda_sigmoid_gate", "muser_cuda_head_rms_norm", "muser_cuda_nvfp4_ffn_gate_up_silu_requant", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
     "muser_cuda_static_sync_status", "muser_cuda_wait_probe", "muser_cuda_quantized_matmul_group",
     "muser_cuda_matmul_host_enqueue", "muser_cuda_comm_unique_id", "muser_cuda_ctx_comm_init", "muser_cuda_ctx_comm_attach",
@@ -108,6 +109,9 @@ def _load() -> C.CDLL:
         "muser_cuda_fp4_pipe_probe": (i32, [vp, u32, u32, u32, u32, vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_requant": (i32, [vp, vp, vp, vp, vp, u32, C.c_float, vp, vp, vp]),
         "muser_cuda_matmul_host_groups_enqueue": (i32, [vp, vp, u32, vp]),
+        "muser_cuda_fused_norm_residual_rms_norm": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, C.c_float, C.c_float, vp]),
+        "muser_cuda_sigmoid_gate": (i32, [vp, vp, vp, C.c_uint64, vp]),
+        "muser_cuda_head_rms_norm": (i32, [vp, vp, vp, C.c_float, u32, u32, u32, vp]),
         "muser_cuda_lm_head_argmax": (i32, [vp, vp, vp, u32, u32, vp, vp, u32, vp, vp, vp, vp]),
         "muser_cuda_nvfp4_ffn_gate_up_silu_prequant": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
         "muser_cuda_tuning_set": (i32, [vp, u32, u32]),

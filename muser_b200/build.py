@@ -10,7 +10,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmuser_cuda.so"
-SOURCES = ["api.cu", "repack.cu", "kquant_decode.cu", "kquant_tc.cu", "nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_static.cu", "nvfp4_a16.cu", "collective.cu"]
+SOURCES = ["api.cu", "repack.cu", "kquant_decode.cu", "kquant_tc.cu", "nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_static.cu", "nvfp4_a16.cu", "collective.cu", "layer_ops.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -489,6 +489,40 @@ muser_cuda_status muser_cuda_lm_head_argmax(muser_cuda_ctx *c, const muser_cuda_
     return MUSER_CUDA_OK;
 }
 
+muser_cuda_status muser_cuda_fused_norm_residual_rms_norm(muser_cuda_ctx *c, float *hidden, const float *src, float *output,
+                                                          const float *weight1, const float *weight2, uint32_t tokens, uint32_t n,
+                                                          float eps1, float eps2, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !hidden || !src || !weight1 || (output && !weight2)) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (tokens == 0 || n == 0 || n % 4) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "rows of a multiple of 4 values");
+    if (!aligned16(hidden) || !aligned16(src) || !aligned16(weight1) || (output && (!aligned16(output) || !aligned16(weight2))))
+        return fail(ctx, MUSER_CUDA_BAD_ALIGN, "rows and weights must be 16-byte aligned");
+    if (!(eps1 >= 0.0f) || !(eps2 >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "epsilons must be non-negative numbers");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_norm_residual_norm(ctx, hidden, src, output, weight1, weight2, tokens, n, eps1, eps2, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_sigmoid_gate(muser_cuda_ctx *c, float *x, const float *gate, uint64_t count, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !x || !gate) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (count == 0 || count % 4) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "a multiple of 4 values");
+    if (!aligned16(x) || !aligned16(gate)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "x and gate must be 16-byte aligned");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_sigmoid_gate(ctx, x, gate, (size_t)count, (cudaStream_t)stream);
+}
+
+muser_cuda_status muser_cuda_head_rms_norm(muser_cuda_ctx *c, float *x, const float *weight, float eps, uint32_t tokens, uint32_t heads,
+                                           uint32_t head_dim, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx || !x || !weight) return fail(ctx, MUSER_CUDA_BAD_ARG, "null argument");
+    if (tokens == 0 || heads == 0 || head_dim == 0 || head_dim % 4 || (uint64_t)tokens * heads > (1u << 30))
+        return fail(ctx, MUSER_CUDA_BAD_SHAPE, "heads of a multiple of 4 values");
+    if (!aligned16(x) || !aligned16(weight)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "x and weight must be 16-byte aligned");
+    if (!(eps >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "epsilon must be a non-negative number");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_head_rms_norm(ctx, x, weight, eps, tokens, heads, head_dim, (cudaStream_t)stream);
+}
+
 // The NVFP4 side of the fused gate/up call: both weights must quantize their input alike, because one set of
 // activation codes feeds both.
 static muser_cuda_status nvfp4_pair_checks(Ctx *ctx, const Weight *g, const Weight *u) {

@@ -198,6 +198,10 @@ muser_cuda_status launch_nvfp4_a16(Ctx *, const Weight *w, const void *x, uint32
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);
 muser_cuda_status launch_f16_mma_probe(Ctx *, uint32_t n_cols, uint32_t iters, double *cycles_per_mma);
 muser_cuda_status nvfp4_build_tensor_map(Ctx *, Weight *);
+muser_cuda_status launch_norm_residual_norm(Ctx *, float *hidden, const float *src, float *output, const float *w1, const float *w2,
+                                            uint32_t tokens, uint32_t n, float eps1, float eps2, cudaStream_t);
+muser_cuda_status launch_sigmoid_gate(Ctx *, float *x, const float *gate, size_t count, cudaStream_t);
+muser_cuda_status launch_head_rms_norm(Ctx *, float *x, const float *w, float eps, uint32_t tokens, uint32_t heads, uint32_t head_dim, cudaStream_t);
 muser_cuda_status launch_nvfp4_pipe_probe(Ctx *, uint32_t mode, uint32_t iters, uint32_t load_kib, uint32_t random, cudaStream_t);
 void nvfp4_free_tensor_map(Weight *);
 

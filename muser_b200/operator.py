@@ -250,6 +250,28 @@ class CudaKernels:
         self.launches += 2
         return index, value, nonfinite
 
+    def encode_fused_norm_residual_rms_norm(self, hidden: torch.Tensor, src: torch.Tensor, weight1: torch.Tensor, eps1: float,
+                                            output: torch.Tensor | None = None, weight2: torch.Tensor | None = None, eps2: float = 0.0) -> None:
+        """hidden += rms_norm(src, eps1) * weight1 in place; output = rms_norm(hidden, eps2) * weight2 when given
+        (rmsnorm_batch_tail.metal:147-200; reference.rs:466-490).  f32 [tokens][n]."""
+        tokens, n = src.shape
+        self.ctx.check(_L.muser_cuda_fused_norm_residual_rms_norm(
+            self.ctx._h, hidden.data_ptr(), src.data_ptr(), output.data_ptr() if output is not None else None, weight1.data_ptr(),
+            weight2.data_ptr() if weight2 is not None else None, tokens, n, C.c_float(eps1), C.c_float(eps2), _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+    def encode_sigmoid_gate(self, x: torch.Tensor, gate: torch.Tensor) -> None:
+        """x *= sigmoid(gate) in place (reference.rs:447-455)."""
+        self.ctx.check(_L.muser_cuda_sigmoid_gate(self.ctx._h, x.data_ptr(), gate.data_ptr(), x.numel(), _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
+    def encode_head_rms_norm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, heads: int) -> None:
+        """Per-head rms_norm_mul of x [tokens][heads * head_dim] in place (reference.rs:384-393)."""
+        tokens = x.shape[0]
+        self.ctx.check(_L.muser_cuda_head_rms_norm(self.ctx._h, x.data_ptr(), weight.data_ptr(), C.c_float(eps), tokens, heads,
+                                                   x.shape[1] // heads, _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
     def encode_ffn_gate_up_silu(self, gate_w: Weight, up_w: Weight, input: torch.Tensor, output: torch.Tensor,
                                 tokens: int, norm_weight=None, norm_eps=0.0) -> None:
         """output[t][j] = silu(gate_j . x_t) * (up_j . x_t); K-quant (tokens <= 16) or NVFP4 weights."""

@@ -804,6 +804,14 @@ ORACLE_API int oracle_matmul_rows(const oracle_tensor_view *w, const float *x, s
 }
 
 /* reference.rs:511-513: silu_fast(gate) * up */
+/* reference.rs:447-455: gate <- 1 / (1 + exp(-gate)); attn_out *= gate */
+ORACLE_API void oracle_sigmoid_gate(float *x, const float *gate, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        float g = 1.0f / (1.0f + expf(-gate[i]));
+        x[i] *= g;
+    }
+}
+
 ORACLE_API void oracle_silu_mul(const float *gate, const float *up, float *out, size_t n) {
     for (size_t i = 0; i < n; ++i) out[i] = oracle_silu_fast(gate[i]) * up[i];
 }

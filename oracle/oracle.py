@@ -102,6 +102,8 @@ def lib() -> C.CDLL:
         L.oracle_rms_norm_mul.argtypes = [f32p, C.c_size_t, C.c_size_t, C.c_float, f32p]
         L.oracle_silu_mul.restype = None
         L.oracle_silu_mul.argtypes = [f32p, f32p, f32p, C.c_size_t]
+        L.oracle_sigmoid_gate.restype = None
+        L.oracle_sigmoid_gate.argtypes = [f32p, f32p, C.c_size_t]
         L.oracle_logit_tail.restype = None
         L.oracle_logit_tail.argtypes = [f32p, C.c_size_t, C.c_float, C.c_float]
         L.oracle_matmul_rows.restype = C.c_int
@@ -313,6 +315,19 @@ def matmul_rows(w: "TensorView", x, rows) -> np.ndarray:
     if lib().oracle_matmul_rows(C.byref(v), _p(x), x.shape[0], idx.ctypes.data, idx.size, _p(out)) != 0:
         raise ValueError("oracle_matmul_rows rejected a row index, the shapes or the dtype")
     return out
+
+
+def sigmoid_gate(x, gate) -> np.ndarray:
+    """reference.rs:447-455: x * sigmoid(gate)."""
+    out, g = _f32(x).copy(), _f32(gate)
+    lib().oracle_sigmoid_gate(_p(out), _p(g), out.size)
+    return out
+
+
+def norm_residual_norm(hidden, src, w1, eps1, w2=None, eps2=0.0):
+    """reference.rs:466-490: hidden + rms_norm_mul(src, eps1, w1), and rms_norm_mul of that with (eps2, w2)."""
+    h = _f32(hidden) + rms_norm_mul(src, eps1, w1)
+    return h, (rms_norm_mul(h, eps2, w2) if w2 is not None else None)
 
 
 def silu_mul(gate, up) -> np.ndarray:
