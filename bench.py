@@ -187,7 +187,8 @@ def run_gpu(args):
     # weights: seeded N(0, 0.02), quantized on the device, repacked into this rank's shard
     projs = layer_projections()
     tokens_all = sorted(set(TOKEN_COUNTS) | set(SKINNY_TOKENS))
-    layer = workloads.DecodeLayer(ctx, kern, plan, tokens_all, dev, all_reduce=all_reduce, autotune=not args.no_autotune)
+    layer = workloads.DecodeLayer(ctx, kern, plan, tokens_all, dev, all_reduce=all_reduce, autotune=not args.no_autotune,
+                                  fuse_all_reduce=bool(collective and collective.oneshot and not args.no_fused_all_reduce))
     launches_per_step = layer.launches_per_pass * len(TOKEN_COUNTS)
 
     def step():
@@ -442,7 +443,9 @@ def run_gpu(args):
             "config": workload_config(world),
             "run": {"launch": f"CUDA graph replays of {per_graph} step(s) each" if graphed else "plain launches",
                     "schedule": "per token count: q|k|v grouped, o, gate|up grouped, down; one stream",
-                    "collective": collective.kind if collective else None},
+                    "collective": collective.kind if collective else None,
+                    "row_parallel": ("projection kernel pushes its partial sums to the peers, a second kernel gathers" if layer.fuse_all_reduce
+                                     else "projection, then all-reduce") if collective else None},
             "roofline": {"bound": "hbm", "achieved": value, "peak": peak * world, "unit": "GB/s", "frac": value / (peak * world),
                          "traffic": MEASURED_STEP_TRAFFIC_BYTES if world == 1 else None, "traffic_per": f"step ({launches_per_step} launches)",
                          "algorithmic_bytes_per_step": step_bytes(2), "peak_kind": f"of {peak_kind}",
@@ -553,6 +556,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="token chunks per row-parallel projection in prefill_layers (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels one by one instead of as a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg through host buffers")
+    ap.add_argument("--no-fused-all-reduce", action="store_true", help="N > 1: projection, then all-reduce, as two calls")
     ap.add_argument("--no-autotune", action="store_true", help="launch plans from the cost model alone (no measuring at load time)")
     ap.add_argument("--lead-seconds", type=float, default=0.5, help="untimed replays under the clock sampler right before the timed region")
     args = ap.parse_args()

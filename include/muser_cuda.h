@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MUSER_CUDA_ABI_VERSION 2u
+#define MUSER_CUDA_ABI_VERSION 3u
 
 #if defined(__GNUC__)
 #define MUSER_CUDA_API __attribute__((visibility("default")))
@@ -91,6 +91,12 @@ typedef struct muser_cuda_epilogue {
     float out_scale;          /* LM-head tail (src/reference.rs:559-570): every output is multiplied by out_scale
                                * (0 is read as 1, so a zeroed struct changes nothing) ... */
     float softcap;            /* ... and, when softcap > 0, becomes softcap * tanh(y / softcap); both before the residual */
+    uint32_t all_reduce;      /* muser_cuda_quantized_matmul on a K-sharded weight (row-parallel o_proj, down_proj): 1 = y is one
+                               * rank's partial sum and the call also sums it over the context's communicator, leaving the
+                               * total in y on every rank (every rank makes the same call).  Up to 16 tokens of f32 the
+                               * projection kernel stores each value into all ranks' exchange cells as its row tile finishes
+                               * and a small second kernel gathers them (the transfer runs beside the projection's remaining
+                               * tiles); otherwise the projection is followed by muser_cuda_all_reduce.  0 elsewhere. */
 } muser_cuda_epilogue;
 
 typedef struct muser_cuda_weight_info {

@@ -5,7 +5,7 @@
 
 use std::os::raw::{c_char, c_int, c_void};
 
-pub const MUSER_CUDA_ABI_VERSION: u32 = 2;
+pub const MUSER_CUDA_ABI_VERSION: u32 = 3;
 
 pub const MUSER_DTYPE_F32: u32 = 0;
 pub const MUSER_DTYPE_F16: u32 = 1;
@@ -75,6 +75,7 @@ pub struct muser_cuda_epilogue {
     pub norm_weight: *const f32,
     pub out_scale: f32,
     pub softcap: f32,
+    pub all_reduce: u32,
 }
 
 #[repr(C)]

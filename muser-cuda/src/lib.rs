@@ -224,6 +224,8 @@ pub struct Epilogue<'a> {
     pub norm: Option<(DeviceSlice<'a>, f32)>,
     pub out_scale: f32,
     pub softcap: f32,
+    /// Row-parallel projection: also sum the output over the context's communicator.
+    pub all_reduce: bool,
 }
 
 impl Default for DeviceSlice<'_> {
@@ -242,6 +244,7 @@ impl Epilogue<'_> {
             norm_weight: self.norm.map_or(ptr::null(), |n| n.0.ptr as *const f32),
             out_scale: self.out_scale,
             softcap: self.softcap,
+            all_reduce: self.all_reduce as u32,
         }
     }
 }

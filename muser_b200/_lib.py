@@ -41,7 +41,7 @@ class Shard(C.Structure):
 
 class Epilogue(C.Structure):
     _fields_ = [("row_scale", C.c_void_p), ("residual", C.c_void_p), ("swiglu", C.c_uint32), ("norm_eps", C.c_float),
-                ("norm_weight", C.c_void_p), ("out_scale", C.c_float), ("softcap", C.c_float)]
+                ("norm_weight", C.c_void_p), ("out_scale", C.c_float), ("softcap", C.c_float), ("all_reduce", C.c_uint32)]
 
 
 class GroupItem(C.Structure):

@@ -165,8 +165,13 @@ static muser_cuda_status check_io(Ctx *ctx, const Weight *w, const void *x, uint
 
 // Public epilogue -> the launchers' form.  The fused input norm needs the whole input row, so it is refused on
 // K shards, and its weight vector must be readable with 16-byte loads.
-static muser_cuda_status take_epilogue(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e) {
+static muser_cuda_status take_epilogue(Ctx *ctx, const Weight *w, const muser_cuda_epilogue *ep, Epilogue *e, bool may_all_reduce = false) {
     if (!ep) return MUSER_CUDA_OK;
+    if (ep->all_reduce) {
+        if (!may_all_reduce) return fail(ctx, MUSER_CUDA_BAD_ARG, "all_reduce is honoured by muser_cuda_quantized_matmul only; elsewhere call muser_cuda_all_reduce after the projection");
+        if (!ctx->comm) return fail(ctx, MUSER_CUDA_BAD_ARG, "all_reduce needs a communicator on this context (muser_cuda_ctx_comm_init / _attach)");
+        e->all_reduce = true;
+    }
     e->row_scale = ep->row_scale;
     e->residual = ep->residual;
     if (!(ep->out_scale == ep->out_scale) || !(ep->softcap >= 0.0f)) return fail(ctx, MUSER_CUDA_BAD_ARG, "out_scale / softcap must be numbers, softcap non-negative");
@@ -395,7 +400,7 @@ muser_cuda_status muser_cuda_quantized_matmul(muser_cuda_ctx *c, const muser_cud
     if (tokens > 64) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "quantized_matmul serves 1..64 tokens per call");
     if (ep && ep->swiglu) return fail(ctx, MUSER_CUDA_BAD_ARG, "use muser_cuda_ffn_gate_up_silu for the fused K-quant gate/up");
     Epilogue e;
-    st = take_epilogue(ctx, w, ep, &e);
+    st = take_epilogue(ctx, w, ep, &e, true);
     if (st != MUSER_CUDA_OK) return st;
     MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return launch_kquant_matmul(ctx, w, nullptr, x, x_dtype, y, y_dtype, tokens, e, (cudaStream_t)stream);

@@ -83,6 +83,7 @@ struct OneShotArgs {
     uint8_t *peer[kMaxRanks];
     float *buf;
     uint32_t count, rank, world;
+    uint32_t push; // 0: the values were pushed by the kernel that produced them (fused projection epilogue)
     int *status;
 };
 
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(256) oneshot_all_reduce_kernel(const OneShotAr
     DeviceCells mem;
     // a thread that gives up stops there: its remaining outputs keep the rank's own partial sums
     if (xchg::exchange_elements(mem, reinterpret_cast<xchg::Cell *const *>(a.peer), a.rank, a.world, seq_s, a.buf, begin, end, tid, 256,
-                                kOneShotWaitLimit) != 0)
+                                kOneShotWaitLimit, a.push != 0) != 0)
         atomicExch(a.status + 1, xchg::kGaveUp);
 }
 
@@ -181,6 +182,26 @@ void comm_destroy(Ctx *ctx) {
     if (cm->own_nccl && cm->nccl) cm->api->CommDestroy(cm->nccl);
     delete cm;
     ctx->comm = nullptr;
+}
+
+// For a projection that pushes its partial sums itself: where they go (null when this context cannot: no peer
+// buffers, or a payload beyond the one-shot limit), and the second half of the all-reduce, which only gathers.
+bool oneshot_push_target(Ctx *ctx, uint64_t count, OneShotPush *out) {
+    Comm *cm = reinterpret_cast<Comm *>(ctx->comm);
+    if (!cm || !cm->oneshot || count * 4 > std::min(cm->oneshot_max_bytes, ctx->oneshot_max_bytes)) return false;
+    for (uint32_t p = 0; p < kMaxRanks; ++p) out->peer[p] = cm->peer[p];
+    out->seq = reinterpret_cast<const uint32_t *>(cm->peer[cm->rank] + kCellBytes);
+    out->rank = cm->rank, out->world = cm->world;
+    return true;
+}
+
+cudaError_t launch_oneshot_gather(Ctx *ctx, float *buf, uint64_t count, cudaStream_t stream) {
+    Comm *cm = reinterpret_cast<Comm *>(ctx->comm);
+    OneShotArgs a;
+    for (uint32_t p = 0; p < kMaxRanks; ++p) a.peer[p] = cm->peer[p];
+    a.buf = buf, a.count = (uint32_t)count, a.rank = cm->rank, a.world = cm->world, a.push = 0, a.status = ctx->dev_status;
+    const uint32_t ctas = ((uint32_t)count + kOneShotChunkElems - 1) / kOneShotChunkElems;
+    return launch_pdl(oneshot_all_reduce_kernel, dim3(ctas), dim3(256), 0, stream, a);
 }
 
 } // namespace muser
@@ -271,6 +292,7 @@ muser_cuda_status muser_cuda_all_reduce(muser_cuda_ctx *c, void *buf, uint64_t c
         a.count = (uint32_t)count;
         a.rank = cm->rank;
         a.world = cm->world;
+        a.push = 1;
         a.status = ctx->dev_status;
         const uint32_t ctas = ((uint32_t)count + kOneShotChunkElems - 1) / kOneShotChunkElems;
         MUSER_CUDA_TRY(ctx, launch_pdl(oneshot_all_reduce_kernel, dim3(ctas), dim3(256), 0, stream, a));

@@ -146,6 +146,16 @@ template <typename T> struct PerDevice {
 };
 
 // ---- launchers implemented in the .cu files ---------------------------------------------------
+// Where a projection kernel pushes its f32 partial sums for the one-shot all-reduce (oneshot_exchange.h): every
+// rank's cell buffer, this rank's per-chunk sequence numbers (read, not bumped: the gathering kernel does that).
+struct OneShotPush {
+    uint8_t *peer[8];
+    const uint32_t *seq;
+    uint32_t rank, world;
+};
+bool oneshot_push_target(Ctx *, uint64_t count, OneShotPush *out);
+cudaError_t launch_oneshot_gather(Ctx *, float *buf, uint64_t count, cudaStream_t);
+
 struct Epilogue {
     const float *row_scale = nullptr;
     const void *residual = nullptr;
@@ -153,6 +163,7 @@ struct Epilogue {
     float norm_eps = 0.0f;
     float out_scale = 1.0f;             // LM-head tail (reference.rs:559-570): y <- y * out_scale,
     float softcap = 0.0f;               // then, if > 0, y <- softcap * tanh(y / softcap)
+    bool all_reduce = false;            // the output is one rank's partial sum: sum it over the context's communicator
 };
 
 #ifdef __CUDACC__
@@ -177,7 +188,8 @@ cudaError_t launch_kquant_tc(Ctx *, const Weight *w, const void *x, uint32_t x_d
 muser_cuda_status decode_autotune(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, uint32_t max_tokens, cudaStream_t);
 cudaError_t launch_kquant_decode(Ctx *, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
-                                 const Epilogue *ep, cudaStream_t, unsigned long long *amax_keys = nullptr, unsigned int *amax_flags = nullptr);
+                                 const Epilogue *ep, cudaStream_t, unsigned long long *amax_keys = nullptr, unsigned int *amax_flags = nullptr,
+                                 const OneShotPush *push = nullptr);
 cudaError_t launch_lm_head_argmax(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *logits, uint32_t logits_dtype,
                                   uint32_t tokens, const Epilogue &ep, uint32_t *out_index, float *out_value, uint32_t *out_nonfinite,
                                   cudaStream_t);

@@ -31,6 +31,7 @@
 
 #include "common.cuh"
 #include "kquant_layout.cuh"
+#include "oneshot_exchange.h"
 #include "rmsnorm.cuh"
 
 namespace muser {
@@ -68,6 +69,7 @@ struct DecArgs {
     uint32_t n_in, nsb, k_off, tokens, x_f32, ksplit, max_tiles, ring /* tiles in flight per warp: 2 or 4 */;
     uint32_t slot_bytes; // bytes of one ring slot: the largest tile among the launch's jobs
     uint32_t wsplit;     // warps of a CTA that share one row tile, each with a part of the CTA's K slice (1: none)
+    OneShotPush push;    // PUSH kernels only: job 0's f32 outputs also go to every rank's all-reduce cells as they finish
 };
 
 namespace dec {
@@ -451,7 +453,14 @@ __device__ __forceinline__ unsigned long long amax_key(float v, uint32_t row) {
     return (unsigned long long)u << 32 | (0xFFFFFFFFu - row);
 }
 
-template <int DT, int NG, bool DUAL, bool AMAX = false>
+// The store half of the one-shot all-reduce's device memory policy (collective.cu has the whole of it).
+struct PushCells {
+    __device__ __forceinline__ void store(xchg::Cell *p, uint32_t bits, uint32_t seq) {
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(seq) : "memory");
+    }
+};
+
+template <int DT, int NG, bool DUAL, bool AMAX = false, bool PUSH = false>
 __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t group, uint32_t slice, uint4 *dyn, float *inv_rms) {
     using Regs = typename RegsOf<DT>::type;
     constexpr int kBytes = Fmt<DT>::kTileBytes, kImages = DUAL ? 2 : 1, TOK = 4 * NG;
@@ -619,6 +628,15 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
                     } else {
                         if (jb.residual) r += reinterpret_cast<const float *>(jb.residual)[o];
                         if (!AMAX || jb.y) reinterpret_cast<float *>(jb.y)[o] = r;
+                        if constexpr (PUSH) {
+                            // the row-parallel projection's partial sum leaves for every rank the moment it exists:
+                            // the transfer over NVLink runs beside the rest of this kernel's tiles, and the kernel
+                            // that follows only gathers.  The call's sequence number is the one that kernel will
+                            // take: this chunk's counter + 1.
+                            PushCells cells;
+                            const uint32_t e = (uint32_t)o, seq = a.push.seq[e / xchg::kChunkElems] + 1;
+                            xchg::push_element(cells, reinterpret_cast<xchg::Cell *const *>(a.push.peer), a.push.rank, a.push.world, seq, e, r);
+                        }
                     }
                     if constexpr (AMAX) {
                         const unsigned long long key = amax_key(r, row);
@@ -670,12 +688,13 @@ __global__ void __launch_bounds__(dec::max_warps(NG) * 32, dec::ctas_per_sm(NG))
         if (i < a.n_jobs && blockIdx.x >= a.job[i].cta0) ji = i;
     const DecJob &jb = a.job[ji];
     const uint32_t local = blockIdx.x - jb.cta0, slice = local % a.ksplit, group = local / a.ksplit;
-    constexpr bool AMAX = FAM >= 2; // FAM 2, 3: FAM 0, 1 with the fused greedy pick over the output rows (the LM head)
+    constexpr bool AMAX = FAM == 2 || FAM == 3; // FAM 0, 1 with the fused greedy pick over the output rows (the LM head)
+    constexpr bool PUSH = FAM == 4;             // FAM 0 whose f32 outputs are also pushed into the all-reduce's cells
     if constexpr ((FAM & 1) == 1) {
-        dec::run<MUSER_DTYPE_Q5_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
+        dec::run<MUSER_DTYPE_Q5_K, NG, DUAL, AMAX, PUSH>(a, jb, group, slice, dec_dyn, inv_rms);
     } else {
-        if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
-        else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL, AMAX>(a, jb, group, slice, dec_dyn, inv_rms);
+        if (jb.dtype == MUSER_DTYPE_Q4_K) dec::run<MUSER_DTYPE_Q4_K, NG, DUAL, AMAX, PUSH>(a, jb, group, slice, dec_dyn, inv_rms);
+        else dec::run<MUSER_DTYPE_Q6_K, NG, DUAL, AMAX, PUSH>(a, jb, group, slice, dec_dyn, inv_rms);
     }
 }
 
@@ -903,7 +922,8 @@ cudaError_t dec_launch(DecArgs &a, Ctx *ctx, const DecPlan &forced, cudaStream_t
 // w_up: the fused gate/up form (one job).  Returns cudaErrorNotSupported when the shape does not fit this kernel.
 cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight *w_up, uint32_t n_jobs, const void *x,
                                  uint32_t x_dtype, void *const *y, const uint32_t *y_dtype, uint32_t tokens,
-                                 const Epilogue *ep, cudaStream_t stream, unsigned long long *amax_keys, unsigned int *amax_flags) {
+                                 const Epilogue *ep, cudaStream_t stream, unsigned long long *amax_keys, unsigned int *amax_flags,
+                                 const OneShotPush *push) {
     if (n_jobs == 0 || n_jobs > (uint32_t)kDecMaxJobs || tokens == 0 || tokens > 16 || w[0]->nsb > 4096) return cudaErrorNotSupported;
     DecArgs a;
     a.n_jobs = n_jobs;
@@ -937,11 +957,22 @@ cudaError_t launch_kquant_decode(Ctx *ctx, const Weight *const *w, const Weight 
     a.k_off = w[0]->k_off;
     a.tokens = tokens;
     a.ksplit = 1, a.max_tiles = 0, a.ring = 2, a.slot_bytes = kQ6TileBytes, a.wsplit = 1;
+    a.push = OneShotPush{};
     const DecPlan forced{(int)ctx->dec_warps, (int)ctx->dec_ksplit, (int)ctx->dec_ring, (int)ctx->dec_wsplit};
     const uint32_t ng = (tokens + 3) / 4;
     uint32_t n_q5 = 0;
     for (uint32_t i = 0; i < n_jobs; ++i) n_q5 += w[i]->dtype == MUSER_DTYPE_Q5_K;
     if (n_q5 != 0 && (n_q5 != n_jobs || w_up)) return cudaErrorNotSupported; // Q5_K jobs run in launches of their own, unfused
+    if (push) { // one row-parallel projection whose f32 partial sums go straight into the all-reduce's cells
+        if (n_jobs != 1 || w_up || n_q5 || amax_keys || y_dtype[0] != MUSER_DTYPE_F32) return cudaErrorNotSupported;
+        a.push = *push;
+        switch (ng) {
+        case 1: return dec_launch<1, false, 4>(a, ctx, forced, stream);
+        case 2: return dec_launch<2, false, 4>(a, ctx, forced, stream);
+        case 3: return dec_launch<3, false, 4>(a, ctx, forced, stream);
+        default: return dec_launch<4, false, 4>(a, ctx, forced, stream);
+        }
+    }
     if (amax_keys) { // the LM head with the fused greedy pick: one projection
         if (n_jobs != 1 || w_up || !amax_flags) return cudaErrorNotSupported;
         if (n_q5) {
@@ -1184,6 +1215,25 @@ muser_cuda_status launch_kquant_matmul(Ctx *ctx, const Weight *w, const Weight *
                 return MUSER_CUDA_OK;
             }
         }
+    }
+    if (ep.all_reduce) {
+        // A row-parallel projection: y is one rank's partial sum.  Up to 16 tokens of f32 the decode kernel pushes
+        // every value into all ranks' exchange cells as its row tile finishes, and a second, small kernel gathers
+        // and adds them: the transfer runs beside the projection's remaining tiles.  Otherwise projection, then all-reduce.
+        Epilogue plain = ep;
+        plain.all_reduce = false;
+        OneShotPush push;
+        const uint64_t count = (uint64_t)tokens * w->n_out;
+        if (!tc_fits && !w_up && tokens <= 16 && y_dtype == MUSER_DTYPE_F32 && w->dtype != MUSER_DTYPE_Q5_K && oneshot_push_target(ctx, count, &push)) {
+            const cudaError_t de = launch_kquant_decode(ctx, &w, nullptr, 1, x, x_dtype, &y, &y_dtype, tokens, &plain, stream, nullptr, nullptr, &push);
+            if (de == cudaErrorNotSupported) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "this shape does not fit the decode kernel");
+            MUSER_CUDA_TRY(ctx, de);
+            MUSER_CUDA_TRY(ctx, launch_oneshot_gather(ctx, reinterpret_cast<float *>(y), count, stream));
+            return MUSER_CUDA_OK;
+        }
+        const muser_cuda_status st = launch_kquant_matmul(ctx, w, w_up, x, x_dtype, y, y_dtype, tokens, plain, stream);
+        if (st != MUSER_CUDA_OK) return st;
+        return muser_cuda_all_reduce(reinterpret_cast<muser_cuda_ctx *>(ctx), y, count, y_dtype, stream);
     }
     const size_t xb = xf32 ? 4 : 2, yb = y_dtype == MUSER_DTYPE_BF16 ? 2 : 4;
     for (uint32_t t0 = 0; t0 < tokens; t0 += 16) {

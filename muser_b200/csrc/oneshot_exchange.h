@@ -44,16 +44,22 @@ MUSER_XCHG size_t cell_index(uint32_t slot, uint32_t sender, uint32_t i) { retur
 
 // Mem supplies: void store(Cell *, uint32_t bits, uint32_t seq); Cell load(const Cell *); void pause(uint32_t polls_so_far);
 // float get(const float *); void put(float *, float)  (how the payload itself is read and written).
-// Elements first, first + stride, ... of [begin, end) are this caller's.
+// One value of this rank into cell (seq & 1, rank, i) of every rank's buffer.
+template <class Mem>
+MUSER_XCHG void push_element(Mem &mem, Cell *const *peer, uint32_t rank, uint32_t world, uint32_t seq, uint32_t i, float value) {
+    union { float f; uint32_t u; } v;
+    v.f = value;
+    for (uint32_t p = 0; p < world; ++p) mem.store(peer[p] + cell_index(seq & 1u, rank, i), v.u, seq);
+}
+
+// Elements first, first + stride, ... of [begin, end) are this caller's.  push = false: the values of this call
+// were pushed earlier by whoever produced them (the projection kernel's epilogue), this rank's own included.
 template <class Mem>
 MUSER_XCHG int exchange_elements(Mem &mem, Cell *const *peer, uint32_t rank, uint32_t world, uint32_t seq, float *buf, uint32_t begin,
-                                 uint32_t end, uint32_t first, uint32_t stride, uint32_t wait_limit) {
+                                 uint32_t end, uint32_t first, uint32_t stride, uint32_t wait_limit, bool push = true) {
     const uint32_t slot = seq & 1u;
-    for (uint32_t i = begin + first; i < end; i += stride) {
-        union { float f; uint32_t u; } v;
-        v.f = mem.get(buf + i);
-        for (uint32_t p = 0; p < world; ++p) mem.store(peer[p] + cell_index(slot, rank, i), v.u, seq);
-    }
+    if (push)
+        for (uint32_t i = begin + first; i < end; i += stride) push_element(mem, peer, rank, world, seq, i, mem.get(buf + i));
     const Cell *mine = peer[rank];
     for (uint32_t i = begin + first; i < end; i += stride) {
         float sum = 0.0f;

@@ -157,16 +157,16 @@ def _row_bytes(dtype: int, n_in: int) -> int:
     raise MuserCudaError(4, f"dtype {dtype} has no CUDA projection kernel")
 
 
-def _epilogue(row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0, softcap=0.0):
+def _epilogue(row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0, softcap=0.0, all_reduce=False):
     """muser_cuda_epilogue; `norm_weight` (f32 [n_in], device) fuses rms_norm_mul(x, eps, norm_weight) in front,
     `out_scale` / `softcap` the LM-head tail y <- softcap * tanh(y * out_scale / softcap) behind."""
-    if row_scale is None and residual is None and norm_weight is None and out_scale == 1.0 and softcap == 0.0:
+    if row_scale is None and residual is None and norm_weight is None and out_scale == 1.0 and softcap == 0.0 and not all_reduce:
         return None
     if norm_weight is not None and norm_weight.dtype != torch.float32:
         raise MuserCudaError(1, "norm_weight must be f32")
     return _lib.Epilogue(row_scale.data_ptr() if row_scale is not None else None,
                          residual.data_ptr() if residual is not None else None, 0, float(norm_eps),
-                         norm_weight.data_ptr() if norm_weight is not None else None, float(out_scale), float(softcap))
+                         norm_weight.data_ptr() if norm_weight is not None else None, float(out_scale), float(softcap), int(bool(all_reduce)))
 
 
 class CudaKernels:
@@ -188,13 +188,14 @@ class CudaKernels:
 
     def encode_quantized_matmul(self, weights: Weight, input: torch.Tensor, output: torch.Tensor, tokens: int,
                                 row_scale=None, residual=None, norm_weight=None, norm_eps=0.0, out_scale=1.0,
-                                softcap=0.0) -> None:
-        """y[t][r] = dot(W_r, x_t) for K-quant weights; input [tokens][n_in] f32|bf16, output [tokens][n_out] f32|bf16."""
-        ep = _epilogue(row_scale, residual, norm_weight, norm_eps, out_scale, softcap)
+                                softcap=0.0, all_reduce=False) -> None:
+        """y[t][r] = dot(W_r, x_t) for K-quant weights; input [tokens][n_in] f32|bf16, output [tokens][n_out] f32|bf16.
+        all_reduce: the weight is a K shard; the call also sums the output over the context's communicator."""
+        ep = _epilogue(row_scale, residual, norm_weight, norm_eps, out_scale, softcap, all_reduce)
         self.ctx.check(_L.muser_cuda_quantized_matmul(
             self.ctx._h, weights._h, input.data_ptr(), _TORCH_DTYPE[input.dtype], output.data_ptr(),
             _TORCH_DTYPE[output.dtype], tokens, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
-        self.launches += 1
+        self.launches += 2 if all_reduce else 1
 
     def encode_quantized_matmul_group(self, weights, input: torch.Tensor, outputs, tokens: int, epilogues=None) -> None:
         """Up to four K-quant projections of the same `input` in one launch (q | k | v, or gate | up), the counterpart

@@ -79,10 +79,12 @@ class DecodeLayer:
 
     GROUPS = (("attn_q", "attn_k", "attn_v"), ("attn_o",), ("ffn_gate", "ffn_up"), ("ffn_down",))
 
-    def __init__(self, ctx, kern, plan: tp.ShardPlan, token_counts, device, all_reduce=None, seed: int = 0, autotune: bool = True):
+    def __init__(self, ctx, kern, plan: tp.ShardPlan, token_counts, device, all_reduce=None, seed: int = 0, autotune: bool = True,
+                 fuse_all_reduce: bool = False):
         self.ctx, self.kern, self.plan, self.dev = ctx, kern, plan, device
         self.projs = synth.LAYER_PROJECTIONS
         self.all_reduce = all_reduce
+        self.fuse_all_reduce = fuse_all_reduce
         self.views, self.weights, self.x, self.y = {}, {}, {}, {}
         for i, (name, (k, n, dt)) in enumerate(self.projs.items()):
             raw = synth.quantize_kquant(synth.normal_weights(n, k, seed=seed, stream=i, device=device), dt)
@@ -109,12 +111,14 @@ class DecodeLayer:
         group = self.GROUPS[gi]
         ws = weights or [self.weights[n] for n in group]
         ys = [self.y[(n, m)] for n in group]
+        reduce = self.all_reduce is not None and self.plan.needs_all_reduce(group[0])
         if len(group) == 1 or m > 16:
             for w, y in zip(ws, ys):
-                self.kern.encode_quantized_matmul(w, self.x[(gi, m)], y, m)
+                # fused: the projection pushes its partial sums to the peers itself and the call completes the sum
+                self.kern.encode_quantized_matmul(w, self.x[(gi, m)], y, m, all_reduce=reduce and self.fuse_all_reduce)
         else:
             self.kern.encode_quantized_matmul_group(ws, self.x[(gi, m)], ys, m)
-        if self.all_reduce is not None and self.plan.needs_all_reduce(group[0]):
+        if reduce and not self.fuse_all_reduce:
             self.all_reduce(ys[0])
 
     def run(self, m: int) -> None:

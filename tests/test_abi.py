@@ -35,7 +35,7 @@ def test_only_the_abi_is_exported(lib):
 
 def test_host_only_entry_points(lib):
     L = lib.lib
-    assert L.muser_cuda_abi_version() == 2
+    assert L.muser_cuda_abi_version() == 3
     for t, ok in [(lib.Q4_K, 1), (lib.Q5_K, 1), (lib.Q6_K, 1), (lib.NVFP4, 1), (lib.F16, 0), (8, 0), (1001, 0)]:
         assert L.muser_cuda_supports_projection(t) == ok
     # [rows/128][n_in/64][32][4][4]

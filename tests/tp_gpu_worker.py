@@ -85,6 +85,39 @@ def main():
         got = layer.y[("attn_k", m)].cpu().numpy()
         assert float(np.linalg.norm(got - ref) / np.linalg.norm(ref)) <= 1e-3
 
+    # 3b. the fused form: the row-parallel projection pushes its partial sums to the peers itself (all_reduce in its
+    #     epilogue) and a small kernel gathers.  Same values in the same rank order as projection + all-reduce, so the
+    #     outputs must carry the same bits, on every rank, also when replayed from a CUDA graph and when interleaved
+    #     with plain all-reduces (the sequence numbers are shared).
+    separate = {(n, m): layer.y[(n, m)].clone() for n in ("attn_o", "ffn_down") for m in (1, 8)}
+    fused_layer = workloads.DecodeLayer(ctx, kern, plan, (1, 8), dev, all_reduce=coll.all_reduce_sum, fuse_all_reduce=True, autotune=False)
+    for m in (1, 8):
+        fused_layer.run(m)
+        coll.all_reduce_sum(buf)          # a plain all-reduce in between
+        fused_layer.run(m)
+        ctx.sync_status()
+        for n in ("attn_o", "ffn_down"):
+            got = fused_layer.y[(n, m)]
+            assert torch.equal(got.view(torch.int32), separate[(n, m)].view(torch.int32)), (n, m, float((got - separate[(n, m)]).abs().max()))
+            gathered = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(gathered, got)
+            assert all(torch.equal(gathered[0], t) for t in gathered)
+    replay_layer = workloads.capture(lambda: fused_layer.run(8))
+    for n in ("attn_o", "ffn_down"):
+        fused_layer.y[(n, 8)].fill_(float("nan"))
+    for _ in range(3):
+        replay_layer()
+    ctx.sync_status()
+    for n in ("attn_o", "ffn_down"):
+        assert torch.equal(fused_layer.y[(n, 8)].view(torch.int32), separate[(n, 8)].view(torch.int32)), n
+    # bf16 outputs and more than 16 tokens fall back to projection + all-reduce inside the same call
+    k_o, n_o, _ = layer.projs["attn_o"]
+    xo = fused_layer.x[(1, 8)]
+    yb = torch.empty((8, n_o), dtype=torch.bfloat16, device=dev)
+    kern.encode_quantized_matmul(fused_layer.weights["attn_o"], xo, yb, 8, all_reduce=True)
+    ctx.sync_status()
+    assert torch.allclose(yb.float(), separate[("attn_o", 8)], rtol=2e-2, atol=2e-2 * float(separate[("attn_o", 8)].abs().max()))
+
     # 4. a wait that runs out: between steps, rank 1 sits one call out.  Rank 0's kernel gives up after about a second,
     #    records its code and returns; the host reads MUSER_CUDA_TIMEOUT; the context still computes.  (Nothing faults:
     #    both processes stay alive and every buffer stays mapped.)
