@@ -634,7 +634,8 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
                             // that follows only gathers.  The call's sequence number is the one that kernel will
                             // take: this chunk's counter + 1.
                             PushCells cells;
-                            const uint32_t e = (uint32_t)o, seq = a.push.seq[e / xchg::kChunkElems] + 1;
+                            // (read past L1: the counter was bumped by a kernel that may have run beside this one's start)
+                            const uint32_t e = (uint32_t)o, seq = __ldcg(a.push.seq + e / xchg::kChunkElems) + 1;
                             xchg::push_element(cells, reinterpret_cast<xchg::Cell *const *>(a.push.peer), a.push.rank, a.push.world, seq, e, r);
                         }
                     }

@@ -133,6 +133,6 @@ def test_a_rank_with_a_short_count(harness):
     assert np.array_equal(data[1, :short].view(np.uint32), want[:short].view(np.uint32))
     assert np.array_equal(data[1, short:], parts[1, short:])
     for r in (0, 2):
-        # chunk 0 (elements 0..2047) is complete; chunk 1 is complete up to element 2999, then stops; chunk 2 gives up at once
+        # every chunk below element 3000 is complete, the chunk that holds it stops there, the chunks behind give up at once
         assert np.array_equal(data[r, :short].view(np.uint32), want[:short].view(np.uint32)), r
         assert np.array_equal(data[r, short:].view(np.uint32), parts[r, short:].view(np.uint32)), r
