@@ -140,7 +140,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_DECODE_KSPLIT 9u      /* decode kernel: K slices (0: from its cost model) */
 #define MUSER_TUNE_DECODE_RING 10u       /* decode kernel: weight tiles in flight per warp, 2 or 4 (0: from its cost model) */
 #define MUSER_TUNE_DECODE_WSPLIT 12u      /* decode kernel: warps of a CTA that share one row tile and split K between them (0: from its cost model) */
-#define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 262144; 0: always NCCL) */
+#define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 1572864; 0: always NCCL) */
 #define MUSER_TUNE_NVFP4_PAIR 13u         /* NVFP4 GEMM: 0 one CTA per 128-token tile (default), 1 pairs of SMs on 256-token tiles (tcgen05 cta_group::2) */
 #define MUSER_TUNE_HOST_DIRECT_OUTPUT 14u /* muser_cuda_matmul_host_groups_enqueue: 1 (default) a kernel stores the outputs into pinned host buffers, 0 one cudaMemcpyAsync per output */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
@@ -362,7 +362,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_ctx_comm_attach(muser_cuda_ctx *ctx,
 MUSER_CUDA_API int muser_cuda_ctx_comm_has_oneshot(const muser_cuda_ctx *ctx);
 /* The all-reduce(sum) after a row-parallel projection (o_proj, down_proj), in place on `buf` (count elements of F32,
  * F16 or BF16), enqueued on `stream`; every rank must make the same calls in the same order.  f32 payloads up to
- * 256 KiB (a decode step's [tokens][hidden] partial sums) take a one-shot exchange over peer memory: each rank stores
+ * 1.5 MiB (a decode or verify step's [tokens][hidden] partial sums) take a one-shot exchange over peer memory: each rank stores
  * its values into every rank's buffer over NVLink, each paired with the call's sequence number, polls its own buffer
  * until every rank's values are there (bounded: a give-up is reported by muser_cuda_sync_status as
  * MUSER_CUDA_TIMEOUT, and the elements that were still waiting keep this rank's partial sums) and adds them in rank

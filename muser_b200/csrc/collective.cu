@@ -3,7 +3,7 @@
 // The reference runs one accelerator and refuses tensor parallelism (scripts/gx10/vllm/muser_vllm/connector.py:119-120),
 // so nothing here has a counterpart there.  A context can be given a communicator of `world` ranks, one process per
 // GPU of one box; muser_cuda_all_reduce then sums a buffer in place across the ranks on the caller's stream:
-//   - payloads up to 256 KiB of f32 (a decode step's [tokens][hidden] partial sums: 20 KB per token) take a one-shot
+//   - payloads up to 1.5 MiB of f32 (a decode or verify step's [tokens][hidden] partial sums: 20 KB per token) take a one-shot
 //     exchange over peer memory: every rank PUSHES each value, paired with the call's sequence number in one 8-byte
 //     store, into a cell of every rank's buffer over NVLink, then polls (bounded) its own cells until every rank's
 //     value of the call is there and adds them in rank order, so all ranks get the same bits.  No flag, no fence:

@@ -26,7 +26,7 @@ namespace muser {
 namespace xchg {
 
 constexpr uint32_t kMaxRanks = 8;
-constexpr uint32_t kMaxBytes = 256u << 10;        // f32 payload per rank and call
+constexpr uint32_t kMaxBytes = 1536u << 10;       // f32 payload per rank and call: 64 tokens x 5120 values and some room
 constexpr uint32_t kMaxElems = kMaxBytes / 4;
 constexpr uint32_t kChunkElems = 256;             // values per CTA (one per thread); each chunk has its own sequence counter
 constexpr uint32_t kMaxChunks = kMaxElems / kChunkElems;

@@ -90,7 +90,7 @@ class Collective:
         stream = torch.cuda.current_stream(dev).cuda_stream
         ctx.check(self._L.muser_cuda_ctx_comm_init(ctx._h, self._id, rank, world, stream))
         self.oneshot = bool(self._L.muser_cuda_ctx_comm_has_oneshot(ctx._h))
-        self.kind = ("library: one-shot peer exchange up to 256 KiB of f32, ncclAllReduce above" if self.oneshot
+        self.kind = ("library: one-shot peer exchange up to 1.5 MiB of f32, ncclAllReduce above" if self.oneshot
                      else "library: ncclAllReduce (peer buffers could not be mapped)")
 
     def all_reduce_sum(self, partial: torch.Tensor) -> torch.Tensor:

@@ -29,7 +29,7 @@ def main():
     assert coll.oneshot, "peer buffers were not mapped: " + (op._L.muser_cuda_last_error(ctx._h) or b"").decode()
 
     # 1. sums of several sizes (one CTA, several CTAs, a ragged tail, the largest one-shot payload, one past it -> NCCL)
-    for count in (4, 5120, 5123, 8 * 5120, 65536, 65540, 1 << 20):
+    for count in (4, 5120, 5123, 8 * 5120, 65536, 393216, 393220, 1 << 20):
         g = torch.Generator(device=dev).manual_seed(100 * rank + count % 97)
         x = torch.randn(count, device=dev, generator=g)
         want = x.clone()
