@@ -8,6 +8,7 @@ algorithmic bytes, TMAC/s, and (with --check) the differential against the CPU l
     python microbench.py nvfp4  --proj ffn_gate --tokens 2048 [--reps 5]
     python microbench.py peak
     python microbench.py layers --tokens 32768 --layers 52 [--chunks 4]      (torchrun for TP > 1)
+    torchrun --nproc-per-node N microbench.py allreduce                      (the one-shot all-reduce beside NCCL)
 
 Shapes are the projections of the synthetic layer in `synth.LAYER_PROJECTIONS`.  K-quant calls rotate over
 enough weight copies to exceed L2 (126 MB) and are replayed as one CUDA graph unless --no-graph is given, so the
@@ -133,6 +134,59 @@ def run_nvfp4(args) -> None:
     print(f"total: {tot_t * 1e6:.1f} us, {tot_f / tot_t / 1e12:.1f} TFLOP/s")
 
 
+def run_allreduce(args) -> None:
+    """The library's all-reduce beside NCCL's, per payload (torchrun, 2-8 ranks): device microseconds per call, 50
+    calls replayed from a CUDA graph, the maximum over the ranks; then the tensor-parallel decode step with and
+    without its all-reduces."""
+    import os
+
+    import torch.distributed as dist
+
+    from muser_b200 import _lib
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ctx = op.Context(local, workspace_bytes=1 << 20)
+    kern = op.CudaKernels(ctx)
+    coll = tp.Collective(ctx, rank, world)
+
+    def timeit(fn, n=50, reps=5):
+        replay = workloads.capture(lambda: [fn() for _ in range(n)])
+        for _ in range(3):
+            replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([workloads.time_calls(replay, reps) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e6
+
+    if rank == 0:
+        print(f"{world} ranks; f32 payload: tokens x 5120 values\n{'tokens':>6} {'KiB':>7} {'one-shot us':>12} {'library NCCL us':>16} {'torch NCCL us':>14}", flush=True)
+    for tokens in (args.tokens or [1, 8, 16, 64]):
+        buf = torch.randn(tokens * 5120, device=dev)
+        t1 = timeit(lambda: coll.all_reduce_sum(buf))
+        ctx.tuning_set(_lib.TUNE_ONESHOT_MAX_BYTES, 0)
+        t2 = timeit(lambda: coll.all_reduce_sum(buf))
+        ctx.tuning_set(_lib.TUNE_ONESHOT_MAX_BYTES, 1536 << 10)
+        t3 = timeit(lambda: dist.all_reduce(buf))
+        if rank == 0:
+            print(f"{tokens:>6} {tokens * 20:>7} {t1:>12.2f} {t2:>16.2f} {t3:>14.2f}", flush=True)
+    layer = workloads.DecodeLayer(ctx, kern, tp.ShardPlan(rank, world), (1, 2, 4, 8), dev, all_reduce=coll.all_reduce_sum, fuse_all_reduce=True)
+    step = lambda: [layer.run(m) for m in (1, 2, 4, 8)]
+    t_fused = timeit(step, n=1, reps=50)
+    layer.fuse_all_reduce = False
+    t_sep = timeit(step, n=1, reps=50)
+    layer.all_reduce = None
+    t_none = timeit(step, n=1, reps=50)
+    if rank == 0:
+        print(f"decode step (M = 1, 2, 4, 8): {t_fused:.1f} us with the partial sums pushed by the projection kernels, {t_sep:.1f} us with "
+              f"projection then all-reduce, {t_none:.1f} us without any all-reduce", flush=True)
+    ctx.sync_status()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
 def run_layers(args) -> None:
     """The linear layers of a prefill pass: `--layers` decoder layers x 7 NVFP4 projections at `--tokens` tokens
     (workloads.PrefillLayer), tensor-parallel over the ranks torchrun started, with one all-reduce after o_proj and
@@ -177,7 +231,7 @@ def run_layers(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["kquant", "groups", "lmhead", "nvfp4", "peak", "layers"])
+    ap.add_argument("what", choices=["kquant", "groups", "lmhead", "nvfp4", "peak", "layers", "allreduce"])
     ap.add_argument("--layers", type=int, default=52)
     ap.add_argument("--chunks", type=int, default=4, help="token chunks per row-parallel projection (TP > 1)")
     ap.add_argument("--proj", type=lambda s: s.split(","), default=list(synth.LAYER_PROJECTIONS))
@@ -198,6 +252,8 @@ def main(argv=None) -> None:
     elif args.what == "nvfp4":
         args.tokens = args.tokens or [2048]
         run_nvfp4(args)
+    elif args.what == "allreduce":
+        run_allreduce(args)
     elif args.what == "layers":
         args.tokens = args.tokens or [32768]
         run_layers(args)
