@@ -104,6 +104,9 @@ def run_lmhead(args) -> None:
 def run_nvfp4(args) -> None:
     ctx = op.Context(0, workspace_bytes=1 << 30)
     kern = op.CudaKernels(ctx)
+    if args.form is not None:
+        from muser_b200._lib import TUNE_NVFP4_PAIR
+        ctx.tuning_set(TUNE_NVFP4_PAIR, args.form)
     print(f"{'shape':<28} {'tokens':>6} {'gemm us':>9} {'TFLOP/s':>9} {'quant us':>9} {'rel_l2':>10}")
     tot_f = tot_t = 0.0
     for name in args.proj:
@@ -239,6 +242,8 @@ def main(argv=None) -> None:
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--check", action="store_true", help="compare with the CPU lane (oracle/)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--form", type=int, default=None, choices=[0, 1, 2],
+                    help="nvfp4: 0 one CTA per tile, 1 pairs of SMs on one tile, 2 two CTAs sharing their weight rows")
     args = ap.parse_args(argv)
     if args.what == "kquant":
         args.tokens = args.tokens or [1, 2, 4, 8]
