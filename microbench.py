@@ -242,8 +242,7 @@ def main(argv=None) -> None:
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--check", action="store_true", help="compare with the CPU lane (oracle/)")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--form", type=int, default=None, choices=[0, 1, 2],
-                    help="nvfp4: 0 one CTA per tile, 1 pairs of SMs on one tile, 2 two CTAs sharing their weight rows")
+    ap.add_argument("--form", type=int, default=None, choices=[0, 1], help="nvfp4: 0 one CTA per tile, 1 pairs of SMs on one tile")
     args = ap.parse_args(argv)
     if args.what == "kquant":
         args.tokens = args.tokens or [1, 2, 4, 8]
