@@ -34,10 +34,39 @@
 
 namespace muser {
 
+// Development aid, compiled in only with -DMUSER_GEMM_WAIT_PROFILE: some roles of the first CTAs add up the SM cycles
+// they spend in each kind of wait, and a debug entry point copies the sums out.
+#ifdef MUSER_GEMM_WAIT_PROFILE
+__device__ unsigned long long g_tc_wait_prof[4 * 8 * 4]; // [cta < 4][role < 8][slot < 4]
+#define TPROF_DECL long long prof_t0 = 0, prof_start = clock64(); unsigned long long prof_acc[3] = {0, 0, 0};
+#define TPROF_BEGIN prof_t0 = clock64();
+#define TPROF_END(i) prof_acc[i] += (unsigned long long)(clock64() - prof_t0);
+#define TPROF_FLUSH(role)                                                                                 \
+    if (blockIdx.x < 4) {                                                                                 \
+        for (int i_ = 0; i_ < 3; ++i_) g_tc_wait_prof[(blockIdx.x * 8 + (role)) * 4 + i_] = prof_acc[i_]; \
+        g_tc_wait_prof[(blockIdx.x * 8 + (role)) * 4 + 3] = (unsigned long long)(clock64() - prof_start); \
+    }
+__device__ unsigned long long g_tc_stamps[8]; // ns: prepare first start, last end; GEMM first entry, CTA 0 set up, last loop end, last exit
+__device__ __forceinline__ unsigned long long tprof_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TPROF_STAMP_MIN(i) atomicMin(&g_tc_stamps[i], tprof_ns());
+#define TPROF_STAMP_MAX(i) atomicMax(&g_tc_stamps[i], tprof_ns());
+#else
+#define TPROF_STAMP_MIN(i)
+#define TPROF_STAMP_MAX(i)
+#define TPROF_DECL
+#define TPROF_BEGIN
+#define TPROF_END(i)
+#define TPROF_FLUSH(role)
+#endif
+
 constexpr int kTcRows = 128;             // weight rows per block = MMA M
-constexpr int kTcStages = 2;             // A stages of 128 inputs each (the unpacked weights are the expensive bytes)
-constexpr int kTcABytes = kTcRows * 256; // 128 rows x 128 f16: two 64-column swizzle atoms of 16 KiB
-constexpr int kTcDequantWarps = 16;           // warp = (row tile of the block, upper / lower eight rows)
+constexpr int kTcStagesA = 8;            // A stages in tensor memory: the four 64-input quarters of two super-block columns
+constexpr int kTcStageCols = 32;         // 64 inputs as f16 pairs
+constexpr int kTcDequantWarps = 16;      // warp = (column parity, half of the column, 32-row quarter of the block)
 
 struct TcArgs {
     const uint8_t *image;
@@ -100,6 +129,32 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with the A operand in tensor memory: lane = row, eight 32-bit columns = 16 f16 along K.
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Issued by the elected lane of a converged warp (tcgen05.cuh).
+__device__ __forceinline__ void mma_f16_elect(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t" MUSER_ELECT_PRED
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_elect(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t" MUSER_ELECT_PRED
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // K-major operand, 32 bytes (16 f16) per row, 32-byte swizzle, 8-row groups 256 bytes apart.
 __device__ __forceinline__ uint64_t operand_desc32(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -134,13 +189,40 @@ __device__ __forceinline__ __half2 byte_pair(uint32_t w, uint32_t idx, float bia
     return __hsub2(u2h(m), __float2half2_rn(bias));
 }
 
+// ------------------------------------------------------------------------------------ weights -> A operand
+// The A operand lives in TENSOR memory, not in shared memory: TMEM lane = weight row of the 128-row block, and a
+// 32-bit column of a lane holds two consecutive inputs as f16 (tcgen05.mma with A from tensor memory reads K = 16 from
+// eight columns).  An unpacking thread therefore owns one ROW: it reads that row's bytes of a weight tile straight
+// from global memory (streaming loads; its warp's 32 rows make whole 512-byte runs), turns them into the f16 integers
+// and writes 32 columns (64 inputs = one A stage) with one tcgen05.st.  Shared memory carries only the activations:
+// with the operand in shared memory the stage stores, the MMA's reads of them and the raw-tile rings together asked
+// the SM's shared-memory pipe for ~200 KB per super-block column, which is what bounded that kernel.
+__device__ __forceinline__ uint4 ldg_stream128(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream64(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------ Q4_K
-// What one unpacking warp holds of a tile: rows g (+ 8 * rowsel, rowsel fixed per warp), lane (g, t).
-// Its ring slot is [2 planes of 512 bytes: sub-blocks 0-3 and 4-7, this lane's eight elements of each][8 row headers].
-constexpr int kTcQ4Slot = 1024 + 128, kTcQ6Slot = 1024 + 512 + 128 + 16;
+// One row's 128 inputs of one half of a super-block (kquant_layout.cuh: uint4 (2 * rowsel + half, lane = 4 g + t),
+// word jj = sub-block 4 * half + jj, elements 8t .. 8t + 7) and the row's header.
 struct TcQ4 {
-    uint4 q[2]; // [half]: word jj = sub-block 4*half + jj, elements 8t .. 8t+7
-    uint4 h;    // the row's header
+    uint4 c[4]; // [t]
+    uint4 h;
 };
 struct TcQ4Hdr {
     float d, dmin;
@@ -157,85 +239,78 @@ __device__ __forceinline__ TcQ4Hdr tc_q4_hdr(uint4 h) {
     s.mn[1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
     return s;
 }
-__device__ __forceinline__ TcQ4 tc_load(const uint8_t *slot, int lane, TcQ4 *) {
+// `tile`: the 16-row tile of this thread's row; r16: the row inside it.
+__device__ __forceinline__ TcQ4 tc_fetch(const uint8_t *tile, uint32_t half, uint32_t r16, TcQ4 *) {
     TcQ4 r;
-    const uint4 *q = reinterpret_cast<const uint4 *>(slot);
-    r.q[0] = q[lane];
-    r.q[1] = q[32 + lane];
-    r.h = reinterpret_cast<const uint4 *>(slot + 1024)[lane >> 2];
+    const uint8_t *p = tile + (2 * (r16 >> 3) + half) * 512 + (r16 & 7) * 64;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) r.c[t] = ldg_stream128(p + 16 * t);
+    r.h = ldg_stream128(tile + 2048 + r16 * 16);
     return r;
 }
-// Inputs 128*HALF .. +127 of row `row` (a multiple of 8 plus g) -> the A stage: sc * q as f16.
-// Column layout (kquant_layout.cuh): word jj of r.q[HALF] holds elements 8t .. 8t+7 of sub-block 4*HALF + jj, i.e.
-// the 16-byte chunk 4*jj + t of the row's 128 inputs: atom jj / 2, chunk (jj % 2) * 4 + t inside it.
-template <int HALF>
-__device__ __forceinline__ void tc_unpack_half(const TcQ4 &r, const TcQ4Hdr &hd, uint32_t stage, uint32_t row, int g, int t) {
-    const uint32_t base = stage + (row >> 3) * 1024u + (row & 7) * 128u;
-    // In one store instruction the lanes of rows g and g + 1 would write the same four chunks of two rows, i.e. the
-    // same banks; odd rows therefore take their words in the order 1, 0, 3, 2, which puts them in the other half of
-    // the 128-byte row and makes the warp's stores conflict-free.
-    const uint32_t odd = (uint32_t)g & 1u;
-    uint4 qv = r.q[HALF];
-    if (odd) qv = make_uint4(qv.y, qv.x, qv.w, qv.z);
+// Sub-block JJ of the half (32 inputs) -> 16 columns, sc * q as exact f16 integers.
+// (word >> 4p) & 0x000F000F is the pair of elements (2p, 2p + 1); the nibbles at bits 4-7 / 20-23 are not shifted
+// down: 0x6400 | (q << 4) is 1024 + 16 q, and the fused multiply-add with sc / 16 and -64 sc gives sc * q just as
+// exactly (one rounding, of an integer below 2048).
+template <int JJ>
+__device__ __forceinline__ void tc_unpack(const TcQ4 &r, uint32_t scw, uint32_t (&o)[16]) {
+    const __half2 sc = byte_pair(scw, (uint32_t)JJ, 1024.0f);
+    const __half2 off = __hmul2(sc, __float2half2_rn(-1024.0f)); // exact: at most 63 * 1024
+    const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f)), off16 = __hmul2(sc, __float2half2_rn(-64.0f));
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-        const uint32_t jj = (uint32_t)wi ^ odd; // sub-block 4*HALF + jj
-        const __half2 sc = byte_pair(hd.sc[HALF], jj, 1024.0f);
-        const __half2 off = __hmul2(sc, __float2half2_rn(-1024.0f)); // exact: at most 63 * 1024
-        const uint32_t w = word_of(qv, wi);
-        uint32_t o[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) { // nibbles p and p + 4 of the word are elements 2p, 2p + 1
-            const uint32_t e = ((w >> (4 * p)) & 0x000F000Fu) | 0x64006400u; // (1024 + q, 1024 + q')
-            o[p] = h2u(__hfma2(u2h(e), sc, off));                            // sc * q, exact
-        }
-        const uint32_t chunk = ((jj & 1u) * 4u + (uint32_t)t) ^ (uint32_t)g;
-        sts128(base + (jj >> 1) * 16384u + chunk * 16u, o[0], o[1], o[2], o[3]);
+    for (int t = 0; t < 4; ++t) {
+        const uint32_t w = word_of(r.c[t], JJ), w8 = w >> 8;
+        o[4 * t + 0] = h2u(__hfma2(u2h((w & 0x000F000Fu) | 0x64006400u), sc, off));
+        o[4 * t + 1] = h2u(__hfma2(u2h((w & 0x00F000F0u) | 0x64006400u), sc16, off16));
+        o[4 * t + 2] = h2u(__hfma2(u2h((w8 & 0x000F000Fu) | 0x64006400u), sc, off));
+        o[4 * t + 3] = h2u(__hfma2(u2h((w8 & 0x00F000F0u) | 0x64006400u), sc16, off16));
     }
 }
 
 // ------------------------------------------------------------------------------------ Q6_K
-// Ring slot: [2 top-nibble planes of 512 bytes][low-two-bits plane, 512][8 x sc[16] int8][8 x d f16].
+// One row's 128 inputs of one half: the top-nibble plane (uint4 per t: word wi covers sub-blocks 8 * half + 2 wi and
+// + 1 in its low / high nibbles, byte b = element 4t + b), the two words of the low-two-bits plane that belong to the
+// half (word v covers sub-blocks 4v .. 4v + 3, two bits each), the half's eight int8 scales, and d.
 struct TcQ6 {
-    uint4 lo[2]; // [half]
-    uint4 hi;
-    uint4 sc;
+    uint4 lo[4]; // [t]
+    uint2 hi[4]; // [t]
+    uint2 sc;
     float d;
 };
-__device__ __forceinline__ TcQ6 tc_load(const uint8_t *slot, int lane, TcQ6 *) {
+__device__ __forceinline__ TcQ6 tc_fetch(const uint8_t *tile, uint32_t half, uint32_t r16, TcQ6 *) {
     TcQ6 r;
-    const uint4 *q = reinterpret_cast<const uint4 *>(slot);
-    r.lo[0] = q[lane];
-    r.lo[1] = q[32 + lane];
-    r.hi = q[64 + lane];
-    r.sc = reinterpret_cast<const uint4 *>(slot + 1536)[lane >> 2];
-    r.d = __half2float(reinterpret_cast<const __half *>(slot + 1664)[lane >> 2]);
+    const uint32_t rowsel = r16 >> 3, g = r16 & 7;
+    const uint8_t *p = tile + (2 * rowsel + half) * 512 + g * 64, *ph = tile + kQ6OffHi + rowsel * 512 + g * 64 + 8 * half;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) r.lo[t] = ldg_stream128(p + 16 * t);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) r.hi[t] = ldg_stream64(ph + 16 * t);
+    r.sc = ldg_stream64(tile + kQ6OffSc + r16 * 16 + 8 * half);
+    r.d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(tile + kQ6OffD) + r16)));
     return r;
 }
-__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
-    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
-}
-// Column layout: the lane holds elements 4t .. 4t+3 of every sub-block of its row, stored as (q - 32) & 63 split
-// into a top-nibble plane (r.lo) and a low-two-bits plane (r.hi); (T << 4) | (L << 2) is the signed byte 4 (q - 32).
-// What goes to the A stage is 4 * sc * (q - 32) as f16 (the factor 4 is a shift of the exponent, so the products are
-// as exact as sc * (q - 32) itself); the drain's d carries the 1/4.
-template <int HALF>
-__device__ __forceinline__ void tc_unpack_half(const TcQ6 &r, uint32_t stage, uint32_t row, int g, int t) {
-    const __half2 k1152 = __float2half2_rn(1152.0f);
-    const uint32_t base = stage + (row >> 3) * 1024u + (row & 7) * 128u + (uint32_t)(t & 1) * 8u;
+// Sub-blocks 2 JJ, 2 JJ + 1 of the half (16 inputs each; JJ = 0..3) -> 16 columns of sc * (q - 32).
+// (T << 4) | (L << 2) is the signed byte 4 (q - 32); with its sign bit flipped, b = 4 (q - 32) + 128, and one fused
+// multiply-add gives (1024 + b) * (sc / 4) - 288 sc = sc (q - 32): every input is exact in f16 (288 |sc| <= 36864 =
+// 2^5 * 9 |sc|), the result is rounded once (to even beyond 2048, as f16 must).
+template <int JJ>
+__device__ __forceinline__ void tc_unpack(const TcQ6 &r, uint32_t (&o)[16]) {
+    const uint32_t scw = ((JJ >> 1) ? r.sc.y : r.sc.x) ^ 0x80808080u; // int8 scales + 128
 #pragma unroll
-    for (int sl = 0; sl < 8; ++sl) { // sub-block 8*HALF + sl: inputs 16*sl + 4t .. + 3 of the half
-        constexpr int kX[4] = {2, 0, -2, -4};
-        const uint32_t tw = word_of(r.lo[HALF], sl >> 1), lw = word_of(r.hi, 2 * HALF + (sl >> 2));
-        const uint32_t top = (sl & 1) ? tw : tw << 4;
-        const int sh = kX[sl & 3];
-        const uint32_t low = sh > 0 ? lw << sh : lw >> (-sh);
-        const uint32_t b = ((top & 0xF0F0F0F0u) | (low & 0x0C0C0C0Cu)) ^ 0x80808080u; // bytes 4 (q - 32) + 128
-        const __half2 sc = byte_pair(word_of(r.sc, 2 * HALF + (sl >> 2)) ^ 0x80808080u, (uint32_t)(sl & 3), 1152.0f); // int8 scale, exact
-        const uint32_t p0 = __byte_perm(b, 0x64646464u, 0x4140u), p1 = __byte_perm(b, 0x64646464u, 0x4342u);
-        const uint32_t o0 = h2u(__hmul2(__hsub2(u2h(p0), k1152), sc)), o1 = h2u(__hmul2(__hsub2(u2h(p1), k1152), sc));
-        const uint32_t chunk = (uint32_t)(2 * (sl & 3) + (t >> 1)) ^ (uint32_t)g;
-        sts64(base + (uint32_t)(sl >> 2) * 16384u + chunk * 16u, o0, o1);
+    for (int ci = 0; ci < 2; ++ci) {
+        const int c = 2 * (JJ & 1) + ci; // sub-block 4 (JJ / 2) + c of the half
+        const __half2 sc = byte_pair(scw, (uint32_t)c, 1152.0f); // exact
+        const __half2 sc4 = __hmul2(sc, __float2half2_rn(0.25f)), off = __hmul2(sc, __float2half2_rn(-288.0f));
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t tw = word_of(r.lo[t], JJ), lw = (JJ >> 1) ? r.hi[t].y : r.hi[t].x;
+            // even sub-blocks sit in the low nibbles of the plane's bytes, odd ones in the high nibbles
+            const uint32_t top = (c & 1) ? ((tw ^ 0x80808080u) & 0xF0F0F0F0u) : (((tw ^ 0x08080808u) & 0x0F0F0F0Fu) << 4);
+            const uint32_t low = c == 0 ? lw << 2 : c == 1 ? lw : c == 2 ? lw >> 2 : lw >> 4;
+            const uint32_t b = top | (low & 0x0C0C0C0Cu);
+            o[8 * ci + 2 * t + 0] = h2u(__hfma2(u2h(__byte_perm(b, 0x64646464u, 0x4140u)), sc4, off));
+            o[8 * ci + 2 * t + 1] = h2u(__hfma2(u2h(__byte_perm(b, 0x64646464u, 0x4342u)), sc4, off));
+        }
     }
 }
 
@@ -243,29 +318,27 @@ __device__ __forceinline__ void tc_unpack_half(const TcQ6 &r, uint32_t stage, ui
 template <int DT, int N>
 struct TcSmem {
     static constexpr bool kQ4 = DT == MUSER_DTYPE_Q4_K;
-    static constexpr int kTile = kQ4 ? kQ4TileBytes : kQ6TileBytes, kSlot = kQ4 ? kTcQ4Slot : kTcQ6Slot;
-    // Raw tiles in flight per unpacking warp.  HBM latency times the stream's rate is ~55 KB per SM, and the warps
-    // run in step, so the rings are made as deep as shared memory allows: 72-105 KB of weights in flight per SM.
-    static constexpr int kRing = (!kQ4 && N == 64) ? 3 : 4;
-    static constexpr int kStagesB = N == 64 ? 3 : 4; // activation slabs come from L2 with ~1500 cycles of latency
+    static constexpr int kTile = kQ4 ? kQ4TileBytes : kQ6TileBytes;
+    static constexpr int kStagesB = 4;               // activation slabs (128 inputs each) come from L2 with ~1500 cycles of latency
     static constexpr int kBBytes = N * 256;          // two atoms of N rows x 128 bytes
     static constexpr int kMinA = kTcRows * 32, kMinB = N * 32 < 1024 ? 1024 : N * 32;
-    static constexpr int kOffB = kTcStages * kTcABytes;
+    static constexpr int kOffB = 0;
     static constexpr int kOffMinA = kOffB + kStagesB * kBBytes;
     static constexpr int kOffMinB = kOffMinA + 2 * kMinA;
-    static constexpr int kOffRing = kOffMinB + 2 * kMinB;
-    static constexpr int kOffHdr = kOffRing + kTcDequantWarps * kRing * kSlot;
+    static constexpr int kOffHdr = kOffMinB + 2 * kMinB;
     static constexpr int kHdrDepth = 8;              // (d, dmin) per row of the last eight super-block columns
     static constexpr int kOffBars = kOffHdr + kHdrDepth * kTcRows * 8;
-    static constexpr int kBufs = 4;                  // accumulator buffers in tensor memory, each kAcc main parts + the min part
+    // Tensor memory: kBufs accumulator buffers (kAcc main parts + the min part each), then the A stages.
     static constexpr int kAcc = N <= 32 ? 2 : 1;     // two main accumulators taken in turn where the columns allow (measured faster)
     static constexpr int kBufCols = (kAcc + 1) * N;
+    static constexpr int kBufs = N == 16 ? 4 : 2;
+    static constexpr uint32_t kACol = kBufs * kBufCols, kTmemCols = 512;
+    static_assert(kACol + kTcStagesA * kTcStageCols <= kTmemCols, "tensor memory exceeded");
     static constexpr int kDrainWarps = N >= 32 ? 8 : 4, kDrainCols = N / (kDrainWarps / 4);
     static constexpr int kThreads = 32 * (2 + kTcDequantWarps + kDrainWarps);
-    static constexpr int kBars = 2 * kTcStages + 2 * kStagesB + 2 * kBufs + kTcDequantWarps * kRing;
+    static constexpr int kBars = 2 * kTcStagesA + 2 * kStagesB + 2 * kBufs;
     static constexpr int kBytes = kOffBars + kBars * 8 + 16 + 1024 /*alignment slack*/;
     static_assert(kBytes <= 227 * 1024, "shared memory of one CTA exceeded");
-    static constexpr uint32_t kTmemCols = N == 16 ? 256 : 512; // kBufs x kBufCols = 192 / 384 / 512, rounded up to a power of two
 };
 
 template <int DT, int N>
@@ -273,23 +346,24 @@ __global__ void __launch_bounds__((TcSmem<DT, N>::kThreads), 1)
 kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_xs, const TcArgs a) {
     using S = TcSmem<DT, N>;
     constexpr bool Q4 = S::kQ4;
+    if (threadIdx.x == 0) { TPROF_STAMP_MIN(2) }
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + S::kOffBars);
-    constexpr int kRing = S::kRing, kStagesB = S::kStagesB;
-    const uint32_t bar_full_a = smem_u32(bars), bar_empty_a = bar_full_a + 8 * kTcStages;
-    const uint32_t bar_full_b = bar_empty_a + 8 * kTcStages, bar_empty_b = bar_full_b + 8 * kStagesB;
+    constexpr int kStagesB = S::kStagesB, kStagesA = kTcStagesA;
+    const uint32_t bar_full_a = smem_u32(bars), bar_empty_a = bar_full_a + 8 * kStagesA;
+    const uint32_t bar_full_b = bar_empty_a + 8 * kStagesA, bar_empty_b = bar_full_b + 8 * kStagesB;
     constexpr int kBufs = S::kBufs;
-    const uint32_t bar_tmem_full = bar_empty_b + 8 * kStagesB, bar_tmem_empty = bar_tmem_full + 8 * kBufs, bar_ring = bar_tmem_empty + 8 * kBufs;
+    const uint32_t bar_tmem_full = bar_empty_b + 8 * kStagesB, bar_tmem_empty = bar_tmem_full + 8 * kBufs;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + S::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float2 *hdr = reinterpret_cast<float2 *>(aligned + S::kOffHdr);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTcStages; ++s) {
-            mbar_init(bar_full_a + 8 * s, kTcDequantWarps);
+        for (int s = 0; s < kStagesA; ++s) {
+            mbar_init(bar_full_a + 8 * s, 4); // the four 32-row quarters of the stage
             mbar_init(bar_empty_a + 8 * s, 1);
         }
         for (int s = 0; s < kStagesB; ++s) {
@@ -300,7 +374,6 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             mbar_init(bar_tmem_full + 8 * b, 1);
             mbar_init(bar_tmem_empty + 8 * b, S::kDrainWarps);
         }
-        for (int i = 0; i < kTcDequantWarps * kRing; ++i) mbar_init(bar_ring + 8 * i, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -313,162 +386,175 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0 && blockIdx.x == 0) { TPROF_STAMP_MAX(3) }
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- activation producer
-        if (lane == 0) {
+        // ---------------------------------------------------------------- activation producer (whole warp, one lane issues)
+        {
             TcWalk w;
             w.start(a);
             uint32_t hs = 0, tc = 0, issued = 0;
-            bool ok = true;
+            bool ok = true; TPROF_DECL
+            pdl_wait(); // the activations come from the kernel before this one; everything up to here overlapped its tail
             for (; !w.done(a) && ok; w.next(a), ++tc) {
                 for (uint32_t h = 0; h < 2; ++h, ++hs) {
                     const uint32_t s = hs % kStagesB, round = hs / kStagesB;
-                    if (round > 0) ok = mbar_wait_relaxed(bar_empty_b + 8 * s, (round - 1) & 1, abort_flag, 32);
+                    TPROF_BEGIN if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_empty_b + 8 * s, (round - 1) & 1, abort_flag, 32)); TPROF_END(0)
                     if (!ok) break;
                     const uint32_t full = bar_full_b + 8 * s, dst = base + S::kOffB + s * S::kBBytes;
                     const bool with_sums = Q4 && h == 1;
-                    mbar_expect_tx(full, S::kBBytes + (with_sums ? N * 32 : 0));
+                    mbar_expect_tx_elect(full, S::kBBytes + (with_sums ? N * 32 : 0));
                     const int x0 = (int)((w.k * 256 + h * 128) * 2);
-                    tma_load_2d(dst, &map_x, x0, 0, full);
-                    tma_load_2d(dst + N * 128, &map_x, x0 + 128, 0, full);
-                    if (with_sums) tma_load_2d(base + S::kOffMinB + (tc & 1) * S::kMinB, &map_xs, (int)(w.k * 32), 0, full);
+                    tma_load_2d_elect(dst, &map_x, x0, 0, full);
+                    tma_load_2d_elect(dst + N * 128, &map_x, x0 + 128, 0, full);
+                    if (with_sums) tma_load_2d_elect(base + S::kOffMinB + (tc & 1) * S::kMinB, &map_xs, (int)(w.k * 32), 0, full);
                     issued = hs + 1;
                 }
             }
+            if (lane == 0) { TPROF_FLUSH(0) }
             if (!ok) {
-                *abort_flag = 1;
-                atomicExch(a.status + 1, 301);
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicExch(a.status + 1, 301);
+                }
                 // let the copies already in flight land before the CTA's shared memory goes away
                 const uint32_t first = issued > (uint32_t)kStagesB ? issued - kStagesB : 0;
                 for (uint32_t k = first; k < issued; ++k) mbar_wait_alone(bar_full_b + 8 * (k % kStagesB), (k / kStagesB) & 1);
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer (whole warp, one lane issues)
+        {
             // kind::f16: f32 accumulator (bit 4), A and B f16 (format 0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
             TcWalk w;
             w.start(a);
             uint32_t hs = 0, tc = 0;
-            bool ok = true;
+            bool ok = true; TPROF_DECL
             for (; !w.done(a) && ok; w.next(a), ++tc) {
                 const uint32_t buf = tc % kBufs, d_main = tmem + buf * S::kBufCols, d_min = d_main + S::kAcc * N;
                 if (tc >= (uint32_t)kBufs) { // the drain warps must have read this buffer's previous contents
-                    ok = mbar_wait(bar_tmem_empty + 8 * buf, ((tc / kBufs) - 1) & 1, abort_flag);
+                    TPROF_BEGIN ok = mbar_wait_warp(bar_tmem_empty + 8 * buf, ((tc / kBufs) - 1) & 1, abort_flag); TPROF_END(0)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                for (uint32_t h = 0; h < 2; ++h, ++hs) {
-                    const uint32_t s = hs % kTcStages, round = hs / kTcStages, s_b = hs % kStagesB, round_b = hs / kStagesB;
-                    ok = mbar_wait(bar_full_b + 8 * s_b, round_b & 1, abort_flag); if (ok) ok = mbar_wait(bar_full_a + 8 * s, round & 1, abort_flag);
+                const uint32_t a_col = tmem + S::kACol + (tc & 1) * 4 * kTcStageCols; // this column's four stages
+                for (uint32_t h = 0; h < 2 && ok; ++h, ++hs) {
+                    const uint32_t s_b = hs % kStagesB, round_b = hs / kStagesB;
+                    TPROF_BEGIN ok = mbar_wait_warp(bar_full_b + 8 * s_b, round_b & 1, abort_flag); TPROF_END(1)
                     if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = base + s * kTcABytes, sb = base + S::kOffB + s_b * S::kBBytes;
+                    const uint32_t sb = base + S::kOffB + s_b * S::kBBytes;
 #pragma unroll
-                    for (uint32_t atom = 0; atom < 2; ++atom) {
-                        const uint64_t da = operand_desc(sa + atom * 16384u), db = operand_desc(sb + atom * (N * 128u));
+                    for (uint32_t atom = 0; atom < 2; ++atom) { // one A stage = 64 inputs = one atom of the activation slab
+                        const uint32_t s = (tc & 1) * 4 + 2 * h + atom;
+                        TPROF_BEGIN ok = mbar_wait_warp(bar_full_a + 8 * s, (tc >> 1) & 1, abort_flag); TPROF_END(1)
+                        if (!ok) break;
+                        TPROF_BEGIN
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t ta = a_col + (2 * h + atom) * kTcStageCols;
+                        const uint64_t db = operand_desc(sb + atom * (N * 128u));
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk) // 16 values = 32 bytes along the swizzled 128-byte rows
-                            mma_f16(d_main + (S::kAcc == 2 ? (kk & 1) * N : 0), da + 2 * kk, db + 2 * kk, idesc,
-                                    (h | atom | (S::kAcc == 2 ? kk >> 1 : kk)) != 0);
+                        for (uint32_t kk = 0; kk < 4; ++kk) // 16 inputs: 8 columns of A, 32 bytes along B's swizzled 128-byte rows
+                            mma_f16_ts_elect(d_main + (S::kAcc == 2 ? (kk & 1) * N : 0), ta + 8 * kk, db + 2 * kk, idesc,
+                                             (h | atom | (S::kAcc == 2 ? kk >> 1 : kk)) != 0);
+                        if (Q4 && h == 1 && atom == 1)
+                            mma_f16_elect(d_min, operand_desc32(base + S::kOffMinA + (tc & 1) * S::kMinA),
+                                          operand_desc32(base + S::kOffMinB + (tc & 1) * S::kMinB), idesc, 0);
+                        mma_commit_elect(bar_empty_a + 8 * s); // the stage (and the min operand) reusable once these MMAs have read it
+                        TPROF_END(2)
                     }
-                    if (Q4 && h == 1)
-                        mma_f16(d_min, operand_desc32(base + S::kOffMinA + (tc & 1) * S::kMinA),
-                                operand_desc32(base + S::kOffMinB + (tc & 1) * S::kMinB), idesc, 0);
-                    mma_commit(bar_empty_a + 8 * s); // stages (and the sum buffers) reusable once these MMAs have read them
-                    mma_commit(bar_empty_b + 8 * s_b);
+                    if (ok) mma_commit_elect(bar_empty_b + 8 * s_b);
                 }
-                if (ok) mma_commit(bar_tmem_full + 8 * buf);
+                if (ok) mma_commit_elect(bar_tmem_full + 8 * buf);
             }
-            if (!ok) {
+            if (lane == 0) { TPROF_FLUSH(1) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicExch(a.status + 1, 302);
             }
         }
     } else if (warp < 2 + kTcDequantWarps) {
         // ---------------------------------------------------------------- weight unpackers
+        // Warp = (column parity p, half of the column, 32-row quarter): thread = one weight row, every other
+        // super-block column, 128 inputs of it = two A stages.  The row's bytes of the NEXT own column are requested
+        // before this one is unpacked (about two column times of latency hidden; ~40 KB in flight per SM).
         using Regs = typename std::conditional<Q4, TcQ4, TcQ6>::type;
-        const int dw = warp - 2, g = lane >> 2, t = lane & 3;
-        const uint32_t rsel = (uint32_t)dw & 1, row = (uint32_t)(dw >> 1) * 16 + g + 8 * rsel; // this lane's row of the block
-        uint8_t *ring = aligned + S::kOffRing + dw * kRing * S::kSlot;
-        const uint32_t rbar = bar_ring + 8 * dw * kRing;
-        auto fetch = [&](const TcWalk &x, uint32_t slot) { // this warp's eight rows of one tile: its planes and headers
-            if (lane == 0) {
-                const uint32_t rt = min(x.rb * (kTcRows / kTileRows) + (uint32_t)(dw >> 1), a.row_tiles - 1); // a short last block repeats its last tile
-                const uint8_t *src = a.image + ((uint64_t)rt * a.nsb + x.k) * S::kTile;
-                const uint32_t dst = smem_u32(ring) + slot * S::kSlot, bar = rbar + 8 * slot;
-                mbar_expect_tx(bar, S::kSlot);
-                bulk_load(dst, src + 1024 * rsel, 1024, bar);
-                if constexpr (Q4) {
-                    bulk_load(dst + 1024, src + 2048 + 128 * rsel, 128, bar);
-                } else {
-                    bulk_load(dst + 1024, src + kQ6OffHi + 512 * rsel, 512, bar);
-                    bulk_load(dst + 1536, src + kQ6OffSc + 128 * rsel, 128, bar);
-                    bulk_load(dst + 1664, src + kQ6OffD + 16 * rsel, 16, bar);
-                }
-            }
+        const uint32_t kg = (uint32_t)(warp - 2) >> 2, p = kg >> 1, half = kg & 1, qd = (uint32_t)warp & 3; // (tensor-memory lanes 32 qd ..)
+        const uint32_t row = qd * 32 + lane, r16 = (uint32_t)lane & 15;
+        const uint32_t st_base = tmem + ((qd * 32) << 16) + S::kACol + (p * 4 + half * 2) * kTcStageCols;
+        auto fetch = [&](const TcWalk &x) {
+            const uint32_t rt = min(x.rb * (kTcRows / kTileRows) + 2 * qd + ((uint32_t)lane >> 4), a.row_tiles - 1); // a short last block repeats its last tile
+            return tc_fetch(a.image + ((uint64_t)rt * a.nsb + x.k) * S::kTile, half, r16, (Regs *)nullptr);
         };
-        TcWalk w, f;
-        w.start(a);
-        f = w;
-        uint32_t fetched = 0;
-        for (; fetched < (uint32_t)kRing && !f.done(a); ++fetched, f.next(a)) fetch(f, fetched);
-        uint32_t n = 0, hs = 0;
-        bool ok = true;
-        // one half (128 inputs) of the tile in `cur` into its stage, then tell the MMA warp
-        auto half_step = [&](const Regs &cur, const TcQ4Hdr &hd, auto half_tag) {
-            constexpr int HALF = decltype(half_tag)::value;
-            const uint32_t s = hs % kTcStages, round = hs / kTcStages;
-            if (round > 0) ok = mbar_wait(bar_empty_a + 8 * s, (round - 1) & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            if constexpr (Q4) tc_unpack_half<HALF>(cur, hd, base + s * kTcABytes, row, g, t);
-            else tc_unpack_half<HALF>(cur, base + s * kTcABytes, row, g, t);
-            if constexpr (HALF == 1) {
-                if constexpr (Q4) {
-                    // min operand: 16 f16 per row, (m_j, m_j) for j = 0..7; lanes t = 0, 1 write the row's two 16-byte chunks
-                    if (t < 2) {
-                        const uint32_t mw = t ? hd.mn[1] : hd.mn[0];
-                        const uint32_t chunk = (uint32_t)t ^ ((row >> 2) & 1);
-                        sts128(base + S::kOffMinA + (n & 1) * S::kMinA + (row >> 3) * 256u + (row & 7) * 32u + chunk * 16u,
-                               h2u(byte_pair(mw, 0, 1024.0f)), h2u(byte_pair(mw, 1, 1024.0f)), h2u(byte_pair(mw, 2, 1024.0f)),
-                               h2u(byte_pair(mw, 3, 1024.0f)));
-                    }
-                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(hd.d, hd.dmin);
-                } else {
-                    if (t == 2) hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(0.25f * cur.d, 0.0f); // the A operand is 4 sc (q - 32)
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic stores -> visible to the MMA's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
-            ++hs;
+        auto advance2 = [&](TcWalk &x) {
+            x.next(a);
+            if (!x.done(a)) x.next(a);
         };
-        for (; !w.done(a) && ok; w.next(a), ++n) {
-            const uint32_t slot = n % kRing;
-            ok = mbar_wait(rbar + 8 * slot, (n / kRing) & 1, abort_flag);
-            if (!ok) break;
-            const Regs cur = tc_load(ring + slot * S::kSlot, lane, (Regs *)nullptr);
-            __syncwarp(); // every lane has its copy: the slot may be refilled
-            if (!f.done(a)) {
-                fetch(f, slot);
-                f.next(a);
-                ++fetched;
+        TcWalk f;
+        f.start(a);
+        if (p && !f.done(a)) f.next(a);
+        bool have = !f.done(a), ok = true; TPROF_DECL
+        Regs nxt{};
+        if (have) {
+            nxt = fetch(f);
+            advance2(f);
+        }
+        for (uint32_t n = p, own = 0; have && ok; n += 2, ++own) { // n: the column's number in this CTA's sequence
+            const Regs cur = nxt;
+            have = !f.done(a);
+            if (have) {
+                nxt = fetch(f);
+                advance2(f);
             }
             TcQ4Hdr hd{};
             if constexpr (Q4) hd = tc_q4_hdr(cur.h);
-            half_step(cur, hd, std::integral_constant<int, 0>{});
-            if (ok) half_step(cur, hd, std::integral_constant<int, 1>{});
+            auto quarter_step = [&](auto quarter_tag) {
+                constexpr int QD = decltype(quarter_tag)::value;
+                const uint32_t s = p * 4 + half * 2 + QD;
+                TPROF_BEGIN if (own > 0) ok = mbar_wait(bar_empty_a + 8 * s, (own - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok); TPROF_END(1)
+                if (!ok) return;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 2; ++j) { // 16 columns at a time keeps the live registers down
+                    uint32_t o[16];
+                    if (j == 0) {
+                        if constexpr (Q4) tc_unpack<2 * QD>(cur, half ? hd.sc[1] : hd.sc[0], o);
+                        else tc_unpack<2 * QD>(cur, o);
+                    } else {
+                        if constexpr (Q4) tc_unpack<2 * QD + 1>(cur, half ? hd.sc[1] : hd.sc[0], o);
+                        else tc_unpack<2 * QD + 1>(cur, o);
+                    }
+                    tmem_st16(st_base + QD * kTcStageCols + 16 * j, o);
+                }
+                if (QD == 1 && half == 1) {
+                    if constexpr (Q4) {
+                        // min operand (shared memory): 16 f16 per row, (m_j, m_j) for j = 0..7, two 16-byte chunks, 32-byte swizzle.
+                        // Its two buffers go by column parity: the wait above covered the min MMA of this parity's last column.
+                        const uint32_t mrow = base + S::kOffMinA + (n & 1) * S::kMinA + (row >> 3) * 256u + (row & 7) * 32u, sw = (row >> 2) & 1;
+                        sts128(mrow + (0u ^ sw) * 16u, h2u(byte_pair(hd.mn[0], 0, 1024.0f)), h2u(byte_pair(hd.mn[0], 1, 1024.0f)),
+                               h2u(byte_pair(hd.mn[0], 2, 1024.0f)), h2u(byte_pair(hd.mn[0], 3, 1024.0f)));
+                        sts128(mrow + (1u ^ sw) * 16u, h2u(byte_pair(hd.mn[1], 0, 1024.0f)), h2u(byte_pair(hd.mn[1], 1, 1024.0f)),
+                               h2u(byte_pair(hd.mn[1], 2, 1024.0f)), h2u(byte_pair(hd.mn[1], 3, 1024.0f)));
+                        hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(hd.d, hd.dmin);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic stores -> visible to the MMA's reads
+                    } else {
+                        hdr[(n % S::kHdrDepth) * kTcRows + row] = make_float2(cur.d, 0.0f);
+                    }
+                }
+                tmem_st_wait();
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+            };
+            quarter_step(std::integral_constant<int, 0>{});
+            if (ok) quarter_step(std::integral_constant<int, 1>{});
         }
+        if (lane == 0 && (warp == 2 || warp == 17)) { TPROF_FLUSH(warp == 2 ? 2 : 3) }
         if (!ok && lane == 0) {
             *abort_flag = 1;
             atomicCAS(a.status + 1, 0, 303);
         }
-        // copies still in flight into this warp's ring must land before the CTA's shared memory goes away
-        if (!ok)
-            for (uint32_t k = n; k < fetched; ++k) mbar_wait_alone(rbar + 8 * (k % kRing), (k / kRing) & 1);
     } else {
         // ---------------------------------------------------------------- drain (the last 4 or 8 warps)
         constexpr int C = S::kDrainCols;                                          // token columns of this warp
@@ -481,10 +567,10 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int i = 0; i < C; ++i) acc[i] = 0.0f;
         TcWalk w;
         w.start(a);
-        uint32_t tc = 0;
+        uint32_t tc = 0; TPROF_DECL
         while (!w.done(a)) {
             const uint32_t buf = tc % kBufs;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_tmem_full + 8 * buf, (tc / kBufs) & 1, abort_flag, 40));
+            TPROF_BEGIN const bool ok = __all_sync(0xffffffffu, mbar_wait_relaxed(bar_tmem_full + 8 * buf, (tc / kBufs) & 1, abort_flag, 40)); TPROF_END(0)
             if (!ok) {
                 if (lane == 0) {
                     *abort_flag = 1;
@@ -519,6 +605,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             w.next(a);
             ++tc;
             if (!last) continue;
+            TPROF_BEGIN
 
             // ---- end of an item: meet the other K slices, then store
             if (a.fold)
@@ -583,12 +670,25 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
 #pragma unroll
             for (int i = 0; i < C; ++i) acc[i] = 0.0f;
+            TPROF_END(1)
         }
+        if (lane == 0 && warp == 2 + kTcDequantWarps) { TPROF_FLUSH(4) }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) { TPROF_STAMP_MAX(4) }
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(S::kTmemCols) : "memory");
+    if (threadIdx.x == 32) { TPROF_STAMP_MAX(5) }
 }
+
+#ifdef MUSER_GEMM_WAIT_PROFILE
+extern "C" __attribute__((visibility("default"))) int muser_cuda_debug_tc_wait_profile(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tc_wait_prof, sizeof(g_tc_wait_prof));
+}
+extern "C" __attribute__((visibility("default"))) int muser_cuda_debug_tc_stamps(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tc_stamps, sizeof(g_tc_stamps));
+}
+#endif
 
 // Activations into the form the kernel reads: f16, N rows (rows past `tokens` zero), columns in the weight image's
 // tile coordinates (a K shard's first tile may start before the shard's first input: those columns are zero), and
@@ -602,6 +702,16 @@ __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__re
     // and has none).  f32 activations
     // are carried (to 22 bits, same range) as an f16 head in row 2t and the remainder in row 2t + 1; the kernel
     // adds the two columns at the end.
+#ifdef MUSER_GEMM_WAIT_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { // (the GEMM cannot start before every block of this grid has passed pdl_release)
+        g_tc_stamps[0] = g_tc_stamps[2] = ~0ull;
+        g_tc_stamps[1] = g_tc_stamps[3] = g_tc_stamps[4] = g_tc_stamps[5] = 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { TPROF_STAMP_MIN(0) }
+#endif
+    pdl_release(); // the GEMM behind this kernel may start its set-up and its weight copies now; it waits before it reads xh / xs
     const uint32_t tile = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
     const uint32_t tok = XF32 ? r >> 1 : r, part = XF32 ? r & 1 : 0;
     const int64_t k = (int64_t)tile * 256 + i - (int64_t)k_off;
@@ -623,6 +733,7 @@ __global__ void __launch_bounds__(256) kquant_tc_prepare_kernel(const void *__re
         dst[0] = head;
         dst[1] = rest;
     }
+    if (threadIdx.x == 0) { TPROF_STAMP_MAX(1) }
 }
 
 // Issue-rate probe for the instruction this kernel is built on: one thread per SM issues `iters` x 4
@@ -719,8 +830,8 @@ static cudaError_t tc_launch(const CUtensorMap &mx, const CUtensorMap &mxs, cons
     using S = TcSmem<DT, N>;
     const cudaError_t ae = ensure_dynamic_smem(reinterpret_cast<const void *>(kquant_tc_kernel<DT, N>), device, S::kBytes);
     if (ae != cudaSuccess) return ae;
-    kquant_tc_kernel<DT, N><<<grid, S::kThreads, S::kBytes, stream>>>(mx, mxs, a);
-    return cudaGetLastError();
+    // may begin while the kernel that prepares its activations is still running: set-up and the first weight tiles overlap it
+    return launch_pdl(kquant_tc_kernel<DT, N>, dim3(grid), dim3(S::kThreads), S::kBytes, stream, mx, mxs, a);
 }
 
 // cudaErrorNotSupported: this shape is not served here (the caller falls back to the other kernels).

@@ -97,6 +97,37 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- the same instructions, issued by ONE ELECTED LANE of a warp that runs its role converged ------------------------
+// TMA copies, tcgen05.mma / cp / commit take their operands from the warp-uniform register file.  Issued from inside a
+// divergent branch (if (lane == 0) { ... }) every one of them cost 100-150 SM cycles of issue time on B200: 16 skinny
+// MMAs with four waits and four commits took 1650 cycles per round against 602 when all 32 lanes ran the loop (waits,
+// address arithmetic) and only the instruction itself was predicated on elect.sync.  So the single-thread roles of
+// these kernels are written as whole-warp loops around the *_elect forms below.  elect.sync names the same lane for
+// the same mask every time, so the commits track the MMAs of the lane that issued them.
+#define MUSER_ELECT_PRED ".reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+__device__ __forceinline__ void mbar_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED
+                 "@e cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_load_elect(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
+}
+// A bounded wait by the whole warp: every lane polls, and the warp agrees on the outcome (a lane that gave up alone
+// would leave the others at the next elect.sync).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+
 // 32 consecutive accumulator columns of this thread's lane (row) into registers; follow with tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
     asm volatile(
