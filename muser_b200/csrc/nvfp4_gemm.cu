@@ -94,6 +94,19 @@ __device__ __forceinline__ void mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint6
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
         : "memory");
 }
+// The same two, issued by the elected lane of a warp that runs its role converged (tcgen05.cuh).
+__device__ __forceinline__ void tmem_cp_scales_elect(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_nvf4_elect(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t" MUSER_ELECT_PRED
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
 // One 32-column strip of one accumulator row: scale, fuse, convert, store (16-byte stores when the row allows).
 template <typename T>
 __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T *res, uint32_t valid, bool vec_ok) {
@@ -204,8 +217,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- producer
-        if (lane == 0) {
+        // ---------------------------------------------------------------- producer (whole warp; one elected lane issues)
+        {
             uint32_t it = 0, issued = 0; // k slabs issued so far, over all tiles
             bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
@@ -215,31 +228,33 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
-                    PROF_BEGIN if (round > 0) ok = mbar_wait(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (round > 0) ok = mbar_wait_warp(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     const uint32_t st = base + s * kStageBytes;
                     const uint32_t full = bar_full + 8 * s;
                     // the last slab may hold fewer than four 64-value blocks: the operand boxes are zero-filled
                     // past the row end, and only the scale chunks that exist are fetched
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
-                    mbar_expect_tx(full, kABytes + kBBytes + 3 * sf_bytes);
-                    tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
+                    mbar_expect_tx_elect(full, kABytes + kBBytes + 3 * sf_bytes);
+                    tma_load_2d_elect(st, &map_a, (int)(kt * (BK / 2)), (int)(tile_m * BM), full);
                     if constexpr (DUAL) {
-                        tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
-                        tma_load_2d(st + kABytes + kBBytes / 2, &map_b2, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
+                        tma_load_2d_elect(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
+                        tma_load_2d_elect(st + kABytes + kBBytes / 2, &map_b2, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
                     } else {
-                        tma_load_2d(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                        tma_load_2d_elect(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
                     }
-                    bulk_load(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
-                    bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
-                    bulk_load(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
+                    bulk_load_elect(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
+                    bulk_load_elect(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
+                    bulk_load_elect(st + kABytes + kBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
                     issued = it + 1;
                 }
             }
-            PROF_FLUSH(0)
+            if (lane == 0) { PROF_FLUSH(0) }
             if (!ok) {
-                *abort_flag = 1;
-                atomicExch(g.status + 1, 101);
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicExch(g.status + 1, 101);
+                }
                 // let the copies already in flight land before the CTA's shared memory goes away
                 const uint32_t first = issued > kStages ? issued - kStages : 0;
                 for (uint32_t k = first; k < issued; ++k) {
@@ -251,8 +266,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer (whole warp; one elected lane issues)
+        {
             // kind::mxf4nvf4: A and B E2M1 (format 1), K-major, UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, local = 0;
@@ -260,13 +275,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++local) {
                 // the accumulator is free again once the epilogue warps have read the previous tile out of it
                 if (local > 0) {
-                    PROF_BEGIN ok = mbar_wait(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
-                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes;
@@ -274,18 +289,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
                     // the scale factors of this slab were copied into tensor memory by the copier warp
                     const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
-                    PROF_BEGIN ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb) // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
-                        mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
-                    mma_commit(bar_sf_empty + 8 * buf);
-                    mma_commit(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
+                        mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
+                    mma_commit_elect(bar_sf_empty + 8 * buf);
+                    mma_commit_elect(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
                 }
-                if (ok) mma_commit(bar_acc_full);
+                if (ok) mma_commit_elect(bar_acc_full);
             }
-            PROF_FLUSH(1)
-            if (!ok) {
+            if (lane == 0) { PROF_FLUSH(1) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicExch(g.status + 1, 102);
             }
@@ -294,28 +309,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ---------------------------------------------------------------- scale copier
         // tcgen05.cp of the slab's scale factors into one of two tensor-memory buffers, issued by a thread of its
         // own: in the MMA thread's instruction stream the twelve copies of a slab took as long as its four MMAs.
-        if (lane == 0) {
+        {
             uint32_t it = 0;
             bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages, buf = it % kSfBufs;
-                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
-                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait_warp(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kStageBytes, sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
                     const uint32_t sf = tmem + kSfCol + buf * kSfBufCols, nkb = min(4u, g.kt64 - 4 * kt);
                     for (uint32_t kb = 0; kb < nkb; ++kb) {
-                        tmem_cp_scales(sf + 4 * kb, scale_desc(sfa + 512 * kb));
-                        tmem_cp_scales(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
-                        tmem_cp_scales(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                        tmem_cp_scales_elect(sf + 4 * kb, scale_desc(sfa + 512 * kb));
+                        tmem_cp_scales_elect(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
+                        tmem_cp_scales_elect(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
                     }
-                    mma_commit(bar_sf_full + 8 * buf);
+                    mma_commit_elect(bar_sf_full + 8 * buf);
                 }
             }
-            PROF_FLUSH(2)
-            if (!ok) {
+            if (lane == 0) { PROF_FLUSH(2) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 105);
             }
