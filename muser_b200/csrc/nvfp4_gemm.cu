@@ -287,14 +287,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint32_t st = base + s * kStageBytes;
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
-                    // the scale factors of this slab were copied into tensor memory by the copier warp
                     const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
+#ifdef MUSER_GEMM_COPIER_WARP
+                    // the scale factors of this slab were copied into tensor memory by the copier warp
                     PROF_BEGIN ok = mbar_wait_warp(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb) // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
                         mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
                     mma_commit_elect(bar_sf_empty + 8 * buf);
+#else
+                    // Each MMA's scale factors go to tensor memory right in front of it, from the same lane: the tensor
+                    // pipe takes both in issue order, so no barrier stands between a copy and the MMA that reads it, and
+                    // the copies run under the MMAs before them (691 cycles per slab in isolation against 548 for the
+                    // MMAs alone).  The buffers alternate so that a copy never lands in what an earlier MMA still reads.
+                    const uint32_t sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
+                    for (uint32_t kb = 0; kb < nkb; ++kb) { // 64 values = 32 bytes further along the swizzled 128-byte rows: +2 in 16-byte units
+                        tmem_cp_scales_elect(sf + 4 * kb, scale_desc(sfa + 512 * kb));
+                        tmem_cp_scales_elect(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
+                        tmem_cp_scales_elect(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                        mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
+                    }
+#endif
                     mma_commit_elect(bar_empty + 8 * s); // the stage may be overwritten once these MMAs have read it
                 }
                 if (ok) mma_commit_elect(bar_acc_full);
@@ -306,9 +320,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else if (warp == 10) {
-        // ---------------------------------------------------------------- scale copier
-        // tcgen05.cp of the slab's scale factors into one of two tensor-memory buffers, issued by a thread of its
-        // own: in the MMA thread's instruction stream the twelve copies of a slab took as long as its four MMAs.
+#ifdef MUSER_GEMM_COPIER_WARP
+        // ---------------------------------------------------------------- scale copier (development alternative)
+        // tcgen05.cp of the slab's scale factors into one of the tensor-memory buffers, issued by a warp of its own.
         {
             uint32_t it = 0;
             bool ok = true; PROF_DECL
@@ -335,6 +349,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 atomicCAS(g.status + 1, 0, 105);
             }
         }
+#endif
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         // Eight warps: two per 32-lane quarter of the accumulator, one for each half of the tile's output columns.
@@ -504,6 +519,28 @@ __device__ __forceinline__ void pair_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, 
         : "memory");
 }
 
+__device__ __forceinline__ bool mbar_wait_pair_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait_pair(bar, parity, abort_flag));
+}
+__device__ __forceinline__ void mbar_arrive_cluster_elect(uint32_t cluster_addr) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n\t}" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void pair_commit_elect(uint32_t cluster_addr) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void pair_cp_scales_elect(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("{\n\t" MUSER_ELECT_PRED "@e tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void pair_mma_nvf4_elect(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                    uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t" MUSER_ELECT_PRED
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
 template <bool DUAL, bool TAIL>
 __global__ void __launch_bounds__(352, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -551,8 +588,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- producer (both CTAs)
-        if (lane == 0) {
+        // ---------------------------------------------------------------- producer (both CTAs; whole warp, one elected lane issues)
+        {
             uint32_t it = 0, issued = 0;
             bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
@@ -569,24 +606,26 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const int b_row = DUAL ? (int)(tile_n * (BN / 2)) : (int)(tile_n * BN + rank * (BN / 2));
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    PROF_BEGIN if (round > 0) ok = mbar_wait_pair(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (round > 0) ok = mbar_wait_pair_warp(bar_empty + 8 * s, (round - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     const uint32_t st = base + s * kPStageBytes;
                     const uint32_t full = bar_full + 8 * s;
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt), sf_bytes = nkb * 512;
-                    mbar_expect_tx(full, kABytes + kPBBytes + 3 * sf_bytes);
-                    tma_load_2d(st, &map_a, (int)(kt * (BK / 2)), (int)(m_block * BM), full);
-                    tma_load_2d(st + kABytes, mb, (int)(kt * (BK / 2)), b_row, full);
-                    bulk_load(st + kABytes + kPBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
-                    bulk_load(st + kABytes + kPBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
-                    bulk_load(st + kABytes + kPBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
+                    mbar_expect_tx_elect(full, kABytes + kPBBytes + 3 * sf_bytes);
+                    tma_load_2d_elect(st, &map_a, (int)(kt * (BK / 2)), (int)(m_block * BM), full);
+                    tma_load_2d_elect(st + kABytes, mb, (int)(kt * (BK / 2)), b_row, full);
+                    bulk_load_elect(st + kABytes + kPBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
+                    bulk_load_elect(st + kABytes + kPBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
+                    bulk_load_elect(st + kABytes + kPBBytes + kSfaBytes + 2048, sfb1 + (size_t)kt * 2048, sf_bytes, full);
                     issued = it + 1;
                 }
             }
-            PROF_FLUSH(0)
+            if (lane == 0) { PROF_FLUSH(0) }
             if (!ok) {
-                *abort_flag = 1;
-                atomicCAS(g.status + 1, 0, 111);
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicCAS(g.status + 1, 0, 111);
+                }
                 // let the copies already in flight land before the CTA's shared memory goes away (bounded: the
                 // leader's phases also need the follower's arrival)
                 const uint32_t first = issued > (uint32_t)kPStages ? issued - kPStages : 0;
@@ -594,8 +633,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
-            // ---------------------------------------------------------------- MMA issuer (leader, for the pair)
+        if (leader) {
+            // ---------------------------------------------------------------- MMA issuer (leader, for the pair; whole warp)
             // M = 256 (128 rows in each CTA), N = 256: N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
             const uint32_t peer_empty = map_to_rank(bar_empty, 1), peer_acc_full = map_to_rank(bar_acc_full, 1);
@@ -603,38 +642,38 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs, ++local) {
                 if (local > 0) {
-                    PROF_BEGIN ok = mbar_wait_pair(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN ok = mbar_wait_pair_warp(bar_acc_empty, (local - 1) & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    PROF_BEGIN ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
+                    PROF_BEGIN ok = mbar_wait_pair_warp(bar_full + 8 * s, round & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     const uint32_t st = base + s * kPStageBytes;
                     const uint64_t da = operand_desc(st), db = operand_desc(st + kABytes);
                     const uint32_t nkb = min(4u, g.kt64 - 4 * kt);
                     const uint32_t buf = it % kSfBufs, sf = tmem + kSfCol + buf * kSfBufCols;
-                    PROF_BEGIN ok = mbar_wait(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_sf_full + 8 * buf, (it / kSfBufs) & 1, abort_flag); PROF_END(2)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (uint32_t kb = 0; kb < nkb; ++kb)
-                        pair_mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
-                    pair_commit(bar_sf_empty + 8 * buf);
-                    pair_commit(bar_empty + 8 * s);   // both CTAs may overwrite the stage once these MMAs have read it
-                    pair_commit(peer_empty + 8 * s);
+                        pair_mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (kt | kb) != 0);
+                    pair_commit_elect(bar_sf_empty + 8 * buf);
+                    pair_commit_elect(bar_empty + 8 * s);   // both CTAs may overwrite the stage once these MMAs have read it
+                    pair_commit_elect(peer_empty + 8 * s);
                 }
                 if (ok) {
-                    pair_commit(bar_acc_full);
-                    pair_commit(peer_acc_full);
+                    pair_commit_elect(bar_acc_full);
+                    pair_commit_elect(peer_acc_full);
                 }
             }
-            PROF_FLUSH(1)
-            if (!ok) {
+            if (lane == 0) { PROF_FLUSH(1) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 112);
             }
-        } else if (lane == 0) {
+        } else {
             // ---------------------------------------------------------------- follower: "my stage has landed"
             const uint32_t leader_full = map_to_rank(bar_full, 0);
             uint32_t it = 0;
@@ -642,41 +681,41 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages;
-                    PROF_BEGIN ok = mbar_wait(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN ok = mbar_wait_warp(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
                     if (!ok) break;
-                    mbar_arrive_cluster(leader_full + 8 * s);
+                    mbar_arrive_cluster_elect(leader_full + 8 * s);
                 }
             }
-            PROF_FLUSH(3)
-            if (!ok) {
+            if (lane == 0) { PROF_FLUSH(3) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 116);
             }
         }
     } else if (warp == 10) {
         // ---------------------------------------------------------------- scale copier (leader, for the pair)
-        if (lane == 0 && leader) {
+        if (leader) { // whole warp
             uint32_t it = 0;
             bool ok = true; PROF_DECL
             for (uint32_t tile = pair; tile < n_tiles_total && ok; tile += pairs) {
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kPStages, round = it / kPStages, buf = it % kSfBufs;
-                    PROF_BEGIN ok = mbar_wait_pair(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
-                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
+                    PROF_BEGIN ok = mbar_wait_pair_warp(bar_full + 8 * s, round & 1, abort_flag); PROF_END(0)
+                    PROF_BEGIN if (ok && it >= kSfBufs) ok = mbar_wait_warp(bar_sf_empty + 8 * buf, ((it / kSfBufs) - 1) & 1, abort_flag); PROF_END(1)
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * kPStageBytes, sfa = st + kABytes + kPBBytes, sfb = sfa + kSfaBytes;
                     const uint32_t sf = tmem + kSfCol + buf * kSfBufCols, nkb = min(4u, g.kt64 - 4 * kt);
                     for (uint32_t kb = 0; kb < nkb; ++kb) { // each CTA copies from its own shared memory into its own tensor memory
-                        pair_cp_scales(sf + 4 * kb, scale_desc(sfa + 512 * kb));
-                        pair_cp_scales(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
-                        pair_cp_scales(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
+                        pair_cp_scales_elect(sf + 4 * kb, scale_desc(sfa + 512 * kb));
+                        pair_cp_scales_elect(sf + 16 + 8 * kb, scale_desc(sfb + 512 * kb));
+                        pair_cp_scales_elect(sf + 16 + 8 * kb + 4, scale_desc(sfb + 2048 + 512 * kb));
                     }
-                    pair_commit(bar_sf_full + 8 * buf);
+                    pair_commit_elect(bar_sf_full + 8 * buf);
                 }
             }
-            PROF_FLUSH(2)
-            if (!ok) {
+            if (lane == 0) { PROF_FLUSH(2) }
+            if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicCAS(g.status + 1, 0, 115);
             }
@@ -781,21 +820,21 @@ __global__ void __launch_bounds__(192, 1) nvfp4_peak_kernel(uint32_t iters, int 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    if (warp == 1 && lane == 0) {
+    if (warp == 1) { // whole warp, one elected lane issues
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         const uint64_t da = operand_desc(base), db = operand_desc(base + kABytes);
         // scale factors: one copy of zeroed chunks so that the accumulator stays finite
         for (uint32_t kb = 0; kb < 4; ++kb) {
-            tmem_cp_scales(tmem + kSfCol + 4 * kb, scale_desc(base + kABytes + kBBytes));
-            tmem_cp_scales(tmem + kSfCol + 16 + 8 * kb, scale_desc(base + kABytes + kBBytes));
-            tmem_cp_scales(tmem + kSfCol + 16 + 8 * kb + 4, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales_elect(tmem + kSfCol + 4 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales_elect(tmem + kSfCol + 16 + 8 * kb, scale_desc(base + kABytes + kBBytes));
+            tmem_cp_scales_elect(tmem + kSfCol + 16 + 8 * kb + 4, scale_desc(base + kABytes + kBBytes));
         }
         for (uint32_t i = 0; i < iters; ++i)
 #pragma unroll
             for (uint32_t kb = 0; kb < 4; ++kb)
-                mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfCol + 4 * kb, tmem + kSfCol + 16 + 8 * kb, (i | kb) != 0);
-        mma_commit(bar_done);
-        if (!mbar_wait(bar_done, 0, abort_flag)) atomicExch(status + 1, 104);
+                mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, tmem + kSfCol + 4 * kb, tmem + kSfCol + 16 + 8 * kb, (i | kb) != 0);
+        mma_commit_elect(bar_done);
+        if (!mbar_wait_warp(bar_done, 0, abort_flag) && lane == 0) atomicExch(status + 1, 104);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -847,43 +886,43 @@ __global__ void __launch_bounds__(192, 1) nvfp4_pipe_probe_kernel(uint32_t mode,
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot, sf = tmem + kSfCol, sf2 = sf + kSfBufCols;
-    if (warp == 1 && lane == 0 && mode != 6) {
+    if (warp == 1 && mode != 6) { // whole warp, one elected lane issues: as the GEMM's roles do
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         const uint64_t da = operand_desc(base), db = operand_desc(base + kABytes);
         auto wide_desc = [&](uint32_t a) { // 128 rows x 32 bytes, the two halves of a row 8 KiB apart
             return (uint64_t)((a >> 4) & 0x3FFF) | (uint64_t)(8192 >> 4) << 16 | (uint64_t)(128 >> 4) << 32 | (uint64_t)1 << 46;
         };
-        for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales(sf + 4 * c, scale_desc(scales + 512 * c)); // what the MMAs read
+        for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales_elect(sf + 4 * c, scale_desc(scales + 512 * c)); // what the MMAs read
         for (uint32_t i = 0; i < iters; ++i) {
             if (mode == 1 || mode == 3)
-                for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales(sf2 + 4 * c, scale_desc(scales + 512 * c));
+                for (uint32_t c = 0; c < 12; ++c) tmem_cp_scales_elect(sf2 + 4 * c, scale_desc(scales + 512 * c));
             if (mode == 4 || mode == 5)
-                for (uint32_t c = 0; c < 6; ++c) asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(sf2 + 8 * c), "l"(wide_desc(scales + 2048 * (c % 3))) : "memory");
+                for (uint32_t c = 0; c < 6; ++c) asm volatile("{\n\t" MUSER_ELECT_PRED "@e tcgen05.cp.cta_group::1.128x256b [%0], %1;\n\t}" ::"r"(sf2 + 8 * c), "l"(wide_desc(scales + 2048 * (c % 3))) : "memory");
             if (mode == 2) {
 #pragma unroll
                 for (uint32_t kb = 0; kb < 4; ++kb) {
-                    for (uint32_t c = 0; c < 3; ++c) tmem_cp_scales(sf2 + 4 * (3 * kb + c), scale_desc(scales + 512 * (3 * kb + c)));
-                    mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
+                    for (uint32_t c = 0; c < 3; ++c) tmem_cp_scales_elect(sf2 + 4 * (3 * kb + c), scale_desc(scales + 512 * (3 * kb + c)));
+                    mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
                 }
             } else if (mode == 0 || mode == 1 || mode == 5) {
 #pragma unroll
-                for (uint32_t kb = 0; kb < 4; ++kb) mma_nvf4(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
+                for (uint32_t kb = 0; kb < 4; ++kb) mma_nvf4_elect(tmem, da + 2 * kb, db + 2 * kb, idesc, sf + 4 * kb, sf + 16 + 8 * kb, (i | kb) != 0);
             }
         }
-        mma_commit(bar_done);
-        if (!mbar_wait(bar_done, 0, abort_flag)) atomicExch(status + 1, 107);
+        mma_commit_elect(bar_done);
+        if (!mbar_wait_warp(bar_done, 0, abort_flag) && lane == 0) atomicExch(status + 1, 107);
     }
-    if (warp == 0 && lane == 0 && load_chunks) {
+    if (warp == 0 && load_chunks) {
         uint32_t at = (blockIdx.x * 977u) % src_chunks;
         for (uint32_t it = 0; it < load_chunks + kProbeLoadRing; ++it) {
             const uint32_t slot = it % kProbeLoadRing, bar = bar_load + 8 * slot;
-            if (it >= (uint32_t)kProbeLoadRing && !mbar_wait(bar, ((it / kProbeLoadRing) - 1) & 1, abort_flag)) {
-                atomicExch(status + 1, 108);
+            if (it >= (uint32_t)kProbeLoadRing && !mbar_wait_warp(bar, ((it / kProbeLoadRing) - 1) & 1, abort_flag)) {
+                if (lane == 0) atomicExch(status + 1, 108);
                 break;
             }
             if (it < load_chunks) {
-                mbar_expect_tx(bar, kProbeLoadChunk);
-                bulk_load(load_base + slot * kProbeLoadChunk, src + (size_t)at * kProbeLoadChunk, kProbeLoadChunk, bar);
+                mbar_expect_tx_elect(bar, kProbeLoadChunk);
+                bulk_load_elect(load_base + slot * kProbeLoadChunk, src + (size_t)at * kProbeLoadChunk, kProbeLoadChunk, bar);
                 at = (at + 149u) % src_chunks;
             }
         }
