@@ -30,6 +30,7 @@ pub const MUSER_TUNE_ONESHOT_MAX_BYTES: u32 = 11;
 pub const MUSER_TUNE_DECODE_WSPLIT: u32 = 12;
 pub const MUSER_TUNE_NVFP4_PAIR: u32 = 13;
 pub const MUSER_TUNE_HOST_DIRECT_OUTPUT: u32 = 14;
+pub const MUSER_TUNE_NVFP4_GROUP_M: u32 = 15;
 
 pub const MUSER_CUDA_COMM_ID_BYTES: usize = 128;
 

@@ -16,6 +16,7 @@ TUNE_TC_MIN_TOKENS_Q4_K, TUNE_TC_MIN_TOKENS_Q6_K, TUNE_TC_MIN_ROWS = 1, 2, 3
 TUNE_DECODE_WARPS, TUNE_DECODE_KSPLIT, TUNE_DECODE_RING, TUNE_ONESHOT_MAX_BYTES, TUNE_DECODE_WSPLIT = 8, 9, 10, 11, 12
 TUNE_NVFP4_PAIR = 13
 TUNE_HOST_DIRECT_OUTPUT = 14
+TUNE_NVFP4_GROUP_M = 15
 STATUS_NAMES = ["OK", "BAD_ARG", "BAD_SHAPE", "BAD_ALIGN", "UNSUPPORTED_DTYPE", "NAN_SCALE", "CUDA_ERROR", "NCCL_ERROR",
                 "TIMEOUT", "WORKSPACE_TOO_SMALL"]
 

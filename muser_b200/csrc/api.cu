@@ -316,6 +316,7 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
         return MUSER_CUDA_OK;
     case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;
     case MUSER_TUNE_HOST_DIRECT_OUTPUT: ctx->host_direct_output = value != 0; return MUSER_CUDA_OK;
+    case MUSER_TUNE_NVFP4_GROUP_M: ctx->nvfp4_group_m = value; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
 }

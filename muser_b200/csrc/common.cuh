@@ -58,6 +58,7 @@ struct Ctx {
     unsigned int *amax_flags = nullptr;
     bool host_direct_output = true;            // host-group entry: a kernel stores the outputs into mapped host buffers (else memcpy)
     uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs (cta_group::2): 0 off, 1 on
+    uint32_t nvfp4_group_m = 0;                // NVFP4 GEMM: token tiles per raster group, 0 = automatic
     uint32_t oneshot_max_bytes = 1536u << 10;  // all-reduce payloads up to this size take the one-shot peer exchange
     std::string last_error;
 };

@@ -88,6 +88,15 @@ __device__ __forceinline__ void tile_fetch(uint32_t dst, const void *src, uint32
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
+// The same, called by the whole (converged) warp: one elected lane issues.  Bulk copies take their operands from the
+// warp-uniform registers, and issued from inside an `if (lane == 0)` branch each one cost the warp 100+ cycles.
+__device__ __forceinline__ void tile_fetch_elect(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+        "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %2;\n\t"
+        "@e cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n\t}"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
 __device__ __forceinline__ bool tile_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kDecWaitLimit; ++i) {
         uint32_t done;
@@ -490,10 +499,10 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     const uint32_t bar0 = smem_addr(bars + warp * ring_n);
     uint32_t f_tile = first_row * a.nsb + sb_first + t_first, f_tl = 0, f_im = 0;
     const uint64_t policy = evict_first_policy();
-    auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, lane 0 issues the copy
+    auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, one elected lane issues the copy
         const uint8_t *base = jb.image;
         if constexpr (DUAL) base = f_im ? jb.image_up : jb.image;
-        if (lane == 0) tile_fetch(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot, policy);
+        tile_fetch_elect(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot, policy);
         ++f_tile;
         if (++f_tl == my_tiles) {
             f_tl = 0;
@@ -534,7 +543,8 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
             for (int gp = 0; gp < NG; ++gp) out[im][gp][0] = out[im][gp][1] = 0.f;
             for (uint32_t tl = t_first; tl < t_first + my_tiles; ++tl, ++n) {
                 const uint32_t slot = n & ring_mask;
-                if (healthy && !tile_wait(bar0 + 8 * slot, (n >> ring_shift) & 1)) {
+                // (the warp agrees on the outcome: the fetch below is issued by an elected lane of the WHOLE warp)
+                if (healthy && !__all_sync(0xffffffffu, tile_wait(bar0 + 8 * slot, (n >> ring_shift) & 1))) {
                     healthy = false;
                     atomicExch(a.status + 1, 211);
                 }

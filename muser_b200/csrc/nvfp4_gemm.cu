@@ -71,7 +71,21 @@ struct GemmArgs {
     uint8_t *q_scales;  // swizzled, ceil(tokens / 128) x (n_out / 64) chunks
     float q_isi;        // the next projection's input_scale_inv
     uint32_t q_kt;      // n_out / 64
+    uint32_t group_m;   // token tiles per raster group (tile_coords)
 };
+
+// Output tile number -> (token tile, weight-row tile).  Tiles are numbered group by group: a group is `group_m` token
+// tiles; inside it the token tile runs fastest, then the weight-row tile.  The CTAs that run side by side thus share
+// a few weight tiles (read from HBM once per group, from L2 by the others) and together touch only the group's
+// activations, which stay in L2 while the group sweeps all weight rows.  With every token tile in one group
+// (group_m >= m_tiles, the case up to a few thousand tokens) this is "token tile fastest"; at 32768 tokens the
+// activations of ffn_down alone are 453 MB, and without groups each of its 20 weight-row tiles re-read them from HBM.
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t m_tiles, uint32_t n_tiles, uint32_t group_m, uint32_t &tile_m, uint32_t &tile_n) {
+    const uint32_t per_group = group_m * n_tiles, group = tile / per_group, r = tile - group * per_group;
+    const uint32_t gm = min(group_m, m_tiles - group * group_m); // the last group may be short
+    tile_n = r / gm;
+    tile_m = group * group_m + (r - tile_n * gm);
+}
 
 // Scale-factor chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr) {
@@ -222,7 +236,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t it = 0, issued = 0; // k slabs issued so far, over all tiles
             bool ok = true; PROF_DECL
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-                const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+                uint32_t tile_m, tile_n;
+                tile_coords(tile, m_tiles, g.n_tiles, g.group_m, tile_m, tile_n);
                 const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
                 const uint8_t *sfb0 = g.b_scales + (size_t)(DUAL ? tile_n : 2 * tile_n) * g.kt64 * 512;
                 const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
@@ -360,7 +375,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         constexpr uint32_t kOutCols = DUAL ? BN / 2 : BN, kPartCols = kOutCols / 2;
         uint32_t local = 0;
         for (uint32_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
-            const uint32_t tile_m = tile % m_tiles, tile_n = tile / m_tiles;
+            uint32_t tile_m, tile_n;
+            tile_coords(tile, m_tiles, g.n_tiles, g.group_m, tile_m, tile_n);
             const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full, local & 1, abort_flag));
             if (!ok) {
                 if (lane == 0) {
@@ -1044,6 +1060,12 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     g.q_scales = qout ? qout->scales : nullptr;
     g.q_isi = qout ? qout->input_scale_inv : 0.0f;
     g.q_kt = (uint32_t)(w->n_out / 64);
+    {   // raster groups of about 32 MB of activations (at least 8 token tiles)
+        const uint64_t tile_bytes = (uint64_t)BM * (w->n_in / 2 + w->n_in / 16);
+        uint32_t gm = (uint32_t)std::max<uint64_t>(8, (32ull << 20) / std::max<uint64_t>(1, tile_bytes));
+        if (ctx->nvfp4_group_m) gm = ctx->nvfp4_group_m;
+        g.group_m = std::max<uint32_t>(1, std::min<uint32_t>(gm, (tokens + BM - 1) / BM));
+    }
     if (qout && (!w_up || w->n_out % 64)) return fail(ctx, MUSER_CUDA_BAD_SHAPE, "quantized outputs come from the fused gate/up form, with n_out % 64 == 0");
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(w_up ? w->tmap_half : w->tmap_cache);
     const CUtensorMap &mb2 = w_up ? *reinterpret_cast<const CUtensorMap *>(w_up->tmap_half) : mb;

@@ -385,3 +385,37 @@ def test_workspace_and_dtype_misuse(gpu):
     assert e.value.status_name == "WORKSPACE_TOO_SMALL"
     w.free()
     small.close()
+
+
+@pytest.mark.parametrize("group_m", [1, 2, 3])
+def test_raster_groups_do_not_change_the_outputs(gpu, group_m):
+    """MUSER_TUNE_NVFP4_GROUP_M only reorders the output tiles (groups of token tiles; the last group short when the
+    tile count is no multiple): every output must carry the same bits as with all token tiles in one group, in the
+    plain, the fused gate/up and the quantized-output forms."""
+    from muser_b200 import synth
+    from muser_b200._lib import TUNE_NVFP4_GROUP_M
+    op, ctx, k = gpu
+    n_out, n_in, tokens = 768, 512, 900  # 8 token tiles (the last one ragged), 3 weight-row tiles
+    packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=91, negative_scales=True)
+    up, us, u2 = make_weight(op, ctx, n_out, n_in, seed=92)
+    x = synth.normal_activations(tokens, n_in, seed=93)
+    isi = synth.activation_input_scale_inv(x)
+    w = op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi))
+    wu = op.Weight(ctx, op.TensorView(up, O.NVFP4, n_in, n_out, us, u2, isi))
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    out = {}
+    try:
+        for gm in (0, group_m):
+            ctx.tuning_set(TUNE_NVFP4_GROUP_M, gm)
+            y = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+            y2 = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+            k.encode_nvfp4_prequant(w, xp, xs, y, tokens)
+            k.encode_nvfp4_ffn_gate_up_silu_prequant(w, wu, xp, xs, y2, tokens)
+            qp, qs = k.encode_nvfp4_ffn_gate_up_silu_requant(w, wu, xp, xs, tokens, 0.37)
+            ctx.sync_status()
+            out[gm] = [t.cpu() for t in (y, y2, qp, qs)]
+    finally:
+        ctx.tuning_set(TUNE_NVFP4_GROUP_M, 0)
+    for i, (a, b) in enumerate(zip(out[0], out[group_m])):
+        assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a, b.view(torch.int32) if b.dtype == torch.float32 else b), f"output {i}"
+    assert not torch.isnan(out[group_m][0]).any()
