@@ -335,7 +335,8 @@ struct TcSmem {
     static constexpr uint32_t kACol = kBufs * kBufCols, kTmemCols = 512;
     static_assert(kACol + kTcStagesA * kTcStageCols <= kTmemCols, "tensor memory exceeded");
     static constexpr int kDrainWarps = N >= 32 ? 8 : 4, kDrainCols = N / (kDrainWarps / 4);
-    static constexpr int kThreads = 32 * (2 + kTcDequantWarps + kDrainWarps);
+    static constexpr int kMmaWarp1 = 2 + kTcDequantWarps + kDrainWarps; // the second MMA warp comes last, so that the others keep their lane quarters
+    static constexpr int kThreads = 32 * (2 + kTcDequantWarps + kDrainWarps + 1);
     static constexpr int kBars = 2 * kTcStagesA + 2 * kStagesB + 2 * kBufs;
     static constexpr int kBytes = kOffBars + kBars * 8 + 16 + 1024 /*alignment slack*/;
     static_assert(kBytes <= 227 * 1024, "shared memory of one CTA exceeded");
@@ -422,16 +423,26 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (uint32_t k = first; k < issued; ++k) mbar_wait_alone(bar_full_b + 8 * (k % kStagesB), (k / kStagesB) & 1);
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer (whole warp, one lane issues)
+    } else if (warp == 1 || warp == S::kMmaWarp1) {
+        // ---------------------------------------------------------------- MMA issuers (whole warps, one lane issues)
+        // Two warps, one for the even and one for the odd super-block columns of the CTA's sequence (their A stages,
+        // activation slabs and accumulator buffers are disjoint by parity): issuing a column's 17 MMAs and 7 commits
+        // takes one warp longer than the tensor pipe needs to run them.
         {
+            const uint32_t par = warp == 1 ? 0u : 1u;
             // kind::f16: f32 accumulator (bit 4), A and B f16 (format 0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
             TcWalk w;
             w.start(a);
-            uint32_t hs = 0, tc = 0;
+            if (par && !w.done(a)) w.next(a);
+            uint32_t tc = par;
             bool ok = true; TPROF_DECL
-            for (; !w.done(a) && ok; w.next(a), ++tc) {
+            auto advance2 = [&]() {
+                w.next(a);
+                if (!w.done(a)) w.next(a);
+            };
+            for (; !w.done(a) && ok; advance2(), tc += 2) {
+                uint32_t hs = 2 * tc; // the column's two activation slabs
                 const uint32_t buf = tc % kBufs, d_main = tmem + buf * S::kBufCols, d_min = d_main + S::kAcc * N;
                 if (tc >= (uint32_t)kBufs) { // the drain warps must have read this buffer's previous contents
                     TPROF_BEGIN ok = mbar_wait_warp(bar_tmem_empty + 8 * buf, ((tc / kBufs) - 1) & 1, abort_flag); TPROF_END(0)
@@ -467,7 +478,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 if (ok) mma_commit_elect(bar_tmem_full + 8 * buf);
             }
-            if (lane == 0) { TPROF_FLUSH(1) }
+            if (lane == 0 && warp == 1) { TPROF_FLUSH(1) }
             if (!ok && lane == 0) {
                 *abort_flag = 1;
                 atomicExch(a.status + 1, 302);
@@ -555,8 +566,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             *abort_flag = 1;
             atomicCAS(a.status + 1, 0, 303);
         }
-    } else {
-        // ---------------------------------------------------------------- drain (the last 4 or 8 warps)
+    } else if (warp < S::kMmaWarp1) {
+        // ---------------------------------------------------------------- drain (4 or 8 warps)
         constexpr int C = S::kDrainCols;                                          // token columns of this warp
         const uint32_t quad = warp & 3, row_in_block = quad * 32 + lane;          // its 32 accumulator lanes = rows
         const uint32_t part = (uint32_t)(warp - 2 - kTcDequantWarps) >> 2, col0 = part * C;
@@ -629,24 +640,32 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 finish = seen == a.ksplit - 1;
                 if (finish) {
                     if (lane == 0) *counter = 0; // ready for the next launch
-                    // slices in order (deterministic); sixteen independent loads in flight per step, not one
+                    // Slices are added in slice order (deterministic), but fetched four at a time: a step's 32 loads
+                    // are in flight together, so eighteen slices cost five trips to L2 instead of eighteen.
 #pragma unroll
-                    for (int c0 = 0; c0 < C; c0 += 16) {
-                        float v[16];
+                    for (int c0 = 0; c0 < C; c0 += 8) {
+                        float v[8];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                        for (uint32_t sl = 0; sl < a.ksplit; ++sl) {
-                            float got[16];
+                        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+                        for (uint32_t sl0 = 0; sl0 < a.ksplit; sl0 += 4) {
+                            float got[4][8];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const uint32_t t = min(tok0 + (uint32_t)(c0 + j), a.tokens - 1); // past `tokens`: re-read the last one
-                                got[j] = __ldcg(a.partial + ((size_t)sl * a.tokens + t) * a.n_out + (live ? row : 0u));
+                            for (uint32_t b = 0; b < 4; ++b) {
+                                const uint32_t sl = min(sl0 + b, a.ksplit - 1); // past the last slice: re-read it, and do not add it
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const uint32_t t = min(tok0 + (uint32_t)(c0 + j), a.tokens - 1); // past `tokens`: re-read the last one
+                                    got[b][j] = __ldcg(a.partial + ((size_t)sl * a.tokens + t) * a.n_out + (live ? row : 0u));
+                                }
                             }
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] += got[j];
+                            for (uint32_t b = 0; b < 4; ++b)
+                                if (sl0 + b < a.ksplit)
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[j] += got[b][j];
                         }
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[c0 + j] = v[j];
+                        for (int j = 0; j < 8; ++j) acc[c0 + j] = v[j];
                     }
                 }
             }
