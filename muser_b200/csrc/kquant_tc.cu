@@ -329,9 +329,12 @@ struct TcSmem {
     static constexpr int kHdrDepth = 8;              // (d, dmin) per row of the last eight super-block columns
     static constexpr int kOffBars = kOffHdr + kHdrDepth * kTcRows * 8;
     // Tensor memory: kBufs accumulator buffers (kAcc main parts + the min part each), then the A stages.
-    static constexpr int kAcc = N <= 32 ? 2 : 1;     // two main accumulators taken in turn where the columns allow (measured faster)
+    // An MMA warp cannot start a column before the drain warps have read that buffer's previous column, so buffers
+    // are worth more than a second main accumulator per buffer (back-to-back MMAs into one accumulator run at the
+    // same 46 cycles as alternating ones): four buffers up to 32 columns, two at 64.
+    static constexpr int kAcc = N == 16 ? 2 : 1;
     static constexpr int kBufCols = (kAcc + 1) * N;
-    static constexpr int kBufs = N == 16 ? 4 : 2;
+    static constexpr int kBufs = N <= 32 ? 4 : 2;
     static constexpr uint32_t kACol = kBufs * kBufCols, kTmemCols = 512;
     static_assert(kACol + kTcStagesA * kTcStageCols <= kTmemCols, "tensor memory exceeded");
     static constexpr int kDrainWarps = N >= 32 ? 8 : 4, kDrainCols = N / (kDrainWarps / 4);
@@ -526,6 +529,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 ok = __all_sync(0xffffffffu, ok); TPROF_END(1)
                 if (!ok) return;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                TPROF_BEGIN
 #pragma unroll
                 for (int j = 0; j < 2; ++j) { // 16 columns at a time keeps the live registers down
                     uint32_t o[16];
@@ -538,6 +542,8 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                     tmem_st16(st_base + QD * kTcStageCols + 16 * j, o);
                 }
+                TPROF_END(0)
+                TPROF_BEGIN
                 if (QD == 1 && half == 1) {
                     if constexpr (Q4) {
                         // min operand (shared memory): 16 f16 per row, (m_j, m_j) for j = 0..7, two 16-byte chunks, 32-byte swizzle.
@@ -557,6 +563,7 @@ kquant_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+                TPROF_END(2)
             };
             quarter_step(std::integral_constant<int, 0>{});
             if (ok) quarter_step(std::integral_constant<int, 1>{});
