@@ -13,16 +13,19 @@
 // sum (X_j = sum of the 32 activations of sub-block j, carried as an f16 head + remainder pair) done by one more
 // MMA.  This is the deferred order of quant/k_block.rs:178-240 and quant/k_block/q6.rs:90-141 with exact inner sums.
 //
-// One CTA per SM, persistent over (128-row block, K slice) items:
+// One CTA per SM, persistent over (128-row block, K slice) items; every role walks the same (item, column) sequence:
 //   warp 0      TMA: activation slabs (N tokens x 128 inputs, 128-byte swizzle) and the X_j pairs (32-byte swizzle)
-//   warp 1      tcgen05.mma kind::f16, M = 128 rows, N = tokens (16 / 32 / 64), K = 16; accumulators in tensor memory,
-//               four buffers so that the drain of one super-block column runs under the MMAs of the next ones
-//   warps 2-17  eight rows of one 16-row weight tile each: bulk copies global -> shared (three or four tiles in flight
-//               per warp), unpack to the f16 integers above, store into the swizzled A stage (two stages of 128 inputs)
-//   warps 18-.. drain (four warps; eight from 32 token columns on, half the columns each, so that the running sums
-//               stay in registers): tcgen05.ld, scale by d / dmin (f32), keep the running sums per row in registers;
-//               at the end of an item add the K slices through the context scratch (last arriver sums in slice
-//               order) and store
+//   warp 1 and the last warp
+//               tcgen05.mma kind::f16, M = 128 rows, N = tokens (16 / 32 / 64), K = 16, the A operand read from
+//               tensor memory; one warp takes the even columns of the sequence, the other the odd ones
+//   warps 2-17  one weight row per thread: (column parity, half of the column, 32-row quarter) per warp; the row's
+//               bytes come straight from global memory, become the f16 integers above and go to tensor memory
+//               (tcgen05.st), 64 inputs = one A stage at a time (eight stages = two columns)
+//   then 4 or 8 drain warps (eight from 32 token columns on, half the columns each, so that the running sums stay in
+//               registers): tcgen05.ld, scale by d / dmin (f32), keep the running sums per row in registers; at the
+//               end of an item add the K slices through the context scratch (last arriver sums in slice order) and
+//               store
+// The producer and MMA warps run their loops converged and issue through an elected lane (tcgen05.cuh).
 // Every wait is bounded; a wait that gives up records a code in the context's status word and the CTA winds down.
 #include <algorithm>
 #include <cmath>

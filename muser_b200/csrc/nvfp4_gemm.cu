@@ -7,8 +7,9 @@
 //
 // Shape of the kernel: persistent CTAs, one per SM, each walking 128-token x 256-row output tiles.  Warp 0 streams 128-byte-swizzled
 // K slabs (256 values) of both operands with TMA plus their scale factors with bulk copies through a
-// 4-stage shared-memory ring; warp 1 copies the scale factors into tensor memory (tcgen05.cp) and issues
-// tcgen05.mma kind::mxf4nvf4 (K = 64 per instruction) into a 128 x 256 f32 accumulator in tensor memory;
+// 4-stage shared-memory ring; warp 1 copies each K = 64 block's scale factors into tensor memory (tcgen05.cp) and
+// issues its tcgen05.mma kind::mxf4nvf4 right behind them into a 128 x 256 f32 accumulator in tensor memory (both
+// warps run their loops converged and issue through an elected lane: tcgen05.cuh);
 // warps 2-9 read the accumulator back (tcgen05.ld), apply the two tensor scales and the fused epilogue, and
 // store.  Every mbarrier wait is bounded: on expiry the CTA records a code in the context's status word,
 // stops issuing work, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
