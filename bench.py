@@ -531,6 +531,20 @@ def prefill_section(ctx, kern, op, synth, projs, dev, torch):
         fused["ffn_gate|up+swiglu"] = {"gemm_tflops": round(2.0 * m * 2 * n_f * k_h / t / 1e12, 1)}
         w_g.free()
         w_u.free()
+        # q | k | v on the same activations in one launch (muser_cuda_nvfp4_matmul_group_prequant)
+        qkv = []
+        for nm in ("attn_q", "attn_k", "attn_v"):
+            n_p = projs[nm][1]
+            p = synth.nvfp4_weight(synth.normal_weights(n_p, k_h, seed=0, stream=names.index(nm), device=dev))
+            qkv.append((op.Weight(ctx, op.TensorView(p[0], NVFP4, k_h, n_p, p[1], p[2], isi)), torch.empty((m, n_p), dtype=torch.bfloat16, device=dev)))
+        t = timed(lambda: kern.encode_nvfp4_group_prequant([w for w, _ in qkv], xp, xs, [y for _, y in qkv], m))
+        fl_qkv = 2.0 * m * sum(projs[nm][1] for nm in ("attn_q", "attn_k", "attn_v")) * k_h
+        fused["attn_q|k|v"] = {"gemm_tflops": round(fl_qkv / t / 1e12, 1)}
+        # the layer as a caller would launch it: q | k | v grouped, the other four as measured above
+        t_rest = sum(2.0 * m * projs[nm][0] * projs[nm][1] / (per[nm]["gemm_tflops"] * 1e12) for nm in ("attn_o", "ffn_gate", "ffn_up", "ffn_down"))
+        fused["layer_with_q|k|v_grouped"] = {"gemm_tflops": round(tot_fl / (t + t_rest) / 1e12, 1)}
+        for w, _ in qkv:
+            w.free()
     except Exception as exc:  # the secondary section must never cost the headline line
         fused = {"error": f"{type(exc).__name__}: {exc}"}
 

@@ -286,6 +286,17 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx
                                                    void *y, uint32_t y_dtype, uint32_t tokens,
                                                    const muser_cuda_epilogue *epilogue, void *stream);
 
+/* The NVFP4 form of muser_cuda_quantized_matmul_group (MetalKernels::encode_quantized_decode_group,
+ * src/metal/encode/qkv.rs:414-449: q | k | v on the same activations in one dispatch): 2..4 NVFP4 weights with the same
+ * n_in and the same input_scale_inv, the activations quantized earlier, one launch whose output tiles run through
+ * all of them, so the small projections fill the SMs that a launch of their own would leave idle.  Every output is
+ * bit-identical to what muser_cuda_nvfp4_matmul_prequant gives for that weight.  Plain outputs (no epilogue), all of
+ * y_dtype, outputs[i] [tokens][n_out of weights[i]]. */
+MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_matmul_group_prequant(muser_cuda_ctx *ctx, const muser_cuda_weight *const *weights,
+                                                         uint32_t n_weights, const uint8_t *x_packed,
+                                                         const uint8_t *x_scales_swizzled, void *const *outputs,
+                                                         uint32_t y_dtype, uint32_t tokens, void *stream);
+
 /* muser_cuda_ffn_gate_up_silu for NVFP4 weights on activations quantized earlier (the pre-quantized form of
  * qkv.rs:13-26 applied to the fused FFN front half). */
 MUSER_CUDA_API muser_cuda_status muser_cuda_nvfp4_ffn_gate_up_silu_prequant(muser_cuda_ctx *ctx, const muser_cuda_weight *w_gate,

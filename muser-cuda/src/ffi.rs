@@ -269,6 +269,17 @@ extern "C" {
         epilogue: *const muser_cuda_epilogue,
         stream: *mut c_void,
     ) -> muser_cuda_status;
+    pub fn muser_cuda_nvfp4_matmul_group_prequant(
+        ctx: *mut muser_cuda_ctx,
+        weights: *const *const muser_cuda_weight,
+        n_weights: u32,
+        x_packed: *const u8,
+        x_scales_swizzled: *const u8,
+        outputs: *const *mut c_void,
+        y_dtype: u32,
+        tokens: u32,
+        stream: *mut c_void,
+    ) -> muser_cuda_status;
     pub fn muser_cuda_nvfp4_ffn_gate_up_silu_prequant(
         ctx: *mut muser_cuda_ctx,
         w_gate: *const muser_cuda_weight,

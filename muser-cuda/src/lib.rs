@@ -380,6 +380,38 @@ impl<'c> CudaKernels<'c> {
         )
     }
 
+    /// q | k | v (2..4 NVFP4 weights with the same inputs and `input_scale_inv`) on activations quantized earlier, one
+    /// launch over the output tiles of all of them; every output equals the single call's, bit for bit.
+    pub fn encode_nvfp4_group_prequant(
+        &self,
+        stream: Stream,
+        weights: &[&CudaWeight],
+        packed: DeviceSlice<'_>,
+        scales_swizzled: DeviceSlice<'_>,
+        outputs: &[DeviceSlice<'_>],
+        columns: usize,
+    ) -> Result<()> {
+        let ws: Vec<*const ffi::muser_cuda_weight> = weights.iter().map(|w| w.raw as *const _).collect();
+        let ys: Vec<*mut std::ffi::c_void> = outputs.iter().map(|o| o.ptr).collect();
+        let y_dtype = outputs.first().map_or(0, |o| o.dtype as u32);
+        check(
+            unsafe {
+                ffi::muser_cuda_nvfp4_matmul_group_prequant(
+                    self.ctx.raw,
+                    ws.as_ptr(),
+                    ws.len() as u32,
+                    packed.ptr as *const u8,
+                    scales_swizzled.ptr as *const u8,
+                    ys.as_ptr(),
+                    y_dtype,
+                    columns as u32,
+                    stream.0,
+                )
+            },
+            self.ctx.raw,
+        )
+    }
+
     /// Measures the decode kernel's launch plans for one projection or group once, at load time.
     pub fn autotune(&self, stream: Stream, weights: &[&CudaWeight], up: Option<&CudaWeight>, max_tokens: usize) -> Result<()> {
         let raw: Vec<*const ffi::muser_cuda_weight> = weights.iter().map(|w| w.raw as *const _).collect();

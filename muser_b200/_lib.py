@@ -26,7 +26,7 @@ EXPORTS = [
     "muser_cuda_last_error", "muser_cuda_sync_status", "muser_cuda_weight_repack", "muser_cuda_weight_repack_device",
     "muser_cuda_weight_free", "muser_cuda_weight_info_get", "muser_cuda_dequant", "muser_cuda_quantized_matmul",
     "muser_cuda_ffn_gate_up_silu", "muser_cuda_quantize_nvfp4_activation", "muser_cuda_nvfp4_swizzled_scale_bytes",
-    "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_matmul_host",
+    "muser_cuda_nvfp4_matmul", "muser_cuda_nvfp4_matmul_prequant", "muser_cuda_nvfp4_matmul_group_prequant", "muser_cuda_matmul_host",
     "muser_cuda_nvfp4_matmul_static", "muser_cuda_fp4_peak_probe", "muser_cuda_fp4_pipe_probe", "muser_cuda_lm_head_argmax", "muser_cuda_matmul_host_groups_enqueue", "muser_cuda_fused_norm_residual_rms_norm",
     "muser_cuda_sigmoid_gate", "muser_cuda_head_rms_norm", "muser_cuda_nvfp4_ffn_gate_up_silu_requant", "muser_cuda_nvfp4_ffn_gate_up_silu_prequant",
     "muser_cuda_rmsnorm_quantize_nvfp4_activation", "muser_cuda_tuning_set", "muser_cuda_f16_mma_probe", "muser_cuda_quantized_matmul_rows",
@@ -96,6 +96,7 @@ def _load() -> C.CDLL:
         "muser_cuda_nvfp4_swizzled_scale_bytes": (C.c_size_t, [u64, u64]),
         "muser_cuda_nvfp4_matmul": (i32, [vp, vp, vp, u32, vp, u32, u32, C.POINTER(Epilogue), vp]),
         "muser_cuda_nvfp4_matmul_prequant": (i32, [vp, vp, vp, vp, vp, u32, u32, C.POINTER(Epilogue), vp]),
+        "muser_cuda_nvfp4_matmul_group_prequant": (i32, [vp, C.POINTER(vp), u32, vp, vp, C.POINTER(vp), u32, u32, vp]),
         "muser_cuda_matmul_host": (i32, [vp, vp, vp, u32, vp]),
         "muser_cuda_matmul_host_enqueue": (i32, [vp, vp, vp, u32, vp, vp]),
         "muser_cuda_comm_unique_id": (i32, [vp, C.c_size_t]),

@@ -674,6 +674,29 @@ muser_cuda_status muser_cuda_nvfp4_matmul_prequant(muser_cuda_ctx *c, const muse
     return launch_nvfp4_gemm(ctx, w, xp, xs, y, y_dtype, tokens, e, (cudaStream_t)stream);
 }
 
+muser_cuda_status muser_cuda_nvfp4_matmul_group_prequant(muser_cuda_ctx *c, const muser_cuda_weight *const *wps, uint32_t n,
+                                                         const uint8_t *xp, const uint8_t *xs, void *const *ys,
+                                                         uint32_t y_dtype, uint32_t tokens, void *stream) {
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    if (!ctx) return MUSER_CUDA_BAD_ARG;
+    if (!wps || !ys || n < 2 || n > 4) return fail(ctx, MUSER_CUDA_BAD_ARG, "a group holds 2 to 4 weights");
+    const Weight *ws[4];
+    for (uint32_t i = 0; i < n; ++i) {
+        ws[i] = reinterpret_cast<const Weight *>(wps[i]);
+        if (!ws[i]) return fail(ctx, MUSER_CUDA_BAD_ARG, "null weight in the group");
+        muser_cuda_status st = check_io(ctx, ws[i], xp, MUSER_DTYPE_BF16, ys[i], y_dtype, tokens, true);
+        if (st != MUSER_CUDA_OK) return st;
+        Epilogue e;
+        st = nvfp4_checks(ctx, ws[i], nullptr, &e);
+        if (st != MUSER_CUDA_OK) return st;
+        if (ws[i]->n_in != ws[0]->n_in || ws[i]->input_scale_inv != ws[0]->input_scale_inv)
+            return fail(ctx, MUSER_CUDA_BAD_SHAPE, "the weights of a group read the same quantized activations: same n_in, same input_scale_inv");
+    }
+    if (!xs || !aligned16(xs)) return fail(ctx, MUSER_CUDA_BAD_ALIGN, "activation scales must be 16-byte aligned");
+    MUSER_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return launch_nvfp4_gemm_group(ctx, ws, n, xp, xs, ys, y_dtype, tokens, (cudaStream_t)stream);
+}
+
 muser_cuda_status muser_cuda_nvfp4_matmul(muser_cuda_ctx *c, const muser_cuda_weight *wp, const void *x, uint32_t x_dtype,
                                           void *y, uint32_t y_dtype, uint32_t tokens, const muser_cuda_epilogue *ep,
                                           void *stream) {

@@ -206,6 +206,8 @@ struct NvFp4Out { // where a GEMM leaves its output as NVFP4 activations for the
 muser_cuda_status launch_nvfp4_gemm(Ctx *, const Weight *w, const uint8_t *x_packed, const uint8_t *x_scales,
                                     void *y, uint32_t y_dtype, uint32_t tokens, const Epilogue &, cudaStream_t,
                                     const Weight *w_up = nullptr, const NvFp4Out *qout = nullptr);
+muser_cuda_status launch_nvfp4_gemm_group(Ctx *, const Weight *const *ws, uint32_t n, const uint8_t *x_packed, const uint8_t *x_scales,
+                                          void *const *ys, uint32_t y_dtype, uint32_t tokens, cudaStream_t);
 muser_cuda_status launch_nvfp4_a16(Ctx *, const Weight *w, const void *x, uint32_t x_dtype, void *y, uint32_t y_dtype, uint32_t tokens,
                                    void *workspace, size_t workspace_bytes, cudaStream_t);
 muser_cuda_status launch_nvfp4_peak(Ctx *, uint32_t iters, double *flops, cudaStream_t);

@@ -73,6 +73,13 @@ struct GemmArgs {
     float q_isi;        // the next projection's input_scale_inv
     uint32_t q_kt;      // n_out / 64
     uint32_t group_m;   // token tiles per raster group (tile_coords)
+    // GROUP form: up to four projections of the same activations in one launch; weight-row tiles are numbered through
+    // all of them (projection p owns tiles grp_tile0[p] .. grp_tile0[p + 1] - 1)
+    uint32_t grp_tile0[5];
+    const uint8_t *grp_b_scales[4];
+    void *grp_y[4];
+    uint32_t grp_n_out[4];
+    float grp_scale2[4];
 };
 
 // Output tile number -> (token tile, weight-row tile).  Tiles are numbered group by group: a group is `group_m` token
@@ -189,10 +196,14 @@ __device__ __forceinline__ void store_strip(const float (&v)[32], T *y, const T 
 // quant::quantize_nvfp4_activation would quantize the f32 product (quant/nvfp4.rs:173-238): a thread holds 64
 // consecutive outputs of its token, i.e. four 16-value groups = one chunk of the swizzled scale plane, and writes
 // 32 bytes of codes and one word of scales.  The 27648-wide intermediate is never written or read as numbers.
-template <bool DUAL, bool TAIL, bool QOUT = false>
+// GROUP: several projections that read the same quantized activations (q | k | v) share one launch: their weight-row
+// tiles form one tile space, so the small ones fill the SMs that a launch of their own would leave idle.  Plain
+// outputs only (no fused tail, row scale or residual).
+template <bool DUAL, bool TAIL, bool QOUT = false, bool GROUP = false>
 __global__ void __launch_bounds__(352, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ CUtensorMap map_b2, const GemmArgs g) {
+                  const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_b3,
+                  const __grid_constant__ CUtensorMap map_b4, const GemmArgs g) {
     constexpr uint32_t kTileRows = DUAL ? BN / 2 : BN; // output columns (weight rows) per tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
@@ -239,8 +250,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (uint32_t tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
                 uint32_t tile_m, tile_n;
                 tile_coords(tile, m_tiles, g.n_tiles, g.group_m, tile_m, tile_n);
+                const uint8_t *b_scales = g.b_scales;
+                const CUtensorMap *mb = &map_b;
+                if constexpr (GROUP) {
+                    const uint32_t p = (tile_n >= g.grp_tile0[1]) + (tile_n >= g.grp_tile0[2]) + (tile_n >= g.grp_tile0[3]);
+                    tile_n -= g.grp_tile0[p];
+                    b_scales = g.grp_b_scales[p];
+                    mb = p == 0 ? &map_b : p == 1 ? &map_b2 : p == 2 ? &map_b3 : &map_b4;
+                }
                 const uint8_t *sfa = g.a_scales + (size_t)tile_m * g.kt64 * 512;
-                const uint8_t *sfb0 = g.b_scales + (size_t)(DUAL ? tile_n : 2 * tile_n) * g.kt64 * 512;
+                const uint8_t *sfb0 = b_scales + (size_t)(DUAL ? tile_n : 2 * tile_n) * g.kt64 * 512;
                 const uint8_t *sfb1 = DUAL ? g.b2_scales + (size_t)tile_n * g.kt64 * 512 : sfb0 + (size_t)g.kt64 * 512;
                 for (uint32_t kt = 0; kt < g.k_tiles; ++kt, ++it) {
                     const uint32_t s = it % kStages, round = it / kStages;
@@ -257,7 +276,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         tma_load_2d_elect(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
                         tma_load_2d_elect(st + kABytes + kBBytes / 2, &map_b2, (int)(kt * (BK / 2)), (int)(tile_n * kTileRows), full);
                     } else {
-                        tma_load_2d_elect(st + kABytes, &map_b, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
+                        tma_load_2d_elect(st + kABytes, mb, (int)(kt * (BK / 2)), (int)(tile_n * BN), full);
                     }
                     bulk_load_elect(st + kABytes + kBBytes, sfa + (size_t)kt * kSfaBytes, sf_bytes, full);
                     bulk_load_elect(st + kABytes + kBBytes + kSfaBytes, sfb0 + (size_t)kt * 2048, sf_bytes, full);
@@ -378,6 +397,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (uint32_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++local) {
             uint32_t tile_m, tile_n;
             tile_coords(tile, m_tiles, g.n_tiles, g.group_m, tile_m, tile_n);
+            uint32_t n_out = g.n_out; // (of this tile's projection)
+            void *y_out = g.y;
+            float scale2 = g.scale2;
+            if constexpr (GROUP) {
+                const uint32_t p = (tile_n >= g.grp_tile0[1]) + (tile_n >= g.grp_tile0[2]) + (tile_n >= g.grp_tile0[3]);
+                tile_n -= g.grp_tile0[p];
+                n_out = g.grp_n_out[p], y_out = g.grp_y[p], scale2 = g.grp_scale2[p];
+            }
             const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full, local & 1, abort_flag));
             if (!ok) {
                 if (lane == 0) {
@@ -389,7 +416,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tok = tile_m * BM + quad * 32 + lane;
             const float rs = (g.row_scale && tok < g.tokens) ? g.row_scale[tok] : 1.0f;
-            const bool vec_ok = (g.n_out & 7) == 0;
+            const bool vec_ok = (n_out & 7) == 0;
             const uint32_t lane_base = tmem + ((quad * 32) << 16), col0 = part * kPartCols;
             // All of this warp's part of the accumulator goes to registers first (128 values a thread) and the
             // accumulator is handed back at once: the MMA warp cannot start the next tile before that, so nothing
@@ -412,33 +439,33 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if constexpr (QOUT) {
                     // rows of the last 128-token block that hold no token get zero scale bytes: the next GEMM reads the
                     // block's whole scale chunk (their codes come from TMA's zero fill)
-                    if (n0 < g.n_out) {
+                    if (n0 < n_out) {
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const float gate = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(__uint_as_float(cur[i]), g.scale2), g.inv_input_scale)));
+                            const float gate = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(__uint_as_float(cur[i]), scale2), g.inv_input_scale)));
                             const float up = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(__uint_as_float(r_up[i]), g.scale2_up), g.inv_input_scale)));
                             v[i] = __fdiv_rn(gate, 1.0f + expf(-gate)) * up;
                         }
                         if (tok < g.tokens) {
-                            uint8_t *codes = g.q_packed + (size_t)tok * (g.n_out / 2) + n0 / 2;
+                            uint8_t *codes = g.q_packed + (size_t)tok * (n_out / 2) + n0 / 2;
                             float(&lo)[16] = *reinterpret_cast<float(*)[16]>(&v[0]);
                             float(&hi)[16] = *reinterpret_cast<float(*)[16]>(&v[16]);
                             q_word |= quantize_group(lo, g.q_isi, codes) << (16 * s);
                             q_word |= quantize_group(hi, g.q_isi, codes + 8) << (16 * s + 8);
                         }
                     }
-                    if (s + 1 == kPartCols / 32 && tile_n * kOutCols + col0 < g.n_out)
+                    if (s + 1 == kPartCols / 32 && tile_n * kOutCols + col0 < n_out)
                         *reinterpret_cast<uint32_t *>(g.q_scales + swizzled_scale_offset(tok, (tile_n * kOutCols + col0) / 16, g.q_kt)) = q_word;
                     continue;
                 }
-                if (tok < g.tokens && n0 < g.n_out) {
-                    const size_t o = (size_t)tok * g.n_out + n0;
-                    const uint32_t valid = min(32u, g.n_out - n0);
+                if (tok < g.tokens && n0 < n_out) {
+                    const size_t o = (size_t)tok * n_out + n0;
+                    const uint32_t valid = min(32u, n_out - n0);
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) { // quant/nvfp4.rs:334-336: tensor scales applied one after the other
-                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(cur[i]), g.scale2), g.inv_input_scale);
+                        v[i] = __fmul_rn(__fmul_rn(__uint_as_float(cur[i]), scale2), g.inv_input_scale);
                         if constexpr (DUAL) {
                             const float gate = __half2float(__float2half_rn(v[i]));
                             const float up = __half2float(__float2half_rn(
@@ -449,13 +476,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if constexpr (TAIL) v[i] = logit_tail(v[i], g.out_scale, g.softcap);
                     }
                     if (g.y_dtype == MUSER_DTYPE_F32)
-                        store_strip<float>(v, reinterpret_cast<float *>(g.y) + o,
+                        store_strip<float>(v, reinterpret_cast<float *>(y_out) + o,
                                            g.residual ? reinterpret_cast<const float *>(g.residual) + o : nullptr, valid, vec_ok);
                     else if (g.y_dtype == MUSER_DTYPE_BF16)
-                        store_strip<__nv_bfloat16>(v, reinterpret_cast<__nv_bfloat16 *>(g.y) + o,
+                        store_strip<__nv_bfloat16>(v, reinterpret_cast<__nv_bfloat16 *>(y_out) + o,
                                                    g.residual ? reinterpret_cast<const __nv_bfloat16 *>(g.residual) + o : nullptr, valid, vec_ok);
                     else
-                        store_strip<__half>(v, reinterpret_cast<__half *>(g.y) + o,
+                        store_strip<__half>(v, reinterpret_cast<__half *>(y_out) + o,
                                             g.residual ? reinterpret_cast<const __half *>(g.residual) + o : nullptr, valid, vec_ok);
                 }
             }
@@ -1125,13 +1152,60 @@ muser_cuda_status launch_nvfp4_gemm(Ctx *ctx, const Weight *w, const uint8_t *x_
     if (qout) {
         const void *qfn = reinterpret_cast<const void *>(nvfp4_gemm_kernel<true, false, true>);
         MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(qfn, ctx->device, kSmemBytes));
-        nvfp4_gemm_kernel<true, false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+        nvfp4_gemm_kernel<true, false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, mb, mb, g);
     } else if (w_up)
-        nvfp4_gemm_kernel<true, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g); // (the fused FFN form has no tail)
+        nvfp4_gemm_kernel<true, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, mb, mb, g); // (the fused FFN form has no tail)
     else if (tail)
-        nvfp4_gemm_kernel<false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+        nvfp4_gemm_kernel<false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, mb, mb, g);
     else
-        nvfp4_gemm_kernel<false, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, g);
+        nvfp4_gemm_kernel<false, false><<<grid, 352, kSmemBytes, stream>>>(map_a, mb, mb2, mb, mb, g);
+    MUSER_CUDA_TRY(ctx, cudaGetLastError());
+    return MUSER_CUDA_OK;
+}
+
+// Up to four projections of the same quantized activations in one launch (GROUP form of the kernel).
+muser_cuda_status launch_nvfp4_gemm_group(Ctx *ctx, const Weight *const *ws, uint32_t n, const uint8_t *x_packed, const uint8_t *x_scales,
+                                          void *const *ys, uint32_t y_dtype, uint32_t tokens, cudaStream_t stream) {
+    const Weight *w0 = ws[0];
+    CUtensorMap map_a;
+    if (!make_map(&map_a, x_packed, tokens, w0->n_in / 2, BM))
+        return fail(ctx, MUSER_CUDA_ERROR, "cuTensorMapEncodeTiled failed for the activations");
+    GemmArgs g = {};
+    g.a_scales = x_scales;
+    g.status = ctx->dev_status;
+    g.tokens = tokens;
+    g.k_tiles = (uint32_t)((w0->n_in + BK - 1) / BK);
+    g.kt64 = (uint32_t)(w0->n_in / 64);
+    g.y_dtype = y_dtype;
+    g.out_scale = 1.0f;
+    g.inv_input_scale = 1.0f / w0->input_scale_inv;
+    uint32_t tiles_n = 0;
+    for (uint32_t p = 0; p < 4; ++p) {
+        g.grp_tile0[p] = tiles_n;
+        if (p >= n) continue;
+        g.grp_b_scales[p] = ws[p]->scales;
+        g.grp_y[p] = ys[p];
+        g.grp_n_out[p] = (uint32_t)ws[p]->n_out;
+        g.grp_scale2[p] = ws[p]->scale2;
+        tiles_n += (uint32_t)(ws[p]->n_out_pad / BN);
+    }
+    g.grp_tile0[4] = tiles_n;
+    for (uint32_t p = n; p < 4; ++p) g.grp_tile0[p] = tiles_n; // no tile falls into a projection that is not there
+    g.n_tiles = tiles_n;
+    g.n_out = g.grp_n_out[0], g.y = g.grp_y[0], g.scale2 = g.grp_scale2[0], g.b_scales = g.grp_b_scales[0];
+    {
+        const uint64_t tile_bytes = (uint64_t)BM * (w0->n_in / 2 + w0->n_in / 16);
+        uint32_t gm = (uint32_t)std::max<uint64_t>(8, (32ull << 20) / std::max<uint64_t>(1, tile_bytes));
+        if (ctx->nvfp4_group_m) gm = ctx->nvfp4_group_m;
+        g.group_m = std::max<uint32_t>(1, std::min<uint32_t>(gm, (tokens + BM - 1) / BM));
+    }
+    const CUtensorMap *maps[4];
+    for (uint32_t p = 0; p < 4; ++p) maps[p] = reinterpret_cast<const CUtensorMap *>(ws[p < n ? p : 0]->tmap_cache);
+    const uint32_t tiles = tiles_n * ((tokens + BM - 1) / BM);
+    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    const void *kfn = reinterpret_cast<const void *>(nvfp4_gemm_kernel<false, false, false, true>);
+    MUSER_CUDA_TRY(ctx, ensure_dynamic_smem(kfn, ctx->device, kSmemBytes));
+    nvfp4_gemm_kernel<false, false, false, true><<<grid, 352, kSmemBytes, stream>>>(map_a, *maps[0], *maps[1], *maps[2], *maps[3], g);
     MUSER_CUDA_TRY(ctx, cudaGetLastError());
     return MUSER_CUDA_OK;
 }

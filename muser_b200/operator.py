@@ -345,6 +345,17 @@ class CudaKernels:
             _TORCH_DTYPE[output.dtype], columns, C.byref(ep) if ep else None, _stream_ptr(self.ctx.device)))
         self.launches += 1
 
+    def encode_nvfp4_group_prequant(self, weights, packed: torch.Tensor, scales: torch.Tensor, outputs, columns: int) -> None:
+        """muser_cuda_nvfp4_matmul_group_prequant: 2..4 NVFP4 projections of the same quantized activations (q | k | v)
+        in one launch; every output carries the bits encode_nvfp4_prequant gives for its weight."""
+        n = len(weights)
+        ws = (C.c_void_p * n)(*[w._h.value for w in weights])
+        ys = (C.c_void_p * n)(*[y.data_ptr() for y in outputs])
+        self.ctx.check(_L.muser_cuda_nvfp4_matmul_group_prequant(
+            self.ctx._h, ws, n, packed.data_ptr(), scales.data_ptr(), ys, _TORCH_DTYPE[outputs[0].dtype], columns,
+            _stream_ptr(self.ctx.device)))
+        self.launches += 1
+
 
 def fp4_peak_tflops(ctx: Context, iters: int = 20000, reps: int = 3) -> float:
     """Dense block-scaled FP4 tensor throughput of this GPU (TFLOP/s), from muser_cuda_fp4_peak_probe."""

@@ -206,9 +206,8 @@ class PrefillLayer:
     def layer(self, x):
         k, W, M = self.kern, self.weights, self.M
         k.quantize_nvfp4_activation(x, self.isi["attn_q"], norm_weight=self.norm_w[0], norm_eps=self.eps, out=self.xq)
-        k.encode_nvfp4_prequant(W["attn_q"], self.xq[0], self.xq[1], self.q, M)
-        k.encode_nvfp4_prequant(W["attn_k"], self.xq[0], self.xq[1], self.k, M)
-        k.encode_nvfp4_prequant(W["attn_v"], self.xq[0], self.xq[1], self.v, M)
+        # q | k | v read the same quantized activations: one launch over all their output tiles
+        k.encode_nvfp4_group_prequant([W["attn_q"], W["attn_k"], W["attn_v"]], self.xq[0], self.xq[1], [self.q, self.k, self.v], M)
         self._row_parallel("attn_o", self.q, x, self.h1)
         if self.requant:
             k.quantize_nvfp4_activation(self.h1, self.isi["ffn_gate"], norm_weight=self.norm_w[1], norm_eps=self.eps, out=self.xq)

@@ -419,3 +419,37 @@ def test_raster_groups_do_not_change_the_outputs(gpu, group_m):
     for i, (a, b) in enumerate(zip(out[0], out[group_m])):
         assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a, b.view(torch.int32) if b.dtype == torch.float32 else b), f"output {i}"
     assert not torch.isnan(out[group_m][0]).any()
+
+
+@pytest.mark.parametrize("shapes,n_in,tokens", [((512, 256, 256), 512, 300), ((300, 128), 1088, 130), ((768, 256, 256, 1000), 256, 700)])
+def test_grouped_projections_equal_the_single_calls(gpu, shapes, n_in, tokens):
+    """muser_cuda_nvfp4_matmul_group_prequant (q | k | v in one launch): every output must carry the bits of
+    muser_cuda_nvfp4_matmul_prequant on that weight alone; rows that do not fill a tile, ragged K and tokens, two to
+    four projections.  Misuse (different n_in or input_scale_inv, one weight, five weights) is refused."""
+    from muser_b200 import synth
+    op, ctx, k = gpu
+    x = synth.normal_activations(tokens, n_in, seed=31)
+    isi = synth.activation_input_scale_inv(x)
+    ws = []
+    for i, n_out in enumerate(shapes):
+        packed, scales, scale2 = make_weight(op, ctx, n_out, n_in, seed=200 + i, negative_scales=(i == 0))
+        ws.append(op.Weight(ctx, op.TensorView(packed, O.NVFP4, n_in, n_out, scales, scale2, isi)))
+    xp, xs = k.quantize_nvfp4_activation(x.cuda(), isi)
+    for dt in (torch.float32, torch.bfloat16):
+        alone = [torch.full((tokens, n), float("nan"), dtype=dt, device="cuda") for n in shapes]
+        for w, y in zip(ws, alone):
+            k.encode_nvfp4_prequant(w, xp, xs, y, tokens)
+        grouped = [torch.full((tokens, n), float("nan"), dtype=dt, device="cuda") for n in shapes]
+        k.encode_nvfp4_group_prequant(ws, xp, xs, grouped, tokens)
+        ctx.sync_status()
+        bits = torch.int32 if dt == torch.float32 else torch.int16
+        for i, (a, b) in enumerate(zip(alone, grouped)):
+            assert torch.equal(a.view(bits), b.view(bits)), f"projection {i} ({dt}) differs from the call on its own"
+    # misuse
+    other = make_weight(op, ctx, 256, n_in, seed=300)
+    w_isi = op.Weight(ctx, op.TensorView(other[0], O.NVFP4, n_in, 256, other[1], other[2], isi * 2.0))
+    y = torch.empty((tokens, 256), dtype=torch.float32, device="cuda")
+    with pytest.raises(op.MuserCudaError):
+        k.encode_nvfp4_group_prequant([ws[0], w_isi], xp, xs, [grouped[0], y], tokens)
+    with pytest.raises(op.MuserCudaError):
+        k.encode_nvfp4_group_prequant([ws[0]], xp, xs, [grouped[0]], tokens)
