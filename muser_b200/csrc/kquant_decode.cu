@@ -83,12 +83,8 @@ __device__ __forceinline__ uint64_t evict_first_policy() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
-__device__ __forceinline__ void tile_fetch(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
-}
-// The same, called by the whole (converged) warp: one elected lane issues.  Bulk copies take their operands from the
+// One weight tile global -> shared (arrive with the byte count, then the bulk copy with the L2 policy), called by the
+// whole (converged) warp: one elected lane issues.  Bulk copies take their operands from the
 // warp-uniform registers, and issued from inside an `if (lane == 0)` branch each one cost the warp 100+ cycles.
 __device__ __forceinline__ void tile_fetch_elect(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile(
