@@ -437,6 +437,26 @@ __device__ __forceinline__ void tile_compute(const Q6Regs &r, const uint4 *fb, c
     }
 }
 
+// Zero, but only once every shared-memory load that filled `r` has delivered: one word of each load goes into an
+// instruction whose result the compiler cannot see through.  The ring slot is refilled by a bulk copy (asynchronous
+// proxy) right after the warp has read it (generic proxy); adding this zero to the copy's byte count makes the copy wait
+// for the reads, which a warp barrier alone does not (it orders the issue of the loads, not their completion).
+__device__ __forceinline__ uint32_t opaque_zero(uint32_t x) {
+    uint32_t z;
+    asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(x));
+    return z;
+}
+__device__ __forceinline__ uint32_t regs_landed(const Q4Regs &r) {
+    return opaque_zero(r.q[0].x ^ r.q[1].x ^ r.q[2].x ^ r.q[3].x ^ r.ha.x ^ r.hb.x);
+}
+__device__ __forceinline__ uint32_t regs_landed(const Q5Regs &r) {
+    return opaque_zero(r.q[0].x ^ r.q[1].x ^ r.q[2].x ^ r.q[3].x ^ r.hbits.x ^ r.ha.x ^ r.hb.x);
+}
+__device__ __forceinline__ uint32_t regs_landed(const Q6Regs &r) {
+    return opaque_zero(r.top[0].x ^ r.top[1].x ^ r.top[2].x ^ r.top[3].x ^ r.low[0].x ^ r.low[1].x ^ r.sa.x ^ r.sb.x ^
+                       __float_as_uint(r.da) ^ __float_as_uint(r.db));
+}
+
 template <int DT> struct RegsOf;
 template <> struct RegsOf<MUSER_DTYPE_Q4_K> { using type = Q4Regs; };
 template <> struct RegsOf<MUSER_DTYPE_Q6_K> { using type = Q6Regs; };
@@ -495,10 +515,10 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
     const uint32_t bar0 = smem_addr(bars + warp * ring_n);
     uint32_t f_tile = first_row * a.nsb + sb_first + t_first, f_tl = 0, f_im = 0;
     const uint64_t policy = evict_first_policy();
-    auto fetch_next = [&](uint32_t slot) { // warp-uniform bookkeeping, one elected lane issues the copy
+    auto fetch_next = [&](uint32_t slot, uint32_t zero_after_reads = 0) { // warp-uniform bookkeeping, one elected lane issues the copy
         const uint8_t *base = jb.image;
         if constexpr (DUAL) base = f_im ? jb.image_up : jb.image;
-        tile_fetch_elect(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes, bar0 + 8 * slot, policy);
+        tile_fetch_elect(smem_addr(ring) + slot * kBytes, base + (uint64_t)f_tile * kBytes, kBytes + zero_after_reads, bar0 + 8 * slot, policy);
         ++f_tile;
         if (++f_tl == my_tiles) {
             f_tl = 0;
@@ -546,8 +566,8 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
                 }
                 if (healthy) {
                     const Regs cur = load_regs(ring + slot * kBytes, lane, (Regs *)nullptr);
-                    __syncwarp(); // every lane has its copy: the slot may be refilled
-                    if (n + ring_n < total) fetch_next(slot);
+                    __syncwarp(); // every lane has issued its loads; regs_landed makes the refill wait for their data
+                    if (n + ring_n < total) fetch_next(slot, regs_landed(cur));
                     tile_compute<NG>(cur, frag + (size_t)tl * NG * kFragU4 + lane, meta + (size_t)tl * TOK * kMetaU4, t, out[im]);
                 }
             }
