@@ -439,8 +439,11 @@ __device__ __forceinline__ void tile_compute(const Q6Regs &r, const uint4 *fb, c
 
 // Zero, but only once every shared-memory load that filled `r` has delivered: one word of each load goes into an
 // instruction whose result the compiler cannot see through.  The ring slot is refilled by a bulk copy (asynchronous
-// proxy) right after the warp has read it (generic proxy); adding this zero to the copy's byte count makes the copy wait
-// for the reads, which a warp barrier alone does not (it orders the issue of the loads, not their completion).
+// proxy) right after the warp has read it (generic proxy): the reads must be complete and a proxy fence must stand
+// between them and the copy.  While one thread issued the copy from inside a divergent branch, the ~100 cycles that
+// cost hid the hazard; with the copy issued 20 cycles after the loads, one call in a few hundred of the 16-token
+// ffn_down projection (ring of two, 14 K slices) read a slot that was being refilled.  Adding this zero to the copy's
+// byte count makes the copy wait for the loaded registers; the fence orders the two proxies.
 __device__ __forceinline__ uint32_t opaque_zero(uint32_t x) {
     uint32_t z;
     asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(x));
@@ -567,6 +570,7 @@ __device__ __forceinline__ void run(const DecArgs &a, const DecJob &jb, uint32_t
                 if (healthy) {
                     const Regs cur = load_regs(ring + slot * kBytes, lane, (Regs *)nullptr);
                     __syncwarp(); // every lane has issued its loads; regs_landed makes the refill wait for their data
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy reads before the async-proxy refill
                     if (n + ring_n < total) fetch_next(slot, regs_landed(cur));
                     tile_compute<NG>(cur, frag + (size_t)tl * NG * kFragU4 + lane, meta + (size_t)tl * TOK * kMetaU4, t, out[im]);
                 }

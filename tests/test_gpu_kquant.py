@@ -607,3 +607,28 @@ def test_misuse_returns_statuses(gpu):
     with pytest.raises(op.MuserCudaError) as e:
         op.Weight(ctx, op.TensorView(raw, O.Q4_K, 256, 16), shard=(0, 3, op.SHARD_ROWS))
     assert e.value.status_name == "BAD_SHAPE"
+
+
+@pytest.mark.parametrize("tokens", [13, 16])
+def test_repeated_calls_are_bit_identical(gpu, tokens):
+    """The 16-token ffn_down projection runs with a ring of two tiles per warp and 14 K slices: the launch plan in
+    which a refill of a ring slot that still had reads in flight showed up as one differing call in a few hundred
+    (rows of one tile, every token).  800 calls must all carry the bits of the first."""
+    op, ctx, k = gpu
+    from muser_b200 import synth
+    n_in, n_out, dtype = synth.LAYER_PROJECTIONS["ffn_down"]
+    raw = synth.quantize_kquant(synth.normal_weights(n_out, n_in, seed=0, stream=11, device="cuda"), dtype)
+    w = op.Weight(ctx, op.TensorView(raw, dtype, n_in, n_out))
+    x = synth.normal_activations(tokens, n_in, seed=tokens, device="cuda")
+    first = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+    k.encode_quantized_matmul(w, x, first, tokens)
+    ctx.sync_status()
+    ys = [torch.full_like(first, float("nan")) for _ in range(16)]
+    differing = 0
+    for _ in range(50):
+        for y in ys:
+            k.encode_quantized_matmul(w, x, y, tokens)
+        ctx.sync_status()
+        differing += sum(0 if torch.equal(y, first) else 1 for y in ys)
+    w.free()
+    assert differing == 0, f"{differing} of 800 calls differ from the first"
