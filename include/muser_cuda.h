@@ -142,7 +142,7 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_sync_status(muser_cuda_ctx *ctx, voi
 #define MUSER_TUNE_DECODE_WSPLIT 12u      /* decode kernel: warps of a CTA that share one row tile and split K between them (0: from its cost model) */
 #define MUSER_TUNE_ONESHOT_MAX_BYTES 11u /* all-reduce: f32 payloads up to this many bytes take the one-shot peer exchange (default and most 1572864; 0: always NCCL) */
 #define MUSER_TUNE_NVFP4_PAIR 13u         /* NVFP4 GEMM: 0 one CTA per 128-token tile (default), 1 pairs of SMs on 256-token tiles (tcgen05 cta_group::2) */
-#define MUSER_TUNE_HOST_DIRECT_OUTPUT 14u /* muser_cuda_matmul_host_groups_enqueue: 1 (default) a kernel stores the outputs into pinned host buffers, 0 one cudaMemcpyAsync per output */
+#define MUSER_TUNE_HOST_DIRECT_OUTPUT 14u /* muser_cuda_matmul_host_groups_enqueue: how the outputs reach the host buffers.  2 (default): one cudaMemcpyAsync per output on the context's copy stream, behind an event of the launch that produced it (the copy engine needs no SM and runs beside the next launches); 1: a kernel stores them into pinned, mapped host buffers; 0: one cudaMemcpyAsync per output on the launches' own stream */
 #define MUSER_TUNE_NVFP4_GROUP_M 15u /* NVFP4 GEMM: 128-token tiles per raster group (the activations one group touches stay in L2 while it sweeps the weight rows); 0 (default) = about 32 MB of activations, at least 8 tiles */
 MUSER_CUDA_API muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *ctx, uint32_t key, uint32_t value);
 

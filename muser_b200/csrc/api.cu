@@ -315,7 +315,10 @@ muser_cuda_status muser_cuda_tuning_set(muser_cuda_ctx *c, uint32_t key, uint32_
         ctx->nvfp4_pair = value;
         return MUSER_CUDA_OK;
     case MUSER_TUNE_ONESHOT_MAX_BYTES: ctx->oneshot_max_bytes = value; return MUSER_CUDA_OK;
-    case MUSER_TUNE_HOST_DIRECT_OUTPUT: ctx->host_direct_output = value != 0; return MUSER_CUDA_OK;
+    case MUSER_TUNE_HOST_DIRECT_OUTPUT:
+        if (value > 2) return fail(ctx, MUSER_CUDA_BAD_ARG, "MUSER_TUNE_HOST_DIRECT_OUTPUT takes 0, 1 or 2");
+        ctx->host_direct_output = value;
+        return MUSER_CUDA_OK;
     case MUSER_TUNE_NVFP4_GROUP_M: ctx->nvfp4_group_m = value; return MUSER_CUDA_OK;
     default: return fail(ctx, MUSER_CUDA_BAD_ARG, "unknown tuning key");
     }
@@ -874,14 +877,24 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
     HostScatter batch;
     batch.n = 0;
     bool copies_pending = false;
+    // mode 2: the copy engine takes the outputs (one copy each) on the copy stream, behind an event of the launch that
+    // produced them; it needs no SM, so it runs beside the next launches, which fill every SM's registers
+    struct PendingCopy { void *dst; const void *src; size_t bytes; };
+    PendingCopy pending[4];
+    uint32_t n_pending = 0;
     auto flush = [&]() -> cudaError_t {
-        if (batch.n == 0) return cudaSuccess;
+        if (batch.n == 0 && n_pending == 0) return cudaSuccess;
         cudaError_t e = cudaEventRecord(ctx->copy_events[kEvents - 1], s);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[kEvents - 1], 0);
         if (e != cudaSuccess) return e;
+        for (uint32_t i = 0; i < n_pending && e == cudaSuccess; ++i)
+            e = cudaMemcpyAsync(pending[i].dst, pending[i].src, pending[i].bytes, cudaMemcpyDeviceToHost, ctx->copy_stream);
+        n_pending = 0;
+        if (e != cudaSuccess) return e;
+        copies_pending = true;
+        if (batch.n == 0) return cudaSuccess;
         host_scatter_kernel<<<32, 256, 0, ctx->copy_stream>>>(batch);
         batch.n = 0;
-        copies_pending = true;
         return cudaGetLastError();
     };
     at = first;
@@ -902,7 +915,9 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
         for (uint32_t i = 0; i < g.n_items; ++i) {
             const size_t yb = (size_t)g.tokens * reinterpret_cast<const Weight *>(g.w[i])->n_out * 4;
             void *mapped = nullptr;
-            if (ctx->host_direct_output && cudaHostGetDevicePointer(&mapped, g.y_host[i], 0) == cudaSuccess && ((uintptr_t)mapped & 15u) == 0 && yb % 16 == 0) {
+            if (ctx->host_direct_output == 2) {
+                pending[n_pending++] = PendingCopy{g.y_host[i], staged[i], yb};
+            } else if (ctx->host_direct_output == 1 && cudaHostGetDevicePointer(&mapped, g.y_host[i], 0) == cudaSuccess && ((uintptr_t)mapped & 15u) == 0 && yb % 16 == 0) {
                 batch.src[batch.n] = reinterpret_cast<const uint4 *>(staged[i]);
                 batch.dst[batch.n] = reinterpret_cast<uint4 *>(mapped);
                 batch.n16[batch.n] = (uint32_t)(yb / 16);
@@ -912,7 +927,7 @@ muser_cuda_status muser_cuda_matmul_host_groups_enqueue(muser_cuda_ctx *c, const
                 MUSER_CUDA_TRY(ctx, cudaMemcpyAsync(g.y_host[i], staged[i], yb, cudaMemcpyDeviceToHost, s));
             }
         }
-        if ((gi & 3) == 3) MUSER_CUDA_TRY(ctx, flush()); // (a store kernel per group measured slower than one per four)
+        if ((gi & 3) == 3 || n_pending) MUSER_CUDA_TRY(ctx, flush()); // (a store kernel per group measured slower than one per four; copies leave per group)
     }
     MUSER_CUDA_TRY(ctx, flush());
     (void)copies_pending; // the caller's wait on `stream` covers the copy stream's stores

@@ -56,7 +56,8 @@ struct Ctx {
     void *comm = nullptr;                      // tensor-parallel communicator (collective.cu), or null
     unsigned long long *amax_keys = nullptr;   // fused greedy pick: one key and one flag word per token (16 each), zero between calls
     unsigned int *amax_flags = nullptr;
-    bool host_direct_output = true;            // host-group entry: a kernel stores the outputs into mapped host buffers (else memcpy)
+    uint32_t host_direct_output = 2;           // host-group entry: 2 one copy per output on the copy stream (beside the next launches), 1 a kernel
+                                               // stores the outputs into mapped host buffers, 0 one copy per output on the launches' stream
     uint32_t nvfp4_pair = 0;                   // NVFP4 GEMM on pairs of SMs (cta_group::2): 0 off, 1 on
     uint32_t nvfp4_group_m = 0;                // NVFP4 GEMM: token tiles per raster group, 0 = automatic
     uint32_t oneshot_max_bytes = 1536u << 10;  // all-reduce payloads up to this size take the one-shot peer exchange
