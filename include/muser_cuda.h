@@ -418,9 +418,10 @@ MUSER_CUDA_API muser_cuda_status muser_cuda_head_rms_norm(muser_cuda_ctx *ctx, f
  * one command buffer (src/decode.rs:5448-5460) and group the projections that read the same hidden state
  * (src/decode.rs:5569-5598, src/metal/encode/qkv.rs:234-281).  Every group is 1..4 K-quant projections of one x_host
  * ([tokens][n_in] f32, 1 <= tokens <= 16): x is copied up once, the group runs as one launch
- * (muser_cuda_quantized_matmul_group), and the outputs y_host[i] ([tokens][n_out_i] f32) leave in batches beside the
- * following groups' launches: stored by a small kernel where the device can address the buffer (pinned, mapped host
- * memory), copied otherwise.  At most 28 groups per call.  Nothing is synchronized: wait with muser_cuda_sync_status,
+ * (muser_cuda_quantized_matmul_group), and the outputs y_host[i] ([tokens][n_out_i] f32) leave beside the following
+ * groups' launches: by default one copy each on the context's copy stream, behind an event of the launch that made
+ * them (MUSER_TUNE_HOST_DIRECT_OUTPUT selects a store kernel into pinned, mapped buffers, or copies on `stream`,
+ * instead).  Pinned host buffers let the copies run asynchronously.  At most 28 groups per call.  Nothing is synchronized: wait with muser_cuda_sync_status,
  * after which the outputs are complete.  Buffers must stay valid until then.  The call can be captured into a CUDA
  * graph on `stream` (after one plain call, which makes the arena and the events) and replayed step after step: the
  * graph then reads and writes the same host buffers and the same part of the arena. */
